@@ -1,0 +1,232 @@
+/*
+ * nnue_b200.h -- C ABI of libnnue_b200.so, the sm_100a implementation of the
+ * sparse feature-transformer hot path of nnue-pytorch.
+ *
+ * Conventions shared by every entry point
+ *   - plain C: pointers, sizes and scalars only; no torch / C++ types.
+ *   - every pointer is a DEVICE pointer owned by the caller unless the
+ *     parameter name starts with `h_` (host).  The library allocates no
+ *     device memory; kernels that need scratch take a caller-provided
+ *     workspace whose size the matching *_workspace_bytes() call returns.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default
+ *     stream).  Work is only enqueued; nothing synchronises with the host.
+ *   - the return value is a status: 0 (NNUE_OK) or a negative NNUE_ERR_*
+ *     code.  nnue_b200_last_error() gives the message for the calling
+ *     thread's most recent failure.  Nothing throws, traps or exits.
+ *   - index lists follow the reference contract: int32, row-major [B, K],
+ *     the first negative entry ends a row; duplicates are summed with
+ *     multiplicity.  Entries >= N are skipped and recorded in the device
+ *     status word (nnue_b200_device_status) instead of being dereferenced.
+ *   - row widths: the vectorised kernels need W % 4 == 0 (and L1 % 8 == 0
+ *     for the fused op) plus 16-byte aligned base pointers; other shapes run
+ *     the scalar kernels of the same library.
+ *
+ * Citations name files of official-stockfish/nnue-pytorch by their path in
+ * that project.
+ */
+#ifndef NNUE_B200_H
+#define NNUE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define NNUE_B200_ABI_VERSION 1
+
+enum {
+    NNUE_OK = 0,
+    NNUE_ERR_ARG = -1,        /* null pointer, negative size, bad enum */
+    NNUE_ERR_ALIGN = -2,      /* pointer not aligned as required */
+    NNUE_ERR_WORKSPACE = -3,  /* workspace too small */
+    NNUE_ERR_UNSUPPORTED = -4,/* shape outside what the kernels cover */
+    NNUE_ERR_CUDA = -5,       /* a CUDA runtime call failed (message has it) */
+    NNUE_ERR_INDEX = -6,      /* device status word reported bad indices */
+    NNUE_ERR_TIMEOUT = -7     /* a bounded device-side wait ran out */
+};
+
+/* Scatter strategy of the backward kernels. */
+enum {
+    NNUE_BWD_AUTO = 0,     /* library picks (segment reduction today) */
+    NNUE_BWD_ATOMIC = 1,   /* vector red.global.add into a zeroed gradient */
+    NNUE_BWD_SEGMENT = 2   /* CSR by row + gather-sum; every row written once */
+};
+
+int nnue_b200_abi_version(void);
+const char* nnue_b200_last_error(void);
+
+/* Tuning knob for experiments ("fwd_u", "bwd_u", "stage_idx", ...).
+ * Unknown keys return NNUE_ERR_ARG.  Process-wide, not thread-safe. */
+int nnue_b200_tune(const char* key, int value);
+
+/* Reads (and clears) the device status word.  SYNCHRONISES `stream`.
+ * h_bad_index_count / h_timeout_count may be NULL.  Returns NNUE_OK,
+ * NNUE_ERR_INDEX or NNUE_ERR_TIMEOUT. */
+int nnue_b200_device_status(void* stream, int64_t* h_bad_index_count,
+                            int64_t* h_timeout_count);
+
+/* ---- A1: sparse linear forward ---------------------------------------
+ * out[b, c] = bias[c] + sum_k weight[idx[b, k], c]   (bias first, k ascending)
+ * Replaces the CuPy kernel `sparse_input_linear_forward`,
+ * model/modules/feature_transformer/sparse_linear_kernel.py:114-157, launched
+ * from model/modules/feature_transformer/sparse_linear_functions.py:78-101. */
+int nnue_ft_sparse_fwd(const int32_t* idx, const float* weight,
+                       const float* bias, float* out,
+                       int64_t B, int32_t K, int64_t N, int32_t W,
+                       void* stream);
+
+/* ---- A2: sparse linear backward --------------------------------------
+ * grad_weight[r, c] = sum over (b, k) with idx[b, k] == r of grad_out[b, c]
+ * grad_bias[c]      = sum_b grad_out[b, c]
+ * Both outputs are fully overwritten (no pre-zeroing by the caller).
+ * Replaces `sparse_input_linear_backward`,
+ * model/modules/feature_transformer/sparse_linear_kernel.py:237-288 and the
+ * torch.zeros + launch in sparse_linear_functions.py:104-136. */
+size_t nnue_ft_sparse_bwd_workspace_bytes(int64_t B, int32_t K, int64_t N,
+                                          int32_t W, int32_t mode);
+int nnue_ft_sparse_bwd(const int32_t* idx, const float* grad_out,
+                       float* grad_weight, float* grad_bias,
+                       int64_t B, int32_t K, int64_t N, int32_t W,
+                       void* workspace, size_t workspace_bytes, int32_t mode,
+                       void* stream);
+
+/* ---- A6: fused double feature transformer, forward --------------------
+ * Per position: w = bias[:L1] + sum weight[white_idx][:L1], b likewise;
+ * x = us*[w, b] + them*[b, w] (2*L1 wide, four chunks of L1/2);
+ * c = clamp(x, 0, max_act); l0 = [c0*c1, c2*c3];
+ * wpsqt = bias[L1+p] + sum weight[white_idx][L1+p], bpsqt likewise,
+ * p = psqt_idx[b].  `saved` [B, 4, L1/2] receives the PRE-clamp x, which is
+ * what nnue_ft_fused_bwd consumes.
+ * Replaces `fused_double_ft_forward`,
+ * model/modules/feature_transformer/fused_ft_kernel.py:27-117, launched from
+ * fused_ft_functions.py:47-75; numerics follow the torch composition in
+ * double_ft_functions.py:62-80. */
+int nnue_ft_fused_fwd(const float* us, const float* them,
+                      const int32_t* white_idx, const int32_t* black_idx,
+                      const int64_t* psqt_idx,
+                      const float* weight, const float* bias, float max_act,
+                      float* l0, float* wpsqt, float* bpsqt, float* saved,
+                      int64_t B, int32_t K, int64_t N, int32_t L1, int32_t P,
+                      void* stream);
+
+/* ---- A7: fused double feature transformer, backward -------------------
+ * Gradient of the op above w.r.t. weight [N, L1+P] and bias [L1+P]; the
+ * clamp passes gradient on the closed interval [0, max_act] like
+ * torch.clamp.  Both outputs are fully overwritten.
+ * Replaces `fused_double_ft_backward`,
+ * model/modules/feature_transformer/fused_ft_kernel.py:147-272 and the
+ * torch.zeros + launch in fused_ft_functions.py:81-122. */
+size_t nnue_ft_fused_bwd_workspace_bytes(int64_t B, int32_t K, int64_t N,
+                                         int32_t L1, int32_t P, int32_t mode);
+int nnue_ft_fused_bwd(const float* us, const float* them,
+                      const int32_t* white_idx, const int32_t* black_idx,
+                      const int64_t* psqt_idx, float max_act,
+                      const float* grad_l0, const float* grad_wpsqt,
+                      const float* grad_bpsqt, const float* saved,
+                      float* grad_weight, float* grad_bias,
+                      int64_t B, int32_t K, int64_t N, int32_t L1, int32_t P,
+                      void* workspace, size_t workspace_bytes, int32_t mode,
+                      void* stream);
+
+/* ---- A12: RangerLite (Adam + positive-negative momentum + lookahead) ---
+ * One fused pass over a parameter tensor viewed as [rows, width]:
+ *   g  = grad * (*d_grad_scale if given) ;
+ *   vm = beta2*vm + (1-beta2)*g*g ; denom = sqrt(vm)/sqrt(bc2) + eps ;
+ *   pnm:  pos = (step odd ? grad_ma : neg_grad_ma) ;
+ *         pos = beta1^2*pos + (1-beta1^2)*g ;
+ *         upd = ((1+f)*pos - f*neg) * (1/noise_norm) ;
+ *   adam: grad_ma = beta1*grad_ma + (1-beta1)*g ; upd = grad_ma ;
+ *   p = p*wd_keep - step_size*upd/denom ;
+ *   if merge: p = alpha*p + (1-alpha)*slow ; slow = p.
+ * `row_active` (optional, uint8 [rows]) implements the touched-rows-only
+ * update: a row whose flag is 0 and whose gradient row is entirely zero is
+ * skipped (bit-identical, because all of its moments are still zero); a row
+ * with any non-zero gradient gets its flag set for good.
+ * Replaces the five CuPy kernels of model/optimizers/ranger_lite.py:46-201,
+ * the per-tensor launches at :325-477 and the lookahead pass at :746-768;
+ * the arithmetic follows the Python path at :592-742. */
+typedef struct nnue_ranger_hparams {
+    /* every constant is derived on the host in double precision, as the
+     * reference's Python code does, and rounded to float once */
+    float beta2;
+    float one_minus_beta2;
+    float mom;             /* beta1^2 with PNM, beta1 without */
+    float one_minus_mom;
+    float one_plus_f;      /* 1 + pnm_momentum */
+    float f;               /* pnm_momentum */
+    float noise_norm_inv;  /* 1/sqrt((1+f)^2 + f^2) */
+    float step_size;       /* lr / bias_correction1 */
+    float bc2_sqrt;        /* sqrt(1 - beta2^step) */
+    float eps;
+    float wd_keep;         /* 1 - decay*lr/variance_norm; 1 = no decay */
+    float alpha;           /* lookahead blending */
+    float one_minus_alpha;
+    int32_t use_pnm;       /* 1 = PNM, 0 = plain Adam */
+    int32_t step_is_odd;   /* PNM buffer selection */
+    int32_t do_merge;      /* 1 = lookahead merge in the same pass */
+    int32_t phase;         /* 0 = full update, 1 = second moment only,
+                              2 = update reading the stored second moment */
+} nnue_ranger_hparams;
+
+int nnue_rangerlite_update(float* p, const float* grad, float* grad_ma,
+                           float* neg_grad_ma, float* variance_ma, float* slow,
+                           uint8_t* row_active, const float* d_grad_scale,
+                           int64_t rows, int64_t width,
+                           const nnue_ranger_hparams* h_hp, void* stream);
+
+/* Standalone lookahead merge, model/optimizers/ranger_lite.py:746-768. */
+int nnue_lookahead_merge(float* p, float* slow, int64_t n, float alpha,
+                         void* stream);
+
+/* Sum of squares of a gradient tensor into *d_out (accumulating, so several
+ * tensors can share one scalar), and the clip coefficient
+ * min(1, max_norm / (sqrt(*d_sumsq) + 1e-6)) that
+ * torch.nn.utils.clip_grad_norm_ applies at trainer/engine.py:308-311. */
+int nnue_grad_sumsq(const float* grad, int64_t n, float* d_out_sumsq,
+                    void* stream);
+int nnue_clip_coef(const float* d_sumsq, float max_norm, float* d_coef,
+                   void* stream);
+
+/* ---- Q: integer quantized evaluation ----------------------------------
+ * Integer restatement of the fake-quantized forward defined by
+ * model/quantize.py:36-56,133-147, model/modules/layer_stacks.py:33-84 and
+ * model/model.py:107-133.  The reference holds no integer evaluator; this is
+ * the arithmetic an engine performs on the exported net.
+ * Weights: ft_w int16 [N, L1], ft_psqt int32 [N, P], ft_b int32 [L1] (bias at
+ * the ft scale), l1_w int8 [buckets, L2, L1] + l1_b int32 [buckets, L2],
+ * l2_w int8 [buckets, L3, 2*L2] + l2_b, out_w int8 [buckets, 2*L2+2*L3] +
+ * out_b int32 [buckets].  `out` int32 [B] is the evaluation in units of
+ * 1/(2*nnue2score*weight_scale_out) of the float model output. */
+typedef struct nnue_quant_params {
+    int32_t ft_max;        /* 255 */
+    int32_t ft_shift;      /* 9: (c0*c1) >> 9 */
+    int32_t hidden_max;    /* 127 */
+    int32_t sqr_shift_l1;  /* 21 */
+    int32_t sqr_eps_l1;    /* 20 */
+    int32_t lin_shift_l1;  /* 7 */
+    int32_t sqr_shift_l2;  /* 19 */
+    int32_t sqr_eps_l2;    /* 5 */
+    int32_t lin_shift_l2;  /* 6 */
+    int32_t skip_mul;      /* (hidden_one*ws_l_out)/(hidden_one*ws_l1) = 1 */
+    int32_t out_mul;       /* 9600 = nnue2score*weight_scale_out */
+    int32_t out_div;       /* 32768 = 2*hidden_one*weight_scale_l_out */
+} nnue_quant_params;
+
+int nnue_quant_eval(const int32_t* white_idx, const int32_t* black_idx,
+                    const uint8_t* stm_white, const int32_t* bucket,
+                    const int16_t* ft_w, const int32_t* ft_psqt,
+                    const int32_t* ft_b,
+                    const int8_t* l1_w, const int32_t* l1_b,
+                    const int8_t* l2_w, const int32_t* l2_b,
+                    const int8_t* out_w, const int32_t* out_b,
+                    int32_t* out,
+                    int64_t B, int32_t K, int64_t N, int32_t L1, int32_t L2,
+                    int32_t L3, int32_t P, int32_t buckets,
+                    const nnue_quant_params* h_qp, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* NNUE_B200_H */

@@ -1,0 +1,211 @@
+"""Thin launch helpers between torch tensors and the C ABI.
+
+torch is used here for device memory, the current stream and nothing else:
+every function takes tensors, checks the contract the reference asserts
+(model/modules/feature_transformer/sparse_linear_functions.py:58-76 and
+fused_ft_functions.py:23-45 of the reference project), and hands raw device
+pointers to libnnue_b200.so.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+
+from . import _lib
+
+_BWD_MODE = "auto"
+
+
+def set_backward_mode(mode: str) -> None:
+    """Select the scatter strategy of the backward kernels: auto | atomic | segment."""
+    global _BWD_MODE
+    _lib.bwd_mode(mode)
+    _BWD_MODE = mode
+
+
+def get_backward_mode() -> str:
+    return _BWD_MODE
+
+
+def _stream(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _require_cuda(*tensors: torch.Tensor) -> torch.device:
+    dev = tensors[0].device
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError(
+                "nnue_pytorch_b200 kernels run on CUDA tensors only (there is no CPU or PyTorch fallback)"
+            )
+        if t.device != dev:
+            raise RuntimeError("all tensors must live on the same CUDA device")
+    return dev
+
+
+def _workspace(nbytes: int, device: torch.device) -> torch.Tensor:
+    return torch.empty(max(int(nbytes), 256), dtype=torch.uint8, device=device)
+
+
+# --------------------------------------------------------------------------
+def sparse_linear_forward(indices: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    assert indices.dim() == 2 and indices.dtype == torch.int32
+    assert weight.dim() == 2 and weight.dtype == torch.float32
+    assert bias.dim() == 1 and bias.dtype == torch.float32
+    assert weight.shape[1] == bias.shape[0]
+    dev = _require_cuda(indices, weight, bias)
+    assert indices.is_contiguous() and weight.is_contiguous() and bias.is_contiguous()
+    B, K = indices.shape
+    N, W = weight.shape
+    out = torch.empty(B, W, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        st = _lib.load().nnue_ft_sparse_fwd(
+            _ptr(indices), _ptr(weight), _ptr(bias), _ptr(out), B, K, N, W, _stream(dev)
+        )
+    _lib.check(st, "nnue_ft_sparse_fwd")
+    return out
+
+
+def sparse_linear_backward(
+    indices: torch.Tensor, grad_out: torch.Tensor, num_inputs: int, mode: str | None = None
+) -> tuple[torch.Tensor, torch.Tensor]:
+    dev = _require_cuda(indices, grad_out)
+    grad_out = grad_out.contiguous()
+    assert grad_out.dtype == torch.float32
+    B, K = indices.shape
+    W = grad_out.shape[1]
+    m = _lib.bwd_mode(mode or _BWD_MODE)
+    lib = _lib.load()
+    grad_w = torch.empty(num_inputs, W, dtype=torch.float32, device=dev)
+    grad_b = torch.empty(W, dtype=torch.float32, device=dev)
+    ws = _workspace(lib.nnue_ft_sparse_bwd_workspace_bytes(B, K, num_inputs, W, m), dev)
+    with torch.cuda.device(dev):
+        st = lib.nnue_ft_sparse_bwd(
+            _ptr(indices), _ptr(grad_out), _ptr(grad_w), _ptr(grad_b), B, K, num_inputs, W,
+            _ptr(ws), ws.numel(), m, _stream(dev),
+        )
+    _lib.check(st, "nnue_ft_sparse_bwd")
+    return grad_w, grad_b
+
+
+# --------------------------------------------------------------------------
+def fused_forward(us, them, white_indices, black_indices, psqt_indices, weight, bias, max_ft_activation, l1_size):
+    assert l1_size % 2 == 0
+    dev = _require_cuda(us, them, white_indices, black_indices, psqt_indices, weight, bias)
+    assert us.dtype == torch.float32 and them.dtype == torch.float32
+    assert white_indices.dtype == torch.int32 and black_indices.dtype == torch.int32
+    assert psqt_indices.dtype == torch.int64
+    assert weight.dtype == torch.float32 and bias.dtype == torch.float32
+    assert white_indices.dim() == 2 and black_indices.dim() == 2 and psqt_indices.dim() == 1
+    assert weight.dim() == 2 and bias.dim() == 1 and weight.shape[1] == bias.shape[0]
+    assert white_indices.shape == black_indices.shape
+    assert white_indices.shape[0] == psqt_indices.shape[0]
+    assert us.numel() == white_indices.shape[0] and them.numel() == white_indices.shape[0]
+    assert us.is_contiguous() and them.is_contiguous()
+    assert white_indices.is_contiguous() and black_indices.is_contiguous() and psqt_indices.is_contiguous()
+    assert weight.is_contiguous() and bias.is_contiguous()
+    B, K = white_indices.shape
+    N, W = weight.shape
+    P = W - l1_size
+    assert P >= 0
+    l0 = torch.empty(B, l1_size, dtype=torch.float32, device=dev)
+    wpsqt = torch.empty(B, 1, dtype=torch.float32, device=dev)
+    bpsqt = torch.empty(B, 1, dtype=torch.float32, device=dev)
+    saved = torch.empty(B, 4, l1_size // 2, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev):
+        st = _lib.load().nnue_ft_fused_fwd(
+            _ptr(us), _ptr(them), _ptr(white_indices), _ptr(black_indices), _ptr(psqt_indices),
+            _ptr(weight), _ptr(bias), float(max_ft_activation),
+            _ptr(l0), _ptr(wpsqt), _ptr(bpsqt), _ptr(saved), B, K, N, l1_size, P, _stream(dev),
+        )
+    _lib.check(st, "nnue_ft_fused_fwd")
+    return l0, wpsqt, bpsqt, saved
+
+
+def fused_backward(
+    us, them, white_indices, black_indices, psqt_indices, max_ft_activation, l1_size, num_inputs, num_outputs,
+    grad_l0, grad_wpsqt, grad_bpsqt, saved, mode: str | None = None,
+):
+    dev = _require_cuda(us, grad_l0, grad_wpsqt, grad_bpsqt, saved)
+    grad_l0 = grad_l0.contiguous()
+    grad_wpsqt = grad_wpsqt.contiguous()
+    grad_bpsqt = grad_bpsqt.contiguous()
+    B, K = white_indices.shape
+    P = num_outputs - l1_size
+    m = _lib.bwd_mode(mode or _BWD_MODE)
+    lib = _lib.load()
+    grad_w = torch.empty(num_inputs, num_outputs, dtype=torch.float32, device=dev)
+    grad_b = torch.empty(num_outputs, dtype=torch.float32, device=dev)
+    ws = _workspace(lib.nnue_ft_fused_bwd_workspace_bytes(B, K, num_inputs, l1_size, P, m), dev)
+    with torch.cuda.device(dev):
+        st = lib.nnue_ft_fused_bwd(
+            _ptr(us), _ptr(them), _ptr(white_indices), _ptr(black_indices), _ptr(psqt_indices),
+            float(max_ft_activation), _ptr(grad_l0), _ptr(grad_wpsqt), _ptr(grad_bpsqt), _ptr(saved),
+            _ptr(grad_w), _ptr(grad_b), B, K, num_inputs, l1_size, P, _ptr(ws), ws.numel(), m, _stream(dev),
+        )
+    _lib.check(st, "nnue_ft_fused_bwd")
+    return grad_w, grad_b
+
+
+# --------------------------------------------------------------------------
+def device_status(device: torch.device | None = None) -> None:
+    """Synchronise and raise if any kernel since the last call skipped an
+    out-of-range index or gave up on a bounded wait."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    with torch.cuda.device(dev):
+        _lib.device_status(_stream(dev))
+
+
+def hparams_struct(**kw) -> _lib.RangerHParams:
+    hp = _lib.RangerHParams()
+    for k, v in kw.items():
+        setattr(hp, k, v)
+    return hp
+
+
+def ranger_update(p, grad, grad_ma, neg_grad_ma, variance_ma, slow, row_active, grad_scale, hp) -> None:
+    dev = _require_cuda(p, grad, grad_ma, variance_ma)
+    for t in (p, grad, grad_ma, neg_grad_ma, variance_ma, slow):
+        if t is not None:
+            assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() == p.numel()
+    if row_active is not None:
+        assert row_active.dtype == torch.uint8 and p.dim() == 2 and row_active.numel() == p.shape[0]
+        rows, width = p.shape
+    else:
+        rows, width = 1, p.numel()
+    with torch.cuda.device(dev):
+        st = _lib.load().nnue_rangerlite_update(
+            _ptr(p), _ptr(grad), _ptr(grad_ma), _ptr(neg_grad_ma), _ptr(variance_ma), _ptr(slow),
+            _ptr(row_active), _ptr(grad_scale), rows, width, C.byref(hp), _stream(dev),
+        )
+    _lib.check(st, "nnue_rangerlite_update")
+
+
+def lookahead_merge(p, slow, alpha: float) -> None:
+    dev = _require_cuda(p, slow)
+    assert p.dtype == torch.float32 and slow.dtype == torch.float32
+    assert p.is_contiguous() and slow.is_contiguous() and p.numel() == slow.numel()
+    with torch.cuda.device(dev):
+        st = _lib.load().nnue_lookahead_merge(_ptr(p), _ptr(slow), p.numel(), float(alpha), _stream(dev))
+    _lib.check(st, "nnue_lookahead_merge")
+
+
+def grad_sumsq(grad, out_sumsq) -> None:
+    dev = _require_cuda(grad, out_sumsq)
+    assert grad.dtype == torch.float32 and grad.is_contiguous()
+    with torch.cuda.device(dev):
+        st = _lib.load().nnue_grad_sumsq(_ptr(grad), grad.numel(), _ptr(out_sumsq), _stream(dev))
+    _lib.check(st, "nnue_grad_sumsq")
+
+
+def clip_coef(sumsq, max_norm: float, out_coef) -> None:
+    dev = _require_cuda(sumsq, out_coef)
+    with torch.cuda.device(dev):
+        st = _lib.load().nnue_clip_coef(_ptr(sumsq), float(max_norm), _ptr(out_coef), _stream(dev))
+    _lib.check(st, "nnue_clip_coef")

@@ -1,0 +1,147 @@
+"""ctypes binding of libnnue_b200.so (declared in include/nnue_b200.h).
+
+Loading never falls back to anything: a missing or unloadable library raises,
+and so does every call made without a CUDA device.  The library is built
+in-tree by `nnue_pytorch_b200._build`.
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+LIB_PATH = Path(__file__).resolve().parent / "libnnue_b200.so"
+
+NNUE_OK = 0
+BWD_AUTO, BWD_ATOMIC, BWD_SEGMENT = 0, 1, 2
+_BWD_MODES = {"auto": BWD_AUTO, "atomic": BWD_ATOMIC, "segment": BWD_SEGMENT}
+
+
+class RangerHParams(C.Structure):
+    """Mirror of `nnue_ranger_hparams`."""
+
+    _fields_ = [
+        ("beta2", C.c_float),
+        ("one_minus_beta2", C.c_float),
+        ("mom", C.c_float),
+        ("one_minus_mom", C.c_float),
+        ("one_plus_f", C.c_float),
+        ("f", C.c_float),
+        ("noise_norm_inv", C.c_float),
+        ("step_size", C.c_float),
+        ("bc2_sqrt", C.c_float),
+        ("eps", C.c_float),
+        ("wd_keep", C.c_float),
+        ("alpha", C.c_float),
+        ("one_minus_alpha", C.c_float),
+        ("use_pnm", C.c_int32),
+        ("step_is_odd", C.c_int32),
+        ("do_merge", C.c_int32),
+        ("phase", C.c_int32),
+    ]
+
+
+class QuantParams(C.Structure):
+    """Mirror of `nnue_quant_params`."""
+
+    _fields_ = [
+        ("ft_max", C.c_int32),
+        ("ft_shift", C.c_int32),
+        ("hidden_max", C.c_int32),
+        ("sqr_shift_l1", C.c_int32),
+        ("sqr_eps_l1", C.c_int32),
+        ("lin_shift_l1", C.c_int32),
+        ("sqr_shift_l2", C.c_int32),
+        ("sqr_eps_l2", C.c_int32),
+        ("lin_shift_l2", C.c_int32),
+        ("skip_mul", C.c_int32),
+        ("out_mul", C.c_int32),
+        ("out_div", C.c_int32),
+    ]
+
+
+_P = C.c_void_p
+_I64 = C.c_int64
+_I32 = C.c_int32
+_SZ = C.c_size_t
+
+# name -> (restype, argtypes); the complete export list of include/nnue_b200.h
+PROTOTYPES = {
+    "nnue_b200_abi_version": (C.c_int, []),
+    "nnue_b200_last_error": (C.c_char_p, []),
+    "nnue_b200_tune": (C.c_int, [C.c_char_p, C.c_int]),
+    "nnue_b200_device_status": (C.c_int, [_P, C.POINTER(_I64), C.POINTER(_I64)]),
+    "nnue_ft_sparse_fwd": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _I64, _I32, _P]),
+    "nnue_ft_sparse_bwd_workspace_bytes": (_SZ, [_I64, _I32, _I64, _I32, _I32]),
+    "nnue_ft_sparse_bwd": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _I64, _I32, _P, _SZ, _I32, _P]),
+    "nnue_ft_fused_fwd": (
+        C.c_int,
+        [_P, _P, _P, _P, _P, _P, _P, C.c_float, _P, _P, _P, _P, _I64, _I32, _I64, _I32, _I32, _P],
+    ),
+    "nnue_ft_fused_bwd_workspace_bytes": (_SZ, [_I64, _I32, _I64, _I32, _I32, _I32]),
+    "nnue_ft_fused_bwd": (
+        C.c_int,
+        [_P, _P, _P, _P, _P, C.c_float, _P, _P, _P, _P, _P, _P, _I64, _I32, _I64, _I32, _I32, _P, _SZ, _I32, _P],
+    ),
+    "nnue_rangerlite_update": (
+        C.c_int,
+        [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, C.POINTER(RangerHParams), _P],
+    ),
+    "nnue_lookahead_merge": (C.c_int, [_P, _P, _I64, C.c_float, _P]),
+    "nnue_grad_sumsq": (C.c_int, [_P, _I64, _P, _P]),
+    "nnue_clip_coef": (C.c_int, [_P, C.c_float, _P, _P]),
+    "nnue_quant_eval": (
+        C.c_int,
+        [_P] * 14 + [_I64, _I32, _I64, _I32, _I32, _I32, _I32, _I32, C.POINTER(QuantParams), _P],
+    ),
+}
+
+_lib = None
+
+
+class NnueB200Error(RuntimeError):
+    pass
+
+
+def load() -> C.CDLL:
+    """Load the shared library once and attach the prototypes."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    if not LIB_PATH.exists():
+        raise NnueB200Error(
+            f"{LIB_PATH} is missing: build it with `python -m nnue_pytorch_b200._build` "
+            "(there is no CPU or PyTorch fallback for these kernels)"
+        )
+    lib = C.CDLL(str(LIB_PATH))
+    for name, (res, args) in PROTOTYPES.items():
+        fn = getattr(lib, name)  # AttributeError if the export is missing
+        fn.restype = res
+        fn.argtypes = args
+    if lib.nnue_b200_abi_version() != 1:
+        raise NnueB200Error("libnnue_b200.so ABI version mismatch; rebuild it")
+    _lib = lib
+    return lib
+
+
+def check(status: int, what: str) -> None:
+    if status != NNUE_OK:
+        msg = load().nnue_b200_last_error().decode("utf-8", "replace")
+        raise NnueB200Error(f"{what} failed with status {status}: {msg}")
+
+
+def bwd_mode(name: str) -> int:
+    try:
+        return _BWD_MODES[name]
+    except KeyError:
+        raise ValueError(f"unknown backward mode {name!r}; expected one of {sorted(_BWD_MODES)}") from None
+
+
+def tune(key: str, value: int) -> None:
+    check(load().nnue_b200_tune(key.encode(), int(value)), f"nnue_b200_tune({key})")
+
+
+def device_status(stream_ptr: int) -> None:
+    """Synchronise the stream and raise if a kernel skipped bad indices or a wait ran out."""
+    bad, tmo = _I64(0), _I64(0)
+    check(load().nnue_b200_device_status(stream_ptr, C.byref(bad), C.byref(tmo)), "device status")

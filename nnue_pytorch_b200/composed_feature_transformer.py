@@ -1,0 +1,122 @@
+"""`ComposedFeatureTransformer`: the module that owns the shared bias, merges
+the per-feature weight tables and calls the fused double-FT operator.
+
+Mirrors model/modules/feature_transformer/composed_feature_transformer.py:11-151
+of the reference project (constructor, attributes, helper methods and
+`forward` signature), so the reference's `NNUEModel` can build it unchanged.
+"""
+
+from __future__ import annotations
+
+import math
+from collections.abc import Callable
+
+import torch
+from torch import nn
+
+from .double_ft_functions import double_feature_transform
+
+
+class ComposedFeatureTransformer(nn.Module):
+    def __init__(self, feature_classes: list[Callable[[int], nn.Module]], l1_size: int, num_psqt_buckets: int, quantization):
+        super().__init__()
+        if l1_size % 2 != 0:
+            raise ValueError(f"l1_size must be even, got {l1_size}.")
+        self.l1_size = l1_size
+        self.num_psqt_buckets = num_psqt_buckets
+        self.num_outputs = l1_size + num_psqt_buckets
+
+        features = [make(self.num_outputs) for make in feature_classes]
+        self.features = nn.ModuleList(features)
+        self.bias = nn.Parameter(torch.empty(self.num_outputs, dtype=torch.float32))
+
+        self.NUM_INPUTS = sum(f.NUM_INPUTS for f in features)
+        self.MAX_ACTIVE_FEATURES = sum(f.MAX_ACTIVE_FEATURES for f in features)
+        self.NUM_REAL_FEATURES = sum(f.NUM_REAL_FEATURES for f in features)
+        self.FEATURE_NAME = "+".join(f.FEATURE_NAME for f in features)
+        self.INPUT_FEATURE_NAME = "+".join(f.INPUT_FEATURE_NAME for f in features)
+        self.HASH = self._combined_hash()
+        self.quantization = quantization
+
+        bound = math.sqrt(1 / self.NUM_INPUTS)
+        with torch.no_grad():
+            self.bias.uniform_(-bound, bound)
+
+    def _combined_hash(self) -> int:
+        h = 0
+        for f in self.features:
+            h = ((h << 1) | (h >> 31)) & 0xFFFFFFFF  # rotate left by one, 32 bits
+            h ^= f.HASH
+        return h
+
+    def merged_weight_and_bias(self, fake_quantize_weights: bool = False):
+        """Table [NUM_INPUTS, l1+psqt] and bias the operator sees this step.
+        The PSQT part of the bias is replaced by zeros (it never trains)."""
+        tables = [f.merged_weight() for f in self.features]
+        merged = tables[0] if len(tables) == 1 else torch.cat(tables, dim=0)
+        b = self.bias[: self.l1_size]
+        if fake_quantize_weights:
+            q = self.quantization
+            merged = torch.cat(
+                [
+                    q.fake_quantize_weights(merged[:, : self.l1_size], "ft_weight"),
+                    q.fake_quantize_weights(merged[:, self.l1_size :], "ft_psqt_weight"),
+                ],
+                dim=1,
+            )
+            b = q.fake_quantize_weights(b, "ft_bias")
+        bias = torch.cat([b, torch.zeros_like(self.bias[self.l1_size :], dtype=b.dtype)], dim=0)
+        return merged, bias
+
+    @torch.no_grad()
+    def coalesce(self) -> None:
+        for f in self.features:
+            f.coalesce()
+
+    @torch.no_grad()
+    def zero_virtual_weights(self) -> None:
+        for f in self.features:
+            f.zero_virtual_weights()
+
+    @torch.no_grad()
+    def init_weights(self) -> None:
+        for f in self.features:
+            f.init_weights(self.num_psqt_buckets, self.quantization.nnue2score)
+        self.bias[self.l1_size :] = 0.0
+
+    @torch.no_grad()
+    def get_export_weights(self) -> torch.Tensor:
+        return torch.cat([f.get_export_weights() for f in self.features], dim=0)
+
+    @torch.no_grad()
+    def load_export_weights(self, export_weight: torch.Tensor) -> None:
+        at = 0
+        for f in self.features:
+            f.load_export_weights(export_weight[at : at + f.NUM_REAL_FEATURES])
+            at += f.NUM_REAL_FEATURES
+
+    def clip_weights(self, quantization) -> None:
+        for f in self.features:
+            f.clip_weights(quantization)
+
+    def forward(
+        self,
+        us: torch.Tensor,
+        them: torch.Tensor,
+        white_indices: torch.Tensor,
+        black_indices: torch.Tensor,
+        psqt_indices: torch.Tensor,
+        fake_quantize_acts: bool,
+        fake_quantize_weights: bool,
+        backend: str = "auto",
+    ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        merged, bias = self.merged_weight_and_bias(fake_quantize_weights)
+        l0, wpsqt, bpsqt = double_feature_transform(
+            us, them, white_indices, black_indices, psqt_indices, merged, bias,
+            self.quantization.max_ft_activation, self.l1_size, backend,
+        )
+        if fake_quantize_acts:
+            l0 = self.quantization.fake_quantize_ft_act(l0)
+        # inference divides by a power of two; the factor keeps both grids aligned
+        l0 = l0 * self.quantization.l0_correction_factor
+        return l0, wpsqt, bpsqt

@@ -1,0 +1,156 @@
+// Shared device/host helpers for libnnue_b200 (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+#include <string.h>
+
+#include "../../include/nnue_b200.h"
+
+#if defined(__CUDA_ARCH__) && (__CUDA_ARCH__ < 1000)
+#error "libnnue_b200 is written for sm_100a (Blackwell B200) only"
+#endif
+
+namespace nnue {
+
+constexpr int kWarpsPerCta = 8;
+constexpr int kThreads = kWarpsPerCta * 32;
+constexpr unsigned kFullMask = 0xffffffffu;
+
+// ---- host-side error plumbing ------------------------------------------
+void set_error(const char* fmt, ...);
+int cuda_fail(cudaError_t e, const char* what);
+
+#define NNUE_CUDA_TRY(expr)                                         \
+    do {                                                            \
+        cudaError_t e__ = (expr);                                   \
+        if (e__ != cudaSuccess) return ::nnue::cuda_fail(e__, #expr); \
+    } while (0)
+
+#define NNUE_REQUIRE(cond, code, ...)      \
+    do {                                   \
+        if (!(cond)) {                     \
+            ::nnue::set_error(__VA_ARGS__);\
+            return (code);                 \
+        }                                  \
+    } while (0)
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+// Device status word: [0] = count of out-of-range indices skipped,
+// [1] = count of bounded waits that ran out.  One per device, lazily resolved.
+unsigned long long* device_status_ptr();
+
+struct Tuning {
+    int fwd_u = 2;        // float4 per lane per half in the fused forward (1, 2 or 4)
+    int bwd_u = 2;        // float4 per lane in the segment gather-sum (1, 2 or 4)
+    int sparse_u = 2;     // float4 per lane in the sparse-linear forward
+    int stage_idx = 1;    // 1 = bulk-copy index lists to shared memory when aligned
+    int long_row = 256;   // rows with more hits are reduced by a whole CTA
+    int prologue_pb = 32; // positions per CTA in the backward prologue
+    int sort_segments = 1;// 1 = order every CSR segment (deterministic sums)
+};
+Tuning& tuning();
+
+int sm_count();
+
+// ---- device helpers -----------------------------------------------------
+#ifdef __CUDACC__
+
+__device__ __forceinline__ float4 ldg4(const float4* p) { return __ldg(p); }
+
+__device__ __forceinline__ void st_stream4(float4* p, float4 v) { __stcs(p, v); }
+
+__device__ __forceinline__ float4 f4_zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+
+__device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
+    return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z),
+                       __fadd_rn(a.w, b.w));
+}
+
+// a*s + b*t with each product and the sum rounded separately, as the
+// elementwise torch composition does (no FMA contraction).
+__device__ __forceinline__ float mix(float s, float a, float t, float b) {
+    return __fadd_rn(__fmul_rn(s, a), __fmul_rn(t, b));
+}
+__device__ __forceinline__ float4 f4_mix(float s, float4 a, float t, float4 b) {
+    return make_float4(mix(s, a.x, t, b.x), mix(s, a.y, t, b.y), mix(s, a.z, t, b.z),
+                       mix(s, a.w, t, b.w));
+}
+
+__device__ __forceinline__ void red_add_v4(float* addr, float4 v) {
+    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(addr), "f"(v.x), "f"(v.y),
+                 "f"(v.z), "f"(v.w)
+                 : "memory");
+}
+
+__device__ __forceinline__ void note_bad_index(unsigned long long* status) {
+    atomicAdd(status, 1ULL);
+}
+__device__ __forceinline__ void note_timeout(unsigned long long* status) {
+    atomicAdd(status + 1, 1ULL);
+}
+
+// Number of leading non-negative entries of list[0..K): the reference stops
+// at the first -1 (sparse_linear_kernel.py:149, fused_ft_kernel.py:69).
+// Whole-warp call; `list` may be shared or global memory.
+__device__ __forceinline__ int count_active(const int32_t* list, int K, int lane) {
+    int n = 0;
+    for (int k0 = 0; k0 < K; k0 += 32) {
+        const int k = k0 + lane;
+        const int v = (k < K) ? list[k] : -1;
+        const unsigned neg = __ballot_sync(kFullMask, v < 0);
+        if (neg) {
+            n += __ffs(neg) - 1;
+            return n;
+        }
+        n += 32;
+    }
+    return n < K ? n : K;
+}
+
+// ---- mbarrier + 1-D bulk copy (global -> shared), no multicast ----------
+__device__ __forceinline__ uint32_t smem_u32(const void* p) {
+    return static_cast<uint32_t>(__cvta_generic_to_shared(p));
+}
+__device__ __forceinline__ void mbar_init(uint64_t* bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void fence_barrier_init() {
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
+                 "r"(bytes)
+                 : "memory");
+}
+// 16-byte aligned src/dst, bytes % 16 == 0.
+__device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src_gmem, unsigned bytes,
+                                         uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::
+            "r"(smem_u32(dst_smem)),
+        "l"(src_gmem), "r"(bytes), "r"(smem_u32(bar))
+        : "memory");
+}
+// Bounded wait on phase `parity`.  Returns false when the limit ran out.
+__device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity) {
+    const uint32_t a = smem_u32(bar);
+    for (int it = 0; it < (1 << 16); ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n\t.reg .pred p;\n\t"
+            "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+            "selp.u32 %0, 1, 0, p;\n\t}"
+            : "=r"(ok)
+            : "r"(a), "r"(parity)
+            : "memory");
+        if (ok) return true;
+    }
+    return false;
+}
+
+#endif  // __CUDACC__
+
+}  // namespace nnue

@@ -1,0 +1,236 @@
+// Integer evaluation of a quantized net: int16 feature-transformer gather,
+// pairwise product >> ft_shift, three int8 layers of the selected layer
+// stack, truncating output division and the PSQT term.  Integer restatement
+// of the fake-quantized float forward of the reference project
+// (model/quantize.py:36-56,133-147, model/modules/layer_stacks.py:33-84,
+// model/model.py:107-133); the reference holds no integer evaluator.
+//
+// One CTA per position (grid-stride).  Thread t owns the 8 int16 columns
+// [8t, 8t+8) of the first half of the accumulator and the same columns of the
+// second half, for both perspectives: every row read is one 16-byte load per
+// half per thread, 384 B contiguous per warp.
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace nnue {
+
+constexpr int kQThreads = 192;
+constexpr int kQMaxL2 = 64;   // widest hidden layers this kernel takes
+constexpr int kQRowsInFlight = 4;
+
+struct QuantDims {
+    int K, L1, L2, L3, P, buckets;
+    int64_t N;
+};
+
+__device__ __forceinline__ void add8(int (&acc)[8], uint4 v) {
+    const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        acc[2 * j] += (int)(short)(w[j] & 0xffffu);
+        acc[2 * j + 1] += (int)(short)(w[j] >> 16);
+    }
+}
+
+__device__ __forceinline__ int clampi(int x, int lo, int hi) { return x < lo ? lo : (x > hi ? hi : x); }
+
+__global__ void __launch_bounds__(kQThreads)
+    k_quant_eval(const int32_t* __restrict__ white_idx, const int32_t* __restrict__ black_idx,
+                 const uint8_t* __restrict__ stm_white, const int32_t* __restrict__ bucket,
+                 const int16_t* __restrict__ ft_w, const int32_t* __restrict__ ft_psqt,
+                 const int32_t* __restrict__ ft_b, const int8_t* __restrict__ l1_w,
+                 const int32_t* __restrict__ l1_b, const int8_t* __restrict__ l2_w,
+                 const int32_t* __restrict__ l2_b, const int8_t* __restrict__ out_w,
+                 const int32_t* __restrict__ out_b, int32_t* __restrict__ out, int64_t B, QuantDims d,
+                 nnue_quant_params q, unsigned long long* status) {
+    extern __shared__ __align__(16) unsigned char s_raw[];
+    int8_t* s_x0 = reinterpret_cast<int8_t*>(s_raw);                  // [L1]
+    int32_t* s_o1 = reinterpret_cast<int32_t*>(s_raw + d.L1);         // [L2]
+    int8_t* s_x1 = reinterpret_cast<int8_t*>(s_o1 + kQMaxL2);         // [2*L2 + 2*L3]
+    __shared__ int s_psq[2];
+    __shared__ int s_n[2];
+
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int nwarps = kQThreads / 32;
+    const int h = d.L1 >> 1;
+    const int h8 = h >> 3;  // 16-byte chunks per half
+
+    for (int64_t p = blockIdx.x; p < B; p += gridDim.x) {
+        const int stm = stm_white[p] ? 1 : 0;
+        int bk = bucket[p];
+        if (bk < 0 || bk >= d.buckets || bk >= d.P) {
+            if (tid == 0) note_bad_index(status);
+            bk = 0;
+        }
+        // "us" is the side to move: its accumulator forms the first half of l0
+        const int32_t* lists[2] = {stm ? white_idx + p * d.K : black_idx + p * d.K,
+                                   stm ? black_idx + p * d.K : white_idx + p * d.K};
+        if (tid < 2) s_psq[tid] = 0;
+        if (warp < 2) {
+            const int n = count_active(lists[warp], d.K, lane);
+            if (lane == 0) s_n[warp] = n;
+        }
+        __syncthreads();
+        // PSQT: integer adds commute, so any order gives the same sum
+        for (int s = 0; s < 2; ++s) {
+            int psq = 0;
+            for (int k = tid; k < s_n[s]; k += kQThreads) {
+                const int r = lists[s][k];
+                if (r >= 0 && (int64_t)r < d.N) psq += ft_psqt[(int64_t)r * d.P + bk];
+                else note_bad_index(status);
+            }
+            if (psq) atomicAdd(&s_psq[s], psq);
+        }
+
+        for (int c0 = 0; c0 < h8; c0 += kQThreads) {
+            const int c = c0 + tid;
+            const bool live = c < h8;
+            int x[2][2][8];  // [perspective][half][column]
+            for (int s = 0; s < 2; ++s) {
+                if (live) {
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) {
+                        x[s][0][j] = ft_b[8 * c + j];
+                        x[s][1][j] = ft_b[h + 8 * c + j];
+                    }
+                }
+                const int32_t* list = lists[s];
+                const int n = s_n[s];
+                for (int k0 = 0; k0 < n; k0 += kQRowsInFlight) {
+                    uint4 v[kQRowsInFlight][2];
+                    bool ok[kQRowsInFlight];
+#pragma unroll
+                    for (int t = 0; t < kQRowsInFlight; ++t) {
+                        const int r = (k0 + t < n) ? list[k0 + t] : -1;
+                        ok[t] = r >= 0 && (int64_t)r < d.N;
+                        if (ok[t] && live) {
+                            const uint4* row = reinterpret_cast<const uint4*>(ft_w + (int64_t)r * d.L1);
+                            v[t][0] = __ldg(row + c);
+                            v[t][1] = __ldg(row + h8 + c);
+                        }
+                    }
+#pragma unroll
+                    for (int t = 0; t < kQRowsInFlight; ++t) {
+                        if (ok[t] && live) {
+                            add8(x[s][0], v[t][0]);
+                            add8(x[s][1], v[t][1]);
+                        }
+                    }
+                }
+            }
+            if (live) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const int a0 = clampi(x[0][0][j], 0, q.ft_max), a1 = clampi(x[0][1][j], 0, q.ft_max);
+                    const int b0 = clampi(x[1][0][j], 0, q.ft_max), b1 = clampi(x[1][1][j], 0, q.ft_max);
+                    s_x0[8 * c + j] = (int8_t)min((a0 * a1) >> q.ft_shift, q.hidden_max);
+                    s_x0[h + 8 * c + j] = (int8_t)min((b0 * b1) >> q.ft_shift, q.hidden_max);
+                }
+            }
+        }
+        __syncthreads();
+
+        // layer 1: L2 outputs over L1 int8 inputs, dp4a on 16-byte chunks
+        {
+            const int chunks = d.L1 >> 4;
+            const int4* xin = reinterpret_cast<const int4*>(s_x0);
+            for (int o = warp; o < d.L2; o += nwarps) {
+                const int4* wrow = reinterpret_cast<const int4*>(l1_w + ((int64_t)bk * d.L2 + o) * d.L1);
+                int acc = 0;
+                for (int ch = lane; ch < chunks; ch += 32) {
+                    const int4 w = __ldg(wrow + ch);
+                    const int4 a = xin[ch];
+                    acc = __dp4a(a.x, w.x, acc);
+                    acc = __dp4a(a.y, w.y, acc);
+                    acc = __dp4a(a.z, w.z, acc);
+                    acc = __dp4a(a.w, w.w, acc);
+                }
+#pragma unroll
+                for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(kFullMask, acc, s);
+                if (lane == 0) s_o1[o] = acc + l1_b[bk * d.L2 + o];
+            }
+        }
+        __syncthreads();
+
+        if (warp == 0) {
+            // squared and linear activations of layer 1 -> x1[0 .. 2*L2)
+            for (int o = lane; o < d.L2; o += 32) {
+                const long long v = s_o1[o];
+                const long long sq = (v * v + q.sqr_eps_l1) >> q.sqr_shift_l1;
+                s_x1[o] = (int8_t)(sq > q.hidden_max ? q.hidden_max : sq);
+                s_x1[d.L2 + o] = (int8_t)clampi((int)(v >> q.lin_shift_l1), 0, q.hidden_max);
+            }
+            __syncwarp();
+            // layer 2: lane = output
+            const int in2 = 2 * d.L2;
+            for (int o = lane; o < d.L3; o += 32) {
+                const int8_t* wrow = l2_w + ((int64_t)bk * d.L3 + o) * in2;
+                int acc = l2_b[bk * d.L3 + o];
+                for (int i = 0; i < in2; ++i) acc += (int)s_x1[i] * (int)wrow[i];
+                const long long v = acc;
+                const long long sq = (v * v + q.sqr_eps_l2) >> q.sqr_shift_l2;
+                s_x1[in2 + o] = (int8_t)(sq > q.hidden_max ? q.hidden_max : sq);
+                s_x1[in2 + d.L3 + o] = (int8_t)clampi((int)(v >> q.lin_shift_l2), 0, q.hidden_max);
+            }
+            __syncwarp();
+            // output layer: one value over 2*L2 + 2*L3 inputs
+            const int in3 = 2 * d.L2 + 2 * d.L3;
+            const int8_t* wrow = out_w + (int64_t)bk * in3;
+            int acc = 0;
+            for (int i = lane; i < in3; i += 32) acc += (int)s_x1[i] * (int)wrow[i];
+#pragma unroll
+            for (int s = 16; s > 0; s >>= 1) acc += __shfl_xor_sync(kFullMask, acc, s);
+            if (lane == 0) {
+                const long long o3 = (long long)acc + out_b[bk];
+                const long long skip = ((long long)s_o1[d.L2 - 2] - (long long)s_o1[d.L2 - 1]) * q.skip_mul;
+                const long long num = 2 * (o3 + skip) * (long long)q.out_mul;
+                const long long pos = num / q.out_div;  // C++ division truncates toward zero
+                // s_psq[0] belongs to the side to move
+                const long long psq_white_minus_black =
+                    stm ? (long long)s_psq[0] - s_psq[1] : (long long)s_psq[1] - s_psq[0];
+                out[p] = (int32_t)(2 * pos + (stm ? psq_white_minus_black : -psq_white_minus_black));
+            }
+        }
+        __syncthreads();
+    }
+}
+
+}  // namespace nnue
+
+using namespace nnue;
+
+extern "C" int nnue_quant_eval(const int32_t* white_idx, const int32_t* black_idx,
+                               const uint8_t* stm_white, const int32_t* bucket, const int16_t* ft_w,
+                               const int32_t* ft_psqt, const int32_t* ft_b, const int8_t* l1_w,
+                               const int32_t* l1_b, const int8_t* l2_w, const int32_t* l2_b,
+                               const int8_t* out_w, const int32_t* out_b, int32_t* out, int64_t B,
+                               int32_t K, int64_t N, int32_t L1, int32_t L2, int32_t L3, int32_t P,
+                               int32_t buckets, const nnue_quant_params* qp, void* stream) {
+    NNUE_REQUIRE(qp != nullptr, NNUE_ERR_ARG, "nnue_quant_eval: null quantization parameters");
+    NNUE_REQUIRE(B >= 0 && K >= 0 && N >= 0 && L1 > 0 && L2 > 1 && L3 > 0 && P > 0 && buckets > 0,
+                 NNUE_ERR_ARG, "nnue_quant_eval: bad size");
+    if (B == 0) return NNUE_OK;
+    NNUE_REQUIRE(white_idx && black_idx && stm_white && bucket && ft_w && ft_psqt && ft_b && l1_w &&
+                     l1_b && l2_w && l2_b && out_w && out_b && out,
+                 NNUE_ERR_ARG, "nnue_quant_eval: null pointer");
+    NNUE_REQUIRE(L1 % 32 == 0, NNUE_ERR_UNSUPPORTED,
+                 "nnue_quant_eval: L1 must be a multiple of 32 (16-byte int16 chunks per half), got %d", L1);
+    NNUE_REQUIRE(L2 <= kQMaxL2 && L3 <= kQMaxL2, NNUE_ERR_UNSUPPORTED,
+                 "nnue_quant_eval: hidden layers wider than %d are not covered", kQMaxL2);
+    NNUE_REQUIRE(aligned16(ft_w) && aligned16(l1_w), NNUE_ERR_ALIGN,
+                 "nnue_quant_eval: ft_w / l1_w must be 16-byte aligned");
+    NNUE_REQUIRE(qp->out_div > 0 && qp->ft_shift >= 0 && qp->sqr_shift_l1 >= 0 && qp->sqr_shift_l2 >= 0,
+                 NNUE_ERR_ARG, "nnue_quant_eval: bad quantization parameters");
+    unsigned long long* status = device_status_ptr();
+    NNUE_REQUIRE(status, NNUE_ERR_CUDA, "nnue_quant_eval: no device status word");
+    QuantDims d{K, L1, L2, L3, P, buckets, N};
+    const size_t smem = (size_t)L1 + kQMaxL2 * sizeof(int32_t) + 4 * kQMaxL2 + 16;
+    NNUE_REQUIRE(smem <= 48 * 1024, NNUE_ERR_UNSUPPORTED, "nnue_quant_eval: L1 too large");
+    const unsigned grid = (unsigned)std::min<int64_t>(B, (int64_t)sm_count() * 10);
+    k_quant_eval<<<grid, kQThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        white_idx, black_idx, stm_white, bucket, ft_w, ft_psqt, ft_b, l1_w, l1_b, l2_w, l2_b, out_w,
+        out_b, out, B, d, *qp, status);
+    NNUE_CUDA_TRY(cudaGetLastError());
+    return NNUE_OK;
+}

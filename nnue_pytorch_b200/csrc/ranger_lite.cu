@@ -1,0 +1,211 @@
+// Fused RangerLite update: Adam second moment, positive-negative momentum,
+// optional stable weight decay, parameter step and lookahead merge in one
+// pass over the tensor (5 reads + 3 writes of 4 bytes per element, +2/+1 on a
+// merge step).  Arithmetic follows model/optimizers/ranger_lite.py:592-742 of
+// the reference project (its Python path); replaces its CuPy kernels (:46-201)
+// and the separate lookahead pass (:746-768).
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace nnue {
+
+using RangerConst = nnue_ranger_hparams;
+
+__device__ __forceinline__ void ranger_elem(const RangerConst& c, float scale, float g, float& p,
+                                            float& gm, float& ngm, float& vm, float& slow) {
+    g = __fmul_rn(g, scale);
+    if (c.phase != 2) vm = __fadd_rn(__fmul_rn(vm, c.beta2), __fmul_rn(c.one_minus_beta2, __fmul_rn(g, g)));
+    if (c.phase == 1) return;
+    const float denom = __fadd_rn(__fdiv_rn(__fsqrt_rn(vm), c.bc2_sqrt), c.eps);
+    float upd;
+    if (c.use_pnm) {
+        float pos = c.step_is_odd ? gm : ngm;
+        const float neg = c.step_is_odd ? ngm : gm;
+        pos = __fadd_rn(__fmul_rn(pos, c.mom), __fmul_rn(c.one_minus_mom, g));
+        upd = __fmul_rn(__fadd_rn(__fmul_rn(pos, c.one_plus_f), __fmul_rn(-c.f, neg)), c.noise_norm_inv);
+        if (c.step_is_odd) gm = pos; else ngm = pos;
+    } else {
+        gm = __fadd_rn(__fmul_rn(gm, c.mom), __fmul_rn(c.one_minus_mom, g));
+        upd = gm;
+    }
+    float q = p;
+    if (c.wd_keep != 1.f) q = __fmul_rn(q, c.wd_keep);
+    q = __fadd_rn(q, __fmul_rn(-c.step_size, __fdiv_rn(upd, denom)));
+    if (c.do_merge) {
+        q = __fadd_rn(__fmul_rn(q, c.alpha), __fmul_rn(c.one_minus_alpha, slow));
+        slow = q;
+    }
+    p = q;
+}
+
+__device__ __forceinline__ void ranger_vec4(const RangerConst& c, float scale, int64_t i,
+                                            const float4* g4, float4* p4, float4* gm4, float4* ngm4,
+                                            float4* vm4, float4* slow4, float4 gv) {
+    float4 pv = p4[i], gmv = gm4[i], vmv = vm4[i];
+    float4 ngv = c.use_pnm ? ngm4[i] : f4_zero();
+    float4 sv = c.do_merge ? slow4[i] : f4_zero();
+    ranger_elem(c, scale, gv.x, pv.x, gmv.x, ngv.x, vmv.x, sv.x);
+    ranger_elem(c, scale, gv.y, pv.y, gmv.y, ngv.y, vmv.y, sv.y);
+    ranger_elem(c, scale, gv.z, pv.z, gmv.z, ngv.z, vmv.z, sv.z);
+    ranger_elem(c, scale, gv.w, pv.w, gmv.w, ngv.w, vmv.w, sv.w);
+    if (c.phase != 2) vm4[i] = vmv;
+    if (c.phase == 1) return;
+    p4[i] = pv;
+    if (!c.use_pnm || c.step_is_odd) gm4[i] = gmv;
+    if (c.use_pnm && !c.step_is_odd) ngm4[i] = ngv;
+    if (c.do_merge) slow4[i] = sv;
+    (void)g4;
+}
+
+// Flat tensor: grid-stride over float4 (VEC) or scalars.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+    k_ranger_flat(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ gm,
+                  float* __restrict__ ngm, float* __restrict__ vm, float* __restrict__ slow,
+                  const float* __restrict__ d_scale, int64_t n, RangerConst c) {
+    const float scale = d_scale ? __ldg(d_scale) : 1.f;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t done = 0;
+    if (VEC) {
+        const int64_t n4 = n >> 2;
+        const float4* g4 = reinterpret_cast<const float4*>(g);
+        for (int64_t i = t0; i < n4; i += stride)
+            ranger_vec4(c, scale, i, g4, reinterpret_cast<float4*>(p), reinterpret_cast<float4*>(gm),
+                        reinterpret_cast<float4*>(ngm), reinterpret_cast<float4*>(vm),
+                        reinterpret_cast<float4*>(slow), __ldg(g4 + i));
+        done = n4 << 2;
+    }
+    for (int64_t i = done + t0; i < n; i += stride) {
+        float pv = p[i], gmv = gm[i], vmv = vm[i];
+        float ngv = c.use_pnm ? ngm[i] : 0.f, sv = c.do_merge ? slow[i] : 0.f;
+        ranger_elem(c, scale, g[i], pv, gmv, ngv, vmv, sv);
+        if (c.phase != 2) vm[i] = vmv;
+        if (c.phase == 1) continue;
+        p[i] = pv;
+        if (!c.use_pnm || c.step_is_odd) gm[i] = gmv;
+        if (c.use_pnm && !c.step_is_odd) ngm[i] = ngv;
+        if (c.do_merge) slow[i] = sv;
+    }
+}
+
+// Row-wise with the touched-rows-only rule.  One CTA walks rows; a row whose
+// flag is clear and whose gradient row is all zero is left alone (all of its
+// moments are zero, so the full update would rewrite the same bits).
+// width4 <= kThreads * kRowSlots float4.
+constexpr int kRowSlots = 4;
+__global__ void __launch_bounds__(kThreads)
+    k_ranger_rows(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ gm,
+                  float* __restrict__ ngm, float* __restrict__ vm, float* __restrict__ slow,
+                  uint8_t* __restrict__ row_active, const float* __restrict__ d_scale, int64_t rows,
+                  int64_t width4, RangerConst c) {
+    const float scale = d_scale ? __ldg(d_scale) : 1.f;
+    const float4* g4 = reinterpret_cast<const float4*>(g);
+    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+        const int64_t base = row * width4;
+        float4 gv[kRowSlots];
+        int nz = 0;
+#pragma unroll
+        for (int s = 0; s < kRowSlots; ++s) {
+            const int64_t col = (int64_t)s * kThreads + threadIdx.x;
+            gv[s] = col < width4 ? __ldg(g4 + base + col) : f4_zero();
+            nz |= (gv[s].x != 0.f) | (gv[s].y != 0.f) | (gv[s].z != 0.f) | (gv[s].w != 0.f);
+        }
+        const int active = row_active[row];
+        const int any = __syncthreads_or(nz);
+        if (!active && !any) continue;  // uniform
+        if (!active && threadIdx.x == 0) row_active[row] = 1;
+#pragma unroll
+        for (int s = 0; s < kRowSlots; ++s) {
+            const int64_t col = (int64_t)s * kThreads + threadIdx.x;
+            if (col < width4)
+                ranger_vec4(c, scale, base + col, g4, reinterpret_cast<float4*>(p),
+                            reinterpret_cast<float4*>(gm), reinterpret_cast<float4*>(ngm),
+                            reinterpret_cast<float4*>(vm), reinterpret_cast<float4*>(slow), gv[s]);
+        }
+    }
+}
+
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+    k_lookahead(float* __restrict__ p, float* __restrict__ slow, int64_t n, float alpha,
+                float one_minus_alpha) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    int64_t done = 0;
+    auto f = [alpha, one_minus_alpha](float a, float b) {
+        return __fadd_rn(__fmul_rn(a, alpha), __fmul_rn(one_minus_alpha, b));
+    };
+    if (VEC) {
+        const int64_t n4 = n >> 2;
+        float4* p4 = reinterpret_cast<float4*>(p);
+        float4* s4 = reinterpret_cast<float4*>(slow);
+        for (int64_t i = t0; i < n4; i += stride) {
+            const float4 a = p4[i], b = s4[i];
+            const float4 r = make_float4(f(a.x, b.x), f(a.y, b.y), f(a.z, b.z), f(a.w, b.w));
+            p4[i] = r;
+            s4[i] = r;
+        }
+        done = n4 << 2;
+    }
+    for (int64_t i = done + t0; i < n; i += stride) {
+        const float r = f(p[i], slow[i]);
+        p[i] = r;
+        slow[i] = r;
+    }
+}
+
+}  // namespace nnue
+
+using namespace nnue;
+
+extern "C" int nnue_rangerlite_update(float* p, const float* grad, float* grad_ma,
+                                      float* neg_grad_ma, float* variance_ma, float* slow,
+                                      uint8_t* row_active, const float* d_grad_scale, int64_t rows,
+                                      int64_t width, const nnue_ranger_hparams* hp, void* stream) {
+    NNUE_REQUIRE(hp != nullptr, NNUE_ERR_ARG, "nnue_rangerlite_update: null hyper-parameters");
+    NNUE_REQUIRE(rows >= 0 && width >= 0, NNUE_ERR_ARG, "nnue_rangerlite_update: negative size");
+    const int64_t n = rows * width;
+    if (n == 0) return NNUE_OK;
+    NNUE_REQUIRE(p && grad && grad_ma && variance_ma, NNUE_ERR_ARG, "nnue_rangerlite_update: null tensor");
+    NNUE_REQUIRE(!hp->use_pnm || neg_grad_ma, NNUE_ERR_ARG, "nnue_rangerlite_update: PNM needs neg_grad_ma");
+    NNUE_REQUIRE(!hp->do_merge || slow, NNUE_ERR_ARG, "nnue_rangerlite_update: merge needs the slow copy");
+    NNUE_REQUIRE(hp->phase >= 0 && hp->phase <= 2, NNUE_ERR_ARG, "nnue_rangerlite_update: bad phase");
+    RangerConst c = *hp;
+    if (c.phase == 1) c.do_merge = 0;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool al = aligned16(p) && aligned16(grad) && aligned16(grad_ma) && aligned16(variance_ma) &&
+                    (!neg_grad_ma || aligned16(neg_grad_ma)) && (!slow || aligned16(slow));
+    const int sms = sm_count();
+    if (row_active && al && width % 4 == 0 && width / 4 <= (int64_t)kThreads * kRowSlots && hp->phase != 1) {
+        const unsigned grid = (unsigned)std::min<int64_t>(rows, (int64_t)sms * 8);
+        k_ranger_rows<<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma, slow,
+                                               row_active, d_grad_scale, rows, width / 4, c);
+    } else {
+        const int64_t work = al ? (n / 4 + 1) : n;
+        const unsigned grid = (unsigned)std::min<int64_t>((work + kThreads - 1) / kThreads, (int64_t)sms * 8);
+        if (al)
+            k_ranger_flat<true><<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma, slow,
+                                                         d_grad_scale, n, c);
+        else
+            k_ranger_flat<false><<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma,
+                                                          slow, d_grad_scale, n, c);
+    }
+    NNUE_CUDA_TRY(cudaGetLastError());
+    return NNUE_OK;
+}
+
+extern "C" int nnue_lookahead_merge(float* p, float* slow, int64_t n, float alpha, void* stream) {
+    NNUE_REQUIRE(n >= 0, NNUE_ERR_ARG, "nnue_lookahead_merge: negative size");
+    if (n == 0) return NNUE_OK;
+    NNUE_REQUIRE(p && slow, NNUE_ERR_ARG, "nnue_lookahead_merge: null tensor");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const bool al = aligned16(p) && aligned16(slow);
+    const int64_t work = al ? (n / 4 + 1) : n;
+    const unsigned grid = (unsigned)std::min<int64_t>((work + kThreads - 1) / kThreads, (int64_t)sm_count() * 8);
+    if (al) k_lookahead<true><<<grid, kThreads, 0, s>>>(p, slow, n, alpha, 1.0f - alpha);
+    else k_lookahead<false><<<grid, kThreads, 0, s>>>(p, slow, n, alpha, 1.0f - alpha);
+    NNUE_CUDA_TRY(cudaGetLastError());
+    return NNUE_OK;
+}
