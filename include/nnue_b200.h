@@ -57,6 +57,10 @@ enum {
 int nnue_b200_abi_version(void);
 const char* nnue_b200_last_error(void);
 
+/* Number of kernels this process has launched through the library so far
+ * (host-side tally, all devices). */
+int64_t nnue_b200_launch_count(void);
+
 /* Tuning knob for experiments ("fwd_u", "bwd_u", "stage_idx", ...).
  * Unknown keys return NNUE_ERR_ARG.  Process-wide, not thread-safe. */
 int nnue_b200_tune(const char* key, int value);

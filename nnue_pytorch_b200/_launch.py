@@ -18,6 +18,55 @@ from . import _lib
 _BWD_MODE = "auto"
 
 
+class KernelTimer:
+    """Optional CUDA-event timing of the C-ABI calls, on the stream they launch
+    on.  Nothing synchronises until `summary()` is read."""
+
+    def __init__(self):
+        self.spans: dict[str, list] = {}
+
+    def span(self, name: str, device: torch.device):
+        return _Span(self, name, device)
+
+    def summary(self) -> dict[str, dict]:
+        torch.cuda.synchronize()
+        out = {}
+        for name, pairs in self.spans.items():
+            ms = [a.elapsed_time(b) for a, b in pairs]
+            out[name] = {"calls": len(ms), "total_ms": sum(ms), "mean_ms": sum(ms) / max(len(ms), 1)}
+        return out
+
+
+class _Span:
+    def __init__(self, timer, name, device):
+        self.timer, self.name, self.device = timer, name, device
+
+    def __enter__(self):
+        self.a = torch.cuda.Event(enable_timing=True)
+        self.b = torch.cuda.Event(enable_timing=True)
+        self.a.record(torch.cuda.current_stream(self.device))
+
+    def __exit__(self, *exc):
+        self.b.record(torch.cuda.current_stream(self.device))
+        self.timer.spans.setdefault(self.name, []).append((self.a, self.b))
+
+
+class _NoSpan:
+    def __enter__(self):
+        return None
+
+    def __exit__(self, *exc):
+        return False
+
+
+TIMER: KernelTimer | None = None
+_NO_SPAN = _NoSpan()
+
+
+def _span(name: str, device: torch.device):
+    return TIMER.span(name, device) if TIMER is not None else _NO_SPAN
+
+
 def set_backward_mode(mode: str) -> None:
     """Select the scatter strategy of the backward kernels: auto | atomic | segment."""
     global _BWD_MODE
@@ -64,7 +113,7 @@ def sparse_linear_forward(indices: torch.Tensor, weight: torch.Tensor, bias: tor
     B, K = indices.shape
     N, W = weight.shape
     out = torch.empty(B, W, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("sparse_fwd", dev):
         st = _lib.load().nnue_ft_sparse_fwd(
             _ptr(indices), _ptr(weight), _ptr(bias), _ptr(out), B, K, N, W, _stream(dev)
         )
@@ -85,7 +134,7 @@ def sparse_linear_backward(
     grad_w = torch.empty(num_inputs, W, dtype=torch.float32, device=dev)
     grad_b = torch.empty(W, dtype=torch.float32, device=dev)
     ws = _workspace(lib.nnue_ft_sparse_bwd_workspace_bytes(B, K, num_inputs, W, m), dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("sparse_bwd", dev):
         st = lib.nnue_ft_sparse_bwd(
             _ptr(indices), _ptr(grad_out), _ptr(grad_w), _ptr(grad_b), B, K, num_inputs, W,
             _ptr(ws), ws.numel(), m, _stream(dev),
@@ -118,7 +167,7 @@ def fused_forward(us, them, white_indices, black_indices, psqt_indices, weight, 
     wpsqt = torch.empty(B, 1, dtype=torch.float32, device=dev)
     bpsqt = torch.empty(B, 1, dtype=torch.float32, device=dev)
     saved = torch.empty(B, 4, l1_size // 2, dtype=torch.float32, device=dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("fused_fwd", dev):
         st = _lib.load().nnue_ft_fused_fwd(
             _ptr(us), _ptr(them), _ptr(white_indices), _ptr(black_indices), _ptr(psqt_indices),
             _ptr(weight), _ptr(bias), float(max_ft_activation),
@@ -143,7 +192,7 @@ def fused_backward(
     grad_w = torch.empty(num_inputs, num_outputs, dtype=torch.float32, device=dev)
     grad_b = torch.empty(num_outputs, dtype=torch.float32, device=dev)
     ws = _workspace(lib.nnue_ft_fused_bwd_workspace_bytes(B, K, num_inputs, l1_size, P, m), dev)
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("fused_bwd", dev):
         st = lib.nnue_ft_fused_bwd(
             _ptr(us), _ptr(them), _ptr(white_indices), _ptr(black_indices), _ptr(psqt_indices),
             float(max_ft_activation), _ptr(grad_l0), _ptr(grad_wpsqt), _ptr(grad_bpsqt), _ptr(saved),
@@ -179,7 +228,7 @@ def ranger_update(p, grad, grad_ma, neg_grad_ma, variance_ma, slow, row_active, 
         rows, width = p.shape
     else:
         rows, width = 1, p.numel()
-    with torch.cuda.device(dev):
+    with torch.cuda.device(dev), _span("ranger_table" if row_active is not None or p.numel() > (1 << 22) else "ranger_small", dev):
         st = _lib.load().nnue_rangerlite_update(
             _ptr(p), _ptr(grad), _ptr(grad_ma), _ptr(neg_grad_ma), _ptr(variance_ma), _ptr(slow),
             _ptr(row_active), _ptr(grad_scale), rows, width, C.byref(hp), _stream(dev),

@@ -69,6 +69,7 @@ _SZ = C.c_size_t
 PROTOTYPES = {
     "nnue_b200_abi_version": (C.c_int, []),
     "nnue_b200_last_error": (C.c_char_p, []),
+    "nnue_b200_launch_count": (C.c_int64, []),
     "nnue_b200_tune": (C.c_int, [C.c_char_p, C.c_int]),
     "nnue_b200_device_status": (C.c_int, [_P, C.POINTER(_I64), C.POINTER(_I64)]),
     "nnue_ft_sparse_fwd": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _I64, _I32, _P]),

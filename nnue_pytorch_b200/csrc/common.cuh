@@ -55,6 +55,9 @@ Tuning& tuning();
 
 int sm_count();
 
+// Host-side tally of kernels this process has launched (for benchmarks).
+void note_launches(int n);
+
 // ---- device helpers -----------------------------------------------------
 #ifdef __CUDACC__
 

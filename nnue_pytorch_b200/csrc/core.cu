@@ -43,6 +43,9 @@ unsigned long long* device_status_ptr() {
     return cache[dev];
 }
 
+static unsigned long long g_launches = 0;
+void note_launches(int n) { g_launches += (unsigned long long)n; }
+
 int sm_count() {
     static int cache[64] = {0};
     int dev = 0;
@@ -96,6 +99,8 @@ extern "C" int nnue_b200_abi_version(void) { return NNUE_B200_ABI_VERSION; }
 
 extern "C" const char* nnue_b200_last_error(void) { return g_error; }
 
+extern "C" int64_t nnue_b200_launch_count(void) { return (int64_t)g_launches; }
+
 extern "C" int nnue_b200_tune(const char* key, int value) {
     NNUE_REQUIRE(key != nullptr, NNUE_ERR_ARG, "nnue_b200_tune: null key");
     Tuning& t = tuning();
@@ -143,6 +148,7 @@ extern "C" int nnue_grad_sumsq(const float* grad, int64_t n, float* d_out_sumsq,
     const int64_t want = (n / 4 + kThreads - 1) / kThreads + 1;
     const unsigned grid = (unsigned)std::min<int64_t>(want, (int64_t)sm_count() * 8);
     k_sumsq<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(grad, n, d_out_sumsq);
+    note_launches(1);
     NNUE_CUDA_TRY(cudaGetLastError());
     return NNUE_OK;
 }
@@ -150,6 +156,7 @@ extern "C" int nnue_grad_sumsq(const float* grad, int64_t n, float* d_out_sumsq,
 extern "C" int nnue_clip_coef(const float* d_sumsq, float max_norm, float* d_coef, void* stream) {
     NNUE_REQUIRE(d_sumsq && d_coef, NNUE_ERR_ARG, "nnue_clip_coef: null pointer");
     k_clip_coef<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(d_sumsq, max_norm, d_coef);
+    note_launches(1);
     NNUE_CUDA_TRY(cudaGetLastError());
     return NNUE_OK;
 }

@@ -526,6 +526,7 @@ extern "C" int nnue_ft_fused_fwd(const float* us, const float* them, const int32
                                                           weight, bias, max_act, l0, wpsqt, bpsqt,
                                                           saved, B, K, N, L1, P, status);
         NNUE_CUDA_TRY(cudaGetLastError());
+        note_launches(1);
         return NNUE_OK;
     }
 
@@ -550,6 +551,7 @@ extern "C" int nnue_ft_fused_fwd(const float* us, const float* them, const int32
     else LAUNCH_FWD(4);
 #undef LAUNCH_FWD
     NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
     return NNUE_OK;
 }
 
@@ -634,6 +636,7 @@ extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32
                                                            saved, grad_weight, grad_bias, B, K, N, L1,
                                                            P, (int)groups, ppc, status);
         NNUE_CUDA_TRY(cudaGetLastError());
+        note_launches(1);
         return NNUE_OK;
     }
 
@@ -665,6 +668,7 @@ extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32
         part_src = G;
     }
     NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
     int rc = column_sum(part_src, part_rows, (int)W, grad_bias, s);
     if (rc != NNUE_OK) return rc;
     // CSR over both perspectives: entry id = 2*p + perspective = row of G

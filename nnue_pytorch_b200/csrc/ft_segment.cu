@@ -394,8 +394,10 @@ int column_sum(const float* src, int64_t rows, int W, float* out, cudaStream_t s
     if (two_stage) {
         launch(src, rows, scratch, kColumnSumSlices);
         launch(scratch, kColumnSumSlices, out, 1);
+        note_launches(2);
     } else {
         launch(src, rows, out, 1);
+        note_launches(1);
     }
     NNUE_CUDA_TRY(cudaGetLastError());
     return NNUE_OK;
@@ -435,8 +437,10 @@ int csr_build_and_reduce(const int32_t* const* lists, int n_lists, int64_t B, in
     if (warps > 0 && K > 0) {
         k_csr_scan_lists<false><<<lgrid, kThreads, 0, s>>>(l0, l1, n_lists, B, K, N, counts, entries,
                                                           status);
+        note_launches(2);  // this pass and the fill pass below
     }
     k_csr_scan<<<1, 1024, 0, s>>>(counts, offsets, cursor, N, long_list, n_long, kWarpSortMax);
+    note_launches(2);  // the scan and the segment gather-sum at the end
     if (warps > 0 && K > 0) {
         k_csr_scan_lists<true><<<lgrid, kThreads, 0, s>>>(l0, l1, n_lists, B, K, N, cursor, entries,
                                                          status);
@@ -444,6 +448,7 @@ int csr_build_and_reduce(const int32_t* const* lists, int n_lists, int64_t B, in
     const int64_t row_groups = (N + kWarpsPerCta - 1) / kWarpsPerCta;
     if (tuning().sort_segments && warps > 0 && K > 0) {
         k_csr_sort_short<<<(unsigned)row_groups, kThreads, 0, s>>>(offsets, entries, N);
+        note_launches(1);
         const int64_t key_space = B * n_lists;
         if (key_space <= kBitmapMaxBits) {
             const int words = (int)((key_space + 31) / 32);
@@ -457,6 +462,7 @@ int csr_build_and_reduce(const int32_t* const* lists, int n_lists, int64_t B, in
             const unsigned g = (unsigned)std::min<int64_t>(N, (int64_t)sm_count() * 4);
             k_csr_sort_long<<<g, kThreads, smem, s>>>(offsets, entries, long_list, n_long, words,
                                                      status);
+            note_launches(1);
         }
     }
     NNUE_CUDA_TRY(cudaGetLastError());

@@ -122,6 +122,7 @@ extern "C" int nnue_ft_sparse_fwd(const int32_t* idx, const float* weight, const
         k_sparse_fwd_scalar<<<(unsigned)(groups * tiles), kThreads, 0, s>>>(
             idx, weight, bias, out, B, K, N, W, (int)groups, status);
         NNUE_CUDA_TRY(cudaGetLastError());
+        note_launches(1);
         return NNUE_OK;
     }
     const int64_t W4 = W / 4;
@@ -138,6 +139,7 @@ extern "C" int nnue_ft_sparse_fwd(const int32_t* idx, const float* weight, const
     else if (U == 2) k_sparse_fwd<2><<<grid, kThreads, 0, s>>>(idx, w4, b4, o4, B, K, N, W4, (int)groups, status);
     else k_sparse_fwd<4><<<grid, kThreads, 0, s>>>(idx, w4, b4, o4, B, K, N, W4, (int)groups, status);
     NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
     return NNUE_OK;
 }
 
@@ -193,6 +195,7 @@ extern "C" int nnue_ft_sparse_bwd(const int32_t* idx, const float* grad_out, flo
         else if (U == 2) k_sparse_bwd_atomic<2><<<grid, kThreads, 0, s>>>(idx, g4, grad_weight, B, K, N, W4, (int)groups, status);
         else k_sparse_bwd_atomic<4><<<grid, kThreads, 0, s>>>(idx, g4, grad_weight, B, K, N, W4, (int)groups, status);
         NNUE_CUDA_TRY(cudaGetLastError());
+        note_launches(1);
         return NNUE_OK;
     }
     const int32_t* lists[1] = {idx};

@@ -232,5 +232,6 @@ extern "C" int nnue_quant_eval(const int32_t* white_idx, const int32_t* black_id
         white_idx, black_idx, stm_white, bucket, ft_w, ft_psqt, ft_b, l1_w, l1_b, l2_w, l2_b, out_w,
         out_b, out, B, d, *qp, status);
     NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
     return NNUE_OK;
 }

@@ -193,6 +193,7 @@ extern "C" int nnue_rangerlite_update(float* p, const float* grad, float* grad_m
                                                           slow, d_grad_scale, n, c);
     }
     NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
     return NNUE_OK;
 }
 
@@ -207,5 +208,6 @@ extern "C" int nnue_lookahead_merge(float* p, float* slow, int64_t n, float alph
     if (al) k_lookahead<true><<<grid, kThreads, 0, s>>>(p, slow, n, alpha, 1.0f - alpha);
     else k_lookahead<false><<<grid, kThreads, 0, s>>>(p, slow, n, alpha, 1.0f - alpha);
     NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
     return NNUE_OK;
 }

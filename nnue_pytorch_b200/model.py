@@ -1,0 +1,230 @@
+"""Host-side network around the feature transformer, for running whole
+training steps without the reference checkout.
+
+The feature transformer is this package's `ComposedFeatureTransformer` (CUDA
+kernels); everything after it is ordinary torch (cuBLAS GEMMs and elementwise
+ops), restating the graph of the reference project:
+  model/model.py:9-133                      `NNUEModel`
+  model/modules/layer_stacks.py:12-84       `LayerStacks`
+  model/modules/stacked_linear.py:9-127     bucketed linear layers
+  model/nnue.py:22-70,117-182               loss and the ten optimizer groups
+Parameter names match the reference so state dicts are interchangeable.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+
+import torch
+import torch.nn.functional as F
+from torch import nn
+
+from .composed_feature_transformer import ComposedFeatureTransformer
+from .features import get_feature_cls
+from .quantize import QuantizationConfig, QuantizationManager
+from .ranger_lite import RangerLite
+
+
+class StackedLinear(nn.Module):
+    """`count` independent linear layers stored as one wide layer; a position
+    uses the slice of its bucket."""
+
+    def __init__(self, in_features: int, out_features: int, count: int, quantization=None, layer_key=None):
+        super().__init__()
+        self.in_features, self.out_features, self.count = in_features, out_features, count
+        self.linear = nn.Linear(in_features, out_features * count)
+        self.quantization, self.layer_key = quantization, layer_key
+        with torch.no_grad():  # every bucket starts from the same weights
+            self.linear.weight.copy_(self.linear.weight[:out_features].repeat(count, 1))
+            self.linear.bias.copy_(self.linear.bias[:out_features].repeat(count))
+
+    def _weights(self):
+        return self.linear.weight, self.linear.bias
+
+    def forward(self, x, ls_indices, fake_quantize_weights: bool = False):
+        w, b = self._weights()
+        if fake_quantize_weights:
+            w = self.quantization.fake_quantize_weights(w, f"{self.layer_key}_weight")
+            b = self.quantization.fake_quantize_weights(b, f"{self.layer_key}_bias")
+        wide = F.linear(x, w, b).reshape(-1, self.out_features)
+        base = torch.arange(0, ls_indices.shape[0] * self.count, self.count, device=wide.device)
+        return wide[ls_indices.flatten() + base]
+
+
+class FactorizedStackedLinear(StackedLinear):
+    """Adds one layer shared by all buckets (folded in weight space)."""
+
+    def __init__(self, in_features, out_features, count, quantization, layer_key):
+        super().__init__(in_features, out_features, count, quantization, layer_key)
+        self.factorized_linear = nn.Linear(in_features, out_features)
+        self.zero_virtual_weights()
+
+    def _weights(self):
+        return (
+            self.linear.weight + self.factorized_linear.weight.repeat(self.count, 1),
+            self.linear.bias + self.factorized_linear.bias.repeat(self.count),
+        )
+
+    @torch.no_grad()
+    def zero_virtual_weights(self):
+        self.factorized_linear.weight.zero_()
+        self.factorized_linear.bias.zero_()
+
+
+class LayerStacks(nn.Module):
+    def __init__(self, count: int, L1: int, L2: int, L3: int, quantization: QuantizationManager):
+        super().__init__()
+        self.count, self.L1, self.L2, self.L3 = count, L1, L2, L3
+        self.quantization = quantization
+        self.l1 = FactorizedStackedLinear(L1, L2, count, quantization, "ls_l1")
+        self.l2 = StackedLinear(L2 * 2, L3, count, quantization, "ls_l2")
+        self.output = StackedLinear(L2 * 2 + L3 * 2, 1, count, quantization, "ls_output")
+        with torch.no_grad():
+            self.output.linear.bias.zero_()
+
+    def _activate(self, x, fake_quantize_acts):
+        q = self.quantization
+        sq = torch.pow(x, 2.0)
+        if fake_quantize_acts:
+            sq = q.fake_quantize_ls_act(sq)
+        sq = sq * q.sqr_crelu_correction_factor
+        if fake_quantize_acts:
+            x = q.fake_quantize_ls_act(x)
+        return q.clip_ls_act(torch.cat([sq, x], dim=1))
+
+    def forward(self, x, ls_indices, fake_quantize_acts=True, fake_quantize_weights=True):
+        o1 = self.l1(x, ls_indices, fake_quantize_weights)
+        skip = o1[:, -2].view(-1, 1) - o1[:, -1].view(-1, 1)
+        x1 = self._activate(o1, fake_quantize_acts)
+        x2 = self._activate(self.l2(x1, ls_indices, fake_quantize_weights), fake_quantize_acts)
+        y = self.output(torch.cat([x1, x2], dim=1), ls_indices, fake_quantize_weights)
+        if fake_quantize_acts:
+            skip = self.quantization.fake_quantize_skip_act(skip)
+        y = y + skip
+        if fake_quantize_acts:
+            y = self.quantization.fake_quantize_output(y)
+        return y
+
+
+@dataclass
+class ModelConfig:
+    L1: int = 1024
+    L2: int = 32
+    L3: int = 32
+    quantize_config: QuantizationConfig = field(default_factory=QuantizationConfig)
+
+
+class NNUEModel(nn.Module):
+    def __init__(self, feature_name: str, config: ModelConfig, num_psqt_buckets: int = 8, num_ls_buckets: int = 8):
+        super().__init__()
+        self.L1, self.L2, self.L3 = config.L1, config.L2, config.L3
+        self.quantization = QuantizationManager(config.quantize_config)
+        self.num_psqt_buckets, self.num_ls_buckets = num_psqt_buckets, num_ls_buckets
+        self.input = ComposedFeatureTransformer(get_feature_cls(feature_name), self.L1, num_psqt_buckets, self.quantization)
+        self.layer_stacks = LayerStacks(num_ls_buckets, self.L1, self.L2, self.L3, self.quantization)
+        self.input.init_weights()
+
+    def forward(self, us, them, white_indices, black_indices, piece_count, fake_quantize_acts=True, fake_quantize_weights=True):
+        bucket = (piece_count - 1) // 4
+        l0, wpsqt, bpsqt = self.input(us, them, white_indices, black_indices, bucket, fake_quantize_acts, fake_quantize_weights)
+        y = self.layer_stacks(l0, bucket, fake_quantize_acts, fake_quantize_weights)
+        # PSQT: averaged over the perspectives, sign by side to move
+        return y + (wpsqt - bpsqt) * (us - 0.5)
+
+
+@dataclass
+class LossParams:
+    in_offset: float = 270.0
+    out_offset: float = 270.0
+    in_scaling: float = 340.0
+    out_scaling: float = 380.0
+    pow_exp: float = 2.5
+    qp_asymmetry: float = 0.0
+    w1: float = 0.0
+    w2: float = 0.5
+    tb_remap_base: float = 4000.0
+    tb_remap_scale: float = 4000.0
+    tb_remap_decay: float = 0.85
+
+
+def sf_loss(scorenet, score, outcome, lp: LossParams, lam: float):
+    """Win-rate-space power loss between the net and the (tablebase-remapped)
+    search score blended with the game outcome."""
+    a = score.abs()
+    remap = lp.tb_remap_base + (lp.tb_remap_decay ** (32000 - a).clamp(min=0)) * lp.tb_remap_scale
+    score = torch.where(a >= 32000 - 245, torch.where(score < 0, -remap, remap), score)
+    q = (scorenet - lp.in_offset) / lp.in_scaling
+    qm = (-scorenet - lp.in_offset) / lp.in_scaling
+    qf = 0.5 * (1.0 + q.sigmoid() - qm.sigmoid())
+    s = (score - lp.out_offset) / lp.out_scaling
+    sm = (-score - lp.out_offset) / lp.out_scaling
+    pf = 0.5 * (1.0 + s.sigmoid() - sm.sigmoid())
+    pt = pf * lam + outcome * (1.0 - lam)
+    loss = torch.pow(torch.abs(pt - qf), lp.pow_exp)
+    if lp.qp_asymmetry != 0.0:
+        loss = loss * ((qf > pt) * lp.qp_asymmetry + 1)
+    weights = 1 + (2.0**lp.w1 - 1) * torch.pow((pf - 0.5) ** 2 * pf * (1 - pf), lp.w2)
+    return (loss * weights).sum() / weights.sum()
+
+
+def optimizer_groups(model: NNUEModel, lr: float, ft_wd=0.0, dense_wd=0.0, factorized_wd=0.0) -> list[dict]:
+    """The ten parameter groups of the reference trainer, in its order."""
+    ft_w = [p for n, p in model.input.named_parameters() if "bias" not in n]
+    ft_b = [p for n, p in model.input.named_parameters() if "bias" in n]
+    ls = model.layer_stacks
+    spec = [
+        (ft_w, ft_wd), (ft_b, 0.0),
+        ([ls.l1.factorized_linear.weight], factorized_wd), ([ls.l1.factorized_linear.bias], 0.0),
+        ([ls.l1.linear.weight], dense_wd), ([ls.l1.linear.bias], 0.0),
+        ([ls.l2.linear.weight], dense_wd), ([ls.l2.linear.bias], 0.0),
+        ([ls.output.linear.weight], dense_wd), ([ls.output.linear.bias], 0.0),
+    ]
+    return [{"params": ps, "lr": lr, "weight_decay": wd} for ps, wd in spec]
+
+
+class TrainStep:
+    """One optimizer step as the reference trainer performs it
+    (trainer/engine.py:295-322): forward, loss, backward, clip the global
+    gradient norm to `clip`, RangerLite update.  The clip is folded into the
+    update kernels: one sum-of-squares pass per gradient, a device scalar, and
+    the update multiplies by it.  `grad_hook(model)` (optional) runs between
+    backward and the norm, which is where data-parallel ranks exchange
+    gradients."""
+
+    def __init__(self, model: NNUEModel, lr: float = 8.75e-4, clip: float = 2.0, lam: float = 1.0,
+                 loss_params: LossParams | None = None, grad_hook=None):
+        self.model = model
+        self.clip, self.lam = clip, lam
+        self.loss_params = loss_params or LossParams()
+        self.grad_hook = grad_hook
+        self.optimizer = RangerLite(
+            optimizer_groups(model, lr), lr=1.0, weight_decay=0.0, use_legacy_scoping_bug=False,
+            normloss_active=False, pnm_activate=True, pnm_momentum=1.0, lookahead_blending_alpha=0.5,
+            lookahead_mergetime=5,
+        )
+        dev = next(model.parameters()).device
+        self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
+        self._coef = torch.ones(1, dtype=torch.float32, device=dev)
+        self.optimizer.grad_scale = self._coef if clip and clip > 0 else None
+
+    def loss(self, batch):
+        us, them, white, black, outcome, score, piece_count = batch
+        y = self.model(us, them, white, black, piece_count, True, True)
+        return sf_loss(y * self.model.quantization.nnue2score, score, outcome, self.loss_params, self.lam)
+
+    def __call__(self, batch):
+        from . import _launch
+
+        loss = self.loss(batch)
+        self.optimizer.zero_grad(set_to_none=True)
+        loss.backward()
+        if self.grad_hook is not None:
+            self.grad_hook(self.model)
+        if self.optimizer.grad_scale is not None:
+            self._sumsq.zero_()
+            for p in self.model.parameters():
+                if p.grad is not None:
+                    _launch.grad_sumsq(p.grad, self._sumsq)
+            _launch.clip_coef(self._sumsq, self.clip, self._coef)
+        self.optimizer.step()
+        return loss.detach()

@@ -1,0 +1,98 @@
+"""CPU-side checks of the C-ABI library: it loads, exports every function
+include/nnue_b200.h declares, and validates arguments on the host before any
+CUDA call.  No kernel runs here."""
+
+import ctypes as C
+import os
+import re
+
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from nnue_pytorch_b200 import _build, _lib
+
+    _build.build()
+    return _lib.load()
+
+
+def _declared_functions():
+    text = open(os.path.join(ROOT, "include", "nnue_b200.h")).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(nnue_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_function_is_exported_and_bound(lib):
+    from nnue_pytorch_b200 import _lib
+
+    names = _declared_functions()
+    assert len(names) >= 14
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in include/nnue_b200.h but not exported"
+    assert sorted(_lib.PROTOTYPES) == names
+
+
+def test_abi_version(lib):
+    assert lib.nnue_b200_abi_version() == 1
+
+
+def test_host_side_argument_validation(lib):
+    # negative sizes and bad enums are rejected before any CUDA call
+    assert lib.nnue_ft_sparse_fwd(None, None, None, None, -1, 4, 4, 4, None) == -1
+    assert b"negative size" in lib.nnue_b200_last_error()
+    assert lib.nnue_ft_fused_fwd(None, None, None, None, None, None, None, 1.0, None, None, None, None,
+                                 4, 4, 4, 7, 8, None) == -1  # odd l1
+    assert b"even" in lib.nnue_b200_last_error()
+    assert lib.nnue_ft_fused_bwd(None, None, None, None, None, 1.0, None, None, None, None, None, None,
+                                 4, 4, 4, 8, 8, None, 0, 9, None) == -1  # unknown mode
+    assert lib.nnue_b200_tune(b"no_such_knob", 1) == -1
+    assert lib.nnue_rangerlite_update(None, None, None, None, None, None, None, None, 1, 1, None, None) == -1
+    # empty batches are a no-op that needs no device
+    assert lib.nnue_ft_sparse_fwd(None, None, None, None, 0, 4, 4, 4, None) == 0
+    assert lib.nnue_ft_fused_fwd(None, None, None, None, None, None, None, 1.0, None, None, None, None,
+                                 0, 4, 4, 8, 8, None) == 0
+
+
+def test_workspace_sizes_are_monotone(lib):
+    f = lib.nnue_ft_fused_bwd_workspace_bytes
+    a = f(1024, 64, 23232, 1024, 8, 2)
+    b = f(16384, 64, 23232, 3072, 8, 2)
+    assert 0 < a < b
+    # G [2B, W] dominates: 2*16384*3080*4 bytes
+    assert b >= 2 * 16384 * 3080 * 4
+    assert f(16384, 64, 23232, 3072, 8, 1) == 256
+    assert f(-1, 64, 23232, 3072, 8, 2) == 0
+
+
+def test_product_refuses_cpu_tensors():
+    import torch
+
+    from nnue_pytorch_b200 import SparseLinearFunction, double_feature_transform
+
+    idx = torch.zeros(2, 4, dtype=torch.int32)
+    w = torch.zeros(8, 16)
+    b = torch.zeros(16)
+    with pytest.raises(RuntimeError):
+        SparseLinearFunction.apply(idx, w, b)
+    with pytest.raises(RuntimeError):
+        SparseLinearFunction.apply(idx, w, b, "torch")
+    with pytest.raises(ValueError):
+        SparseLinearFunction.apply(idx, w, b, "nonsense")
+    us = torch.zeros(2, 1)
+    with pytest.raises(RuntimeError):
+        double_feature_transform(us, us, idx, idx, torch.zeros(2, dtype=torch.int64), w, b, 1.0, 8)
+    with pytest.raises(ValueError):
+        double_feature_transform(us, us, idx, idx, torch.zeros(2, dtype=torch.int64), w, b, 1.0, 8, "nonsense")
+
+
+def test_product_never_imports_the_oracle():
+    pkg = os.path.join(ROOT, "nnue_pytorch_b200")
+    for dirpath, _, files in os.walk(pkg):
+        for f in files:
+            if f.endswith((".py", ".cu", ".cuh")):
+                src = open(os.path.join(dirpath, f)).read()
+                assert not re.search(r"^\s*(from|import)\s+oracle\b", src, flags=re.M), f
+                assert "_work/" not in src, f

@@ -1,0 +1,342 @@
+"""GPU parity of the feature-transformer kernels against the CPU oracle and the
+golden fixtures.  Everything goes through the C ABI (ctypes) by way of the
+reference-shaped Python operators."""
+
+import numpy as np
+import pytest
+import torch
+
+from _util import load_golden, max_rel_err, t
+
+pytestmark = pytest.mark.gpu
+
+TOL = 1e-5  # relative to the tensor's max-norm, fp32 (the stated parity bar)
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from nnue_pytorch_b200 import _lib
+
+    _lib.load()  # fail loudly if the library is missing
+    return torch.device("cuda:0")
+
+
+def _check(ours: torch.Tensor, ref32: torch.Tensor, ref64: torch.Tensor | None, what: str):
+    ours = ours.detach().cpu()
+    assert ours.shape == ref32.shape, what
+    err = max_rel_err(ours, ref32)
+    assert err <= TOL, f"{what}: max-norm relative error {err:.3e} > {TOL}"
+    scale = max(float(ref32.abs().max()), 1e-30)
+    assert torch.allclose(ours, ref32, rtol=1e-5, atol=1e-5 * scale), what
+    if ref64 is not None:
+        # kernel error vs float64 truth is no worse than the fp32 oracle's own
+        e_ours = float((ours.double() - ref64).abs().max())
+        e_ref = float((ref32.double() - ref64).abs().max())
+        assert e_ours <= 2 * e_ref + 1e-7 * scale, f"{what}: {e_ours:.3e} vs oracle's own {e_ref:.3e}"
+
+
+def _run_sparse(dev, idx, w, b, go, mode):
+    from nnue_pytorch_b200 import SparseLinearFunction, _launch
+
+    _launch.set_backward_mode(mode)
+    try:
+        wd = w.to(dev).requires_grad_(True)
+        bd = b.to(dev).requires_grad_(True)
+        out = SparseLinearFunction.apply(idx.to(dev), wd, bd)
+        (out * go.to(dev)).sum().backward()
+        _launch.device_status(dev)
+        return out.detach(), wd.grad, bd.grad
+    finally:
+        _launch.set_backward_mode("auto")
+
+
+@pytest.mark.parametrize("mode", ["segment", "atomic"])
+def test_sparse_linear_golden(dev, mode):
+    g = load_golden("sparse_linear")
+    out, gw, gb = _run_sparse(dev, t(g["indices"]), t(g["weight"]), t(g["bias"]), t(g["grad_out"]), mode)
+    _check(out, t(g["out"]), None, "out")
+    _check(gw, t(g["grad_weight"]), None, "grad_weight")
+    _check(gb, t(g["grad_bias"]), None, "grad_bias")
+
+
+def test_sparse_linear_reference_test_shapes(dev):
+    """The two cases of the reference's tests/test_feature_transformer.py: dense
+    emulation with duplicate indices (tolerance 1e-4 there) and trailing padding."""
+    from nnue_pytorch_b200 import SparseLinearFunction
+
+    torch.manual_seed(0)
+    w = torch.rand(10, 128)
+    b = torch.rand(128)
+    idx = (torch.rand(16, 32) * 10).to(torch.int32)
+    counts = torch.zeros(16, 10)
+    for i in range(16):
+        for j in range(32):
+            counts[i, idx[i, j]] += 1
+    dense = torch.mm(counts, w) + b
+    out = SparseLinearFunction.apply(idx.to(dev), w.to(dev), b.to(dev))
+    assert float((out.cpu() - dense).abs().max()) < 1e-4
+    torch.manual_seed(42)
+    w = torch.rand(10, 64, device=dev)
+    b = torch.rand(64, device=dev)
+    act = (torch.rand(8, 5) * 10).to(torch.int32).to(dev)
+    pad = torch.full((8, 3), -1, dtype=torch.int32, device=dev)
+    a = SparseLinearFunction.apply(act, w, b)
+    c = SparseLinearFunction.apply(torch.cat([act, pad], dim=1), w, b)
+    assert torch.equal(a, c)
+
+
+@pytest.mark.parametrize("B,N,K,W", [(1, 7, 1, 4), (37, 50, 9, 132), (300, 1000, 64, 1032), (64, 33, 40, 130), (5, 9, 3, 7)])
+def test_sparse_linear_random_shapes(dev, B, N, K, W):
+    from oracle import ft_oracle
+
+    gen = torch.Generator().manual_seed(B * 1000 + W)
+    idx = torch.randint(0, N, (B, K), generator=gen, dtype=torch.int32)
+    n_act = torch.randint(0, K + 1, (B,), generator=gen)
+    idx[torch.arange(K)[None, :] >= n_act[:, None]] = -1
+    w = torch.randn(N, W, generator=gen) * 0.1
+    b = torch.randn(W, generator=gen) * 0.1
+    go = torch.randn(B, W, generator=gen)
+    r32 = ft_oracle.sparse_linear_with_grads(idx, w, b, go)
+    r64 = ft_oracle.sparse_linear_with_grads(idx, w.double(), b.double(), go.double())
+    for mode in ("segment", "atomic"):
+        out, gw, gb = _run_sparse(dev, idx, w, b, go, mode)
+        _check(out, r32["out"], r64["out"], f"out[{mode}]")
+        _check(gw, r32["grad_weight"], r64["grad_weight"], f"grad_weight[{mode}]")
+        _check(gb, r32["grad_bias"], r64["grad_bias"], f"grad_bias[{mode}]")
+
+
+def _run_fused(dev, c, mode, backend="fused"):
+    from nnue_pytorch_b200 import _launch, double_feature_transform
+
+    _launch.set_backward_mode(mode)
+    try:
+        wd = c["weight"].to(dev).requires_grad_(True)
+        bd = c["bias"].to(dev).requires_grad_(True)
+        l0, wp, bp = double_feature_transform(
+            c["us"].to(dev), c["them"].to(dev), c["white"].to(dev), c["black"].to(dev), c["psqt"].to(dev),
+            wd, bd, c["max_act"], c["l1"], backend)
+        loss = (l0 * c["grad_l0"].to(dev)).sum() + (wp * c["grad_wpsqt"].to(dev)).sum() + (bp * c["grad_bpsqt"].to(dev)).sum()
+        loss.backward()
+        _launch.device_status(dev)
+        return {"l0": l0.detach(), "wpsqt": wp.detach(), "bpsqt": bp.detach(), "grad_weight": wd.grad, "grad_bias": bd.grad}
+    finally:
+        _launch.set_backward_mode("auto")
+
+
+def _golden_case(name):
+    g = load_golden(name)
+    c = {k: t(g[k]) for k in ("us", "them", "white", "black", "psqt", "weight", "bias", "grad_l0", "grad_wpsqt", "grad_bpsqt")}
+    c["max_act"], c["l1"] = float(g["max_act"]), int(g["l1"])
+    ref = {k: t(g[k]) for k in ("l0", "wpsqt", "bpsqt", "grad_weight", "grad_bias")}
+    return c, ref
+
+
+@pytest.mark.parametrize("name", ["fused_ft_randn", "fused_ft_stm"])
+@pytest.mark.parametrize("mode", ["segment", "atomic"])
+def test_fused_golden(dev, name, mode):
+    c, ref = _golden_case(name)
+    r = _run_fused(dev, c, mode)
+    for k, v in ref.items():
+        _check(r[k], v, None, f"{name}.{k}[{mode}]")
+
+
+def _random_case(B, N, K, l1, P, seed, stm01=True, max_act=255.0 / 256.0, wscale=0.05, dup=True):
+    gen = torch.Generator().manual_seed(seed)
+    c = {}
+    if stm01:
+        c["us"] = torch.randint(0, 2, (B, 1), generator=gen).float()
+        c["them"] = 1.0 - c["us"]
+    else:
+        c["us"] = torch.randn(B, 1, generator=gen)
+        c["them"] = torch.randn(B, 1, generator=gen)
+    for key in ("white", "black"):
+        idx = torch.randint(0, N, (B, K), generator=gen, dtype=torch.int32)
+        if not dup:
+            idx = torch.stack([torch.randperm(N, generator=gen)[:K] for _ in range(B)]).to(torch.int32)
+        n_act = torch.randint(0, K + 1, (B,), generator=gen)
+        idx[torch.arange(K)[None, :] >= n_act[:, None]] = -1
+        c[key] = idx
+    c["psqt"] = torch.randint(0, max(P, 1), (B,), generator=gen, dtype=torch.int64)
+    c["weight"] = torch.randn(N, l1 + P, generator=gen) * wscale
+    c["bias"] = torch.randn(l1 + P, generator=gen) * wscale
+    c["grad_l0"] = torch.randn(B, l1, generator=gen)
+    c["grad_wpsqt"] = torch.randn(B, 1, generator=gen)
+    c["grad_bpsqt"] = torch.randn(B, 1, generator=gen)
+    c["max_act"], c["l1"] = max_act, l1
+    return c
+
+
+def _oracle(c, dtype):
+    from oracle import ft_oracle
+
+    f = lambda x: x.to(dtype)  # noqa: E731
+    return ft_oracle.double_feature_transform_with_grads(
+        f(c["us"]), f(c["them"]), c["white"], c["black"], c["psqt"], f(c["weight"]), f(c["bias"]),
+        c["max_act"], c["l1"], f(c["grad_l0"]), f(c["grad_wpsqt"]), f(c["grad_bpsqt"]))
+
+
+CASES = [
+    # B, N, K, l1, P, stm01, max_act, wscale
+    (4, 100, 32, 32, 8, False, 127.0, 1.0),       # reference test shape, l1 = 32
+    (4, 100, 32, 2048, 8, False, 127.0, 1.0),     # reference test shape, l1 = 2048
+    (13, 64, 5, 8, 4, True, 255.0 / 256.0, 0.3),  # one float4 per half, ragged batch
+    (67, 500, 64, 512, 8, True, 255.0 / 256.0, 0.08),
+    (40, 300, 33, 1024, 8, True, 255.0 / 256.0, 0.06),   # K not a multiple of 32
+    (24, 200, 70, 3072, 8, True, 255.0 / 256.0, 0.04),   # K > 64, headline width
+    (9, 50, 12, 6, 3, True, 255.0 / 256.0, 0.4),         # scalar kernels: l1 % 8 != 0, P % 4 != 0
+]
+
+
+@pytest.mark.parametrize("case", CASES, ids=[f"B{c[0]}-N{c[1]}-K{c[2]}-L{c[3]}-P{c[4]}" for c in CASES])
+def test_fused_random_shapes(dev, case):
+    B, N, K, l1, P, stm01, max_act, wscale = case
+    c = _random_case(B, N, K, l1, P, seed=l1 * 7 + B, stm01=stm01, max_act=max_act, wscale=wscale)
+    r32, r64 = _oracle(c, torch.float32), _oracle(c, torch.float64)
+    for mode in ("segment", "atomic"):
+        r = _run_fused(dev, c, mode)
+        for k in ("l0", "wpsqt", "bpsqt", "grad_weight", "grad_bias"):
+            _check(r[k], r32[k], r64[k], f"{k}[{mode}]")
+
+
+def test_fused_equals_sparse_composition(dev):
+    """`backend="sparse"` (two sparse-linear kernels + torch glue) and the fused
+    kernels agree, as the reference's tests/test_fused_double_ft.py checks."""
+    c = _random_case(32, 400, 32, 256, 8, seed=5, stm01=False, max_act=127.0, wscale=0.5)
+    a = _run_fused(dev, c, "segment", "fused")
+    b = _run_fused(dev, c, "segment", "sparse")
+    torch.testing.assert_close(a["l0"], b["l0"], atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(a["wpsqt"], b["wpsqt"], atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(a["grad_weight"], b["grad_weight"], atol=1e-4, rtol=1e-3)
+    torch.testing.assert_close(a["grad_bias"], b["grad_bias"], atol=1e-4, rtol=1e-3)
+
+
+def test_forward_is_bitwise_the_sequential_sum(dev):
+    """bias first, then rows in list order: the accumulation order of the
+    reference's CUDA kernels, reproduced bit for bit (0/1 side to move)."""
+    c = _random_case(16, 300, 40, 64, 8, seed=77, dup=True)
+    r = _run_fused(dev, c, "segment")
+    W = c["weight"].numpy()
+    bias = c["bias"].numpy()
+    l1, h = 64, 32
+    for p in range(16):
+        acc = []
+        for lst in (c["white"][p], c["black"][p]):
+            a = bias.copy()
+            for r_ in lst.tolist():
+                if r_ < 0:
+                    break
+                a = (a + W[r_]).astype(np.float32)
+            acc.append(a)
+        first, second = (acc[0], acc[1]) if c["us"][p, 0] == 1 else (acc[1], acc[0])
+        x = np.concatenate([first[:l1], second[:l1]])
+        cl = np.clip(x, 0.0, np.float32(c["max_act"]))
+        want = np.concatenate([cl[:h] * cl[h:l1], cl[l1:l1 + h] * cl[l1 + h:]]).astype(np.float32)
+        assert np.array_equal(r["l0"][p].cpu().numpy(), want)
+        pi = int(c["psqt"][p])
+        assert float(r["wpsqt"][p, 0]) == float(acc[0][l1 + pi])
+        assert float(r["bpsqt"][p, 0]) == float(acc[1][l1 + pi])
+
+
+def test_config0_baseline_layout_parity(dev):
+    """BASELINE configs[0]: HalfKAv2_hm^ as 22528 real + 704 factor rows,
+    L1 = 1024, batch 1024, weights ~ N(0, 0.01), fp32."""
+    from nnue_pytorch_b200 import positions
+
+    b = positions.generate_batch(1024, 0, layout="baseline")
+    gen = torch.Generator().manual_seed(1)
+    L1, P = 1024, 8
+    c = {
+        "us": t(b.us), "them": t(b.them), "white": t(b.white), "black": t(b.black),
+        "psqt": t((b.piece_count - 1) // 4),
+        "weight": torch.randn(positions.NUM_INPUTS_BASELINE, L1 + P, generator=gen) * 0.01,
+        "bias": torch.randn(L1 + P, generator=gen) * 0.01,
+        "grad_l0": torch.randn(1024, L1, generator=gen), "grad_wpsqt": torch.randn(1024, 1, generator=gen),
+        "grad_bpsqt": torch.randn(1024, 1, generator=gen), "max_act": 255.0 / 256.0, "l1": L1,
+    }
+    r32, r64 = _oracle(c, torch.float32), _oracle(c, torch.float64)
+    for mode in ("segment", "atomic"):
+        r = _run_fused(dev, c, mode)
+        for k in ("l0", "wpsqt", "bpsqt", "grad_weight", "grad_bias"):
+            _check(r[k], r32[k], r64[k], f"config0.{k}[{mode}]")
+
+
+def test_segment_backward_is_reproducible(dev):
+    """Two runs of the segment-reduce backward give identical bits, including
+    rows that collect thousands of hits (factor rows)."""
+    from nnue_pytorch_b200 import positions
+
+    b = positions.generate_batch(4096, 3, layout="baseline")
+    gen = torch.Generator().manual_seed(2)
+    L1, P = 256, 8
+    c = {
+        "us": t(b.us), "them": t(b.them), "white": t(b.white), "black": t(b.black),
+        "psqt": t((b.piece_count - 1) // 4),
+        "weight": torch.randn(positions.NUM_INPUTS_BASELINE, L1 + P, generator=gen) * 0.02,
+        "bias": torch.randn(L1 + P, generator=gen) * 0.02,
+        "grad_l0": torch.randn(4096, L1, generator=gen), "grad_wpsqt": torch.randn(4096, 1, generator=gen),
+        "grad_bpsqt": torch.randn(4096, 1, generator=gen), "max_act": 255.0 / 256.0, "l1": L1,
+    }
+    a = _run_fused(dev, c, "segment")
+    for _ in range(2):
+        b2 = _run_fused(dev, c, "segment")
+        assert torch.equal(a["grad_weight"], b2["grad_weight"])
+        assert torch.equal(a["grad_bias"], b2["grad_bias"])
+    r32 = _oracle(c, torch.float32)
+    _check(a["grad_weight"], r32["grad_weight"], None, "grad_weight")
+
+
+def test_linearity_at_full_size(dev):
+    """Size-independent property at the headline shape (L1 = 3072, batch
+    16384, 23232 rows): the backward is linear in the incoming gradient, and
+    the bias gradient equals the column sum identity sum_rows(gW[:, :L1]) ==
+    sum over hits, checked through a scalar checksum."""
+    from nnue_pytorch_b200 import _launch, double_feature_transform, positions
+
+    B, L1, P = 16384, 3072, 8
+    b = positions.generate_batch(B, 0, layout="baseline")
+    gen = torch.Generator(device=dev).manual_seed(1)
+    w = (torch.randn(positions.NUM_INPUTS_BASELINE, L1 + P, generator=gen, device=dev) * 0.01).requires_grad_(True)
+    bias = (torch.randn(L1 + P, generator=gen, device=dev) * 0.01).requires_grad_(True)
+    us, them, wi, bi = (t(x).to(dev) for x in (b.us, b.them, b.white, b.black))
+    ps = t((b.piece_count - 1) // 4).to(dev)
+    l0, wp, bp = double_feature_transform(us, them, wi, bi, ps, w, bias, 255.0 / 256.0, L1)
+    g1 = torch.randn(B, L1, generator=gen, device=dev)
+    g2 = torch.randn(B, L1, generator=gen, device=dev)
+    z = torch.zeros(B, 1, device=dev)
+
+    def grads(g):
+        gw, gb = torch.autograd.grad([l0, wp, bp], [w, bias], [g, z, z], retain_graph=True)
+        return gw, gb
+
+    a, ab = grads(g1)
+    b_, bb = grads(g2)
+    s, sb = grads(g1 + g2)
+    _launch.device_status(dev)
+    scale = float(s.abs().max())
+    assert float((a + b_ - s).abs().max()) <= 1e-5 * scale
+    assert float((ab + bb - sb).abs().max()) <= 1e-5 * float(sb.abs().max())
+    # every position contributes its gradient row once per active index: with n_w + n_b
+    # active rows, sum over all table rows of gW[:, :L1] == sum_p (n_w(p) g_w(p) + n_b(p) g_b(p)).
+    # Check the cheaper corollary on the PSQT block, which is exact to rounding:
+    k = t(b.piece_count).to(dev).float()
+    gp = torch.ones(B, 1, device=dev)
+    gw_p, gb_p = torch.autograd.grad([l0, wp, bp], [w, bias], [torch.zeros_like(l0), gp, gp], retain_graph=False)
+    assert abs(float(gw_p[:, L1:].sum()) - float((4 * k).sum())) <= 1e-3 * float((4 * k).sum())
+    assert abs(float(gb_p[L1:].sum()) - 2 * B) <= 1e-3 * 2 * B
+
+
+def test_bad_indices_are_skipped_not_dereferenced(dev):
+    from nnue_pytorch_b200 import SparseLinearFunction, _launch, _lib
+
+    w = torch.randn(10, 16, device=dev)
+    b = torch.zeros(16, device=dev)
+    idx = torch.tensor([[1, 2, 10_000_000, 3], [4, -1, 5, 6]], dtype=torch.int32, device=dev)
+    _launch.device_status(dev)  # clear
+    out = SparseLinearFunction.apply(idx, w, b)
+    with pytest.raises(_lib.NnueB200Error):
+        _launch.device_status(dev)
+    _launch.device_status(dev)  # reading clears the word
+    assert torch.allclose(out[0], w[1] + w[2] + w[3])
+    assert torch.allclose(out[1], w[4])  # the first -1 ends the row

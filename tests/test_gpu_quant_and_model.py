@@ -1,0 +1,159 @@
+"""GPU checks of the integer evaluation (bit-exact) and of the whole training
+step around the feature transformer."""
+
+import numpy as np
+import pytest
+import torch
+
+from _util import load_golden, max_rel_err, small_model_params, t
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def dev():
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    return torch.device("cuda:0")
+
+
+def _net_from_params(p, L1, dev, buckets=8):
+    from nnue_pytorch_b200.quantized_eval import QuantizedNet
+
+    f = lambda a: t(np.asarray(a), torch.float64).to(dev)  # noqa: E731
+    l1_w = f(p["l1_w"] + np.tile(p["l1f_w"], (buckets, 1)))
+    l1_b = f(p["l1_b"] + np.tile(p["l1f_b"], buckets))
+    return QuantizedNet(f(p["ft_weight"]), f(p["ft_bias"]), l1_w, l1_b, f(p["l2_w"]), f(p["l2_b"]),
+                        f(p["out_w"]), f(p["out_b"]), L1, buckets)
+
+
+def test_integer_eval_matches_reference_float64(dev):
+    """The reference's float64 fake-quantized forward, x19200 and rounded,
+    on the golden positions (native HalfKAv2_hm^ layout)."""
+    from nnue_pytorch_b200 import positions
+
+    g = load_golden("model_small")
+    net = _net_from_params(small_model_params(), 64, dev)
+    b = positions.generate_batch(96, 21, layout="native")
+    out = net.evaluate(t(b.white).to(dev), t(b.black).to(dev), t(b.us[:, 0] > 0.5), t(b.piece_count))
+    assert np.array_equal(out.cpu().numpy().astype(np.int64), g["eval_int"][:, 0])
+
+
+def _random_quant_params(L1, N, gen, buckets=8, L2=32, L3=32):
+    p = {}
+    w = gen.integers(-24, 25, (N, L1 + 8)) / 256.0
+    w[:, L1:] = gen.integers(-2000, 2001, (N, 8)) / 9600.0
+    p["ft_weight"] = w
+    bias = np.zeros(L1 + 8)
+    bias[:L1] = gen.integers(-60, 61, L1) / 256.0
+    p["ft_bias"] = bias
+    p["l1_w"] = gen.integers(-100, 101, (buckets * L2, L1)) / 128.0
+    p["l1f_w"] = gen.integers(-27, 28, (L2, L1)) / 128.0
+    p["l1_b"] = gen.integers(-9000, 9001, buckets * L2) / 16384.0
+    p["l1f_b"] = gen.integers(-3000, 3001, L2) / 16384.0
+    p["l2_w"] = gen.integers(-127, 128, (buckets * L3, 2 * L2)) / 64.0
+    p["l2_b"] = gen.integers(-6000, 6001, buckets * L3) / 8192.0
+    p["out_w"] = gen.integers(-127, 128, (buckets, 2 * L2 + 2 * L3)) / 128.0
+    p["out_b"] = gen.integers(-9000, 9001, buckets) / 16384.0
+    return p
+
+
+@pytest.mark.parametrize("L1,layout,B", [(1024, "baseline", 4096), (3072, "baseline", 2048), (256, "native", 3000)])
+def test_integer_eval_matches_integer_oracle(dev, L1, layout, B):
+    from oracle import quant_oracle
+    from nnue_pytorch_b200 import positions
+    from nnue_pytorch_b200.quantize import QuantizationManager
+
+    gen = np.random.default_rng(L1)
+    N = positions.NUM_INPUTS_BASELINE if layout == "baseline" else positions.NUM_INPUTS_NATIVE
+    p = _random_quant_params(L1, N, gen)
+    b = positions.generate_batch(B, 17, layout=layout)
+    consts = QuantizationManager().integer_constants()
+    want = quant_oracle.integer_eval(quant_oracle.quantize_params(p, L1), b.white, b.black, b.us[:, 0] > 0.5,
+                                     (b.piece_count - 1) // 4, consts)
+    net = _net_from_params(p, L1, dev)
+    got = net.evaluate(t(b.white).to(dev), t(b.black).to(dev), t(b.us[:, 0] > 0.5), t(b.piece_count))
+    assert np.array_equal(got.cpu().numpy().astype(np.int64), want)
+    assert len(np.unique(want)) > B // 4  # the outputs are not degenerate
+
+
+def test_quantization_refuses_out_of_range_weights(dev):
+    p = _random_quant_params(64, 100, np.random.default_rng(0))
+    p["l2_w"][0, 0] = 3.0  # 3.0 * 64 = 192 > 127
+    with pytest.raises(RuntimeError, match="out of bounds"):
+        _net_from_params(p, 64, dev)
+
+
+def test_model_forward_and_gradients_match_oracle(dev):
+    """Whole network (feature transformer kernels + torch layer stacks + loss)
+    against the oracle on the golden model: same loss, same gradients."""
+    from oracle import model_oracle
+    from nnue_pytorch_b200 import positions
+    from nnue_pytorch_b200.model import LossParams, ModelConfig, NNUEModel, sf_loss
+
+    g = load_golden("model_small")
+    p = small_model_params()
+    m = NNUEModel("HalfKAv2_hm^", ModelConfig(L1=64, L2=32, L3=32))
+    with torch.no_grad():
+        f = m.input.features[0]
+        f.weight.copy_(t(p["ft_real"], torch.float32))
+        f.virtual_weight.copy_(t(p["ft_virtual"], torch.float32))
+        m.input.bias.copy_(t(p["ft_bias"], torch.float32))
+        ls = m.layer_stacks
+        for mod, wk, bk in ((ls.l1.linear, "l1_w", "l1_b"), (ls.l1.factorized_linear, "l1f_w", "l1f_b"),
+                            (ls.l2.linear, "l2_w", "l2_b"), (ls.output.linear, "out_w", "out_b")):
+            mod.weight.copy_(t(p[wk], torch.float32))
+            mod.bias.copy_(t(p[bk], torch.float32))
+    m.to(dev)
+    b = positions.generate_batch(96, 21, layout="native")
+    us, them, white, black, outcome, score, pc = (t(a).to(dev) for a in b.as_tuple())
+    y = m(us, them, white, black, pc, True, True)
+    assert max_rel_err(y.detach().cpu(), t(g["scorenet32"])) <= 1e-5
+    loss = sf_loss(y * 600.0, score, outcome, LossParams(), 1.0)
+    loss.backward()
+    assert abs(float(loss) - float(g["loss"])) <= 1e-5 * float(g["loss"])
+    f = m.input.features[0]
+    for ours, key in ((f.weight.grad, "g_ft_weight"), (f.virtual_weight.grad, "g_ft_virtual"),
+                      (m.input.bias.grad, "g_ft_bias"), (m.layer_stacks.l1.linear.weight.grad, "g_l1_w"),
+                      (m.layer_stacks.output.linear.weight.grad, "g_out_w")):
+        assert max_rel_err(ours.cpu(), t(g[key])) <= 2e-5, key
+    _ = model_oracle
+
+
+def test_training_steps_track_the_oracle(dev):
+    """Five optimizer steps (one lookahead merge) of the whole model on the
+    baseline layout: loss curve and the touched part of the table follow the
+    CPU oracle (forward + autograd + RangerLite restatement)."""
+    from oracle import model_oracle, ranger_lite_oracle
+    from nnue_pytorch_b200 import positions
+    from nnue_pytorch_b200.model import ModelConfig, NNUEModel, TrainStep
+
+    torch.manual_seed(0)
+    m = NNUEModel("HalfKAv2_hm^flat", ModelConfig(L1=128, L2=32, L3=32))
+    with torch.no_grad():
+        m.input.features[0].weight[:, :128].normal_(0, 0.05)
+        m.layer_stacks.l1.linear.weight.normal_(0, 0.05)
+    names = {"ft_weight": m.input.features[0].weight, "ft_bias": m.input.bias,
+             "l1f_w": m.layer_stacks.l1.factorized_linear.weight, "l1f_b": m.layer_stacks.l1.factorized_linear.bias,
+             "l1_w": m.layer_stacks.l1.linear.weight, "l1_b": m.layer_stacks.l1.linear.bias,
+             "l2_w": m.layer_stacks.l2.linear.weight, "l2_b": m.layer_stacks.l2.linear.bias,
+             "out_w": m.layer_stacks.output.linear.weight, "out_b": m.layer_stacks.output.linear.bias}
+    order = list(names)  # the trainer's ten groups, in its order
+    cpu = {k: v.detach().clone() for k, v in names.items()}
+    state = ranger_lite_oracle.RangerLiteState([cpu[k] for k in order])
+    m.to(dev)
+    step = TrainStep(m, lr=8.75e-4, clip=2.0)
+    for i in range(5):
+        b = positions.generate_batch(512, 100 + i, layout="baseline")
+        batch = tuple(t(a) for a in b.as_tuple())
+        params = {k: v.clone().requires_grad_(True) for k, v in cpu.items()}
+        loss_ref = model_oracle.training_loss(params, batch)
+        loss_ref.backward()
+        grads = [params[k].grad for k in order]
+        total = torch.linalg.vector_norm(torch.stack([torch.linalg.vector_norm(g_) for g_ in grads]))
+        coef = torch.clamp(2.0 / (total + 1e-6), max=1.0)
+        ranger_lite_oracle.ranger_lite_step([cpu[k] for k in order], [g_ * coef for g_ in grads], state, lr=8.75e-4)
+        loss = step(tuple(x.to(dev) for x in batch))
+        assert abs(float(loss) - float(loss_ref)) <= 2e-5 * abs(float(loss_ref)), i
+    for k in order:
+        assert max_rel_err(names[k].detach().cpu(), cpu[k]) <= 1e-4, k
