@@ -43,13 +43,17 @@ inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 
 unsigned long long* device_status_ptr();
 
 struct Tuning {
-    int fwd_u = 2;        // float4 per lane per half in the fused forward (1, 2 or 4)
+    int fwd_u = 1;        // float4 per lane per half in the fused forward (1, 2 or 4)
     int bwd_u = 2;        // float4 per lane in the segment gather-sum (1, 2 or 4)
     int sparse_u = 2;     // float4 per lane in the sparse-linear forward
     int stage_idx = 1;    // 1 = bulk-copy index lists to shared memory when aligned
     int long_row = 256;   // rows with more hits are reduced by a whole CTA
     int prologue_pb = 32; // positions per CTA in the backward prologue
     int sort_segments = 1;// 1 = order every CSR segment (deterministic sums)
+    int seg_chunk = 256;  // entries per warp in the chunked segment gather-sum; 0 = one warp per row
+    int bwd_r = 0;        // compiled variant of the chunked gather-sum (see LAUNCH_CHUNKS)
+    int fwd_variant = 0;  // compiled variant of the fused forward (see LAUNCH_FWD)
+    int overlap_csr = 1;  // 1 = build the CSR on the helper stream, beside the backward prologue
 };
 Tuning& tuning();
 

@@ -111,6 +111,10 @@ extern "C" int nnue_b200_tune(const char* key, int value) {
     else if (!strcmp(key, "long_row")) t.long_row = value > 0 ? value : 1;
     else if (!strcmp(key, "prologue_pb")) t.prologue_pb = value > 0 ? value : 1;
     else if (!strcmp(key, "sort_segments")) t.sort_segments = value;
+    else if (!strcmp(key, "seg_chunk")) t.seg_chunk = value > 0 ? value : 0;
+    else if (!strcmp(key, "bwd_r")) t.bwd_r = value;
+    else if (!strcmp(key, "fwd_variant")) t.fwd_variant = value;
+    else if (!strcmp(key, "overlap_csr")) t.overlap_csr = value;
     else {
         set_error("nnue_b200_tune: unknown key '%s'", key);
         return NNUE_ERR_ARG;

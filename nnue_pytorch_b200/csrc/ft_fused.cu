@@ -84,8 +84,8 @@ __device__ __forceinline__ float psqt_sum(const float* __restrict__ weight, int6
     return s;
 }
 
-template <int U>
-__global__ void __launch_bounds__(kThreads)
+template <int U, int R, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
     k_fused_fwd(const float* __restrict__ us, const float* __restrict__ them,
                 const int32_t* __restrict__ wi, const int32_t* __restrict__ bi,
                 const int64_t* __restrict__ psqt_idx, const float* __restrict__ weight,
@@ -125,12 +125,11 @@ __global__ void __launch_bounds__(kThreads)
 
     float4 accw[2 * U], accb[2 * U];
 #pragma unroll
-    for (int c = 0; c < 2 * U; ++c) {
-        accw[c] = ok[c] ? ldg4(bias4 + col[c]) : f4_zero();
-        accb[c] = accw[c];
-    }
-    gather_sum<2 * U, 8 / U>(table, W4, N, lists.w, nw, col, ok, accw, lane, status);
-    gather_sum<2 * U, 8 / U>(table, W4, N, lists.b, nb, col, ok, accb, lane, status);
+    for (int c = 0; c < 2 * U; ++c) accw[c] = ok[c] ? ldg4(bias4 + col[c]) : f4_zero();
+    gather_sum<2 * U, R>(table, W4, N, lists.w, nw, col, ok, accw, lane, status);
+#pragma unroll
+    for (int c = 0; c < 2 * U; ++c) accb[c] = ok[c] ? ldg4(bias4 + col[c]) : f4_zero();
+    gather_sum<2 * U, R>(table, W4, N, lists.b, nb, col, ok, accb, lane, status);
 
     const float u_ = __ldg(us + p), t_ = __ldg(them + p);
     const int h = L1 >> 1;
@@ -542,13 +541,22 @@ extern "C" int nnue_ft_fused_fwd(const float* us, const float* them, const int32
     const int stage = tuning().stage_idx && K > 0 && smem <= 48 * 1024 && aligned16(white_idx) &&
                       aligned16(black_idx);
     const unsigned grid = (unsigned)(groups * tiles);
-#define LAUNCH_FWD(UU)                                                                          \
-    k_fused_fwd<UU><<<grid, kThreads, stage ? smem : 0, s>>>(                                   \
+#define LAUNCH_FWD(UU, RR, MB)                                                                  \
+    k_fused_fwd<UU, RR, MB><<<grid, kThreads, stage ? smem : 0, s>>>(                           \
         us, them, white_idx, black_idx, psqt_idx, weight, bias, max_act, l0, wpsqt, bpsqt, saved, B, \
         K, N, L1, P, (int)groups, stage, status)
-    if (U == 1) LAUNCH_FWD(1);
-    else if (U == 2) LAUNCH_FWD(2);
-    else LAUNCH_FWD(4);
+    // variant = rows in flight per warp (R) and CTAs per SM the register budget must allow
+    const int v = tuning().fwd_variant;
+    if (U == 1) {
+        if (v == 1) LAUNCH_FWD(1, 2, 6); else if (v == 2) LAUNCH_FWD(1, 4, 3);
+        else if (v == 3) LAUNCH_FWD(1, 2, 4); else if (v == 4) LAUNCH_FWD(1, 6, 3);
+        else LAUNCH_FWD(1, 4, 4);
+    } else if (U == 2) {
+        if (v == 1) LAUNCH_FWD(2, 4, 2); else if (v == 2) LAUNCH_FWD(2, 1, 4);
+        else LAUNCH_FWD(2, 2, 3);
+    } else {
+        LAUNCH_FWD(4, 2, 2);
+    }
 #undef LAUNCH_FWD
     NNUE_CUDA_TRY(cudaGetLastError());
     note_launches(1);
@@ -574,7 +582,7 @@ extern "C" size_t nnue_ft_fused_bwd_workspace_bytes(int64_t B, int32_t K, int64_
     size_t bytes = 0;
     bytes += align_up((size_t)(2 * B) * W * sizeof(float), 256);
     bytes += align_up((size_t)nblk * W * sizeof(float), 256);
-    bytes += csr_workspace_bytes(2 * B * (int64_t)K, N);
+    bytes += csr_workspace_bytes(2 * B * (int64_t)K, N, (int)W);
     return bytes + 256;
 }
 
@@ -650,30 +658,42 @@ extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32
     float* bias_part = reinterpret_cast<float*>(ws);
     ws += align_up((size_t)nblk * W * sizeof(float), 256);
 
-    int64_t part_rows;
-    const float* part_src;
-    if (vec) {
-        const int cols4 = L1 / 8 + P / 4;
-        const int chunks = (cols4 + kThreads - 1) / kThreads;
-        NNUE_REQUIRE(nblk * chunks <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "grid too large");
-        k_bwd_prologue<<<(unsigned)(nblk * chunks), kThreads, 0, s>>>(
-            us, them, psqt_idx, max_act, grad_l0, grad_wpsqt, grad_bpsqt, saved, G, bias_part, B, L1,
-            P, pb, chunks);
-        part_rows = nblk;
-        part_src = bias_part;
-    } else {
-        k_bwd_prologue_scalar<<<(unsigned)B, 128, 0, s>>>(us, them, psqt_idx, max_act, grad_l0,
-                                                         grad_wpsqt, grad_bpsqt, saved, G, B, L1, P);
-        part_rows = 2 * B;  // bias = column sum of G itself
-        part_src = G;
-    }
-    NNUE_CUDA_TRY(cudaGetLastError());
-    note_launches(1);
-    int rc = column_sum(part_src, part_rows, (int)W, grad_bias, s);
+    // CSR over both perspectives: entry id = 2*p + perspective = row of G.  It depends on the
+    // index lists only, so it is built on the helper stream while the prologue streams G.
+    CsrPlan plan;
+    int rc = csr_plan(plan, 2, B, K, N, (int)W, ws,
+                      workspace_bytes - (size_t)(ws - static_cast<char*>(workspace)));
     if (rc != NNUE_OK) return rc;
-    // CSR over both perspectives: entry id = 2*p + perspective = row of G
     const int32_t* lists[2] = {white_idx, black_idx};
-    rc = csr_build_and_reduce(lists, 2, B, K, N, G, (int)W, grad_weight, ws,
-                              workspace_bytes - (size_t)(ws - static_cast<char*>(workspace)), s);
-    return rc;
+    CsrJoin join;
+    rc = csr_build_overlapped(plan, lists, s, join);
+
+    int64_t part_rows = 0;
+    const float* part_src = nullptr;
+    cudaError_t launch_err = cudaSuccess;
+    if (rc == NNUE_OK) {
+        if (vec) {
+            const int cols4 = L1 / 8 + P / 4;
+            const int chunks = (cols4 + kThreads - 1) / kThreads;
+            k_bwd_prologue<<<(unsigned)(nblk * chunks), kThreads, 0, s>>>(
+                us, them, psqt_idx, max_act, grad_l0, grad_wpsqt, grad_bpsqt, saved, G, bias_part, B,
+                L1, P, pb, chunks);
+            part_rows = nblk;
+            part_src = bias_part;
+        } else {
+            k_bwd_prologue_scalar<<<(unsigned)B, 128, 0, s>>>(us, them, psqt_idx, max_act, grad_l0,
+                                                             grad_wpsqt, grad_bpsqt, saved, G, B, L1,
+                                                             P);
+            part_rows = 2 * B;  // bias = column sum of G itself
+            part_src = G;
+        }
+        launch_err = cudaGetLastError();
+        note_launches(1);
+        if (launch_err == cudaSuccess) rc = column_sum(part_src, part_rows, (int)W, grad_bias, s);
+    }
+    const int rj = csr_join(join, s);  // always: the caller's stream must see the helper's work
+    if (launch_err != cudaSuccess) return cuda_fail(launch_err, "backward prologue launch");
+    if (rc != NNUE_OK) return rc;
+    if (rj != NNUE_OK) return rj;
+    return csr_reduce(plan, G, (int)W, grad_weight, s);
 }

@@ -13,13 +13,20 @@ namespace nnue {
 
 static size_t align_up(size_t x, size_t a) { return (x + a - 1) / a * a; }
 
-size_t csr_workspace_bytes(int64_t max_entries, int64_t n_rows) {
+static int64_t max_chunks_for(int64_t max_entries, int S) { return (max_entries + S - 1) / S + 1; }
+
+size_t csr_workspace_bytes(int64_t max_entries, int64_t n_rows, int W) {
     size_t b = 0;
+    const int S = tuning().seg_chunk;
+    if (S > 0) {
+        const int64_t mc = max_chunks_for(max_entries, S);
+        b += align_up((size_t)mc * sizeof(int32_t), 256);               // chunk -> first row
+        b += align_up((size_t)mc * 2 * (size_t)W * sizeof(float), 256);  // partial sums
+    }
     b += align_up((size_t)(n_rows + 1) * sizeof(int32_t), 256);  // counts + long-row counter
     b += align_up((size_t)n_rows * sizeof(int32_t), 256);        // long-row list
     b += align_up((size_t)(n_rows + 1) * sizeof(int32_t), 256);  // offsets
-    b += align_up((size_t)n_rows * sizeof(int32_t), 256);        // cursors
-    b += align_up((size_t)(max_entries > 0 ? max_entries : 1) * sizeof(int32_t), 256);  // entries
+    b += 2 * align_up((size_t)(max_entries > 0 ? max_entries : 1) * sizeof(int32_t), 256);  // ranks, entries
     return b + 256;
 }
 
@@ -28,7 +35,8 @@ template <bool FILL>
 __global__ void __launch_bounds__(kThreads)
     k_csr_scan_lists(const int32_t* __restrict__ list0, const int32_t* __restrict__ list1,
                      int n_lists, int64_t B, int K, int64_t N, int32_t* __restrict__ counts_or_cursor,
-                     int32_t* __restrict__ entries, unsigned long long* status) {
+                     int32_t* __restrict__ ranks, int32_t* __restrict__ entries,
+                     unsigned long long* status) {
     const int lane = threadIdx.x & 31;
     const int64_t wid = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     if (wid >= B * n_lists) return;
@@ -43,12 +51,10 @@ __global__ void __launch_bounds__(kThreads)
         const int m = neg ? (__ffs(neg) - 1) : 32;
         if (lane < m) {
             if ((int64_t)r < N) {
-                if (FILL) {
-                    const int pos = atomicAdd(counts_or_cursor + r, 1);
-                    entries[pos] = e;
-                } else {
-                    atomicAdd(counts_or_cursor + r, 1);
-                }
+                // count pass: the value the atomic returns is this entry's slot
+                // inside its row; the fill pass needs no atomics
+                if (FILL) entries[counts_or_cursor[r] + ranks[wid * K + k]] = e;
+                else ranks[wid * K + k] = atomicAdd(counts_or_cursor + r, 1);
             } else if (!FILL) {
                 note_bad_index(status);
             }
@@ -274,7 +280,7 @@ __global__ void __launch_bounds__(kThreads)
             float4 acc[U];
 #pragma unroll
             for (int u = 0; u < U; ++u) acc[u] = f4_zero();
-            gather_sum<U, 16 / U>(src, W4, src_rows, entries + beg, len, col, ok, acc, lane, status);
+            gather_sum<U, 8 / U>(src, W4, src_rows, entries + beg, len, col, ok, acc, lane, status);
 #pragma unroll
             for (int u = 0; u < U; ++u)
                 if (ok[u]) out[row * W4 + col[u]] = acc[u];
@@ -290,7 +296,7 @@ __global__ void __launch_bounds__(kThreads)
         float4 acc[U];
 #pragma unroll
         for (int u = 0; u < U; ++u) acc[u] = f4_zero();
-        gather_sum<U, 16 / U>(src, W4, src_rows, entries + beg + mb, me - mb, col, ok, acc, lane, status);
+        gather_sum<U, 8 / U>(src, W4, src_rows, entries + beg + mb, me - mb, col, ok, acc, lane, status);
         __syncthreads();
 #pragma unroll
         for (int u = 0; u < U; ++u) s_part[warp][u][lane] = acc[u];
@@ -304,6 +310,133 @@ __global__ void __launch_bounds__(kThreads)
             }
         }
     }
+}
+
+// ---- pass 5, balanced form: one warp per CHUNK of the entry array ---------
+// A chunk is `S` consecutive entries of the CSR, whatever rows they belong to,
+// so every warp streams the same number of source rows and the load pipeline
+// never drains at a row end; rows that one batch hits 16 000 times cost the
+// same per entry as rows hit twice.  Inside a chunk the warp walks the row
+// boundaries (warp-uniform branches).  A row that lies wholly inside the chunk
+// is stored straight to `out`.  A row that crosses a chunk border leaves
+// partial sums in `partial[chunk][0]` (piece that started in an earlier chunk)
+// or `partial[chunk][1]` (piece that runs on into the next chunk);
+// k_segment_fixup adds them in chunk order, k_zero_empty_rows writes the rows
+// nobody touched.  Every order is fixed, so the result is reproducible.
+__global__ void __launch_bounds__(kThreads)
+    k_chunk_rows(const int32_t* __restrict__ offsets, int64_t N, int S, int max_chunks,
+                 int32_t* __restrict__ chunk_row) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= max_chunks) return;
+    const int64_t e = (int64_t)c * S;
+    if (e >= offsets[N]) {
+        chunk_row[c] = -1;
+        return;
+    }
+    // first index with offsets[i] > e, minus one: offsets[r] <= e < offsets[r+1]
+    int64_t lo = 0, hi = N;  // answer in (lo, hi]
+    while (hi - lo > 1) {
+        const int64_t mid = (lo + hi) >> 1;
+        if (offsets[mid] <= e) lo = mid; else hi = mid;
+    }
+    chunk_row[c] = (int32_t)lo;
+}
+
+template <int U, int R, int MINB>
+__global__ void __launch_bounds__(kThreads, MINB)
+    k_segment_chunks(const float4* __restrict__ src, int64_t W4, int64_t src_rows,
+                     const int32_t* __restrict__ offsets, const int32_t* __restrict__ entries,
+                     const int32_t* __restrict__ chunk_row, float4* __restrict__ out,
+                     float4* __restrict__ partial, int64_t N, int n_chunk_groups, int S,
+                     unsigned long long* status) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / n_chunk_groups;
+    const int c = (blockIdx.x % n_chunk_groups) * kWarpsPerCta + warp;
+    const int E = __ldg(offsets + N);
+    const int e_beg = c * S;
+    if (e_beg >= E) return;  // warp-uniform
+    const int e_end = min(E, e_beg + S);
+
+    int col[U];
+    bool ok[U];
+    float4 acc[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        col[u] = tile * (32 * U) + u * 32 + lane;
+        ok[u] = col[u] < W4;
+        acc[u] = f4_zero();
+    }
+    int row = __ldg(chunk_row + c);
+    int row_beg = __ldg(offsets + row), next_b = __ldg(offsets + row + 1);
+    int piece_beg = e_beg;
+
+    auto flush = [&](int pe) {  // piece [piece_beg, pe) of `row`
+        if (next_b == row_beg) return;  // empty row: k_zero_empty_rows owns it
+        float4* dst;
+        if (piece_beg == row_beg && pe == next_b) dst = out + (int64_t)row * W4;
+        else if (piece_beg == e_beg && row_beg < e_beg) dst = partial + ((int64_t)c * 2 + 0) * W4;
+        else dst = partial + ((int64_t)c * 2 + 1) * W4;
+#pragma unroll
+        for (int u = 0; u < U; ++u)
+            if (ok[u]) dst[col[u]] = acc[u];
+    };
+
+    // entry i of this chunk is entry e_beg + i of the CSR; a row ends where the
+    // running index meets `next_b` (the loop also steps over empty rows)
+    auto at_entry = [&](int i) {
+        const int e = e_beg + i;
+        while (e == next_b) {
+            flush(e);
+            ++row;
+            row_beg = next_b;
+            next_b = __ldg(offsets + row + 1);
+            piece_beg = e;
+#pragma unroll
+            for (int u = 0; u < U; ++u) acc[u] = f4_zero();
+        }
+    };
+    gather_sum_pipelined<U, R>(src, W4, src_rows, entries + e_beg, e_end - e_beg, col, ok, acc, lane,
+                               status, tile == 0, at_entry);
+    flush(e_end);
+}
+
+// One warp per (chunk, tile): if the row whose piece opens this chunk also ends
+// in this chunk, add up its pieces from the chunk it started in to this one.
+template <int U>
+__global__ void __launch_bounds__(kThreads)
+    k_segment_fixup(const int32_t* __restrict__ offsets, const int32_t* __restrict__ chunk_row,
+                    const float4* __restrict__ partial, float4* __restrict__ out, int64_t W4,
+                    int64_t N, int n_chunk_groups, int S) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tile = blockIdx.x / n_chunk_groups;
+    const int c = (blockIdx.x % n_chunk_groups) * kWarpsPerCta + warp;
+    const int E = __ldg(offsets + N);
+    const int e_beg = c * S;
+    if (e_beg >= E) return;
+    const int r = __ldg(chunk_row + c);
+    const int rb = __ldg(offsets + r), re = __ldg(offsets + r + 1);
+    if (rb >= e_beg) return;        // the opening row starts here: it has no earlier piece
+    if (re > e_beg + S) return;     // it runs on: a later chunk finishes it
+    const int a = rb / S;           // chunk the row started in (its piece there is a [1] piece)
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+        const int cc = tile * (32 * U) + u * 32 + lane;
+        if (cc >= W4) continue;
+        float4 s = partial[((int64_t)a * 2 + 1) * W4 + cc];
+        for (int x = a + 1; x <= c; ++x) s = f4_add(s, partial[((int64_t)x * 2 + 0) * W4 + cc]);
+        out[(int64_t)r * W4 + cc] = s;
+    }
+}
+
+// One warp per row: rows without a single entry get zeros.
+__global__ void __launch_bounds__(kThreads)
+    k_zero_empty_rows(const int32_t* __restrict__ offsets, float4* __restrict__ out, int64_t W4,
+                      int64_t N) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    if (row >= N) return;
+    if (__ldg(offsets + row) != __ldg(offsets + row + 1)) return;
+    for (int64_t c = lane; c < W4; c += 32) out[row * W4 + c] = f4_zero();
 }
 
 // Scalar twin for W % 4 != 0 or unaligned buffers: lane = one column.
@@ -403,51 +536,67 @@ int column_sum(const float* src, int64_t rows, int W, float* out, cudaStream_t s
     return NNUE_OK;
 }
 
-int csr_build_and_reduce(const int32_t* const* lists, int n_lists, int64_t B, int K, int64_t N,
-                         const float* src, int W, float* out, void* ws, size_t ws_bytes,
-                         cudaStream_t s) {
+int csr_plan(CsrPlan& plan, int n_lists, int64_t B, int K, int64_t N, int W, void* ws,
+             size_t ws_bytes) {
     NNUE_REQUIRE(n_lists == 1 || n_lists == 2, NNUE_ERR_ARG, "csr: n_lists must be 1 or 2");
-    if (N == 0) return NNUE_OK;
     NNUE_REQUIRE(N < 0x7fffffffLL && B * n_lists < 0x7fffffffLL &&
                      B * (int64_t)n_lists * K < 0x7fffffffLL,
                  NNUE_ERR_UNSUPPORTED, "csr: sizes exceed 31-bit entry ids");
-    const size_t need = csr_workspace_bytes(B * (int64_t)n_lists * K, N);
+    const int64_t max_entries = B * (int64_t)n_lists * K;
+    const size_t need = csr_workspace_bytes(max_entries, N, W);
     NNUE_REQUIRE(ws && ws_bytes >= need, NNUE_ERR_WORKSPACE, "csr: workspace %zu < required %zu",
                  ws_bytes, need);
+    plan.n_lists = n_lists;
+    plan.B = B;
+    plan.K = K;
+    plan.N = N;
+    plan.S = tuning().seg_chunk;
+    plan.max_chunks = plan.S > 0 ? max_chunks_for(max_entries, plan.S) : 0;
+    char* p = reinterpret_cast<char*>(align_up(reinterpret_cast<uintptr_t>(ws), 256));
+    auto take = [&p](size_t bytes) {
+        char* r = p;
+        p += align_up(bytes, 256);
+        return r;
+    };
+    const size_t ent = (size_t)(max_entries > 0 ? max_entries : 1) * sizeof(int32_t);
+    plan.counts = reinterpret_cast<int32_t*>(take((size_t)(N + 1) * sizeof(int32_t)));
+    plan.n_long = plan.counts + N;  // counts[N] is the long-row counter
+    plan.long_list = reinterpret_cast<int32_t*>(take((size_t)N * sizeof(int32_t)));
+    plan.offsets = reinterpret_cast<int32_t*>(take((size_t)(N + 1) * sizeof(int32_t)));
+    plan.ranks = reinterpret_cast<int32_t*>(take(ent));
+    plan.entries = reinterpret_cast<int32_t*>(take(ent));
+    plan.chunk_row = reinterpret_cast<int32_t*>(take((size_t)plan.max_chunks * sizeof(int32_t)));
+    plan.partial = reinterpret_cast<float*>(p);
+    return NNUE_OK;
+}
+
+int csr_build(const CsrPlan& plan, const int32_t* const* lists, cudaStream_t s) {
+    const int64_t N = plan.N, B = plan.B;
+    const int K = plan.K, n_lists = plan.n_lists;
+    if (N == 0) return NNUE_OK;
     unsigned long long* status = device_status_ptr();
     NNUE_REQUIRE(status, NNUE_ERR_CUDA, "csr: no device status word");
-
-    char* p = reinterpret_cast<char*>(align_up(reinterpret_cast<uintptr_t>(ws), 256));
-    int32_t* counts = reinterpret_cast<int32_t*>(p);  // counts[N] is the long-row counter
-    int32_t* n_long = counts + N;
-    p += align_up((size_t)(N + 1) * sizeof(int32_t), 256);
-    int32_t* long_list = reinterpret_cast<int32_t*>(p);
-    p += align_up((size_t)N * sizeof(int32_t), 256);
-    int32_t* offsets = reinterpret_cast<int32_t*>(p);
-    p += align_up((size_t)(N + 1) * sizeof(int32_t), 256);
-    int32_t* cursor = reinterpret_cast<int32_t*>(p);
-    p += align_up((size_t)N * sizeof(int32_t), 256);
-    int32_t* entries = reinterpret_cast<int32_t*>(p);
-
-    NNUE_CUDA_TRY(cudaMemsetAsync(counts, 0, (size_t)(N + 1) * sizeof(int32_t), s));
+    NNUE_CUDA_TRY(cudaMemsetAsync(plan.counts, 0, (size_t)(N + 1) * sizeof(int32_t), s));
     const int64_t warps = B * n_lists;
     const unsigned lgrid = (unsigned)((warps + kWarpsPerCta - 1) / kWarpsPerCta);
     const int32_t* l0 = lists[0];
     const int32_t* l1 = n_lists > 1 ? lists[1] : lists[0];
     if (warps > 0 && K > 0) {
-        k_csr_scan_lists<false><<<lgrid, kThreads, 0, s>>>(l0, l1, n_lists, B, K, N, counts, entries,
-                                                          status);
-        note_launches(2);  // this pass and the fill pass below
+        k_csr_scan_lists<false><<<lgrid, kThreads, 0, s>>>(l0, l1, n_lists, B, K, N, plan.counts,
+                                                          plan.ranks, plan.entries, status);
+        note_launches(1);
     }
-    k_csr_scan<<<1, 1024, 0, s>>>(counts, offsets, cursor, N, long_list, n_long, kWarpSortMax);
-    note_launches(2);  // the scan and the segment gather-sum at the end
+    k_csr_scan<<<1, 1024, 0, s>>>(plan.counts, plan.offsets, plan.offsets, N, plan.long_list,
+                                  plan.n_long, kWarpSortMax);
+    note_launches(1);
     if (warps > 0 && K > 0) {
-        k_csr_scan_lists<true><<<lgrid, kThreads, 0, s>>>(l0, l1, n_lists, B, K, N, cursor, entries,
-                                                         status);
+        k_csr_scan_lists<true><<<lgrid, kThreads, 0, s>>>(l0, l1, n_lists, B, K, N, plan.offsets,
+                                                         plan.ranks, plan.entries, status);
+        note_launches(1);
     }
     const int64_t row_groups = (N + kWarpsPerCta - 1) / kWarpsPerCta;
     if (tuning().sort_segments && warps > 0 && K > 0) {
-        k_csr_sort_short<<<(unsigned)row_groups, kThreads, 0, s>>>(offsets, entries, N);
+        k_csr_sort_short<<<(unsigned)row_groups, kThreads, 0, s>>>(plan.offsets, plan.entries, N);
         note_launches(1);
         const int64_t key_space = B * n_lists;
         if (key_space <= kBitmapMaxBits) {
@@ -460,13 +609,27 @@ int csr_build_and_reduce(const int32_t* const* lists, int n_lists, int64_t B, in
                 attr_smem = smem;
             }
             const unsigned g = (unsigned)std::min<int64_t>(N, (int64_t)sm_count() * 4);
-            k_csr_sort_long<<<g, kThreads, smem, s>>>(offsets, entries, long_list, n_long, words,
-                                                     status);
+            k_csr_sort_long<<<g, kThreads, smem, s>>>(plan.offsets, plan.entries, plan.long_list,
+                                                     plan.n_long, words, status);
             note_launches(1);
         }
     }
+    if (plan.S > 0) {
+        k_chunk_rows<<<(unsigned)((plan.max_chunks + kThreads - 1) / kThreads), kThreads, 0, s>>>(
+            plan.offsets, N, plan.S, (int)plan.max_chunks, plan.chunk_row);
+        note_launches(1);
+    }
     NNUE_CUDA_TRY(cudaGetLastError());
+    return NNUE_OK;
+}
 
+int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStream_t s) {
+    const int64_t N = plan.N, src_rows = plan.B * plan.n_lists;
+    if (N == 0) return NNUE_OK;
+    unsigned long long* status = device_status_ptr();
+    NNUE_REQUIRE(status, NNUE_ERR_CUDA, "csr: no device status word");
+    const int64_t row_groups = (N + kWarpsPerCta - 1) / kWarpsPerCta;
+    const int S = plan.S;
     const bool vec = (W % 4 == 0) && aligned16(src) && aligned16(out);
     if (vec) {
         const int64_t W4 = W / 4;
@@ -474,27 +637,101 @@ int csr_build_and_reduce(const int32_t* const* lists, int n_lists, int64_t B, in
         if (U != 1 && U != 2 && U != 4) U = 2;
         while (U > 1 && W4 <= 32 * (U / 2)) U /= 2;
         const int64_t tiles = (W4 + 32 * U - 1) / (32 * U);
-        NNUE_REQUIRE(tiles * row_groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
-        const unsigned grid = (unsigned)(tiles * row_groups);
         const float4* s4 = reinterpret_cast<const float4*>(src);
         float4* o4 = reinterpret_cast<float4*>(out);
-        const int long_row = tuning().long_row;
-        if (U == 1)
-            k_segment_reduce<1><<<grid, kThreads, 0, s>>>(s4, W4, B * n_lists, offsets, entries, o4, N,
-                                                         (int)row_groups, long_row, status);
-        else if (U == 2)
-            k_segment_reduce<2><<<grid, kThreads, 0, s>>>(s4, W4, B * n_lists, offsets, entries, o4, N,
-                                                         (int)row_groups, long_row, status);
-        else
-            k_segment_reduce<4><<<grid, kThreads, 0, s>>>(s4, W4, B * n_lists, offsets, entries, o4, N,
-                                                         (int)row_groups, long_row, status);
+        if (S > 0) {
+            const int64_t groups = (plan.max_chunks + kWarpsPerCta - 1) / kWarpsPerCta;
+            NNUE_REQUIRE(tiles * groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
+            const unsigned grid = (unsigned)(tiles * groups);
+            float4* p4 = reinterpret_cast<float4*>(plan.partial);
+            k_zero_empty_rows<<<(unsigned)row_groups, kThreads, 0, s>>>(plan.offsets, o4, W4, N);
+            // variant = rows per register buffer (R) and CTAs per SM the register budget must allow
+            const int v = tuning().bwd_r;
+#define LAUNCH_CHUNKS(UU, RR, MB)                                                                  \
+    k_segment_chunks<UU, RR, MB><<<grid, kThreads, 0, s>>>(s4, W4, src_rows, plan.offsets,         \
+                                                           plan.entries, plan.chunk_row, o4, p4, N, \
+                                                           (int)groups, S, status)
+            if (U == 1) {
+                if (v == 1) LAUNCH_CHUNKS(1, 2, 6); else if (v == 2) LAUNCH_CHUNKS(1, 4, 4);
+                else LAUNCH_CHUNKS(1, 2, 4);
+            } else if (U == 2) {
+                if (v == 1) LAUNCH_CHUNKS(2, 1, 6); else if (v == 2) LAUNCH_CHUNKS(2, 2, 4);
+                else if (v == 3) LAUNCH_CHUNKS(2, 1, 5); else if (v == 4) LAUNCH_CHUNKS(2, 2, 3);
+                else LAUNCH_CHUNKS(2, 1, 4);
+            } else {
+                if (v == 1) LAUNCH_CHUNKS(4, 1, 3); else LAUNCH_CHUNKS(4, 1, 4);
+            }
+#undef LAUNCH_CHUNKS
+            if (U == 1) k_segment_fixup<1><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S);
+            else if (U == 2) k_segment_fixup<2><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S);
+            else k_segment_fixup<4><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S);
+            note_launches(3);
+        } else {
+            NNUE_REQUIRE(tiles * row_groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
+            const unsigned grid = (unsigned)(tiles * row_groups);
+            const int long_row = tuning().long_row;
+            if (U == 1)
+                k_segment_reduce<1><<<grid, kThreads, 0, s>>>(s4, W4, src_rows, plan.offsets, plan.entries,
+                                                             o4, N, (int)row_groups, long_row, status);
+            else if (U == 2)
+                k_segment_reduce<2><<<grid, kThreads, 0, s>>>(s4, W4, src_rows, plan.offsets, plan.entries,
+                                                             o4, N, (int)row_groups, long_row, status);
+            else
+                k_segment_reduce<4><<<grid, kThreads, 0, s>>>(s4, W4, src_rows, plan.offsets, plan.entries,
+                                                             o4, N, (int)row_groups, long_row, status);
+            note_launches(1);
+        }
     } else {
         const int64_t tiles = (W + 31) / 32;
         NNUE_REQUIRE(tiles * row_groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
         k_segment_reduce_scalar<<<(unsigned)(tiles * row_groups), kThreads, 0, s>>>(
-            src, W, B * n_lists, offsets, entries, out, N, (int)row_groups, status);
+            src, W, src_rows, plan.offsets, plan.entries, out, N, (int)row_groups, status);
+        note_launches(1);
     }
     NNUE_CUDA_TRY(cudaGetLastError());
+    return NNUE_OK;
+}
+
+// Per-device helper stream and events for overlapping the CSR build (atomics,
+// latency bound) with DRAM-bound work on the caller's stream.  The fork/join
+// pattern below is also legal inside a stream capture.
+struct SideStream {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+static SideStream* side_stream() {
+    static SideStream table[64];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    SideStream& t = table[dev];
+    if (!t.stream) {
+        if (cudaStreamCreateWithFlags(&t.stream, cudaStreamNonBlocking) != cudaSuccess) return nullptr;
+        if (cudaEventCreateWithFlags(&t.fork, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+        if (cudaEventCreateWithFlags(&t.join, cudaEventDisableTiming) != cudaSuccess) return nullptr;
+    }
+    return &t;
+}
+
+int csr_build_overlapped(const CsrPlan& plan, const int32_t* const* lists, cudaStream_t s,
+                         CsrJoin& join) {
+    join.pending = false;
+    SideStream* side = tuning().overlap_csr ? side_stream() : nullptr;
+    if (!side) return csr_build(plan, lists, s);
+    NNUE_CUDA_TRY(cudaEventRecord(side->fork, s));
+    NNUE_CUDA_TRY(cudaStreamWaitEvent(side->stream, side->fork, 0));
+    const int rc = csr_build(plan, lists, side->stream);
+    // always join, also after a failed launch, so the caller's stream stays ordered
+    NNUE_CUDA_TRY(cudaEventRecord(side->join, side->stream));
+    join.pending = true;
+    join.event = side->join;
+    return rc;
+}
+
+int csr_join(CsrJoin& join, cudaStream_t s) {
+    if (join.pending) {
+        NNUE_CUDA_TRY(cudaStreamWaitEvent(s, join.event, 0));
+        join.pending = false;
+    }
     return NNUE_OK;
 }
 

@@ -29,7 +29,7 @@ __global__ void __launch_bounds__(kThreads)
     }
     const int32_t* list = idx + p * K;
     const int n = count_active(list, K, lane);
-    gather_sum<U, 16 / U>(weight, W4, N, list, n, col, ok, acc, lane, status);
+    gather_sum<U, 8 / U>(weight, W4, N, list, n, col, ok, acc, lane, status);
 #pragma unroll
     for (int u = 0; u < U; ++u)
         if (ok[u]) st_stream4(out + p * W4 + col[u], acc[u]);
@@ -149,7 +149,7 @@ extern "C" size_t nnue_ft_sparse_bwd_workspace_bytes(int64_t B, int32_t K, int64
     (void)mode;
     if (B < 0 || K < 0 || N < 0 || W <= 0) return 0;
     return align_up_((size_t)kColumnSumSlices * W * sizeof(float), 256) +
-           csr_workspace_bytes(B * (int64_t)K, N) + 256;
+           csr_workspace_bytes(B * (int64_t)K, N, W) + 256;
 }
 
 extern "C" int nnue_ft_sparse_bwd(const int32_t* idx, const float* grad_out, float* grad_weight,
@@ -199,6 +199,10 @@ extern "C" int nnue_ft_sparse_bwd(const int32_t* idx, const float* grad_out, flo
         return NNUE_OK;
     }
     const int32_t* lists[1] = {idx};
-    return csr_build_and_reduce(lists, 1, B, K, N, grad_out, W, grad_weight, ws,
-                                workspace_bytes - (size_t)(ws - static_cast<char*>(workspace)), s);
+    CsrPlan plan;
+    rc = csr_plan(plan, 1, B, K, N, W, ws, workspace_bytes - (size_t)(ws - static_cast<char*>(workspace)));
+    if (rc != NNUE_OK) return rc;
+    rc = csr_build(plan, lists, s);
+    if (rc != NNUE_OK) return rc;
+    return csr_reduce(plan, grad_out, W, grad_weight, s);
 }

@@ -2,16 +2,26 @@
 // sparse-linear forward, the fused double-FT forward and the segment-reduce
 // backward.  A warp owns C float4 column slots per lane (C*32 float4 = C*512
 // bytes of each row, every load a fully coalesced 512-byte warp request) and
-// adds the listed rows in list order, R rows (C*R independent 16-byte loads
-// per lane) in flight at a time.
+// adds the listed rows in list order.
+//
+// Two forms, chosen by measurement on B200:
+//   gather_sum            R rows (C*R independent 16-byte loads per lane) are
+//                         loaded, then added; fewest instructions per load.
+//                         Fastest for the forward kernels, which run at
+//                         4 CTAs per SM and are close to the L2 fabric limit.
+//   gather_sum_pipelined  two register buffers of R rows; the loads of batch
+//                         b+1 are issued before the adds of batch b and the ids
+//                         of the next 32 entries are fetched early.  Fastest
+//                         for the segment reduction, whose per-entry hook
+//                         (row boundaries) lengthens the add phase.
 #pragma once
 
 #include "common.cuh"
 
 namespace nnue {
 
-// list : n row ids (shared or global memory); every id must be >= 0.
-// rows >= n_rows are skipped and counted in `status`.
+// list : n row ids (shared or global memory).  Ids outside [0, n_rows) are
+// skipped and tallied in `status`.
 template <int C, int R>
 __device__ __forceinline__ void gather_sum(const float4* __restrict__ table, int64_t stride4,
                                            int64_t n_rows, const int32_t* list, int n,
@@ -47,6 +57,65 @@ __device__ __forceinline__ void gather_sum(const float4* __restrict__ table, int
                     for (int c = 0; c < C; ++c) acc[c] = f4_add(acc[c], v[t][c]);
                 }
             }
+        }
+    }
+}
+
+// pre(i) runs before entry i (0-based position in `list`) is added, in order;
+// the segment kernel uses it to close a row when i crosses a row boundary.
+// Bad ids are tallied only when `count_bad`.
+template <int C, int R, class Pre>
+__device__ __forceinline__ void gather_sum_pipelined(const float4* __restrict__ table,
+                                                     int64_t stride4, int64_t n_rows,
+                                                     const int32_t* list, int n,
+                                                     const int (&col)[C], const bool (&ok)[C],
+                                                     float4 (&acc)[C], int lane,
+                                                     unsigned long long* status, bool count_bad,
+                                                     Pre pre) {
+    int next_mine = (lane < min(32, n)) ? list[lane] : 0;
+    for (int k0 = 0; k0 < n; k0 += 32) {
+        const int m = min(32, n - k0);
+        int mine = next_mine;
+        if (k0 + 32 < n) next_mine = (lane < min(32, n - k0 - 32)) ? list[k0 + 32 + lane] : 0;
+        if ((unsigned)mine >= (unsigned long long)n_rows) {
+            if (lane < m && count_bad) note_bad_index(status);
+            mine = -1;
+        }
+        const int nb = (m + R - 1) / R;
+        float4 va[R][C], vb[R][C];
+
+        auto issue = [&](float4 (&v)[R][C], int b) {
+#pragma unroll
+            for (int t = 0; t < R; ++t) {
+                const int j = b * R + t;
+                const int r = __shfl_sync(kFullMask, mine, j & 31);
+                const bool live = (j < m) && (r >= 0);
+                const float4* row = table + (int64_t)(live ? r : 0) * stride4;
+#pragma unroll
+                for (int c = 0; c < C; ++c) v[t][c] = (live && ok[c]) ? ldg4(row + col[c]) : f4_zero();
+            }
+        };
+        auto consume = [&](float4 (&v)[R][C], int b) {
+#pragma unroll
+            for (int t = 0; t < R; ++t) {
+                const int j = b * R + t;
+                if (j < m) {  // warp-uniform
+                    const int r = __shfl_sync(kFullMask, mine, j & 31);
+                    pre(k0 + j);
+                    if (r >= 0) {
+#pragma unroll
+                        for (int c = 0; c < C; ++c) acc[c] = f4_add(acc[c], v[t][c]);
+                    }
+                }
+            }
+        };
+
+        issue(va, 0);
+        for (int b = 0; b < nb; b += 2) {
+            if (b + 1 < nb) issue(vb, b + 1);
+            consume(va, b);
+            if (b + 2 < nb) issue(va, b + 2);
+            if (b + 1 < nb) consume(vb, b + 1);
         }
     }
 }

@@ -1,0 +1,125 @@
+"""Forward / backward sweep of the fused double feature-transformer kernels.
+
+    python -m nnue_pytorch_b200.ft_sweep                       # the full sweep
+    python -m nnue_pytorch_b200.ft_sweep --l1 3072 --batch 16384 --active 0 \
+        --tune bwd_u=1 --tune seg_chunk=256                   # one point, with tuning knobs
+
+Shapes: HalfKAv2_hm^ as 22528 real + 704 factor rows (N = 23232, K = 64),
+L1 in {1024, 2048, 3072}, batch in {4096, 16384, 65536}, `active` real
+features per perspective fixed at 2, 8, 16 or 32 (0 = piece count ~ U[2,32]),
+fp32 weights ~ N(0, 0.01).  Each point prints one JSON line with the mean
+kernel time (CUDA events on the launching stream, L2 flushed between
+iterations unless --no-flush) and the algorithmic GB/s: every (position,
+active row) counts one full row, as in an embedding bag; bytes served by the
+L2 are therefore counted too and the figure can exceed the DRAM bandwidth.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import _launch, _lib, positions
+
+N_ROWS = positions.NUM_INPUTS_BASELINE
+K = positions.MAX_ACTIVE_BASELINE
+
+
+def _peak():
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    try:
+        with open(os.path.join(root, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:  # noqa: BLE001
+        return 6650.0, "fallback"
+
+
+def _time(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1.0)  # 512 MB read-modify-write evicts the 126 MB L2
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def run_point(l1: int, batch: int, active: int, mode: str, iters: int, warmup: int, flush: bool, dev):
+    P = 8
+    W = l1 + P
+    b = positions.generate_batch(batch, 0, layout="baseline", fixed_count=active if active else None)
+    rows_per_persp = 2.0 * (active if active else float(b.piece_count.mean()))
+    us, them, wi, bi = (torch.from_numpy(x).to(dev) for x in (b.us, b.them, b.white, b.black))
+    ps = torch.from_numpy((b.piece_count - 1) // 4).to(dev)
+    g = torch.Generator(device=dev).manual_seed(1)
+    w = torch.randn(N_ROWS, W, generator=g, device=dev) * 0.01
+    bias = torch.randn(W, generator=g, device=dev) * 0.01
+    gl0 = torch.randn(batch, l1, generator=g, device=dev)
+    gp = torch.randn(batch, 1, generator=g, device=dev)
+    fl = torch.zeros(128 * 1024 * 1024, device=dev) if flush else None
+    max_act = 255.0 / 256.0
+
+    saved = [None]
+
+    def fwd():
+        saved[0] = _launch.fused_forward(us, them, wi, bi, ps, w, bias, max_act, l1)[3]
+
+    def bwd():
+        _launch.fused_backward(us, them, wi, bi, ps, max_act, l1, N_ROWS, W, gl0, gp, gp, saved[0], mode)
+
+    t_f = _time(fwd, iters, warmup, fl)
+    t_b = _time(bwd, iters, warmup, fl)
+    _launch.device_status(dev)
+    common = batch * (2 * rows_per_persp * W * 4 + 2 * K * 4 + 24 + 3 * l1 * 4 + 8)
+    peak, kind = _peak()
+    out = {
+        "l1": l1, "batch": batch, "active_real_per_perspective": active or "U[2,32]", "rows_per_perspective": rows_per_persp,
+        "fwd_ms": t_f, "fwd_algorithmic_GBps": common / t_f / 1e6, "fwd_frac_of_hbm": common / t_f / 1e6 / peak,
+        "bwd_ms": t_b, "bwd_algorithmic_GBps": (common + N_ROWS * W * 4) / t_b / 1e6,
+        "bwd_frac_of_hbm": (common + N_ROWS * W * 4) / t_b / 1e6 / peak,
+        "bwd_mode": mode, "hbm_peak_GBps": peak, "peak_source": kind, "l2_flushed": bool(flush),
+    }
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--l1", type=int, nargs="*", default=[1024, 2048, 3072])
+    ap.add_argument("--batch", type=int, nargs="*", default=[4096, 16384, 65536])
+    ap.add_argument("--active", type=int, nargs="*", default=[2, 8, 16, 32])
+    ap.add_argument("--mode", default="auto", choices=["auto", "atomic", "segment"])
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--tune", action="append", default=[], help="key=value, passed to nnue_b200_tune")
+    a = ap.parse_args()
+    if not torch.cuda.is_available():
+        raise SystemExit("ft_sweep needs a CUDA device")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    _lib.load()
+    tuned = {}
+    for kv in a.tune:
+        k, v = kv.split("=")
+        _lib.tune(k, int(v))
+        tuned[k] = int(v)
+    for l1 in a.l1:
+        for batch in a.batch:
+            for act in a.active:
+                r = run_point(l1, batch, act, a.mode, a.iters, a.warmup, not a.no_flush, dev)
+                if tuned:
+                    r["tune"] = tuned
+                print(json.dumps(r), flush=True)
+                torch.cuda.empty_cache()
+
+
+if __name__ == "__main__":
+    main()

@@ -119,7 +119,9 @@ def test_eval_train_swap_and_state_dict_round_trip(dev):
     assert torch.equal(p.detach(), slow)
     opt.train()
     assert torch.equal(p.detach(), fast)
-    sd = opt.state_dict()
+    import copy
+
+    sd = copy.deepcopy(opt.state_dict())  # a checkpoint holds its own tensors
     p2 = torch.nn.Parameter(p.detach().clone())
     q2 = torch.nn.Parameter(q.detach().clone())
     opt2 = _make([p2, q2], 0.0)
