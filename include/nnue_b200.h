@@ -102,7 +102,12 @@ int nnue_ft_sparse_bwd(const int32_t* idx, const float* grad_out,
  * c = clamp(x, 0, max_act); l0 = [c0*c1, c2*c3];
  * wpsqt = bias[L1+p] + sum weight[white_idx][L1+p], bpsqt likewise,
  * p = psqt_idx[b].  `saved` [B, 4, L1/2] receives the PRE-clamp x, which is
- * what nnue_ft_fused_bwd consumes.
+ * what nnue_ft_fused_bwd consumes.  Optional epilogue, fused because it would
+ * otherwise be several dense passes over l0: with act_quant_scale > 0,
+ * l0 = floor(l0 * act_quant_scale + act_quant_eps) / act_quant_scale (the
+ * reference's fake_quantize_ft_act, model/quantize.py:36-45, straight-through
+ * in the backward), then l0 *= out_scale (its l0_correction_factor,
+ * composed_feature_transformer.py:143-149).  Pass 0, 0, 1 for the bare op.
  * Replaces `fused_double_ft_forward`,
  * model/modules/feature_transformer/fused_ft_kernel.py:27-117, launched from
  * fused_ft_functions.py:47-75; numerics follow the torch composition in
@@ -111,6 +116,7 @@ int nnue_ft_fused_fwd(const float* us, const float* them,
                       const int32_t* white_idx, const int32_t* black_idx,
                       const int64_t* psqt_idx,
                       const float* weight, const float* bias, float max_act,
+                      float act_quant_scale, float act_quant_eps, float out_scale,
                       float* l0, float* wpsqt, float* bpsqt, float* saved,
                       int64_t B, int32_t K, int64_t N, int32_t L1, int32_t P,
                       void* stream);
@@ -126,13 +132,30 @@ size_t nnue_ft_fused_bwd_workspace_bytes(int64_t B, int32_t K, int64_t N,
                                          int32_t L1, int32_t P, int32_t mode);
 int nnue_ft_fused_bwd(const float* us, const float* them,
                       const int32_t* white_idx, const int32_t* black_idx,
-                      const int64_t* psqt_idx, float max_act,
+                      const int64_t* psqt_idx, float max_act, float out_scale,
                       const float* grad_l0, const float* grad_wpsqt,
                       const float* grad_bpsqt, const float* saved,
                       float* grad_weight, float* grad_bias,
                       int64_t B, int32_t K, int64_t N, int32_t L1, int32_t P,
                       void* workspace, size_t workspace_bytes, int32_t mode,
                       void* stream);
+
+/* ---- A10/A11: table preparation --------------------------------------
+ * out[r, c] = fq(weight[r, c] + virtual_weight[r % n_virtual, c]) in one pass,
+ * fq(x) = round_half_even(x * s) / s with s = scale_main for c < L1 and
+ * scale_psqt for the P PSQT columns; virtual_weight may be NULL (no folding),
+ * scale_main <= 0 switches the quantization off.  Replaces the dense passes of
+ * model/modules/features/halfka_v2_hm.py:68-69 (weight + virtual.repeat) and
+ * model/modules/feature_transformer/composed_feature_transformer.py:61-76
+ * (two fake-quantizations and a concat).  The gradient of `out` is the
+ * gradient of `weight` unchanged (straight-through); the factor rows receive
+ * nnue_ft_virtual_grad: out[v, c] = sum_b grad[b * n_virtual + v, c]. */
+int nnue_ft_prepare_table(const float* weight, const float* virtual_weight,
+                          float* out, int64_t N, int64_t n_virtual,
+                          int32_t L1, int32_t P, float scale_main,
+                          float scale_psqt, void* stream);
+int nnue_ft_virtual_grad(const float* grad, float* out, int64_t N,
+                         int64_t n_virtual, int32_t W, void* stream);
 
 /* ---- A12: RangerLite (Adam + positive-negative momentum + lookahead) ---
  * One fused pass over a parameter tensor viewed as [rows, width]:

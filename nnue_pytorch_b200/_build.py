@@ -23,6 +23,7 @@ SOURCES = [
     "ft_sparse.cu",
     "ft_fused.cu",
     "ft_segment.cu",
+    "ft_table.cu",
     "ranger_lite.cu",
     "quant_eval.cu",
 ]

@@ -144,7 +144,8 @@ def sparse_linear_backward(
 
 
 # --------------------------------------------------------------------------
-def fused_forward(us, them, white_indices, black_indices, psqt_indices, weight, bias, max_ft_activation, l1_size):
+def fused_forward(us, them, white_indices, black_indices, psqt_indices, weight, bias, max_ft_activation, l1_size,
+                  act_quant_scale: float = 0.0, act_quant_eps: float = 0.0, out_scale: float = 1.0):
     assert l1_size % 2 == 0
     dev = _require_cuda(us, them, white_indices, black_indices, psqt_indices, weight, bias)
     assert us.dtype == torch.float32 and them.dtype == torch.float32
@@ -171,6 +172,7 @@ def fused_forward(us, them, white_indices, black_indices, psqt_indices, weight, 
         st = _lib.load().nnue_ft_fused_fwd(
             _ptr(us), _ptr(them), _ptr(white_indices), _ptr(black_indices), _ptr(psqt_indices),
             _ptr(weight), _ptr(bias), float(max_ft_activation),
+            float(act_quant_scale), float(act_quant_eps), float(out_scale),
             _ptr(l0), _ptr(wpsqt), _ptr(bpsqt), _ptr(saved), B, K, N, l1_size, P, _stream(dev),
         )
     _lib.check(st, "nnue_ft_fused_fwd")
@@ -179,7 +181,7 @@ def fused_forward(us, them, white_indices, black_indices, psqt_indices, weight, 
 
 def fused_backward(
     us, them, white_indices, black_indices, psqt_indices, max_ft_activation, l1_size, num_inputs, num_outputs,
-    grad_l0, grad_wpsqt, grad_bpsqt, saved, mode: str | None = None,
+    grad_l0, grad_wpsqt, grad_bpsqt, saved, mode: str | None = None, out_scale: float = 1.0,
 ):
     dev = _require_cuda(us, grad_l0, grad_wpsqt, grad_bpsqt, saved)
     grad_l0 = grad_l0.contiguous()
@@ -195,7 +197,7 @@ def fused_backward(
     with torch.cuda.device(dev), _span("fused_bwd", dev):
         st = lib.nnue_ft_fused_bwd(
             _ptr(us), _ptr(them), _ptr(white_indices), _ptr(black_indices), _ptr(psqt_indices),
-            float(max_ft_activation), _ptr(grad_l0), _ptr(grad_wpsqt), _ptr(grad_bpsqt), _ptr(saved),
+            float(max_ft_activation), float(out_scale), _ptr(grad_l0), _ptr(grad_wpsqt), _ptr(grad_bpsqt), _ptr(saved),
             _ptr(grad_w), _ptr(grad_b), B, K, num_inputs, l1_size, P, _ptr(ws), ws.numel(), m, _stream(dev),
         )
     _lib.check(st, "nnue_ft_fused_bwd")
@@ -203,6 +205,37 @@ def fused_backward(
 
 
 # --------------------------------------------------------------------------
+def prepare_table(weight, virtual_weight, l1_size: int, scale_main: float, scale_psqt: float) -> torch.Tensor:
+    """fq(weight + virtual_weight.repeat(N // n_virtual, 1)) in one pass (see nnue_ft_prepare_table)."""
+    dev = _require_cuda(weight) if virtual_weight is None else _require_cuda(weight, virtual_weight)
+    assert weight.dtype == torch.float32 and weight.dim() == 2 and weight.is_contiguous()
+    N, W = weight.shape
+    nv = 0
+    if virtual_weight is not None:
+        assert virtual_weight.dtype == torch.float32 and virtual_weight.is_contiguous()
+        assert virtual_weight.shape[1] == W and N % virtual_weight.shape[0] == 0
+        nv = virtual_weight.shape[0]
+    out = torch.empty_like(weight)
+    with torch.cuda.device(dev), _span("prepare_table", dev):
+        st = _lib.load().nnue_ft_prepare_table(
+            _ptr(weight), _ptr(virtual_weight), _ptr(out), N, nv, l1_size, W - l1_size,
+            float(scale_main), float(scale_psqt), _stream(dev),
+        )
+    _lib.check(st, "nnue_ft_prepare_table")
+    return out
+
+
+def virtual_grad(grad: torch.Tensor, n_virtual: int) -> torch.Tensor:
+    dev = _require_cuda(grad)
+    grad = grad.contiguous()
+    N, W = grad.shape
+    out = torch.empty(n_virtual, W, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev), _span("virtual_grad", dev):
+        st = _lib.load().nnue_ft_virtual_grad(_ptr(grad), _ptr(out), N, n_virtual, W, _stream(dev))
+    _lib.check(st, "nnue_ft_virtual_grad")
+    return out
+
+
 def device_status(device: torch.device | None = None) -> None:
     """Synchronise and raise if any kernel since the last call skipped an
     out-of-range index or gave up on a bounded wait."""

@@ -77,13 +77,17 @@ PROTOTYPES = {
     "nnue_ft_sparse_bwd": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _I64, _I32, _P, _SZ, _I32, _P]),
     "nnue_ft_fused_fwd": (
         C.c_int,
-        [_P, _P, _P, _P, _P, _P, _P, C.c_float, _P, _P, _P, _P, _I64, _I32, _I64, _I32, _I32, _P],
+        [_P, _P, _P, _P, _P, _P, _P, C.c_float, C.c_float, C.c_float, C.c_float, _P, _P, _P, _P,
+         _I64, _I32, _I64, _I32, _I32, _P],
     ),
     "nnue_ft_fused_bwd_workspace_bytes": (_SZ, [_I64, _I32, _I64, _I32, _I32, _I32]),
     "nnue_ft_fused_bwd": (
         C.c_int,
-        [_P, _P, _P, _P, _P, C.c_float, _P, _P, _P, _P, _P, _P, _I64, _I32, _I64, _I32, _I32, _P, _SZ, _I32, _P],
+        [_P, _P, _P, _P, _P, C.c_float, C.c_float, _P, _P, _P, _P, _P, _P, _I64, _I32, _I64, _I32, _I32,
+         _P, _SZ, _I32, _P],
     ),
+    "nnue_ft_prepare_table": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, C.c_float, C.c_float, _P]),
+    "nnue_ft_virtual_grad": (C.c_int, [_P, _P, _I64, _I64, _I32, _P]),
     "nnue_rangerlite_update": (
         C.c_int,
         [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, C.POINTER(RangerHParams), _P],

@@ -15,6 +15,14 @@ import torch
 from torch import nn
 
 from .double_ft_functions import double_feature_transform
+from .fused_ft_functions import FusedDoubleFtFunction, PrepareTableFunction
+
+_FAKE_QUANTIZE_EPS = 1e-5  # model/quantize.py:10 of the reference
+
+
+def _fusable_feature(f) -> bool:
+    """Features whose merged table is `weight` or `weight + virtual_weight.repeat(k, 1)`."""
+    return getattr(f, "FUSED_TABLE", False) or type(f).__name__ == "HalfKav2Hm"
 
 
 class ComposedFeatureTransformer(nn.Module):
@@ -52,11 +60,27 @@ class ComposedFeatureTransformer(nn.Module):
     def merged_weight_and_bias(self, fake_quantize_weights: bool = False):
         """Table [NUM_INPUTS, l1+psqt] and bias the operator sees this step.
         The PSQT part of the bias is replaced by zeros (it never trains)."""
+        b = self.bias[: self.l1_size]
+        q = self.quantization
+        if self.bias.is_cuda and all(_fusable_feature(f) for f in self.features):
+            # one kernel per feature block: fold the factor rows and quantize in a single pass
+            sm = q.weight_scales_dict["ft_weight"] if fake_quantize_weights else 0.0
+            sp = q.weight_scales_dict["ft_psqt_weight"] if fake_quantize_weights else 0.0
+            tables = []
+            for f in self.features:
+                virt = getattr(f, "virtual_weight", None)
+                if virt is None and not fake_quantize_weights:
+                    tables.append(f.weight)
+                else:
+                    tables.append(PrepareTableFunction.apply(f.weight, virt, self.l1_size, sm, sp))
+            merged = tables[0] if len(tables) == 1 else torch.cat(tables, dim=0)
+            if fake_quantize_weights:
+                b = q.fake_quantize_weights(b, "ft_bias")
+            bias = torch.cat([b, torch.zeros_like(self.bias[self.l1_size :], dtype=b.dtype)], dim=0)
+            return merged, bias
         tables = [f.merged_weight() for f in self.features]
         merged = tables[0] if len(tables) == 1 else torch.cat(tables, dim=0)
-        b = self.bias[: self.l1_size]
         if fake_quantize_weights:
-            q = self.quantization
             merged = torch.cat(
                 [
                     q.fake_quantize_weights(merged[:, : self.l1_size], "ft_weight"),
@@ -111,6 +135,14 @@ class ComposedFeatureTransformer(nn.Module):
         backend: str = "auto",
     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
         merged, bias = self.merged_weight_and_bias(fake_quantize_weights)
+        if backend in ("auto", "fused") and merged.is_cuda:
+            # activation fake quantization and the correction factor ride in the kernel epilogue
+            q = self.quantization
+            return FusedDoubleFtFunction.apply(
+                us, them, white_indices, black_indices, psqt_indices, merged, bias, q.max_ft_activation,
+                self.l1_size, q.config.hidden_quantized_one if fake_quantize_acts else 0.0, _FAKE_QUANTIZE_EPS,
+                q.l0_correction_factor,
+            )
         l0, wpsqt, bpsqt = double_feature_transform(
             us, them, white_indices, black_indices, psqt_indices, merged, bias,
             self.quantization.max_ft_activation, self.l1_size, backend,

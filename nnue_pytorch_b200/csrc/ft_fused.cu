@@ -10,10 +10,33 @@
 // the SLOW grid dimension: all positions of tile 0 run before tile 1, so the
 // slice of the weight table a tile touches (N * U KiB) stays resident in the
 // 126 MB L2 while every position re-reads it.
+#include <math.h>
+
 #include "gather.cuh"
 #include "segment.cuh"
 
 namespace nnue {
+
+// Activation constants of one call: clamp bound, optional fake quantization of
+// the pairwise product (floor(x * act_scale + act_eps) / act_scale, the
+// reference's `fake_quantize_ft_act`, model/quantize.py:36-45) and the
+// correction factor applied after it (composed_feature_transformer.py:143-149).
+struct FtAct {
+    float max_act;
+    float act_scale;  // 0 = no fake quantization
+    float act_eps;
+    float out_scale;  // 1 = none
+    float act_inv;    // 1 / act_scale when that is exact (power of two), else 0
+};
+
+__device__ __forceinline__ float finish_l0(float x, const FtAct& a) {
+    if (a.act_scale > 0.f) {
+        const float q = floorf(__fadd_rn(__fmul_rn(x, a.act_scale), a.act_eps));
+        x = a.act_inv != 0.f ? __fmul_rn(q, a.act_inv) : __fdiv_rn(q, a.act_scale);
+    }
+    if (a.out_scale != 1.f) x = __fmul_rn(x, a.out_scale);
+    return x;
+}
 
 // ---------------------------------------------------------------------------
 // index staging: the K-entry lists of the 8 positions of a CTA are contiguous
@@ -89,7 +112,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
     k_fused_fwd(const float* __restrict__ us, const float* __restrict__ them,
                 const int32_t* __restrict__ wi, const int32_t* __restrict__ bi,
                 const int64_t* __restrict__ psqt_idx, const float* __restrict__ weight,
-                const float* __restrict__ bias, float max_act, float* __restrict__ l0,
+                const float* __restrict__ bias, FtAct act, float* __restrict__ l0,
                 float* __restrict__ wpsqt, float* __restrict__ bpsqt, float* __restrict__ saved,
                 int64_t B, int K, int64_t N, int L1, int P, int n_pos_groups, int want_stage,
                 unsigned long long* status) {
@@ -149,11 +172,11 @@ __global__ void __launch_bounds__(kThreads, MINB)
         st_stream4(sv + 1 * h4 + c, x1);
         st_stream4(sv + 2 * h4 + c, x2);
         st_stream4(sv + 3 * h4 + c, x3);
+        const float max_act = act.max_act;
         auto cl = [max_act](float x) { return fminf(fmaxf(x, 0.f), max_act); };
-        const float4 a = make_float4(__fmul_rn(cl(x0.x), cl(x1.x)), __fmul_rn(cl(x0.y), cl(x1.y)),
-                                     __fmul_rn(cl(x0.z), cl(x1.z)), __fmul_rn(cl(x0.w), cl(x1.w)));
-        const float4 b = make_float4(__fmul_rn(cl(x2.x), cl(x3.x)), __fmul_rn(cl(x2.y), cl(x3.y)),
-                                     __fmul_rn(cl(x2.z), cl(x3.z)), __fmul_rn(cl(x2.w), cl(x3.w)));
+        auto pr = [&](float p, float q) { return finish_l0(__fmul_rn(cl(p), cl(q)), act); };
+        const float4 a = make_float4(pr(x0.x, x1.x), pr(x0.y, x1.y), pr(x0.z, x1.z), pr(x0.w, x1.w));
+        const float4 b = make_float4(pr(x2.x, x3.x), pr(x2.y, x3.y), pr(x2.z, x3.z), pr(x2.w, x3.w));
         st_stream4(l0p + c, a);
         st_stream4(l0p + h4 + c, b);
     }
@@ -184,7 +207,7 @@ __global__ void k_fused_fwd_scalar(const float* __restrict__ us, const float* __
                                    const int32_t* __restrict__ wi, const int32_t* __restrict__ bi,
                                    const int64_t* __restrict__ psqt_idx,
                                    const float* __restrict__ weight, const float* __restrict__ bias,
-                                   float max_act, float* __restrict__ l0, float* __restrict__ wpsqt,
+                                   FtAct act, float* __restrict__ l0, float* __restrict__ wpsqt,
                                    float* __restrict__ bpsqt, float* __restrict__ saved, int64_t B,
                                    int K, int64_t N, int L1, int P, unsigned long long* status) {
     const int64_t p = blockIdx.x;
@@ -213,9 +236,10 @@ __global__ void k_fused_fwd_scalar(const float* __restrict__ us, const float* __
         const float x2 = mix(u_, b0, t_, w0), x3 = mix(u_, b1, t_, w1);
         float* sv = saved + p * 2 * (int64_t)L1;
         sv[i] = x0; sv[h + i] = x1; sv[2 * h + i] = x2; sv[3 * h + i] = x3;
+        const float max_act = act.max_act;
         auto cl = [max_act](float x) { return fminf(fmaxf(x, 0.f), max_act); };
-        l0[p * L1 + i] = __fmul_rn(cl(x0), cl(x1));
-        l0[p * L1 + h + i] = __fmul_rn(cl(x2), cl(x3));
+        l0[p * L1 + i] = finish_l0(__fmul_rn(cl(x0), cl(x1)), act);
+        l0[p * L1 + h + i] = finish_l0(__fmul_rn(cl(x2), cl(x3)), act);
     }
     if (threadIdx.x == 0) {
         const int64_t pi = psqt_idx[p];
@@ -267,11 +291,12 @@ __device__ __forceinline__ float4 f4_mask(float4 g, float4 x, float m) {
 
 __global__ void __launch_bounds__(kThreads)
     k_bwd_prologue(const float* __restrict__ us, const float* __restrict__ them,
-                   const int64_t* __restrict__ psqt_idx, float max_act,
+                   const int64_t* __restrict__ psqt_idx, FtAct act,
                    const float* __restrict__ grad_l0, const float* __restrict__ grad_wpsqt,
                    const float* __restrict__ grad_bpsqt, const float* __restrict__ saved,
                    float* __restrict__ G, float* __restrict__ bias_part, int64_t B, int L1, int P,
                    int pb, int n_col_chunks) {
+    const float max_act = act.max_act;
     const int chunk = blockIdx.x % n_col_chunks;
     const int64_t blk = blockIdx.x / n_col_chunks;
     const int64_t p_beg = blk * pb;
@@ -290,7 +315,12 @@ __global__ void __launch_bounds__(kThreads)
             const float4* gl = reinterpret_cast<const float4*>(grad_l0 + p * (int64_t)L1);
             const float4 x0 = __ldcs(sv + c), x1 = __ldcs(sv + h4 + c);
             const float4 x2 = __ldcs(sv + 2 * h4 + c), x3 = __ldcs(sv + 3 * h4 + c);
-            const float4 ga = __ldcs(gl + c), gb = __ldcs(gl + h4 + c);
+            float4 ga = __ldcs(gl + c), gb = __ldcs(gl + h4 + c);
+            if (act.out_scale != 1.f) {  // gradient of `l0 * out_scale`; the fake quantization is straight-through
+                const float4 k = make_float4(act.out_scale, act.out_scale, act.out_scale, act.out_scale);
+                ga = f4_mul(ga, k);
+                gb = f4_mul(gb, k);
+            }
             const float4 d0 = f4_mask(f4_mul(ga, f4_clamp(x1, max_act)), x0, max_act);
             const float4 d1 = f4_mask(f4_mul(ga, f4_clamp(x0, max_act)), x1, max_act);
             const float4 d2 = f4_mask(f4_mul(gb, f4_clamp(x3, max_act)), x2, max_act);
@@ -336,12 +366,13 @@ __global__ void __launch_bounds__(kThreads)
 
 // Scalar prologue for unaligned shapes: same outputs, one thread per column.
 __global__ void k_bwd_prologue_scalar(const float* __restrict__ us, const float* __restrict__ them,
-                                      const int64_t* __restrict__ psqt_idx, float max_act,
+                                      const int64_t* __restrict__ psqt_idx, FtAct act,
                                       const float* __restrict__ grad_l0,
                                       const float* __restrict__ grad_wpsqt,
                                       const float* __restrict__ grad_bpsqt,
                                       const float* __restrict__ saved, float* __restrict__ G,
                                       int64_t B, int L1, int P) {
+    const float max_act = act.max_act;
     const int64_t p = blockIdx.x;
     if (p >= B) return;
     const int h = L1 >> 1, W = L1 + P;
@@ -354,7 +385,8 @@ __global__ void k_bwd_prologue_scalar(const float* __restrict__ us, const float*
     auto in = [max_act](float x) { return x >= 0.f && x <= max_act; };
     for (int i = threadIdx.x; i < h; i += blockDim.x) {
         const float x0 = sv[i], x1 = sv[h + i], x2 = sv[2 * h + i], x3 = sv[3 * h + i];
-        const float ga = gl[i], gb = gl[h + i];
+        float ga = gl[i], gb = gl[h + i];
+        if (act.out_scale != 1.f) { ga = __fmul_rn(ga, act.out_scale); gb = __fmul_rn(gb, act.out_scale); }
         const float d0 = in(x0) ? __fmul_rn(ga, cl(x1)) : 0.f;
         const float d1 = in(x1) ? __fmul_rn(ga, cl(x0)) : 0.f;
         const float d2 = in(x2) ? __fmul_rn(gb, cl(x3)) : 0.f;
@@ -382,12 +414,13 @@ template <int U>
 __global__ void __launch_bounds__(kThreads)
     k_fused_bwd_atomic(const float* __restrict__ us, const float* __restrict__ them,
                        const int32_t* __restrict__ wi, const int32_t* __restrict__ bi,
-                       const int64_t* __restrict__ psqt_idx, float max_act,
+                       const int64_t* __restrict__ psqt_idx, FtAct act,
                        const float* __restrict__ grad_l0, const float* __restrict__ grad_wpsqt,
                        const float* __restrict__ grad_bpsqt, const float* __restrict__ saved,
                        float* __restrict__ grad_weight, float* __restrict__ grad_bias, int64_t B,
                        int K, int64_t N, int L1, int P, int n_pos_groups, int pos_per_cta,
                        unsigned long long* status) {
+    const float max_act = act.max_act;
     __shared__ float4 s_bias[kWarpsPerCta][2 * U][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x / n_pos_groups;
@@ -420,7 +453,12 @@ __global__ void __launch_bounds__(kThreads)
                 const int c = col[u];
                 const float4 x0 = __ldcs(sv + c), x1 = __ldcs(sv + h4 + c);
                 const float4 x2 = __ldcs(sv + 2 * h4 + c), x3 = __ldcs(sv + 3 * h4 + c);
-                const float4 ga = __ldcs(gl + c), gbv = __ldcs(gl + h4 + c);
+                float4 ga = __ldcs(gl + c), gbv = __ldcs(gl + h4 + c);
+                if (act.out_scale != 1.f) {
+                    const float4 k = make_float4(act.out_scale, act.out_scale, act.out_scale, act.out_scale);
+                    ga = f4_mul(ga, k);
+                    gbv = f4_mul(gbv, k);
+                }
                 const float4 d0 = f4_mask(f4_mul(ga, f4_clamp(x1, max_act)), x0, max_act);
                 const float4 d1 = f4_mask(f4_mul(ga, f4_clamp(x0, max_act)), x1, max_act);
                 const float4 d2 = f4_mask(f4_mul(gbv, f4_clamp(x3, max_act)), x2, max_act);
@@ -502,9 +540,13 @@ static bool fused_vec_ok(int L1, int P, const void* a, const void* b, const void
 
 extern "C" int nnue_ft_fused_fwd(const float* us, const float* them, const int32_t* white_idx,
                                  const int32_t* black_idx, const int64_t* psqt_idx,
-                                 const float* weight, const float* bias, float max_act, float* l0,
-                                 float* wpsqt, float* bpsqt, float* saved, int64_t B, int32_t K,
-                                 int64_t N, int32_t L1, int32_t P, void* stream) {
+                                 const float* weight, const float* bias, float max_act,
+                                 float act_quant_scale, float act_quant_eps, float out_scale,
+                                 float* l0, float* wpsqt, float* bpsqt, float* saved, int64_t B,
+                                 int32_t K, int64_t N, int32_t L1, int32_t P, void* stream) {
+    int sc_exp = 0;
+    const bool pow2 = act_quant_scale > 0.f && frexpf(act_quant_scale, &sc_exp) == 0.5f;
+    const FtAct act{max_act, act_quant_scale, act_quant_eps, out_scale, pow2 ? 1.0f / act_quant_scale : 0.f};
     NNUE_REQUIRE(B >= 0 && K >= 0 && N >= 0 && L1 > 0 && P >= 0, NNUE_ERR_ARG,
                  "nnue_ft_fused_fwd: negative size (B=%lld K=%d N=%lld L1=%d P=%d)", (long long)B, K,
                  (long long)N, L1, P);
@@ -522,7 +564,7 @@ extern "C" int nnue_ft_fused_fwd(const float* us, const float* them, const int32
         const int threads = 128;
         NNUE_REQUIRE(B <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "nnue_ft_fused_fwd: batch too large");
         k_fused_fwd_scalar<<<(unsigned)B, threads, 0, s>>>(us, them, white_idx, black_idx, psqt_idx,
-                                                          weight, bias, max_act, l0, wpsqt, bpsqt,
+                                                          weight, bias, act, l0, wpsqt, bpsqt,
                                                           saved, B, K, N, L1, P, status);
         NNUE_CUDA_TRY(cudaGetLastError());
         note_launches(1);
@@ -543,7 +585,7 @@ extern "C" int nnue_ft_fused_fwd(const float* us, const float* them, const int32
     const unsigned grid = (unsigned)(groups * tiles);
 #define LAUNCH_FWD(UU, RR, MB)                                                                  \
     k_fused_fwd<UU, RR, MB><<<grid, kThreads, stage ? smem : 0, s>>>(                           \
-        us, them, white_idx, black_idx, psqt_idx, weight, bias, max_act, l0, wpsqt, bpsqt, saved, B, \
+        us, them, white_idx, black_idx, psqt_idx, weight, bias, act, l0, wpsqt, bpsqt, saved, B, \
         K, N, L1, P, (int)groups, stage, status)
     // variant = rows in flight per warp (R) and CTAs per SM the register budget must allow
     const int v = tuning().fwd_variant;
@@ -588,11 +630,12 @@ extern "C" size_t nnue_ft_fused_bwd_workspace_bytes(int64_t B, int32_t K, int64_
 
 extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32_t* white_idx,
                                  const int32_t* black_idx, const int64_t* psqt_idx, float max_act,
-                                 const float* grad_l0, const float* grad_wpsqt,
+                                 float out_scale, const float* grad_l0, const float* grad_wpsqt,
                                  const float* grad_bpsqt, const float* saved, float* grad_weight,
                                  float* grad_bias, int64_t B, int32_t K, int64_t N, int32_t L1,
                                  int32_t P, void* workspace, size_t workspace_bytes, int32_t mode,
                                  void* stream) {
+    const FtAct act{max_act, 0.f, 0.f, out_scale, 0.f};
     NNUE_REQUIRE(B >= 0 && K >= 0 && N >= 0 && L1 > 0 && P >= 0, NNUE_ERR_ARG,
                  "nnue_ft_fused_bwd: negative size");
     NNUE_REQUIRE(L1 % 2 == 0, NNUE_ERR_ARG, "nnue_ft_fused_bwd: l1_size must be even, got %d", L1);
@@ -635,12 +678,12 @@ extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32
         const unsigned grid = (unsigned)(groups * tiles);
         if (U == 1)
             k_fused_bwd_atomic<1><<<grid, kThreads, 0, s>>>(us, them, white_idx, black_idx, psqt_idx,
-                                                           max_act, grad_l0, grad_wpsqt, grad_bpsqt,
+                                                           act, grad_l0, grad_wpsqt, grad_bpsqt,
                                                            saved, grad_weight, grad_bias, B, K, N, L1,
                                                            P, (int)groups, ppc, status);
         else
             k_fused_bwd_atomic<2><<<grid, kThreads, 0, s>>>(us, them, white_idx, black_idx, psqt_idx,
-                                                           max_act, grad_l0, grad_wpsqt, grad_bpsqt,
+                                                           act, grad_l0, grad_wpsqt, grad_bpsqt,
                                                            saved, grad_weight, grad_bias, B, K, N, L1,
                                                            P, (int)groups, ppc, status);
         NNUE_CUDA_TRY(cudaGetLastError());
@@ -676,12 +719,12 @@ extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32
             const int cols4 = L1 / 8 + P / 4;
             const int chunks = (cols4 + kThreads - 1) / kThreads;
             k_bwd_prologue<<<(unsigned)(nblk * chunks), kThreads, 0, s>>>(
-                us, them, psqt_idx, max_act, grad_l0, grad_wpsqt, grad_bpsqt, saved, G, bias_part, B,
+                us, them, psqt_idx, act, grad_l0, grad_wpsqt, grad_bpsqt, saved, G, bias_part, B,
                 L1, P, pb, chunks);
             part_rows = nblk;
             part_src = bias_part;
         } else {
-            k_bwd_prologue_scalar<<<(unsigned)B, 128, 0, s>>>(us, them, psqt_idx, max_act, grad_l0,
+            k_bwd_prologue_scalar<<<(unsigned)B, 128, 0, s>>>(us, them, psqt_idx, act, grad_l0,
                                                              grad_wpsqt, grad_bpsqt, saved, G, B, L1,
                                                              P);
             part_rows = 2 * B;  // bias = column sum of G itself

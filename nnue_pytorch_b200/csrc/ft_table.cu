@@ -1,0 +1,134 @@
+// One-pass preparation of the table the feature-transformer kernels read:
+// fold the factor ("virtual") rows into the real rows and fake-quantize, and
+// the matching backward for the factor rows.  Replaces the chain of dense
+// elementwise passes the reference runs every step
+// (model/modules/features/halfka_v2_hm.py:68-69 `weight + virtual.repeat(32, 1)`,
+// model/modules/feature_transformer/composed_feature_transformer.py:61-76 with
+// model/quantize.py:47-56: round(x * scale) / scale, two scales, a concat).
+#include <algorithm>
+
+#include "common.cuh"
+
+namespace nnue {
+
+__device__ __forceinline__ float fq1(float x, float scale) {
+    return __fdiv_rn(rintf(__fmul_rn(x, scale)), scale);  // rintf: half to even, like torch.round
+}
+
+// out[r, c] = fq(weight[r, c] + virtual[r % n_virtual, c]); thread = float4.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+    k_prepare_table(const float* __restrict__ weight, const float* __restrict__ virt,
+                    float* __restrict__ out, int64_t N, int64_t n_virtual, int W, int L1,
+                    float scale_main, float scale_psqt) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (VEC) {
+        const int W4 = W >> 2;
+        const int64_t n4 = N * W4;
+        const float4* w4 = reinterpret_cast<const float4*>(weight);
+        const float4* v4 = reinterpret_cast<const float4*>(virt);
+        float4* o4 = reinterpret_cast<float4*>(out);
+        for (int64_t i = t0; i < n4; i += stride) {
+            const int64_t r = i / W4;
+            const int c4 = (int)(i - r * W4);
+            float4 x = __ldcs(w4 + i);
+            if (virt) x = f4_add(x, __ldg(v4 + (r % n_virtual) * W4 + c4));
+            if (scale_main > 0.f) {
+                // a float4 never straddles the L1 | PSQT border (L1 % 4 == 0)
+                const float s = (4 * c4 < L1) ? scale_main : scale_psqt;
+                x = make_float4(fq1(x.x, s), fq1(x.y, s), fq1(x.z, s), fq1(x.w, s));
+            }
+            o4[i] = x;
+        }
+    } else {
+        const int64_t n = N * W;
+        for (int64_t i = t0; i < n; i += stride) {
+            const int64_t r = i / W;
+            const int c = (int)(i - r * W);
+            float x = weight[i];
+            if (virt) x = __fadd_rn(x, virt[(r % n_virtual) * W + c]);
+            if (scale_main > 0.f) x = fq1(x, c < L1 ? scale_main : scale_psqt);
+            out[i] = x;
+        }
+    }
+}
+
+// out[v, c] = sum over b of grad[b * n_virtual + v, c], b ascending.
+template <bool VEC>
+__global__ void __launch_bounds__(kThreads)
+    k_virtual_grad(const float* __restrict__ grad, float* __restrict__ out, int64_t repeats,
+                   int64_t n_virtual, int W) {
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (VEC) {
+        const int64_t per = n_virtual * (W >> 2);
+        const float4* g4 = reinterpret_cast<const float4*>(grad);
+        float4* o4 = reinterpret_cast<float4*>(out);
+        for (int64_t i = t0; i < per; i += stride) {
+            float4 s = __ldg(g4 + i);
+            for (int64_t b = 1; b < repeats; ++b) s = f4_add(s, __ldg(g4 + b * per + i));
+            o4[i] = s;
+        }
+    } else {
+        const int64_t per = n_virtual * W;
+        for (int64_t i = t0; i < per; i += stride) {
+            float s = grad[i];
+            for (int64_t b = 1; b < repeats; ++b) s = __fadd_rn(s, grad[b * per + i]);
+            out[i] = s;
+        }
+    }
+}
+
+}  // namespace nnue
+
+using namespace nnue;
+
+extern "C" int nnue_ft_prepare_table(const float* weight, const float* virtual_weight, float* out,
+                                     int64_t N, int64_t n_virtual, int32_t L1, int32_t P,
+                                     float scale_main, float scale_psqt, void* stream) {
+    NNUE_REQUIRE(N >= 0 && L1 > 0 && P >= 0 && n_virtual >= 0, NNUE_ERR_ARG,
+                 "nnue_ft_prepare_table: bad size");
+    if (N == 0) return NNUE_OK;
+    NNUE_REQUIRE(weight && out, NNUE_ERR_ARG, "nnue_ft_prepare_table: null pointer");
+    NNUE_REQUIRE(!virtual_weight || (n_virtual > 0 && N % n_virtual == 0), NNUE_ERR_ARG,
+                 "nnue_ft_prepare_table: N (%lld) is not a multiple of the factor rows (%lld)",
+                 (long long)N, (long long)n_virtual);
+    NNUE_REQUIRE(scale_main <= 0.f || scale_psqt > 0.f, NNUE_ERR_ARG,
+                 "nnue_ft_prepare_table: both scales must be positive when quantizing");
+    const int W = L1 + P;
+    const bool vec = (W % 4 == 0) && (L1 % 4 == 0) && aligned16(weight) && aligned16(out) &&
+                     (!virtual_weight || aligned16(virtual_weight));
+    const int64_t work = vec ? N * (W / 4) : N * (int64_t)W;
+    const unsigned grid = (unsigned)std::min<int64_t>((work + kThreads - 1) / kThreads, (int64_t)sm_count() * 16);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (vec)
+        k_prepare_table<true><<<grid, kThreads, 0, s>>>(weight, virtual_weight, out, N, n_virtual ? n_virtual : 1,
+                                                       W, L1, scale_main, scale_psqt);
+    else
+        k_prepare_table<false><<<grid, kThreads, 0, s>>>(weight, virtual_weight, out, N, n_virtual ? n_virtual : 1,
+                                                        W, L1, scale_main, scale_psqt);
+    NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
+    return NNUE_OK;
+}
+
+extern "C" int nnue_ft_virtual_grad(const float* grad, float* out, int64_t N, int64_t n_virtual,
+                                    int32_t W, void* stream) {
+    NNUE_REQUIRE(N >= 0 && n_virtual > 0 && W > 0 && N % n_virtual == 0, NNUE_ERR_ARG,
+                 "nnue_ft_virtual_grad: bad size");
+    NNUE_REQUIRE(grad && out, NNUE_ERR_ARG, "nnue_ft_virtual_grad: null pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (N == 0) {
+        NNUE_CUDA_TRY(cudaMemsetAsync(out, 0, (size_t)n_virtual * W * sizeof(float), s));
+        return NNUE_OK;
+    }
+    const bool vec = (W % 4 == 0) && aligned16(grad) && aligned16(out);
+    const int64_t work = vec ? n_virtual * (W / 4) : n_virtual * (int64_t)W;
+    const unsigned grid = (unsigned)((work + kThreads - 1) / kThreads);
+    if (vec) k_virtual_grad<true><<<grid, kThreads, 0, s>>>(grad, out, N / n_virtual, n_virtual, W);
+    else k_virtual_grad<false><<<grid, kThreads, 0, s>>>(grad, out, N / n_virtual, n_virtual, W);
+    NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
+    return NNUE_OK;
+}

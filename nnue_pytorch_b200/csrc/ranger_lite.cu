@@ -112,10 +112,12 @@ __global__ void __launch_bounds__(kThreads)
             gv[s] = col < width4 ? __ldg(g4 + base + col) : f4_zero();
             nz |= (gv[s].x != 0.f) | (gv[s].y != 0.f) | (gv[s].z != 0.f) | (gv[s].w != 0.f);
         }
-        const int active = row_active[row];
-        const int any = __syncthreads_or(nz);
-        if (!active && !any) continue;  // uniform
-        if (!active && threadIdx.x == 0) row_active[row] = 1;
+        const int active = row_active[row];  // same byte for the whole CTA: uniform
+        if (!active) {
+            // the barrier also orders every thread's read of the flag before the write below
+            if (!__syncthreads_or(nz)) continue;
+            if (threadIdx.x == 0) row_active[row] = 1;
+        }
 #pragma unroll
         for (int s = 0; s < kRowSlots; ++s) {
             const int64_t col = (int64_t)s * kThreads + threadIdx.x;

@@ -54,6 +54,7 @@ def _inverse_king_buckets() -> list[int]:
 
 
 class HalfKav2Hm(InputFeature):
+    FUSED_TABLE = True  # merged table = weight + virtual_weight.repeat(buckets, 1)
     HASH = 0x7F234CB8
     FEATURE_NAME = "HalfKAv2_hm^"
     INPUT_FEATURE_NAME = "HalfKAv2_hm"
@@ -131,6 +132,7 @@ class HalfKav2HmFlat(InputFeature):
     """22528 real + 704 factor rows in one table; factor rows are addressed by
     the position's own index list (see positions.baseline_indices)."""
 
+    FUSED_TABLE = True  # merged table = weight
     HASH = 0x7F234CB8
     FEATURE_NAME = "HalfKAv2_hm^"
     INPUT_FEATURE_NAME = "HalfKAv2_hm^"

@@ -21,12 +21,21 @@ BACKWARD_TILE_SIZE = 1  # kept for importers of the reference module; unused her
 
 
 class FusedDoubleFtFunction(autograd.Function):
+    """The reference's nine arguments, plus three optional ones that fuse the
+    dense passes the reference runs right after the op on `l0`
+    (composed_feature_transformer.py:143-149): `act_quant_scale` > 0 applies
+    floor(l0 * scale + act_quant_eps) / scale with a straight-through gradient,
+    `out_scale` multiplies the result (and the incoming gradient)."""
+
     @staticmethod
-    def forward(ctx, us, them, white_indices, black_indices, psqt_indices, weight, bias, max_ft_activation, l1_size):
+    def forward(ctx, us, them, white_indices, black_indices, psqt_indices, weight, bias, max_ft_activation, l1_size,
+                act_quant_scale=0.0, act_quant_eps=0.0, out_scale=1.0):
         ctx.max_ft_activation = float(max_ft_activation)
         ctx.l1_size = int(l1_size)
+        ctx.out_scale = float(out_scale)
         l0, wpsqt, bpsqt, saved = _launch.fused_forward(
-            us, them, white_indices, black_indices, psqt_indices, weight, bias, max_ft_activation, int(l1_size)
+            us, them, white_indices, black_indices, psqt_indices, weight, bias, max_ft_activation, int(l1_size),
+            act_quant_scale, act_quant_eps, out_scale,
         )
         ctx.save_for_backward(us, them, white_indices, black_indices, psqt_indices, saved)
         ctx.weight_shape = tuple(weight.shape)
@@ -38,6 +47,25 @@ class FusedDoubleFtFunction(autograd.Function):
         num_inputs, num_outputs = ctx.weight_shape
         grad_weight, grad_bias = _launch.fused_backward(
             us, them, white_indices, black_indices, psqt_indices, ctx.max_ft_activation, ctx.l1_size,
-            num_inputs, num_outputs, grad_l0, grad_wpsqt, grad_bpsqt, saved,
+            num_inputs, num_outputs, grad_l0, grad_wpsqt, grad_bpsqt, saved, out_scale=ctx.out_scale,
         )
-        return None, None, None, None, None, grad_weight, grad_bias, None, None
+        return None, None, None, None, None, grad_weight, grad_bias, None, None, None, None, None
+
+
+class PrepareTableFunction(autograd.Function):
+    """table = fq(weight + virtual_weight.repeat(buckets, 1)) in one kernel.
+    Backward: straight-through to `weight` (the same tensor, no copy), the
+    bucket sum to `virtual_weight` (halfka_v2_hm.py:68-69 and the fake
+    quantization of composed_feature_transformer.py:61-76 of the reference)."""
+
+    @staticmethod
+    def forward(ctx, weight, virtual_weight, l1_size, scale_main, scale_psqt):
+        ctx.n_virtual = 0 if virtual_weight is None else virtual_weight.shape[0]
+        return _launch.prepare_table(weight, virtual_weight, int(l1_size), scale_main, scale_psqt)
+
+    @staticmethod
+    def backward(ctx, grad):
+        gv = None
+        if ctx.n_virtual and ctx.needs_input_grad[1]:
+            gv = _launch.virtual_grad(grad, ctx.n_virtual)
+        return grad, gv, None, None, None

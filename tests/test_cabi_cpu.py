@@ -43,16 +43,16 @@ def test_host_side_argument_validation(lib):
     # negative sizes and bad enums are rejected before any CUDA call
     assert lib.nnue_ft_sparse_fwd(None, None, None, None, -1, 4, 4, 4, None) == -1
     assert b"negative size" in lib.nnue_b200_last_error()
-    assert lib.nnue_ft_fused_fwd(None, None, None, None, None, None, None, 1.0, None, None, None, None,
+    assert lib.nnue_ft_fused_fwd(None, None, None, None, None, None, None, 1.0, 0.0, 0.0, 1.0, None, None, None, None,
                                  4, 4, 4, 7, 8, None) == -1  # odd l1
     assert b"even" in lib.nnue_b200_last_error()
-    assert lib.nnue_ft_fused_bwd(None, None, None, None, None, 1.0, None, None, None, None, None, None,
+    assert lib.nnue_ft_fused_bwd(None, None, None, None, None, 1.0, 1.0, None, None, None, None, None, None,
                                  4, 4, 4, 8, 8, None, 0, 9, None) == -1  # unknown mode
     assert lib.nnue_b200_tune(b"no_such_knob", 1) == -1
     assert lib.nnue_rangerlite_update(None, None, None, None, None, None, None, None, 1, 1, None, None) == -1
     # empty batches are a no-op that needs no device
     assert lib.nnue_ft_sparse_fwd(None, None, None, None, 0, 4, 4, 4, None) == 0
-    assert lib.nnue_ft_fused_fwd(None, None, None, None, None, None, None, 1.0, None, None, None, None,
+    assert lib.nnue_ft_fused_fwd(None, None, None, None, None, None, None, 1.0, 0.0, 0.0, 1.0, None, None, None, None,
                                  0, 4, 4, 8, 8, None) == 0
 
 

@@ -340,3 +340,60 @@ def test_bad_indices_are_skipped_not_dereferenced(dev):
     _launch.device_status(dev)  # reading clears the word
     assert torch.allclose(out[0], w[1] + w[2] + w[3])
     assert torch.allclose(out[1], w[4])  # the first -1 ends the row
+
+
+def test_prepare_table_matches_torch_composition(dev):
+    """weight + virtual.repeat(32, 1), two fake quantizations and the concat of the
+    reference module, against the one-pass kernel (bit for bit vs the CPU ops)."""
+    from nnue_pytorch_b200.fused_ft_functions import PrepareTableFunction
+
+    gen = torch.Generator().manual_seed(3)
+    N, nv, L1, P = 768, 24, 40, 8
+    w = torch.randn(N, L1 + P, generator=gen) * 0.3
+    v = torch.randn(nv, L1 + P, generator=gen) * 0.1
+    go = torch.randn(N, L1 + P, generator=gen)
+
+    def ref(w, v, quant):
+        m = w + v.repeat(N // nv, 1) if v is not None else w
+        if not quant:
+            return m
+        fq = lambda x, s: x.mul(s).round().div(s)  # noqa: E731
+        return torch.cat([fq(m[:, :L1], 256.0), fq(m[:, L1:], 9600.0)], dim=1)
+
+    for virt, quant in ((v, True), (v, False), (None, True)):
+        wd = w.to(dev).requires_grad_(True)
+        vd = virt.to(dev).requires_grad_(True) if virt is not None else None
+        out = PrepareTableFunction.apply(wd, vd, L1, 256.0 if quant else 0.0, 9600.0 if quant else 0.0)
+        assert torch.equal(out.detach().cpu(), ref(w, virt, quant))
+        out.backward(go.to(dev))
+        assert torch.equal(wd.grad.cpu(), go)  # straight-through
+        if virt is not None:
+            want = go.view(N // nv, nv, -1).sum(0)
+            assert max_rel_err(vd.grad.cpu(), want) <= 1e-6
+
+
+def test_fused_epilogue_matches_separate_ops(dev):
+    """Activation fake quantization and the correction factor inside the kernel
+    equal the reference's separate tensor ops after the bare operator."""
+    from nnue_pytorch_b200 import double_feature_transform
+    from nnue_pytorch_b200.fused_ft_functions import FusedDoubleFtFunction
+
+    c = _random_case(50, 300, 32, 128, 8, seed=9, wscale=0.1)
+    for corr in (1.0, 0.75):
+        outs = []
+        for fused in (True, False):
+            wd = c["weight"].to(dev).requires_grad_(True)
+            bd = c["bias"].to(dev).requires_grad_(True)
+            args = (c["us"].to(dev), c["them"].to(dev), c["white"].to(dev), c["black"].to(dev), c["psqt"].to(dev), wd, bd)
+            if fused:
+                l0, wp, bp = FusedDoubleFtFunction.apply(*args, c["max_act"], 128, 128.0, 1e-5, corr)
+            else:
+                l0, wp, bp = double_feature_transform(*args, c["max_act"], 128)
+                hard = l0.mul(128.0).add(1e-5).floor().div(128.0)
+                l0 = (hard.detach() + (l0 - l0.detach())) * corr
+            ((l0 * c["grad_l0"].to(dev)).sum() + wp.sum()).backward()
+            outs.append((l0.detach(), wd.grad, bd.grad))
+        assert torch.equal(outs[0][0], outs[1][0])
+        assert torch.equal(outs[0][1], outs[1][1])
+        assert torch.equal(outs[0][2], outs[1][2])
+        assert len(torch.unique(outs[0][0] * 128 / corr)) <= 129
