@@ -96,6 +96,30 @@ int nnue_ft_sparse_bwd(const int32_t* idx, const float* grad_out,
                        void* workspace, size_t workspace_bytes, int32_t mode,
                        void* stream);
 
+/* ---- sparse linear backward without any allocation ---------------------
+ * No counterpart in the reference project.
+ * Same result as nnue_ft_sparse_bwd (segment route), for hosts that cannot
+ * obtain a workspace because they must not allocate device memory when the
+ * call is made: a process whose device memory is owned by its own pool, a
+ * service that forbids allocation after start-up, code between the begin and
+ * the end of a stream capture.  The scratch is a fixed array of
+ * NNUE_SPARSE_BWD_STATIC_SCRATCH_BYTES inside the library's device image
+ * (every GPU that loads the library carries it until the process ends); the
+ * call allocates nothing and frees nothing.
+ *   - shapes whose scratch need (nnue_ft_sparse_bwd_workspace_bytes) exceeds
+ *     the array are refused with NNUE_ERR_WORKSPACE and a message;
+ *   - the first call on each device looks up the array's address
+ *     (cudaGetSymbolAddress); make that first call outside any stream capture;
+ *   - all calls share the one array: two calls that can overlap on the GPU
+ *     (different streams, no ordering between them) race on it.  Calls on one
+ *     stream, or otherwise ordered, are safe; nothing has to be cleared by the
+ *     caller between calls. */
+#define NNUE_SPARSE_BWD_STATIC_SCRATCH_BYTES ((size_t)32 << 20)
+int nnue_ft_sparse_bwd_static(const int32_t* idx, const float* grad_out,
+                              float* grad_weight, float* grad_bias,
+                              int64_t B, int32_t K, int64_t N, int32_t W,
+                              void* stream);
+
 /* ---- A6: fused double feature transformer, forward --------------------
  * Per position: w = bias[:L1] + sum weight[white_idx][:L1], b likewise;
  * x = us*[w, b] + them*[b, w] (2*L1 wide, four chunks of L1/2);

@@ -21,6 +21,7 @@ LIB_PATH = PKG_DIR / "libnnue_b200.so"
 SOURCES = [
     "core.cu",
     "ft_sparse.cu",
+    "ft_sparse_static.cu",
     "ft_fused.cu",
     "ft_segment.cu",
     "ft_table.cu",

@@ -75,6 +75,7 @@ PROTOTYPES = {
     "nnue_ft_sparse_fwd": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _I64, _I32, _P]),
     "nnue_ft_sparse_bwd_workspace_bytes": (_SZ, [_I64, _I32, _I64, _I32, _I32]),
     "nnue_ft_sparse_bwd": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _I64, _I32, _P, _SZ, _I32, _P]),
+    "nnue_ft_sparse_bwd_static": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _I64, _I32, _P]),
     "nnue_ft_fused_fwd": (
         C.c_int,
         [_P, _P, _P, _P, _P, _P, _P, C.c_float, C.c_float, C.c_float, C.c_float, _P, _P, _P, _P,
