@@ -172,8 +172,8 @@ def run_b200(args):
     with torch.no_grad():  # config: weights ~ N(0, 0.01) (standard deviation), PSQT columns keep their material init
         model.input.features[0].weight[:, : args.l1].normal_(0.0, 0.01)
     model.to(dev)
-    hook = make_grad_hook(model, world) if world > 1 else None
-    step = TrainStep(model, lr=8.75e-4, clip=2.0, lam=1.0, grad_hook=hook)
+    hook = make_grad_hook(model, world, average=False) if world > 1 else None
+    step = TrainStep(model, lr=8.75e-4, clip=2.0, lam=1.0, grad_hook=hook, grad_prescale=1.0 / world)
 
     pool_host = [to_pinned(b) for b in make_pool(args, rank, args.pool, args.batch)]
     pool_dev = [tuple(x.to(dev) for x in b) for b in pool_host]

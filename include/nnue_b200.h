@@ -233,12 +233,14 @@ int nnue_lookahead_merge(float* p, float* slow, int64_t n, float alpha,
 
 /* Sum of squares of a gradient tensor into *d_out (accumulating, so several
  * tensors can share one scalar), and the clip coefficient
- * min(1, max_norm / (sqrt(*d_sumsq) + 1e-6)) that
- * torch.nn.utils.clip_grad_norm_ applies at trainer/engine.py:308-311. */
+ * prescale * min(1, max_norm / (prescale * sqrt(*d_sumsq) + 1e-6)) that
+ * torch.nn.utils.clip_grad_norm_ applies at trainer/engine.py:308-311.
+ * `prescale` is 1, or 1/world when the gradients are rank SUMS that still
+ * have to become means (the division rides in the coefficient). */
 int nnue_grad_sumsq(const float* grad, int64_t n, float* d_out_sumsq,
                     void* stream);
-int nnue_clip_coef(const float* d_sumsq, float max_norm, float* d_coef,
-                   void* stream);
+int nnue_clip_coef(const float* d_sumsq, float max_norm, float prescale,
+                   float* d_coef, void* stream);
 
 /* ---- Q: integer quantized evaluation ----------------------------------
  * Integer restatement of the fake-quantized forward defined by

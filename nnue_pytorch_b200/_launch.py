@@ -286,8 +286,8 @@ def grad_sumsq(grad, out_sumsq) -> None:
     _lib.check(st, "nnue_grad_sumsq")
 
 
-def clip_coef(sumsq, max_norm: float, out_coef) -> None:
+def clip_coef(sumsq, max_norm: float, out_coef, prescale: float = 1.0) -> None:
     dev = _require_cuda(sumsq, out_coef)
     with torch.cuda.device(dev):
-        st = _lib.load().nnue_clip_coef(_ptr(sumsq), float(max_norm), _ptr(out_coef), _stream(dev))
+        st = _lib.load().nnue_clip_coef(_ptr(sumsq), float(max_norm), float(prescale), _ptr(out_coef), _stream(dev))
     _lib.check(st, "nnue_clip_coef")

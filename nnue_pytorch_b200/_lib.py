@@ -95,7 +95,7 @@ PROTOTYPES = {
     ),
     "nnue_lookahead_merge": (C.c_int, [_P, _P, _I64, C.c_float, _P]),
     "nnue_grad_sumsq": (C.c_int, [_P, _I64, _P, _P]),
-    "nnue_clip_coef": (C.c_int, [_P, C.c_float, _P, _P]),
+    "nnue_clip_coef": (C.c_int, [_P, C.c_float, C.c_float, _P, _P]),
     "nnue_quant_eval": (
         C.c_int,
         [_P] * 14 + [_I64, _I32, _I64, _I32, _I32, _I32, _I32, _I32, C.POINTER(QuantParams), _P],

@@ -85,10 +85,13 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
-__global__ void k_clip_coef(const float* __restrict__ sumsq, float max_norm, float* __restrict__ coef) {
-    const float total = sqrtf(*sumsq);
+// The gradients the norm was taken over are `prescale` times the true ones
+// (data-parallel ranks sum before they average): the coefficient folds both.
+__global__ void k_clip_coef(const float* __restrict__ sumsq, float max_norm, float prescale,
+                            float* __restrict__ coef) {
+    const float total = prescale * sqrtf(*sumsq);
     const float c = max_norm / (total + 1e-6f);
-    *coef = c < 1.f ? c : 1.f;
+    *coef = prescale * (c < 1.f ? c : 1.f);
 }
 
 }  // namespace nnue
@@ -157,9 +160,10 @@ extern "C" int nnue_grad_sumsq(const float* grad, int64_t n, float* d_out_sumsq,
     return NNUE_OK;
 }
 
-extern "C" int nnue_clip_coef(const float* d_sumsq, float max_norm, float* d_coef, void* stream) {
+extern "C" int nnue_clip_coef(const float* d_sumsq, float max_norm, float prescale, float* d_coef,
+                              void* stream) {
     NNUE_REQUIRE(d_sumsq && d_coef, NNUE_ERR_ARG, "nnue_clip_coef: null pointer");
-    k_clip_coef<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(d_sumsq, max_norm, d_coef);
+    k_clip_coef<<<1, 1, 0, static_cast<cudaStream_t>(stream)>>>(d_sumsq, max_norm, prescale, d_coef);
     note_launches(1);
     NNUE_CUDA_TRY(cudaGetLastError());
     return NNUE_OK;

@@ -17,10 +17,13 @@ import torch.distributed as dist
 _BIG = 1 << 22  # elements; tensors at least this large are reduced on their own
 
 
-def make_grad_hook(model: torch.nn.Module, world: int):
+def make_grad_hook(model: torch.nn.Module, world: int, average: bool = True):
+    """`average=False` leaves rank SUMS in `.grad`; the caller then folds the
+    division by `world` into the scalar its optimizer multiplies gradients by
+    (`TrainStep` does), which saves a read-modify-write pass over the table."""
     if world <= 1:
         return None
-    inv = 1.0 / world
+    inv = 1.0 / world if average else 1.0
 
     def hook(m: torch.nn.Module) -> None:
         grads = [p.grad for p in m.parameters() if p.grad is not None]
@@ -28,11 +31,13 @@ def make_grad_hook(model: torch.nn.Module, world: int):
         for g in grads:
             if g.numel() >= _BIG:
                 dist.all_reduce(g)
-                g.mul_(inv)
+                if inv != 1.0:
+                    g.mul_(inv)
         if small:
             flat = torch.cat([g.reshape(-1) for g in small])
             dist.all_reduce(flat)
-            flat.mul_(inv)
+            if inv != 1.0:
+                flat.mul_(inv)
             at = 0
             for g in small:
                 n = g.numel()

@@ -192,7 +192,9 @@ class TrainStep:
     gradients."""
 
     def __init__(self, model: NNUEModel, lr: float = 8.75e-4, clip: float = 2.0, lam: float = 1.0,
-                 loss_params: LossParams | None = None, grad_hook=None):
+                 loss_params: LossParams | None = None, grad_hook=None, grad_prescale: float = 1.0):
+        """`grad_prescale`: factor that turns what `grad_hook` leaves in `.grad` into the true
+        gradient (1/world when the hook sums over ranks without averaging)."""
         self.model = model
         self.clip, self.lam = clip, lam
         self.loss_params = loss_params or LossParams()
@@ -204,8 +206,10 @@ class TrainStep:
         )
         dev = next(model.parameters()).device
         self._sumsq = torch.zeros(1, dtype=torch.float32, device=dev)
-        self._coef = torch.ones(1, dtype=torch.float32, device=dev)
-        self.optimizer.grad_scale = self._coef if clip and clip > 0 else None
+        self.grad_prescale = float(grad_prescale)
+        self._coef = torch.full((1,), self.grad_prescale, dtype=torch.float32, device=dev)
+        self._clipping = bool(clip and clip > 0)
+        self.optimizer.grad_scale = self._coef if (self._clipping or self.grad_prescale != 1.0) else None
 
     def loss(self, batch):
         us, them, white, black, outcome, score, piece_count = batch
@@ -220,11 +224,11 @@ class TrainStep:
         loss.backward()
         if self.grad_hook is not None:
             self.grad_hook(self.model)
-        if self.optimizer.grad_scale is not None:
+        if self._clipping:
             self._sumsq.zero_()
             for p in self.model.parameters():
                 if p.grad is not None:
                     _launch.grad_sumsq(p.grad, self._sumsq)
-            _launch.clip_coef(self._sumsq, self.clip, self._coef)
+            _launch.clip_coef(self._sumsq, self.clip, self._coef, self.grad_prescale)
         self.optimizer.step()
         return loss.detach()

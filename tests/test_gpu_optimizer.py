@@ -149,3 +149,7 @@ def test_clip_coefficient_matches_torch(dev):
         total = torch.linalg.vector_norm(torch.stack([torch.linalg.vector_norm(g) for g in gs]))
         want = torch.clamp(max_norm / (total + 1e-6), max=1.0)
         assert abs(float(coef) - float(want)) <= 1e-5 * float(want)
+        # gradients that are sums over 4 ranks: the same clip on their mean, times 1/4
+        _launch.clip_coef(sumsq, max_norm, coef, 0.25)
+        want = 0.25 * torch.clamp(max_norm / (0.25 * total + 1e-6), max=1.0)
+        assert abs(float(coef) - float(want)) <= 1e-5 * float(want)
