@@ -53,6 +53,8 @@ def parse_args():
     ap.add_argument("--bwd-mode", default="auto", choices=["auto", "atomic", "segment"])
     ap.add_argument("--cpu-sample-batch", type=int, default=2048)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--ddp", default="fused", choices=["fused", "allreduce"],
+                    help="table exchange at N > 1: peer-memory reduce-scatter/update/all-gather kernels, or NCCL all-reduce")
     return ap.parse_args()
 
 
@@ -172,8 +174,16 @@ def run_b200(args):
     with torch.no_grad():  # config: weights ~ N(0, 0.01) (standard deviation), PSQT columns keep their material init
         model.input.features[0].weight[:, : args.l1].normal_(0.0, 0.01)
     model.to(dev)
-    hook = make_grad_hook(model, world, average=False) if world > 1 else None
-    step = TrainStep(model, lr=8.75e-4, clip=2.0, lam=1.0, grad_hook=hook, grad_prescale=1.0 / world)
+    hook = exchange = None
+    if world > 1:
+        table = model.input.features[0].weight
+        if args.ddp == "fused":
+            from nnue_pytorch_b200.ddp import ShardedTableExchange
+
+            exchange = ShardedTableExchange(table)
+        hook = make_grad_hook(model, world, average=False, skip=[table] if exchange is not None else [])
+    step = TrainStep(model, lr=8.75e-4, clip=2.0, lam=1.0, grad_hook=hook, grad_prescale=1.0 / world,
+                     table_exchange=exchange)
 
     pool_host = [to_pinned(b) for b in make_pool(args, rank, args.pool, args.batch)]
     pool_dev = [tuple(x.to(dev) for x in b) for b in pool_host]
@@ -259,6 +269,7 @@ def run_b200(args):
             "global_batch": world * args.batch,
             "l1": args.l1,
             "parallelism": f"dp{world}",
+            "table_exchange": (args.ddp if world > 1 else "none"),
             "backward": args.bwd_mode,
             "l2_policy": "working set per step (table 286 MB + gradient + moments + activations > 2 GB) exceeds the 126 MB L2; "
                          f"{args.pool} distinct batches cycled",

@@ -242,6 +242,31 @@ int nnue_grad_sumsq(const float* grad, int64_t n, float* d_out_sumsq,
 int nnue_clip_coef(const float* d_sumsq, float max_norm, float prescale,
                    float* d_coef, void* stream);
 
+/* ---- A14: data-parallel exchange fused with the optimizer ----------------
+ * Replaces, for the feature-transformer table, the DistributedDataParallel
+ * all-reduce of trainer/engine.py:149-162 followed by a full optimizer step on
+ * every rank.  h_*_ptrs are HOST arrays of `world` DEVICE pointers: the same
+ * [N*W] float buffer on every rank, mapped into this process (symmetric memory
+ * or CUDA IPC).  [elem_begin, elem_end) is this rank's shard in elements
+ * (multiples of 4).  Plain peer loads/stores only.
+ *   nnue_ddp_reduce_shard: own_grad[i] = sum_r grad_r[i] (rank order) for the
+ *     shard, and *d_sumsq += sum of squares of those sums.
+ *   nnue_ddp_update_shard: RangerLite (nnue_rangerlite_update arithmetic,
+ *     phase 0) on the shard, reading `grad` (this rank's buffer, full size)
+ *     and shard-sized moment tensors, and storing the new values into every
+ *     rank's table.
+ * The caller orders the ranks: every rank's backward before any reduce, every
+ * reduce before the next backward, every update before the next forward (a
+ * small NCCL collective on the same stream between the phases does it). */
+int nnue_ddp_reduce_shard(float* const* h_grad_ptrs, int32_t world, int32_t rank,
+                          int64_t elem_begin, int64_t elem_end, float* d_sumsq,
+                          void* stream);
+int nnue_ddp_update_shard(float* const* h_table_ptrs, int32_t world, int32_t rank,
+                          int64_t elem_begin, int64_t elem_end, const float* grad,
+                          float* grad_ma, float* neg_grad_ma, float* variance_ma,
+                          float* slow, const float* d_grad_scale,
+                          const nnue_ranger_hparams* h_hp, void* stream);
+
 /* ---- Q: integer quantized evaluation ----------------------------------
  * Integer restatement of the fake-quantized forward defined by
  * model/quantize.py:36-56,133-147, model/modules/layer_stacks.py:33-84 and

@@ -26,6 +26,7 @@ SOURCES = [
     "ft_segment.cu",
     "ft_table.cu",
     "ranger_lite.cu",
+    "ddp_fused.cu",
     "quant_eval.cu",
 ]
 

@@ -59,6 +59,16 @@ class _NoSpan:
         return False
 
 
+# When set (data-parallel table exchange), the fused backward writes the table
+# gradient into this preallocated [N, W] buffer instead of a fresh tensor, and
+# the autograd functions hand no gradient to the parameter: the exchange owns it.
+GRAD_SINK: torch.Tensor | None = None
+
+
+def is_grad_sink(t: torch.Tensor | None) -> bool:
+    return t is not None and GRAD_SINK is not None and t.data_ptr() == GRAD_SINK.data_ptr()
+
+
 TIMER: KernelTimer | None = None
 _NO_SPAN = _NoSpan()
 
@@ -191,7 +201,10 @@ def fused_backward(
     P = num_outputs - l1_size
     m = _lib.bwd_mode(mode or _BWD_MODE)
     lib = _lib.load()
-    grad_w = torch.empty(num_inputs, num_outputs, dtype=torch.float32, device=dev)
+    if GRAD_SINK is not None and tuple(GRAD_SINK.shape) == (num_inputs, num_outputs) and GRAD_SINK.device == dev:
+        grad_w = GRAD_SINK
+    else:
+        grad_w = torch.empty(num_inputs, num_outputs, dtype=torch.float32, device=dev)
     grad_b = torch.empty(num_outputs, dtype=torch.float32, device=dev)
     ws = _workspace(lib.nnue_ft_fused_bwd_workspace_bytes(B, K, num_inputs, l1_size, P, m), dev)
     with torch.cuda.device(dev), _span("fused_bwd", dev):
@@ -291,3 +304,23 @@ def clip_coef(sumsq, max_norm: float, out_coef, prescale: float = 1.0) -> None:
     with torch.cuda.device(dev):
         st = _lib.load().nnue_clip_coef(_ptr(sumsq), float(max_norm), float(prescale), _ptr(out_coef), _stream(dev))
     _lib.check(st, "nnue_clip_coef")
+
+
+def ddp_reduce_shard(grad_ptrs: list[int], rank: int, elem_begin: int, elem_end: int, sumsq: torch.Tensor) -> None:
+    dev = _require_cuda(sumsq)
+    arr = (C.c_void_p * len(grad_ptrs))(*grad_ptrs)
+    with torch.cuda.device(dev), _span("ddp_reduce", dev):
+        st = _lib.load().nnue_ddp_reduce_shard(arr, len(grad_ptrs), rank, elem_begin, elem_end, _ptr(sumsq), _stream(dev))
+    _lib.check(st, "nnue_ddp_reduce_shard")
+
+
+def ddp_update_shard(table_ptrs: list[int], rank: int, elem_begin: int, elem_end: int, grad, grad_ma, neg_grad_ma,
+                     variance_ma, slow, grad_scale, hp) -> None:
+    dev = _require_cuda(grad, grad_ma, variance_ma)
+    arr = (C.c_void_p * len(table_ptrs))(*table_ptrs)
+    with torch.cuda.device(dev), _span("ddp_update", dev):
+        st = _lib.load().nnue_ddp_update_shard(
+            arr, len(table_ptrs), rank, elem_begin, elem_end, _ptr(grad), _ptr(grad_ma), _ptr(neg_grad_ma),
+            _ptr(variance_ma), _ptr(slow), _ptr(grad_scale), C.byref(hp), _stream(dev),
+        )
+    _lib.check(st, "nnue_ddp_update_shard")

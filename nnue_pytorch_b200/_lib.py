@@ -93,6 +93,11 @@ PROTOTYPES = {
         C.c_int,
         [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, C.POINTER(RangerHParams), _P],
     ),
+    "nnue_ddp_reduce_shard": (C.c_int, [C.POINTER(_P), _I32, _I32, _I64, _I64, _P, _P]),
+    "nnue_ddp_update_shard": (
+        C.c_int,
+        [C.POINTER(_P), _I32, _I32, _I64, _I64, _P, _P, _P, _P, _P, _P, C.POINTER(RangerHParams), _P],
+    ),
     "nnue_lookahead_merge": (C.c_int, [_P, _P, _I64, C.c_float, _P]),
     "nnue_grad_sumsq": (C.c_int, [_P, _I64, _P, _P]),
     "nnue_clip_coef": (C.c_int, [_P, C.c_float, C.c_float, _P, _P]),

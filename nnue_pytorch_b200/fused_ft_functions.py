@@ -39,6 +39,8 @@ class FusedDoubleFtFunction(autograd.Function):
         )
         ctx.save_for_backward(us, them, white_indices, black_indices, psqt_indices, saved)
         ctx.weight_shape = tuple(weight.shape)
+        # a table made by PrepareTableFunction still needs its gradient routed to the factor rows
+        ctx.table_is_derived = weight.grad_fn is not None
         return l0, wpsqt, bpsqt
 
     @staticmethod
@@ -49,6 +51,8 @@ class FusedDoubleFtFunction(autograd.Function):
             us, them, white_indices, black_indices, psqt_indices, ctx.max_ft_activation, ctx.l1_size,
             num_inputs, num_outputs, grad_l0, grad_wpsqt, grad_bpsqt, saved, out_scale=ctx.out_scale,
         )
+        if _launch.is_grad_sink(grad_weight) and not ctx.table_is_derived:
+            grad_weight = None  # the data-parallel exchange reads the sink buffer itself
         return None, None, None, None, None, grad_weight, grad_bias, None, None, None, None, None
 
 
@@ -68,4 +72,6 @@ class PrepareTableFunction(autograd.Function):
         gv = None
         if ctx.n_virtual and ctx.needs_input_grad[1]:
             gv = _launch.virtual_grad(grad, ctx.n_virtual)
+        if _launch.is_grad_sink(grad):
+            grad = None  # the data-parallel exchange reads the sink buffer itself
         return grad, gv, None, None, None

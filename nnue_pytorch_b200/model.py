@@ -192,15 +192,26 @@ class TrainStep:
     gradients."""
 
     def __init__(self, model: NNUEModel, lr: float = 8.75e-4, clip: float = 2.0, lam: float = 1.0,
-                 loss_params: LossParams | None = None, grad_hook=None, grad_prescale: float = 1.0):
+                 loss_params: LossParams | None = None, grad_hook=None, grad_prescale: float = 1.0,
+                 table_exchange=None):
         """`grad_prescale`: factor that turns what `grad_hook` leaves in `.grad` into the true
-        gradient (1/world when the hook sums over ranks without averaging)."""
+        gradient (1/world when the hook sums over ranks without averaging).
+        `table_exchange`: a `ddp.ShardedTableExchange` that owns the feature-transformer table
+        (gradient reduce-scatter, sharded update, all-gather); the table then leaves the
+        optimizer's parameter groups."""
         self.model = model
         self.clip, self.lam = clip, lam
         self.loss_params = loss_params or LossParams()
         self.grad_hook = grad_hook
+        self.table_exchange = table_exchange
+        groups = optimizer_groups(model, lr)
+        if table_exchange is not None:
+            groups[0]["params"] = [p for p in groups[0]["params"] if p is not table_exchange.param]
+            groups = [g for g in groups if g["params"]]
+            table_exchange.install()
+        self._table_group = {"lr": lr, "betas": (0.9, 0.999), "eps": 1e-7, "pnm_momentum": 1.0}
         self.optimizer = RangerLite(
-            optimizer_groups(model, lr), lr=1.0, weight_decay=0.0, use_legacy_scoping_bug=False,
+            groups, lr=1.0, weight_decay=0.0, use_legacy_scoping_bug=False,
             normloss_active=False, pnm_activate=True, pnm_momentum=1.0, lookahead_blending_alpha=0.5,
             lookahead_mergetime=5,
         )
@@ -222,13 +233,25 @@ class TrainStep:
         loss = self.loss(batch)
         self.optimizer.zero_grad(set_to_none=True)
         loss.backward()
+        ex = self.table_exchange
+        if ex is not None:
+            ex.param.grad = None  # its gradient lives in the exchange's buffer
         if self.grad_hook is not None:
-            self.grad_hook(self.model)
+            self.grad_hook(self.model)  # a collective: every rank's backward is complete after it
+        if ex is not None:
+            ft_sumsq = ex.reduce()
         if self._clipping:
             self._sumsq.zero_()
             for p in self.model.parameters():
                 if p.grad is not None:
                     _launch.grad_sumsq(p.grad, self._sumsq)
+            if ex is not None:
+                self._sumsq.add_(ft_sumsq)
             _launch.clip_coef(self._sumsq, self.clip, self._coef, self.grad_prescale)
-        self.optimizer.step()
+        opt = self.optimizer
+        merge = opt.lookahead_active and opt.lookahead_step + 1 >= opt.lookahead_mergetime
+        opt.step()
+        if ex is not None:
+            ex.step += 1
+            ex.update(opt._hparams(self._table_group, ex.step, merge, phase=0), opt.grad_scale)
         return loss.detach()

@@ -1,0 +1,99 @@
+"""Two-GPU check of the peer-memory table exchange (reduce-scatter + sharded
+RangerLite + all-gather kernels) against the plain NCCL all-reduce followed by
+the full optimizer step on every rank.  Needs two CUDA devices; on a
+single-GPU box the test reports itself as skipped."""
+
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port():
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank, world, port, out_dir):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world),
+                      NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from nnue_pytorch_b200 import _launch, positions
+        from nnue_pytorch_b200.ddp import ShardedTableExchange, make_grad_hook
+        from nnue_pytorch_b200.model import ModelConfig, NNUEModel, TrainStep
+
+        def build():
+            torch.manual_seed(0)
+            m = NNUEModel("HalfKAv2_hm^flat", ModelConfig(L1=128, L2=32, L3=32))
+            with torch.no_grad():
+                m.input.features[0].weight[:, :128].normal_(0, 0.05)
+                m.layer_stacks.l1.linear.weight.normal_(0, 0.05)
+            return m.to(dev)
+
+        batches = []
+        for i in range(6):
+            b = positions.generate_batch(256, 50 + 10 * i + rank, layout="baseline")
+            batches.append(tuple(torch.from_numpy(a).to(dev) for a in b.as_tuple()))
+
+        ref = build()
+        step_ref = TrainStep(ref, clip=2.0, grad_hook=make_grad_hook(ref, world, average=False),
+                             grad_prescale=1.0 / world)
+        losses_ref = [float(step_ref(b)) for b in batches]
+        ref_table = ref.input.features[0].weight.detach().clone()
+        ref_state = {k: v.clone() for k, v in step_ref.optimizer.state[ref.input.features[0].weight].items()
+                     if torch.is_tensor(v)}
+
+        fused = build()
+        table = fused.input.features[0].weight
+        ex = ShardedTableExchange(table)
+        step = TrainStep(fused, clip=2.0, grad_hook=make_grad_hook(fused, world, average=False, skip=[table]),
+                         grad_prescale=1.0 / world, table_exchange=ex)
+        losses = [float(step(b)) for b in batches]
+        _launch.GRAD_SINK = None
+        _launch.device_status(dev)
+        sd = ex.state_dict()
+
+        def rel(a, b):
+            return float((a - b).abs().max()) / max(float(b.abs().max()), 1e-30)
+
+        report = {
+            "loss": max(abs(a - b) / abs(b) for a, b in zip(losses, losses_ref)),
+            "table": rel(table.detach(), ref_table),
+            "small": max(rel(p.detach(), q.detach()) for (n, p), (_, q) in
+                         zip(fused.named_parameters(), ref.named_parameters()) if "features" not in n),
+            "state": max(rel(sd[k], ref_state[k]) for k in ("grad_ma", "neg_grad_ma", "variance_ma", "lookahead_params")),
+            "step": sd["step"],
+        }
+        # every rank must hold the same table after the all-gather
+        mine = table.detach().clone()
+        other = mine.clone()
+        dist.broadcast(other, src=0)
+        report["ranks_agree"] = bool(torch.equal(mine, other))
+        torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_table_exchange_matches_allreduce(tmp_path):
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    import torch.multiprocessing as mp
+
+    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    for r in range(2):
+        rep = torch.load(tmp_path / f"rank{r}.pt")
+        assert rep["ranks_agree"], rep
+        assert rep["step"] == 6
+        assert rep["loss"] <= 1e-5, rep
+        assert rep["table"] <= 1e-5 and rep["small"] <= 1e-5 and rep["state"] <= 1e-5, rep
