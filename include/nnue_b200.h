@@ -267,6 +267,51 @@ int nnue_ddp_update_shard(float* const* h_table_ptrs, int32_t world, int32_t ran
                           float* slow, const float* d_grad_scale,
                           const nnue_ranger_hparams* h_hp, void* stream);
 
+/* ---- layer stack behind the feature transformer --------------------------
+ * Bucket-aware replacement of the three wide F.linear calls + row selection of
+ * model/modules/stacked_linear.py:38-66 and of the activation / skip / output
+ * quantization code of model/modules/layer_stacks.py:33-84: only the weight
+ * block of a position's own bucket is multiplied.  L2 = L3 = 32, L1 % 32 == 0,
+ * at most 16 buckets.  Weight layouts are the reference's (after factor merge
+ * and fake quantization, which stay with the caller): W1 [C*32, L1], b1 [C*32],
+ * W2 [C*32, 64], b2 [C*32], W3 [C, 128], b3 [C].
+ *   nnue_ls_plan      groups the batch by bucket into tiles (stable); `plan`
+ *                     is caller memory of nnue_ls_plan_bytes(B, C) bytes and is
+ *                     shared by the forward and backward calls of one batch.
+ *   nnue_ls_l1_fwd    o1 [B, 32] = W1[bucket] x + b1[bucket]
+ *   nnue_ls_l1_bwd    dx [B, L1] (skipped when NULL), dW1, db1 (overwritten)
+ *   nnue_ls_tail_fwd  y [B] and the saved pre-activations o2 [B, 32]
+ *   nnue_ls_tail_bwd  d_o1 [B, 32], dW2, db2, dW3, db3 (overwritten) */
+typedef struct nnue_ls_params {
+    float act_scale;      /* hidden_quantized_one (128); 0 = no activation fake quantization */
+    float act_eps;        /* 1e-5 */
+    float sqr_corr;       /* sqr_crelu_correction_factor */
+    float max_hidden;     /* hidden_quantized_max / hidden_quantized_one */
+    float out_den;        /* 2 * hidden_one * weight_scale_l_out (32768) */
+    float out_mul;        /* nnue2score * weight_scale_out (9600) */
+    int32_t quantize_out; /* 1 = output fake quantization (truncating division) */
+} nnue_ls_params;
+
+size_t nnue_ls_plan_bytes(int64_t B, int32_t C);
+int nnue_ls_plan(const int64_t* bucket, int64_t B, int32_t C, void* plan,
+                 size_t plan_bytes, void* stream);
+int nnue_ls_l1_fwd(const float* x, const float* W1, const float* b1,
+                   const void* plan, float* o1, int64_t B, int32_t L1, int32_t C,
+                   void* stream);
+int nnue_ls_l1_bwd(const float* x, const float* W1, const float* d_o1,
+                   const void* plan, float* dx, float* dW1, float* db1,
+                   int64_t B, int32_t L1, int32_t C, void* stream);
+int nnue_ls_tail_fwd(const float* o1, const void* plan, const float* W2,
+                     const float* b2, const float* W3, const float* b3,
+                     const nnue_ls_params* h_params, float* o2, float* y,
+                     int64_t B, int32_t C, void* stream);
+size_t nnue_ls_tail_bwd_workspace_bytes(int64_t B, int32_t C);
+int nnue_ls_tail_bwd(const float* o1, const float* o2, const void* plan,
+                     const float* W2, const float* W3, const float* grad_y,
+                     const nnue_ls_params* h_params, float* d_o1, float* dW2,
+                     float* db2, float* dW3, float* db3, void* workspace,
+                     size_t workspace_bytes, int64_t B, int32_t C, void* stream);
+
 /* ---- Q: integer quantized evaluation ----------------------------------
  * Integer restatement of the fake-quantized forward defined by
  * model/quantize.py:36-56,133-147, model/modules/layer_stacks.py:33-84 and

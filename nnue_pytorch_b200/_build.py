@@ -28,6 +28,9 @@ SOURCES = [
     "ranger_lite.cu",
     "ddp_fused.cu",
     "quant_eval.cu",
+    "layer_stack.cu",
+    "layer_stack_l1.cu",
+    "layer_stack_tail.cu",
 ]
 
 NVCC_FLAGS = [

@@ -60,6 +60,20 @@ class QuantParams(C.Structure):
     ]
 
 
+class LsParams(C.Structure):
+    """Mirror of `nnue_ls_params`."""
+
+    _fields_ = [
+        ("act_scale", C.c_float),
+        ("act_eps", C.c_float),
+        ("sqr_corr", C.c_float),
+        ("max_hidden", C.c_float),
+        ("out_den", C.c_float),
+        ("out_mul", C.c_float),
+        ("quantize_out", C.c_int32),
+    ]
+
+
 _P = C.c_void_p
 _I64 = C.c_int64
 _I32 = C.c_int32
@@ -101,6 +115,16 @@ PROTOTYPES = {
     "nnue_lookahead_merge": (C.c_int, [_P, _P, _I64, C.c_float, _P]),
     "nnue_grad_sumsq": (C.c_int, [_P, _I64, _P, _P]),
     "nnue_clip_coef": (C.c_int, [_P, C.c_float, C.c_float, _P, _P]),
+    "nnue_ls_plan_bytes": (_SZ, [_I64, _I32]),
+    "nnue_ls_plan": (C.c_int, [_P, _I64, _I32, _P, _SZ, _P]),
+    "nnue_ls_l1_fwd": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _P]),
+    "nnue_ls_l1_bwd": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _P]),
+    "nnue_ls_tail_fwd": (C.c_int, [_P, _P, _P, _P, _P, _P, C.POINTER(LsParams), _P, _P, _I64, _I32, _P]),
+    "nnue_ls_tail_bwd_workspace_bytes": (_SZ, [_I64, _I32]),
+    "nnue_ls_tail_bwd": (
+        C.c_int,
+        [_P, _P, _P, _P, _P, _P, C.POINTER(LsParams), _P, _P, _P, _P, _P, _P, _SZ, _I64, _I32, _P],
+    ),
     "nnue_quant_eval": (
         C.c_int,
         [_P] * 14 + [_I64, _I32, _I64, _I32, _I32, _I32, _I32, _I32, C.POINTER(QuantParams), _P],

@@ -1,0 +1,96 @@
+"""`FusedLayerStackFunction`: the bucketed layer stack as one autograd op.
+
+Same mathematics as `LayerStacks.forward` of the reference project
+(model/modules/layer_stacks.py:33-84 with model/modules/stacked_linear.py:38-66):
+three bucketed linear layers, squared + linear clipped activations with
+straight-through fake quantization, the skip connection from the first
+layer's last two outputs and the output fake quantization.  The reference
+multiplies every position with the weights of all buckets and then selects;
+the kernels behind this op (csrc/layer_stack*.cu) group the batch by bucket
+and multiply each position with its own bucket's block only.
+
+Inputs are the effective weights of this step (factor already merged, weight
+fake quantization already applied by the caller, where gradients flow through
+ordinary autograd): W1 [C*32, L1], b1 [C*32], W2 [C*32, 64], b2 [C*32],
+W3 [C, 128], b3 [C].
+"""
+
+from __future__ import annotations
+
+import ctypes as C
+
+import torch
+from torch import autograd
+
+from . import _lib
+from ._launch import _ptr, _require_cuda, _span, _stream
+
+
+def _params(quantization, fake_quantize_acts: bool) -> _lib.LsParams:
+    c = quantization.config
+    p = _lib.LsParams()
+    p.act_scale = float(c.hidden_quantized_one) if fake_quantize_acts else 0.0
+    p.act_eps = 1e-5
+    p.sqr_corr = float(quantization.sqr_crelu_correction_factor)
+    p.max_hidden = float(quantization.max_hidden_activation)
+    p.out_den = float(int(c.hidden_quantized_one * c.weight_scale_l_out * 2.0))
+    p.out_mul = float(int(c.nnue2score * c.weight_scale_out))
+    p.quantize_out = 1 if fake_quantize_acts else 0
+    return p
+
+
+def supported(x: torch.Tensor, l1: int, l2: int, l3: int, count: int) -> bool:
+    return x.is_cuda and x.dtype == torch.float32 and l2 == 32 and l3 == 32 and l1 % 32 == 0 and 1 <= count <= 16
+
+
+class FusedLayerStackFunction(autograd.Function):
+    @staticmethod
+    def forward(ctx, x, bucket, W1, b1, W2, b2, W3, b3, quantization, fake_quantize_acts):
+        dev = _require_cuda(x, bucket, W1, b1, W2, b2, W3, b3)
+        x, W1, b1, W2, b2, W3, b3 = (t.contiguous() for t in (x, W1, b1, W2, b2, W3, b3))
+        bucket = bucket.reshape(-1).to(torch.int64).contiguous()
+        B, L1 = x.shape
+        count = W3.shape[0]
+        assert W1.shape == (count * 32, L1) and W2.shape == (count * 32, 64) and W3.shape == (count, 128)
+        lib = _lib.load()
+        params = _params(quantization, fake_quantize_acts)
+        plan = torch.empty(lib.nnue_ls_plan_bytes(B, count) // 4 + 4, dtype=torch.int32, device=dev)
+        o1 = torch.empty(B, 32, device=dev)
+        o2 = torch.empty(B, 32, device=dev)
+        y = torch.empty(B, 1, device=dev)
+        s = _stream(dev)
+        with torch.cuda.device(dev), _span("layer_stack_fwd", dev):
+            _lib.check(lib.nnue_ls_plan(_ptr(bucket), B, count, _ptr(plan), plan.numel() * 4, s), "nnue_ls_plan")
+            _lib.check(lib.nnue_ls_l1_fwd(_ptr(x), _ptr(W1), _ptr(b1), _ptr(plan), _ptr(o1), B, L1, count, s),
+                       "nnue_ls_l1_fwd")
+            _lib.check(lib.nnue_ls_tail_fwd(_ptr(o1), _ptr(plan), _ptr(W2), _ptr(b2), _ptr(W3), _ptr(b3.reshape(-1)),
+                                            C.byref(params), _ptr(o2), _ptr(y), B, count, s), "nnue_ls_tail_fwd")
+        ctx.save_for_backward(x, W1, W2, W3, o1, o2, plan)
+        ctx.params, ctx.count, ctx.b3_shape = params, count, tuple(b3.shape)
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        x, W1, W2, W3, o1, o2, plan = ctx.saved_tensors
+        dev = x.device
+        B, L1 = x.shape
+        count = ctx.count
+        lib = _lib.load()
+        gy = gy.contiguous()
+        d_o1 = torch.empty(B, 32, device=dev)
+        dW1 = torch.empty_like(W1)
+        db1 = torch.empty(count * 32, device=dev)
+        dW2 = torch.empty_like(W2)
+        db2 = torch.empty(count * 32, device=dev)
+        dW3 = torch.empty_like(W3)
+        db3 = torch.empty(count, device=dev)
+        dx = torch.empty_like(x) if ctx.needs_input_grad[0] else None
+        ws = torch.empty(lib.nnue_ls_tail_bwd_workspace_bytes(B, count), dtype=torch.uint8, device=dev)
+        s = _stream(dev)
+        with torch.cuda.device(dev), _span("layer_stack_bwd", dev):
+            _lib.check(lib.nnue_ls_tail_bwd(_ptr(o1), _ptr(o2), _ptr(plan), _ptr(W2), _ptr(W3), _ptr(gy),
+                                            C.byref(ctx.params), _ptr(d_o1), _ptr(dW2), _ptr(db2), _ptr(dW3),
+                                            _ptr(db3), _ptr(ws), ws.numel(), B, count, s), "nnue_ls_tail_bwd")
+            _lib.check(lib.nnue_ls_l1_bwd(_ptr(x), _ptr(W1), _ptr(d_o1), _ptr(plan), _ptr(dx), _ptr(dW1), _ptr(db1),
+                                          B, L1, count, s), "nnue_ls_l1_bwd")
+        return dx, None, dW1, db1, dW2, db2, dW3, db3.view(ctx.b3_shape), None, None

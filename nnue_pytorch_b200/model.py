@@ -92,7 +92,24 @@ class LayerStacks(nn.Module):
             x = q.fake_quantize_ls_act(x)
         return q.clip_ls_act(torch.cat([sq, x], dim=1))
 
+    fused = True  # use the bucket-aware kernels when the shapes allow it
+
+    def _effective(self, layer, fake_quantize_weights):
+        w, b = layer._weights()
+        if fake_quantize_weights:
+            w = self.quantization.fake_quantize_weights(w, f"{layer.layer_key}_weight")
+            b = self.quantization.fake_quantize_weights(b, f"{layer.layer_key}_bias")
+        return w, b
+
     def forward(self, x, ls_indices, fake_quantize_acts=True, fake_quantize_weights=True):
+        from . import layer_stack_functions as lsf
+
+        if self.fused and lsf.supported(x, self.L1, self.L2, self.L3, self.count):
+            w1, b1 = self._effective(self.l1, fake_quantize_weights)
+            w2, b2 = self._effective(self.l2, fake_quantize_weights)
+            w3, b3 = self._effective(self.output, fake_quantize_weights)
+            return lsf.FusedLayerStackFunction.apply(x, ls_indices, w1, b1, w2, b2, w3, b3, self.quantization,
+                                                     fake_quantize_acts)
         o1 = self.l1(x, ls_indices, fake_quantize_weights)
         skip = o1[:, -2].view(-1, 1) - o1[:, -1].view(-1, 1)
         x1 = self._activate(o1, fake_quantize_acts)

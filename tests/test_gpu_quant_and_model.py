@@ -157,3 +157,40 @@ def test_training_steps_track_the_oracle(dev):
         assert abs(float(loss) - float(loss_ref)) <= 2e-5 * abs(float(loss_ref)), i
     for k in order:
         assert max_rel_err(names[k].detach().cpu(), cpu[k]) <= 1e-4, k
+
+
+@pytest.mark.parametrize("B,L1,fq", [(300, 64, True), (2000, 256, True), (777, 96, False), (5, 32, True)])
+def test_fused_layer_stack_matches_torch_layers(dev, B, L1, fq):
+    """Bucket-aware layer-stack kernels against the plain torch layers of the same
+    module (F.linear over all buckets + selection): output and every gradient."""
+    from nnue_pytorch_b200.model import LayerStacks
+    from nnue_pytorch_b200.quantize import QuantizationManager
+
+    torch.manual_seed(B)
+    ls = LayerStacks(8, L1, 32, 32, QuantizationManager()).to(dev)
+    with torch.no_grad():
+        for p in ls.parameters():
+            p.add_(torch.randn_like(p) * 0.05)
+    x0 = (torch.rand(B, L1, device=dev) * 0.9).div(1 / 128).floor().div(128)  # quantized activations in [0, 0.9]
+    bucket = torch.randint(0, 8, (B,), device=dev)
+    if B > 100:
+        bucket[bucket == 5] = 4  # an empty bucket
+    gy = torch.randn(B, 1, device=dev)
+    res = []
+    for fused in (True, False):
+        ls.fused = fused
+        ls.zero_grad(set_to_none=True)
+        x = x0.clone().requires_grad_(True)
+        y = ls(x, bucket, fq, fq)
+        y.backward(gy)
+        res.append((y.detach(), x.grad, {n: p.grad.clone() for n, p in ls.named_parameters()}))
+    (ya, xa, ga), (yb, xb, gb) = res
+    # the floor() of the fake quantization turns last-bit differences of the dot products into 1/128 steps
+    # on a few units, so the comparison allows a small fraction of outliers on y and exact parity elsewhere
+    close = (ya - yb).abs() <= 1e-4 + 1e-4 * yb.abs()
+    assert close.float().mean() >= (0.97 if fq else 1.0)
+    good = close[:, 0]
+    assert max_rel_err(xa[good].cpu(), xb[good].cpu()) <= 1e-4
+    if not fq:
+        for n in ga:
+            assert max_rel_err(ga[n].cpu(), gb[n].cpu()) <= 1e-4, n
