@@ -42,42 +42,41 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
-// Row-wise with the touched-rows-only rule.  One CTA walks rows; a row whose
-// flag is clear and whose gradient row is all zero is left alone (all of its
-// moments are zero, so the full update would rewrite the same bits).
-// width4 <= kThreads * kRowSlots float4.
-constexpr int kRowSlots = 4;
+// Touched-rows-only rule, in two kernels.  A row whose flag is clear and whose
+// gradient row is all zero is left alone: all of its moments are zero, so the
+// full update would rewrite the same bits.
+//   k_rows_activate  one warp per row that is still inactive: any non-zero
+//                    gradient element sets the flag for good;
+//   k_ranger_rows    the flat update, skipping float4 of inactive rows.
+__global__ void __launch_bounds__(kThreads)
+    k_rows_activate(const float* __restrict__ g, uint8_t* __restrict__ row_active, int64_t rows,
+                    int64_t width4) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    if (row >= rows || row_active[row]) return;  // warp-uniform
+    const float4* g4 = reinterpret_cast<const float4*>(g) + row * width4;
+    int nz = 0;
+    for (int64_t c = lane; c < width4 && !nz; c += 32) {
+        const float4 v = __ldg(g4 + c);
+        nz = (v.x != 0.f) | (v.y != 0.f) | (v.z != 0.f) | (v.w != 0.f);
+    }
+    if (__any_sync(kFullMask, nz) && lane == 0) row_active[row] = 1;
+}
+
 __global__ void __launch_bounds__(kThreads)
     k_ranger_rows(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ gm,
                   float* __restrict__ ngm, float* __restrict__ vm, float* __restrict__ slow,
-                  uint8_t* __restrict__ row_active, const float* __restrict__ d_scale, int64_t rows,
+                  const uint8_t* __restrict__ row_active, const float* __restrict__ d_scale, int64_t rows,
                   int64_t width4, RangerConst c) {
     const float scale = d_scale ? __ldg(d_scale) : 1.f;
     const float4* g4 = reinterpret_cast<const float4*>(g);
-    for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
-        const int64_t base = row * width4;
-        float4 gv[kRowSlots];
-        int nz = 0;
-#pragma unroll
-        for (int s = 0; s < kRowSlots; ++s) {
-            const int64_t col = (int64_t)s * kThreads + threadIdx.x;
-            gv[s] = col < width4 ? __ldg(g4 + base + col) : f4_zero();
-            nz |= (gv[s].x != 0.f) | (gv[s].y != 0.f) | (gv[s].z != 0.f) | (gv[s].w != 0.f);
-        }
-        const int active = row_active[row];  // same byte for the whole CTA: uniform
-        if (!active) {
-            // the barrier also orders every thread's read of the flag before the write below
-            if (!__syncthreads_or(nz)) continue;
-            if (threadIdx.x == 0) row_active[row] = 1;
-        }
-#pragma unroll
-        for (int s = 0; s < kRowSlots; ++s) {
-            const int64_t col = (int64_t)s * kThreads + threadIdx.x;
-            if (col < width4)
-                ranger_vec4(c, scale, base + col, g4, reinterpret_cast<float4*>(p),
-                            reinterpret_cast<float4*>(gm), reinterpret_cast<float4*>(ngm),
-                            reinterpret_cast<float4*>(vm), reinterpret_cast<float4*>(slow), gv[s]);
-        }
+    const int64_t n4 = rows * width4;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        if (!__ldg(row_active + i / width4)) continue;
+        ranger_vec4(c, scale, i, g4, reinterpret_cast<float4*>(p), reinterpret_cast<float4*>(gm),
+                    reinterpret_cast<float4*>(ngm), reinterpret_cast<float4*>(vm),
+                    reinterpret_cast<float4*>(slow), __ldg(g4 + i));
     }
 }
 
@@ -132,10 +131,13 @@ extern "C" int nnue_rangerlite_update(float* p, const float* grad, float* grad_m
     const bool al = aligned16(p) && aligned16(grad) && aligned16(grad_ma) && aligned16(variance_ma) &&
                     (!neg_grad_ma || aligned16(neg_grad_ma)) && (!slow || aligned16(slow));
     const int sms = sm_count();
-    if (row_active && al && width % 4 == 0 && width / 4 <= (int64_t)kThreads * kRowSlots && hp->phase != 1) {
-        const unsigned grid = (unsigned)std::min<int64_t>(rows, (int64_t)sms * 8);
+    if (row_active && al && width % 4 == 0 && hp->phase != 1) {
+        k_rows_activate<<<(unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta), kThreads, 0, s>>>(
+            grad, row_active, rows, width / 4);
+        const unsigned grid = (unsigned)std::min<int64_t>((n / 4 + kThreads - 1) / kThreads, (int64_t)sms * 8);
         k_ranger_rows<<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma, slow,
                                                row_active, d_grad_scale, rows, width / 4, c);
+        note_launches(1);
     } else {
         const int64_t work = al ? (n / 4 + 1) : n;
         const unsigned grid = (unsigned)std::min<int64_t>((work + kThreads - 1) / kThreads, (int64_t)sms * 8);

@@ -96,7 +96,7 @@ class RangerLite(torch.optim.Optimizer):
     def _rows_flag(self, p, group):
         if not self.touched_rows_only or p.dim() != 2 or p.shape[0] < _ROW_TABLE_MIN_ROWS:
             return None
-        if p.shape[1] % 4 != 0 or p.shape[1] > 4096:
+        if p.shape[1] % 4 != 0:
             return None
         if group.get("weight_decay", 0.0) != 0.0:
             return None
