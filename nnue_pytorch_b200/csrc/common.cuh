@@ -71,9 +71,29 @@ __device__ __forceinline__ void st_stream4(float4* p, float4 v) { __stcs(p, v); 
 
 __device__ __forceinline__ float4 f4_zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
 
+// Blackwell's packed fp32 add (add.rn.f32x2: two IEEE round-to-nearest adds in
+// one instruction).  The gather kernels are instruction-issue bound, and half
+// of their instructions are these adds.
+#ifndef NNUE_F32X2
+#define NNUE_F32X2 1
+#endif
 __device__ __forceinline__ float4 f4_add(float4 a, float4 b) {
+#if NNUE_F32X2
+    unsigned long long a01, a23, b01, b23, r01, r23;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a01) : "f"(a.x), "f"(a.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(a23) : "f"(a.z), "f"(a.w));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(b01) : "f"(b.x), "f"(b.y));
+    asm("mov.b64 %0, {%1, %2};" : "=l"(b23) : "f"(b.z), "f"(b.w));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r01) : "l"(a01), "l"(b01));
+    asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r23) : "l"(a23), "l"(b23));
+    float4 r;
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.x), "=f"(r.y) : "l"(r01));
+    asm("mov.b64 {%0, %1}, %2;" : "=f"(r.z), "=f"(r.w) : "l"(r23));
+    return r;
+#else
     return make_float4(__fadd_rn(a.x, b.x), __fadd_rn(a.y, b.y), __fadd_rn(a.z, b.z),
                        __fadd_rn(a.w, b.w));
+#endif
 }
 
 // a*s + b*t with each product and the sum rounded separately, as the
