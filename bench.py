@@ -14,7 +14,10 @@ forward + backward + optimizer update over one batch.
 One JSON line is printed by rank 0.  `value` is positions/s with the batches
 already resident in HBM; `e2e` repeats the measurement with the batch copied
 from pinned host memory on a side stream (one batch ahead) and the loss of
-every step copied back to the host, which reads it one step later.
+every step copied back to the host, which reads it one step later.  With
+`--feed packed` (default) the host copy is the 72-byte packed position records
+and the index lists are written on the GPU inside the timed region; with
+`--feed lists` it is the expanded lists, as the reference's loader ships them.
 """
 
 from __future__ import annotations
@@ -54,6 +57,9 @@ def parse_args():
     ap.add_argument("--bwd-mode", default="auto", choices=["auto", "atomic", "segment"])
     ap.add_argument("--cpu-sample-batch", type=int, default=2048)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--feed", default="packed", choices=["packed", "lists"],
+                    help="what the end-to-end run copies from pinned host memory every step: 72-byte packed "
+                         "positions expanded on the GPU, or the expanded index lists")
     ap.add_argument("--ddp", default="fused", choices=["fused", "allreduce"],
                     help="table exchange at N > 1: peer-memory reduce-scatter/update/all-gather kernels, or NCCL all-reduce")
     return ap.parse_args()
@@ -139,6 +145,19 @@ def make_pool(args, rank: int, n: int, batch: int):
     return [positions.generate_batch(batch, 1000 * rank + i, layout="baseline") for i in range(n)]
 
 
+def make_packed_pool(args, rank: int, n: int, batch: int):
+    """The same positions as `make_pool`, as pinned [B, 72] byte records."""
+    from nnue_pytorch_b200 import batch_build, positions
+
+    out = []
+    for i in range(n):
+        seed = 1000 * rank + i
+        score, outcome = positions.generate_targets(batch, seed)
+        rec = batch_build.pack_positions(positions.generate_positions(batch, seed), score, outcome)
+        out.append((batch_build.as_bytes(rec).pin_memory(),))
+    return out
+
+
 def to_pinned(b):
     out = []
     for a in b.as_tuple():
@@ -188,7 +207,13 @@ def run_b200(args):
 
     pool_host = [to_pinned(b) for b in make_pool(args, rank, args.pool, args.batch)]
     pool_dev = [tuple(x.to(dev) for x in b) for b in pool_host]
-    h2d_bytes = sum(x.numel() * x.element_size() for x in pool_host[0])
+    if args.feed == "packed":
+        from nnue_pytorch_b200.batch_build import build_batch
+
+        feed_host = make_packed_pool(args, rank, args.pool, args.batch)
+    else:
+        feed_host = pool_host
+    h2d_bytes = sum(x.numel() * x.element_size() for x in feed_host[0])
 
     def barrier():
         if world > 1:
@@ -209,10 +234,12 @@ def run_b200(args):
         else:
             # every batch starts in pinned host memory inside the timed region: its copy runs on a side
             # stream while the previous step computes, and the loss is read back by the host every step
-            host_iter = (pool_host[i % len(pool_host)] for i in range(n_steps))
+            host_iter = (feed_host[i % len(feed_host)] for i in range(n_steps))
             slots = [torch.empty(1, dtype=torch.float32).pin_memory() for _ in range(2)]
             done = [torch.cuda.Event(), torch.cuda.Event()]
             for i, batch in enumerate(DevicePrefetcher(host_iter, dev)):
+                if args.feed == "packed":
+                    batch = build_batch(batch[0], "baseline")  # index lists and targets written on the GPU
                 loss = step(batch)
                 slots[i % 2].copy_(loss.reshape(1), non_blocking=True)  # device -> host, every step
                 done[i % 2].record()
@@ -288,7 +315,7 @@ def run_b200(args):
                          f"{args.pool} distinct batches cycled",
         },
         "e2e": {"value": world * args.batch / (ms_e2e * 1e-3), "unit": UNIT, "ms_per_step": ms_e2e,
-                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4},
+                "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "feed": args.feed},
         "gpu_launches": int(launches) * args.steps,
         "gpu_launches_per_step": int(launches),
         "loss": loss_val,
@@ -312,6 +339,7 @@ def run_b200(args):
             "ranger_table": {"ms": opt_ms, "GBps_at_32B_per_element": opt_gbs,
                              "frac": (opt_gbs / peak) if opt_gbs else None},
         },
+        "spans_ms": {k: round(v["mean_ms"], 4) for k, v in sorted(spans.items())},
     }
     if not args.no_cpu_baseline and world == 1:
         line["cpu_baseline"] = cpu_reference_steps(args, steps=2, warmup=1)

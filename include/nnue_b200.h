@@ -349,6 +349,40 @@ int nnue_quant_eval(const int32_t* white_idx, const int32_t* black_idx,
                     int32_t L3, int32_t P, int32_t buckets,
                     const nnue_quant_params* h_qp, void* stream);
 
+/* ---- N3: device-side batch construction ----------------------------------
+ * Replaces the CPU fill of `SparseBatch` (data_loader/cpp/training_data_loader.cpp:29-73)
+ * and the shipping of expanded index lists (data_loader/_native.py:48-96): the
+ * host ships one 72-byte record per position, the GPU writes the tensors that
+ * `get_tensors` returns.  Index formula: model/modules/features/halfka_v2_hm.py:8-36.
+ *
+ * piece[s]: bits 0-5 square (0 = a1, 63 = h8), bits 6-8 piece type 1..6
+ * (P N B R Q K), bit 9 = white piece.  Slots >= count are ignored.  Lists are
+ * written in slot order and padded with -1.
+ * NNUE_LAYOUT_NATIVE: 12 piece planes, rows [0, 24576), K >= 32.
+ * NNUE_LAYOUT_FLAT:   11 planes (kings share plane 10): the `count` real rows
+ * [0, 22528), then the `count` matching factor rows [22528, 23232), K >= 64.
+ * us/them/outcome/score are float [B]; piece_count and bucket_idx
+ * ((count-1)/4, the PSQT / layer-stack bucket) are int64 [B] and may be NULL.
+ * A record with a count outside 2..32, a piece type outside 1..6, an outcome
+ * above 2, or not exactly one king per side is tallied in the device status
+ * word and yields two empty lists. */
+typedef struct nnue_packed_position {
+    uint16_t piece[32];
+    int16_t score;      /* centipawns */
+    uint8_t outcome2;   /* game result x 2: 0, 1, 2 */
+    uint8_t stm_white;  /* 1 = white to move */
+    uint8_t count;      /* pieces on the board, 2..32 */
+    uint8_t pad[3];
+} nnue_packed_position;
+
+enum { NNUE_LAYOUT_NATIVE = 0, NNUE_LAYOUT_FLAT = 1 };
+
+int nnue_batch_build_halfka(const nnue_packed_position* positions, int64_t B,
+                            int32_t layout, int32_t K, int32_t* white_idx,
+                            int32_t* black_idx, float* us, float* them,
+                            float* outcome, float* score, int64_t* piece_count,
+                            int64_t* bucket_idx, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -31,6 +31,7 @@ SOURCES = [
     "layer_stack.cu",
     "layer_stack_l1.cu",
     "layer_stack_tail.cu",
+    "batch_build.cu",
 ]
 
 NVCC_FLAGS = [

@@ -129,6 +129,7 @@ PROTOTYPES = {
         C.c_int,
         [_P] * 14 + [_I64, _I32, _I64, _I32, _I32, _I32, _I32, _I32, C.POINTER(QuantParams), _P],
     ),
+    "nnue_batch_build_halfka": (C.c_int, [_P, _I64, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
 }
 
 _lib = None

@@ -61,8 +61,9 @@ class FusedLayerStackFunction(autograd.Function):
         s = _stream(dev)
         with torch.cuda.device(dev), _span("layer_stack_fwd", dev):
             _lib.check(lib.nnue_ls_plan(_ptr(bucket), B, count, _ptr(plan), plan.numel() * 4, s), "nnue_ls_plan")
-            _lib.check(lib.nnue_ls_l1_fwd(_ptr(x), _ptr(W1), _ptr(b1), _ptr(plan), _ptr(o1), B, L1, count, s),
-                       "nnue_ls_l1_fwd")
+            with _span("ls_l1_fwd", dev):
+                _lib.check(lib.nnue_ls_l1_fwd(_ptr(x), _ptr(W1), _ptr(b1), _ptr(plan), _ptr(o1), B, L1, count, s),
+                           "nnue_ls_l1_fwd")
             _lib.check(lib.nnue_ls_tail_fwd(_ptr(o1), _ptr(plan), _ptr(W2), _ptr(b2), _ptr(W3), _ptr(b3.reshape(-1)),
                                             C.byref(params), _ptr(o2), _ptr(y), B, count, s), "nnue_ls_tail_fwd")
         ctx.save_for_backward(x, W1, W2, W3, o1, o2, plan)
@@ -91,6 +92,7 @@ class FusedLayerStackFunction(autograd.Function):
             _lib.check(lib.nnue_ls_tail_bwd(_ptr(o1), _ptr(o2), _ptr(plan), _ptr(W2), _ptr(W3), _ptr(gy),
                                             C.byref(ctx.params), _ptr(d_o1), _ptr(dW2), _ptr(db2), _ptr(dW3),
                                             _ptr(db3), _ptr(ws), ws.numel(), B, count, s), "nnue_ls_tail_bwd")
-            _lib.check(lib.nnue_ls_l1_bwd(_ptr(x), _ptr(W1), _ptr(d_o1), _ptr(plan), _ptr(dx), _ptr(dW1), _ptr(db1),
-                                          B, L1, count, s), "nnue_ls_l1_bwd")
+            with _span("ls_l1_bwd", dev):
+                _lib.check(lib.nnue_ls_l1_bwd(_ptr(x), _ptr(W1), _ptr(d_o1), _ptr(plan), _ptr(dx), _ptr(dW1),
+                                              _ptr(db1), B, L1, count, s), "nnue_ls_l1_bwd")
         return dx, None, dW1, db1, dW2, db2, dW3, db3.view(ctx.b3_shape), None, None

@@ -123,11 +123,18 @@ class TrainingBatch:
         return (self.us, self.them, self.white, self.black, self.outcome, self.score, self.piece_count)
 
 
+def generate_targets(batch: int, seed: int) -> tuple[np.ndarray, np.ndarray]:
+    """score [B, 1] ~ N(0, 400) cp clipped to +-3000 and outcome [B, 1] uniform
+    in {0, 0.5, 1}."""
+    rng = np.random.default_rng([seed, 0x7A7])
+    score = np.clip(rng.normal(0.0, 400.0, size=(batch, 1)), -3000, 3000).astype(np.float32)
+    outcome = (rng.integers(0, 3, size=(batch, 1)) * 0.5).astype(np.float32)
+    return score, outcome
+
+
 def generate_batch(batch: int, seed: int, layout: str = "baseline", fixed_count: int | None = None) -> TrainingBatch:
     pos = generate_positions(batch, seed, fixed_count)
     fn = {"baseline": baseline_indices, "native": native_indices}[layout]
-    rng = np.random.default_rng([seed, 0x7A7])
+    score, outcome = generate_targets(batch, seed)
     us = pos.stm_white.astype(np.float32)[:, None]
-    score = np.clip(rng.normal(0.0, 400.0, size=(batch, 1)), -3000, 3000).astype(np.float32)
-    outcome = (rng.integers(0, 3, size=(batch, 1)) * 0.5).astype(np.float32)
     return TrainingBatch(us, 1.0 - us, fn(pos, True), fn(pos, False), outcome, score, pos.piece_count.copy())

@@ -96,3 +96,21 @@ def test_product_never_imports_the_oracle():
                 src = open(os.path.join(dirpath, f)).read()
                 assert not re.search(r"^\s*(from|import)\s+oracle\b", src, flags=re.M), f
                 assert "_work/" not in src, f
+
+
+def test_packed_position_record_matches_the_header_struct():
+    import ctypes as C
+
+    from nnue_pytorch_b200 import batch_build
+
+    class Packed(C.Structure):  # field by field as declared in include/nnue_b200.h
+        _fields_ = [("piece", C.c_uint16 * 32), ("score", C.c_int16), ("outcome2", C.c_uint8),
+                    ("stm_white", C.c_uint8), ("count", C.c_uint8), ("pad", C.c_uint8 * 3)]
+
+    assert C.sizeof(Packed) == batch_build.PACKED_DTYPE.itemsize == 72
+    for name in ("piece", "score", "outcome2", "stm_white", "count", "pad"):
+        assert getattr(Packed, name).offset == batch_build.PACKED_DTYPE.fields[name][1]
+    header = open(os.path.join(ROOT, "include", "nnue_b200.h")).read()
+    body = header[header.index("typedef struct nnue_packed_position {"):header.index("} nnue_packed_position;")]
+    assert [ln.split()[1].split("[")[0].rstrip(";") for ln in body.splitlines()[1:] if ln.strip()] == [
+        "piece", "score", "outcome2", "stm_white", "count", "pad"]
