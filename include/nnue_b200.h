@@ -312,6 +312,30 @@ int nnue_ls_tail_bwd(const float* o1, const float* o2, const void* plan,
                      float* db2, float* dW3, float* db3, void* workspace,
                      size_t workspace_bytes, int64_t B, int32_t C, void* stream);
 
+/* Effective layer-stack weights of one step, all six tensors in one launch:
+ * w1 = fq(l1_w + repeat(l1f_w, C)), b1 likewise (model/modules/stacked_linear.py:96-127),
+ * w2, b2, w3, b3 = fq of their parameters, fq(v) = round_half_even(v * scale) / scale
+ * when scales.quantize (model/quantize.py:49-50), else v.  l1f_w / l1f_b may both be NULL.
+ * Shapes: l1_w [C*32, L1], l1_b [C*32], l1f_w [32, L1], l1f_b [32], l2_w [C*32, 64],
+ * l2_b [C*32], out_w [C, 128], out_b [C]; outputs alike.
+ * The straight-through backward is the identity on every tensor plus
+ * nnue_ls_fold_grads: d_l1f_w = sum over buckets of dW1 (bucket order), d_l1f_b likewise. */
+typedef struct nnue_ls_weight_scales {
+    float w1, b1, w2, b2, w3, b3;
+    int32_t quantize;
+} nnue_ls_weight_scales;
+
+int nnue_ls_effective_weights(const float* l1_w, const float* l1_b,
+                              const float* l1f_w, const float* l1f_b,
+                              const float* l2_w, const float* l2_b,
+                              const float* out_w, const float* out_b,
+                              const nnue_ls_weight_scales* h_scales,
+                              float* w1, float* b1, float* w2, float* b2,
+                              float* w3, float* b3, int32_t L1, int32_t C,
+                              void* stream);
+int nnue_ls_fold_grads(const float* dW1, const float* db1, float* d_l1f_w,
+                       float* d_l1f_b, int32_t L1, int32_t C, void* stream);
+
 /* ---- Q: integer quantized evaluation ----------------------------------
  * Integer restatement of the fake-quantized forward defined by
  * model/quantize.py:36-56,133-147, model/modules/layer_stacks.py:33-84 and
@@ -348,6 +372,35 @@ int nnue_quant_eval(const int32_t* white_idx, const int32_t* black_idx,
                     int64_t B, int32_t K, int64_t N, int32_t L1, int32_t L2,
                     int32_t L3, int32_t P, int32_t buckets,
                     const nnue_quant_params* h_qp, void* stream);
+
+/* ---- L: training loss and its gradient, one launch ------------------------
+ * `calculate_sf_loss` with `remap_tablebase_score` (model/nnue.py:18-69), fused
+ * with the PSQT term of the model output (model/model.py:107-133) and the
+ * scaling to centipawns:
+ *   net_i = y_i + (wpsqt_i - bpsqt_i) * (us_i - 0.5)      (PSQT inputs may be NULL)
+ *   loss  = sum_i w_i |pt_i - qf(net_i * net_scale)|^pow_exp / sum_i w_i
+ * `loss` is a device scalar.  d_y (and d_wpsqt, d_bpsqt), when not NULL,
+ * receive d loss / d y (d wpsqt, d bpsqt), float [B].  `workspace` holds
+ * nnue_sf_loss_workspace_bytes() bytes, 8-byte aligned, zeroed once by the
+ * caller before the first call and left zeroed by every call; two calls that
+ * share a workspace must not overlap on the GPU.  All sums run in a fixed order. */
+typedef struct nnue_loss_params {
+    float in_offset, out_offset;      /* 270, 270 */
+    float in_scaling, out_scaling;    /* 340, 380 */
+    float pow_exp;                    /* 2.5 */
+    float qp_asymmetry;               /* 0 */
+    float w1, w2;                     /* 0, 0.5 */
+    float tb_remap_base, tb_remap_scale, tb_remap_decay; /* 4000, 4000, 0.85 */
+    float lambda;                     /* weight of the search score against the game outcome */
+    float net_scale;                  /* nnue2score = 600 */
+} nnue_loss_params;
+
+size_t nnue_sf_loss_workspace_bytes(void);
+int nnue_sf_loss(const float* y, const float* wpsqt, const float* bpsqt,
+                 const float* us, const float* score, const float* outcome,
+                 const nnue_loss_params* h_params, float* loss, float* d_y,
+                 float* d_wpsqt, float* d_bpsqt, void* workspace, int64_t B,
+                 void* stream);
 
 /* ---- N3: device-side batch construction ----------------------------------
  * Replaces the CPU fill of `SparseBatch` (data_loader/cpp/training_data_loader.cpp:29-73)

@@ -31,7 +31,9 @@ SOURCES = [
     "layer_stack.cu",
     "layer_stack_l1.cu",
     "layer_stack_tail.cu",
+    "layer_stack_weights.cu",
     "batch_build.cu",
+    "sf_loss.cu",
 ]
 
 NVCC_FLAGS = [

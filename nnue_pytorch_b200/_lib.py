@@ -60,6 +60,20 @@ class QuantParams(C.Structure):
     ]
 
 
+class LsWeightScales(C.Structure):
+    """Mirror of `nnue_ls_weight_scales`."""
+
+    _fields_ = [(n, C.c_float) for n in ("w1", "b1", "w2", "b2", "w3", "b3")] + [("quantize", C.c_int32)]
+
+
+class LossParams(C.Structure):
+    """Mirror of `nnue_loss_params`."""
+
+    _fields_ = [(n, C.c_float) for n in (
+        "in_offset", "out_offset", "in_scaling", "out_scaling", "pow_exp", "qp_asymmetry", "w1", "w2",
+        "tb_remap_base", "tb_remap_scale", "tb_remap_decay", "lam", "net_scale")]
+
+
 class LsParams(C.Structure):
     """Mirror of `nnue_ls_params`."""
 
@@ -129,6 +143,10 @@ PROTOTYPES = {
         C.c_int,
         [_P] * 14 + [_I64, _I32, _I64, _I32, _I32, _I32, _I32, _I32, C.POINTER(QuantParams), _P],
     ),
+    "nnue_ls_effective_weights": (C.c_int, [_P] * 8 + [C.POINTER(LsWeightScales)] + [_P] * 6 + [_I32, _I32, _P]),
+    "nnue_ls_fold_grads": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _P]),
+    "nnue_sf_loss_workspace_bytes": (_SZ, []),
+    "nnue_sf_loss": (C.c_int, [_P] * 6 + [C.POINTER(LossParams), _P, _P, _P, _P, _P, _I64, _P]),
     "nnue_batch_build_halfka": (C.c_int, [_P, _I64, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
 }
 

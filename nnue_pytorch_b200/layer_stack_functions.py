@@ -96,3 +96,49 @@ class FusedLayerStackFunction(autograd.Function):
                 _lib.check(lib.nnue_ls_l1_bwd(_ptr(x), _ptr(W1), _ptr(d_o1), _ptr(plan), _ptr(dx), _ptr(dW1),
                                               _ptr(db1), B, L1, count, s), "nnue_ls_l1_bwd")
         return dx, None, dW1, db1, dW2, db2, dW3, db3.view(ctx.b3_shape), None, None
+
+
+class LayerStackWeightsFunction(autograd.Function):
+    """(w1, b1, w2, b2, w3, b3) = effective weights of this step: the shared
+    factor layer merged into every bucket of the first layer
+    (model/modules/stacked_linear.py:96-127 of the reference project) and the
+    weight fake quantization with its straight-through gradient
+    (model/quantize.py:49-50), written by one kernel launch.  Backward: every
+    gradient passes through; the factor layer receives the first layer's
+    gradient summed over buckets."""
+
+    @staticmethod
+    def forward(ctx, l1_w, l1_b, l1f_w, l1f_b, l2_w, l2_b, out_w, out_b, quantization, fake_quantize_weights):
+        dev = _require_cuda(l1_w, l1_b, l1f_w, l1f_b, l2_w, l2_b, out_w, out_b)
+        ins = [t.detach().contiguous() for t in (l1_w, l1_b, l1f_w, l1f_b, l2_w, l2_b, out_w, out_b)]
+        count = out_w.shape[0]
+        L1 = l1_w.shape[1]
+        assert l1_w.shape == (count * 32, L1) and l1f_w.shape == (32, L1) and l2_w.shape == (count * 32, 64)
+        assert out_w.shape == (count, 128) and l1_b.numel() == count * 32 and l1f_b.numel() == 32
+        sc = _lib.LsWeightScales()
+        d = quantization.weight_scales_dict
+        sc.w1, sc.b1 = d["ls_l1_weight"], d["ls_l1_bias"]
+        sc.w2, sc.b2 = d["ls_l2_weight"], d["ls_l2_bias"]
+        sc.w3, sc.b3 = d["ls_output_weight"], d["ls_output_bias"]
+        sc.quantize = 1 if fake_quantize_weights else 0
+        outs = [torch.empty_like(ins[i]) for i in (0, 1, 4, 5, 6, 7)]
+        with torch.cuda.device(dev):
+            _lib.check(
+                _lib.load().nnue_ls_effective_weights(*[_ptr(t) for t in ins], C.byref(sc), *[_ptr(t) for t in outs],
+                                                      L1, count, _stream(dev)),
+                "nnue_ls_effective_weights",
+            )
+        ctx.dims = (L1, count, l1f_b.shape)
+        return tuple(outs)
+
+    @staticmethod
+    def backward(ctx, g_w1, g_b1, g_w2, g_b2, g_w3, g_b3):
+        L1, count, fb_shape = ctx.dims
+        g_w1, g_b1 = g_w1.contiguous(), g_b1.contiguous()
+        dev = g_w1.device
+        g_fw = torch.empty(32, L1, device=dev)
+        g_fb = torch.empty(fb_shape, device=dev)
+        with torch.cuda.device(dev):
+            _lib.check(_lib.load().nnue_ls_fold_grads(_ptr(g_w1), _ptr(g_b1), _ptr(g_fw), _ptr(g_fb), L1, count,
+                                                      _stream(dev)), "nnue_ls_fold_grads")
+        return g_w1, g_b1, g_fw, g_fb, g_w2, g_b2, g_w3, g_b3, None, None

@@ -94,20 +94,15 @@ class LayerStacks(nn.Module):
 
     fused = True  # use the bucket-aware kernels when the shapes allow it
 
-    def _effective(self, layer, fake_quantize_weights):
-        w, b = layer._weights()
-        if fake_quantize_weights:
-            w = self.quantization.fake_quantize_weights(w, f"{layer.layer_key}_weight")
-            b = self.quantization.fake_quantize_weights(b, f"{layer.layer_key}_bias")
-        return w, b
-
     def forward(self, x, ls_indices, fake_quantize_acts=True, fake_quantize_weights=True):
         from . import layer_stack_functions as lsf
 
         if self.fused and lsf.supported(x, self.L1, self.L2, self.L3, self.count):
-            w1, b1 = self._effective(self.l1, fake_quantize_weights)
-            w2, b2 = self._effective(self.l2, fake_quantize_weights)
-            w3, b3 = self._effective(self.output, fake_quantize_weights)
+            l1, l2, out = self.l1, self.l2, self.output
+            w1, b1, w2, b2, w3, b3 = lsf.LayerStackWeightsFunction.apply(
+                l1.linear.weight, l1.linear.bias, l1.factorized_linear.weight, l1.factorized_linear.bias,
+                l2.linear.weight, l2.linear.bias, out.linear.weight, out.linear.bias, self.quantization,
+                fake_quantize_weights)
             return lsf.FusedLayerStackFunction.apply(x, ls_indices, w1, b1, w2, b2, w3, b3, self.quantization,
                                                      fake_quantize_acts)
         o1 = self.l1(x, ls_indices, fake_quantize_weights)
@@ -141,10 +136,17 @@ class NNUEModel(nn.Module):
         self.layer_stacks = LayerStacks(num_ls_buckets, self.L1, self.L2, self.L3, self.quantization)
         self.input.init_weights()
 
-    def forward(self, us, them, white_indices, black_indices, piece_count, fake_quantize_acts=True, fake_quantize_weights=True):
+    def forward_parts(self, us, them, white_indices, black_indices, piece_count, fake_quantize_acts=True,
+                      fake_quantize_weights=True):
+        """(layer-stack output, white PSQT, black PSQT), each [B, 1]: the three
+        terms `forward` combines."""
         bucket = (piece_count - 1) // 4
         l0, wpsqt, bpsqt = self.input(us, them, white_indices, black_indices, bucket, fake_quantize_acts, fake_quantize_weights)
-        y = self.layer_stacks(l0, bucket, fake_quantize_acts, fake_quantize_weights)
+        return self.layer_stacks(l0, bucket, fake_quantize_acts, fake_quantize_weights), wpsqt, bpsqt
+
+    def forward(self, us, them, white_indices, black_indices, piece_count, fake_quantize_acts=True, fake_quantize_weights=True):
+        y, wpsqt, bpsqt = self.forward_parts(us, them, white_indices, black_indices, piece_count, fake_quantize_acts,
+                                             fake_quantize_weights)
         # PSQT: averaged over the perspectives, sign by side to move
         return y + (wpsqt - bpsqt) * (us - 0.5)
 
@@ -210,7 +212,7 @@ class TrainStep:
 
     def __init__(self, model: NNUEModel, lr: float = 8.75e-4, clip: float = 2.0, lam: float = 1.0,
                  loss_params: LossParams | None = None, grad_hook=None, grad_prescale: float = 1.0,
-                 table_exchange=None):
+                 table_exchange=None, fused_loss: bool = True):
         """`grad_prescale`: factor that turns what `grad_hook` leaves in `.grad` into the true
         gradient (1/world when the hook sums over ranks without averaging).
         `table_exchange`: a `ddp.ShardedTableExchange` that owns the feature-transformer table
@@ -218,6 +220,7 @@ class TrainStep:
         optimizer's parameter groups."""
         self.model = model
         self.clip, self.lam = clip, lam
+        self.fused_loss = fused_loss  # False: the loss as elementwise torch ops (`sf_loss`) under autograd
         self.loss_params = loss_params or LossParams()
         self.grad_hook = grad_hook
         self.table_exchange = table_exchange
@@ -244,12 +247,29 @@ class TrainStep:
         y = self.model(us, them, white, black, piece_count, True, True)
         return sf_loss(y * self.model.quantization.nnue2score, score, outcome, self.loss_params, self.lam)
 
+    def _loss_and_backward(self, batch):
+        """Forward, loss and backward with the loss head (PSQT term, scaling,
+        loss, its gradient) as one kernel: the backward pass starts from the
+        gradients of the three model outputs."""
+        from .loss_functions import sf_loss_fused
+
+        us, them, white, black, outcome, score, piece_count = batch
+        y, wpsqt, bpsqt = self.model.forward_parts(us, them, white, black, piece_count, True, True)
+        loss, d_y, d_wp, d_bp = sf_loss_fused(y, wpsqt, bpsqt, us, score, outcome, self.loss_params, self.lam,
+                                              self.model.quantization.nnue2score)
+        self.optimizer.zero_grad(set_to_none=True)
+        torch.autograd.backward([y, wpsqt, bpsqt], [d_y.view_as(y), d_wp.view_as(wpsqt), d_bp.view_as(bpsqt)])
+        return loss
+
     def __call__(self, batch):
         from . import _launch
 
-        loss = self.loss(batch)
-        self.optimizer.zero_grad(set_to_none=True)
-        loss.backward()
+        if self.fused_loss and batch[0].is_cuda:
+            loss = self._loss_and_backward(batch)
+        else:
+            loss = self.loss(batch)
+            self.optimizer.zero_grad(set_to_none=True)
+            loss.backward()
         ex = self.table_exchange
         if ex is not None:
             ex.param.grad = None  # its gradient lives in the exchange's buffer
