@@ -220,6 +220,8 @@ def run_b200(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    host_ms = [0.0]
+
     def timed(n_steps, resident: bool):
         """Returns (ms per step over this rank, last loss)."""
         from nnue_pytorch_b200.prefetch import DevicePrefetcher
@@ -229,8 +231,10 @@ def run_b200(args):
         loss_host = 0.0
         e0.record()
         if resident:
+            t_host = time.perf_counter()
             for i in range(n_steps):
                 loss = step(pool_dev[i % len(pool_dev)])
+            host_ms[0] = (time.perf_counter() - t_host) * 1e3 / n_steps  # host time to enqueue one step
         else:
             # every batch starts in pinned host memory inside the timed region: its copy runs on a side
             # stream while the previous step computes, and the loss is read back by the host every step
@@ -318,6 +322,7 @@ def run_b200(args):
                 "h2d_bytes_per_step": h2d_bytes, "d2h_bytes_per_step": 4, "feed": args.feed},
         "gpu_launches": int(launches) * args.steps,
         "gpu_launches_per_step": int(launches),
+        "host_enqueue_ms_per_step": round(host_ms[0], 3),
         "loss": loss_val,
         "clocks": clocks.summary(),
         "roofline": {

@@ -242,6 +242,29 @@ int nnue_grad_sumsq(const float* grad, int64_t n, float* d_out_sumsq,
 int nnue_clip_coef(const float* d_sumsq, float max_norm, float prescale,
                    float* d_coef, void* stream);
 
+/* Several tensors per launch (at most NNUE_MULTI_MAX per launch; longer lists
+ * are split).  Same arithmetic as nnue_grad_sumsq / nnue_rangerlite_update
+ * (no row flags); each tensor carries its own constants, as each of the
+ * trainer's ten parameter groups (model/nnue.py:117-182) may differ.  The
+ * arrays are HOST arrays; their contents are copied into the launch. */
+#define NNUE_MULTI_MAX 16
+typedef struct nnue_ranger_tensor {
+    float* p;
+    const float* grad;
+    float* grad_ma;
+    float* neg_grad_ma;   /* NULL unless hp.use_pnm */
+    float* variance_ma;
+    float* slow;          /* NULL unless hp.do_merge */
+    int64_t n;
+    nnue_ranger_hparams hp;
+} nnue_ranger_tensor;
+
+int nnue_grad_sumsq_multi(const float* const* h_grads, const int64_t* h_n,
+                          int32_t count, float* d_out_sumsq, void* stream);
+int nnue_rangerlite_update_multi(const nnue_ranger_tensor* h_tensors,
+                                 int32_t count, const float* d_grad_scale,
+                                 void* stream);
+
 /* ---- A14: data-parallel exchange fused with the optimizer ----------------
  * Replaces, for the feature-transformer table, the DistributedDataParallel
  * all-reduce of trainer/engine.py:149-162 followed by a full optimizer step on

@@ -26,6 +26,7 @@ SOURCES = [
     "ft_segment.cu",
     "ft_table.cu",
     "ranger_lite.cu",
+    "multi_tensor.cu",
     "ddp_fused.cu",
     "quant_eval.cu",
     "layer_stack.cu",

@@ -218,8 +218,10 @@ def fused_backward(
 
 
 # --------------------------------------------------------------------------
-def prepare_table(weight, virtual_weight, l1_size: int, scale_main: float, scale_psqt: float) -> torch.Tensor:
-    """fq(weight + virtual_weight.repeat(N // n_virtual, 1)) in one pass (see nnue_ft_prepare_table)."""
+def prepare_table(weight, virtual_weight, l1_size: int, scale_main: float, scale_psqt: float,
+                  out: torch.Tensor | None = None, span: str = "prepare_table") -> torch.Tensor:
+    """fq(weight + virtual_weight.repeat(N // n_virtual, 1)) in one pass (see nnue_ft_prepare_table).
+    `out`: optional contiguous destination with at least weight.numel() elements."""
     dev = _require_cuda(weight) if virtual_weight is None else _require_cuda(weight, virtual_weight)
     assert weight.dtype == torch.float32 and weight.dim() == 2 and weight.is_contiguous()
     N, W = weight.shape
@@ -228,8 +230,11 @@ def prepare_table(weight, virtual_weight, l1_size: int, scale_main: float, scale
         assert virtual_weight.dtype == torch.float32 and virtual_weight.is_contiguous()
         assert virtual_weight.shape[1] == W and N % virtual_weight.shape[0] == 0
         nv = virtual_weight.shape[0]
-    out = torch.empty_like(weight)
-    with torch.cuda.device(dev), _span("prepare_table", dev):
+    if out is None:
+        out = torch.empty_like(weight)
+    else:
+        assert out.dtype == torch.float32 and out.is_contiguous() and out.numel() >= weight.numel() and out.device == dev
+    with torch.cuda.device(dev), _span(span, dev):
         st = _lib.load().nnue_ft_prepare_table(
             _ptr(weight), _ptr(virtual_weight), _ptr(out), N, nv, l1_size, W - l1_size,
             float(scale_main), float(scale_psqt), _stream(dev),
@@ -280,6 +285,38 @@ def ranger_update(p, grad, grad_ma, neg_grad_ma, variance_ma, slow, row_active, 
             _ptr(row_active), _ptr(grad_scale), rows, width, C.byref(hp), _stream(dev),
         )
     _lib.check(st, "nnue_rangerlite_update")
+
+
+def ranger_update_multi(items, grad_scale) -> None:
+    """items: list of (p, grad, grad_ma, neg_grad_ma, variance_ma, slow, hp): all
+    of them updated by one launch per sixteen tensors."""
+    if not items:
+        return
+    dev = _require_cuda(items[0][0])
+    arr = (_lib.RangerTensor * len(items))()
+    for d, (p, grad, grad_ma, neg_grad_ma, variance_ma, slow, hp) in zip(arr, items):
+        for t in (p, grad, grad_ma, neg_grad_ma, variance_ma, slow):
+            if t is not None:
+                assert t.dtype == torch.float32 and t.is_contiguous() and t.numel() == p.numel() and t.device == dev
+        d.p, d.grad, d.grad_ma, d.neg_grad_ma = _ptr(p), _ptr(grad), _ptr(grad_ma), _ptr(neg_grad_ma)
+        d.variance_ma, d.slow, d.n, d.hp = _ptr(variance_ma), _ptr(slow), p.numel(), hp
+    with torch.cuda.device(dev), _span("ranger_small", dev):
+        st = _lib.load().nnue_rangerlite_update_multi(arr, len(items), _ptr(grad_scale), _stream(dev))
+    _lib.check(st, "nnue_rangerlite_update_multi")
+
+
+def grad_sumsq_multi(grads, out_sumsq) -> None:
+    """out_sumsq += sum over the listed gradients of their sums of squares."""
+    if not grads:
+        return
+    dev = _require_cuda(out_sumsq, *grads)
+    for g in grads:
+        assert g.dtype == torch.float32 and g.is_contiguous()
+    ptrs = (C.c_void_p * len(grads))(*[g.data_ptr() for g in grads])
+    sizes = (C.c_int64 * len(grads))(*[g.numel() for g in grads])
+    with torch.cuda.device(dev):
+        st = _lib.load().nnue_grad_sumsq_multi(ptrs, sizes, len(grads), _ptr(out_sumsq), _stream(dev))
+    _lib.check(st, "nnue_grad_sumsq_multi")
 
 
 def lookahead_merge(p, slow, alpha: float) -> None:

@@ -41,6 +41,16 @@ class RangerHParams(C.Structure):
     ]
 
 
+class RangerTensor(C.Structure):
+    """Mirror of `nnue_ranger_tensor`."""
+
+    _fields_ = [("p", C.c_void_p), ("grad", C.c_void_p), ("grad_ma", C.c_void_p), ("neg_grad_ma", C.c_void_p),
+                ("variance_ma", C.c_void_p), ("slow", C.c_void_p), ("n", C.c_int64), ("hp", RangerHParams)]
+
+
+MULTI_MAX = 16  # NNUE_MULTI_MAX
+
+
 class QuantParams(C.Structure):
     """Mirror of `nnue_quant_params`."""
 
@@ -126,6 +136,8 @@ PROTOTYPES = {
         C.c_int,
         [C.POINTER(_P), _I32, _I32, _I64, _I64, _P, _P, _P, _P, _P, _P, C.POINTER(RangerHParams), _P],
     ),
+    "nnue_grad_sumsq_multi": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_int64), _I32, _P, _P]),
+    "nnue_rangerlite_update_multi": (C.c_int, [C.POINTER(RangerTensor), _I32, _P, _P]),
     "nnue_lookahead_merge": (C.c_int, [_P, _P, _I64, C.c_float, _P]),
     "nnue_grad_sumsq": (C.c_int, [_P, _I64, _P, _P]),
     "nnue_clip_coef": (C.c_int, [_P, C.c_float, C.c_float, _P, _P]),

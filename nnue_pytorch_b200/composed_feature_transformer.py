@@ -15,7 +15,7 @@ import torch
 from torch import nn
 
 from .double_ft_functions import double_feature_transform
-from .fused_ft_functions import FusedDoubleFtFunction, PrepareTableFunction
+from .fused_ft_functions import FusedDoubleFtFunction, PrepareBiasFunction, PrepareTableFunction
 
 _FAKE_QUANTIZE_EPS = 1e-5  # model/quantize.py:10 of the reference
 
@@ -74,10 +74,8 @@ class ComposedFeatureTransformer(nn.Module):
                 else:
                     tables.append(PrepareTableFunction.apply(f.weight, virt, self.l1_size, sm, sp))
             merged = tables[0] if len(tables) == 1 else torch.cat(tables, dim=0)
-            if fake_quantize_weights:
-                b = q.fake_quantize_weights(b, "ft_bias")
-            bias = torch.cat([b, torch.zeros_like(self.bias[self.l1_size :], dtype=b.dtype)], dim=0)
-            return merged, bias
+            sb = q.weight_scales_dict["ft_bias"] if fake_quantize_weights else 0.0
+            return merged, PrepareBiasFunction.apply(self.bias, self.l1_size, sb)
         tables = [f.merged_weight() for f in self.features]
         merged = tables[0] if len(tables) == 1 else torch.cat(tables, dim=0)
         if fake_quantize_weights:

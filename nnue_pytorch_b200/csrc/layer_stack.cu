@@ -16,16 +16,18 @@
 
 namespace nnue {
 
-// Single CTA: per-thread histograms over a contiguous slice of positions, a
-// scan per bucket across threads, then an in-order fill (stable).
-constexpr int kPlanThreads = 512;
-constexpr int kMaxBuckets = 16;  // kMaxBuckets * kPlanThreads counters fit 48 KB of shared memory
+// Single CTA: per-thread histograms over a contiguous slice of positions, one
+// warp per bucket scans them across the threads, tiles are listed in parallel,
+// then an in-order fill (stable).
+constexpr int kPlanThreads = 1024;
+constexpr int kMaxBuckets = 16;
+// counters [C][kPlanThreads] live in dynamic shared memory (64 KB at 16 buckets)
 __global__ void __launch_bounds__(kPlanThreads)
     k_ls_plan(const int64_t* __restrict__ bucket, int64_t B, int C, int32_t* __restrict__ plan,
               unsigned long long* status) {
-    extern __shared__ int32_t s_cnt[];  // [C][kPlanThreads] then [C]
-    int32_t* s_base = s_cnt + C * kPlanThreads;
-    const int tid = threadIdx.x;
+    extern __shared__ int32_t s_cnt[];  // [C][kPlanThreads]
+    __shared__ int32_t s_size[kMaxBuckets], s_base[kMaxBuckets], s_tile0[kMaxBuckets + 1];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int64_t per = (B + kPlanThreads - 1) / kPlanThreads;
     const int64_t lo = min(B, tid * per), hi = min(B, lo + per);
     for (int c = 0; c < C; ++c) s_cnt[c * kPlanThreads + tid] = 0;
@@ -35,14 +37,23 @@ __global__ void __launch_bounds__(kPlanThreads)
         s_cnt[(int)b * kPlanThreads + tid] += 1;
     }
     __syncthreads();
-    if (tid < C) {  // exclusive scan over the threads, one bucket per scanning thread
-        int run = 0;
-        for (int t = 0; t < kPlanThreads; ++t) {
-            const int v = s_cnt[tid * kPlanThreads + t];
-            s_cnt[tid * kPlanThreads + t] = run;
+    if (warp < C) {  // exclusive scan of bucket `warp` over the threads: 32 consecutive counters per lane
+        int32_t* row = s_cnt + warp * kPlanThreads + lane * (kPlanThreads / 32);
+        int sum = 0;
+        for (int i = 0; i < kPlanThreads / 32; ++i) sum += row[i];
+        int incl = sum;
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) {
+            const int v = __shfl_up_sync(kFullMask, incl, d);
+            if (lane >= d) incl += v;
+        }
+        int run = incl - sum;
+        for (int i = 0; i < kPlanThreads / 32; ++i) {
+            const int v = row[i];
+            row[i] = run;
             run += v;
         }
-        s_base[tid] = run;  // bucket size for now
+        if (lane == 31) s_size[warp] = incl;
     }
     __syncthreads();
     const int64_t T = ls_max_tiles(B, C);
@@ -54,21 +65,25 @@ __global__ void __launch_bounds__(kPlanThreads)
     if (tid == 0) {
         int pos = 0, tile = 0;
         for (int c = 0; c < C; ++c) {
-            const int n = s_base[c];
             s_base[c] = pos;
+            s_tile0[c] = tile;
             bucket_tile[c] = tile;
-            for (int o = 0; o < n; o += kTP) {
-                tile_start[tile] = pos + o;
-                tile_count[tile] = min(kTP, n - o);
-                tile_bucket[tile] = c;
-                ++tile;
-            }
-            pos += n;
+            pos += s_size[c];
+            tile += (s_size[c] + kTP - 1) / kTP;
         }
+        s_tile0[C] = tile;
         bucket_tile[C] = tile;
         plan[0] = tile;
     }
     __syncthreads();
+    for (int t = tid; t < s_tile0[C]; t += kPlanThreads) {
+        int c = 0;
+        while (t >= s_tile0[c + 1]) ++c;
+        const int o = (t - s_tile0[c]) * kTP;
+        tile_start[t] = s_base[c] + o;
+        tile_count[t] = min(kTP, s_size[c] - o);
+        tile_bucket[t] = c;
+    }
     // s_cnt[c][tid] holds this thread's first slot inside bucket c; advance it in place
     for (int64_t p = lo; p < hi; ++p) {
         int64_t b = bucket[p];
@@ -98,7 +113,15 @@ extern "C" int nnue_ls_plan(const int64_t* bucket, int64_t B, int32_t C, void* p
     NNUE_REQUIRE(B == 0 || bucket, NNUE_ERR_ARG, "nnue_ls_plan: null bucket list");
     unsigned long long* status = device_status_ptr();
     NNUE_REQUIRE(status, NNUE_ERR_CUDA, "nnue_ls_plan: no device status word");
-    const size_t smem = ((size_t)C * kPlanThreads + C) * sizeof(int32_t);
+    const size_t smem = (size_t)C * kPlanThreads * sizeof(int32_t);
+    static bool opted[64] = {};  // more than 48 KB of dynamic shared memory needs the opt-in, once per device
+    int dev = 0;
+    NNUE_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev < 0 || dev >= 64 || !opted[dev]) {
+        NNUE_CUDA_TRY(cudaFuncSetAttribute(k_ls_plan, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                           kMaxBuckets * kPlanThreads * (int)sizeof(int32_t)));
+        if (dev >= 0 && dev < 64) opted[dev] = true;
+    }
     k_ls_plan<<<1, kPlanThreads, smem, static_cast<cudaStream_t>(stream)>>>(
         bucket, B, C, static_cast<int32_t*>(plan), status);
     NNUE_CUDA_TRY(cudaGetLastError());

@@ -12,6 +12,7 @@ a segment reduction that writes every row once (no `torch.zeros` pass).
 
 from __future__ import annotations
 
+import torch
 from torch import autograd
 
 from . import _launch
@@ -75,3 +76,23 @@ class PrepareTableFunction(autograd.Function):
         if _launch.is_grad_sink(grad):
             grad = None  # the data-parallel exchange reads the sink buffer itself
         return grad, gv, None, None, None
+
+
+class PrepareBiasFunction(autograd.Function):
+    """bias_full = [fq(bias[:l1]), zeros(psqt)]: the bias the operator adds
+    (composed_feature_transformer.py:61-76 of the reference fake-quantizes the
+    bias and drops its PSQT part, which never trains).  One fill and one kernel;
+    the backward is a view of the incoming gradient."""
+
+    @staticmethod
+    def forward(ctx, bias, l1_size, scale):
+        l1 = int(l1_size)
+        out = torch.zeros_like(bias)
+        _launch.prepare_table(bias.detach()[:l1].reshape(1, l1), None, l1, scale, 1.0, out=out, span="prepare_bias")
+        ctx.pad = bias.numel() - l1
+        ctx.l1 = l1
+        return out
+
+    @staticmethod
+    def backward(ctx, grad):
+        return torch.nn.functional.pad(grad[: ctx.l1], (0, ctx.pad)), None, None

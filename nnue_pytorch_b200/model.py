@@ -279,9 +279,9 @@ class TrainStep:
             ft_sumsq = ex.reduce()
         if self._clipping:
             self._sumsq.zero_()
-            for p in self.model.parameters():
-                if p.grad is not None:
-                    _launch.grad_sumsq(p.grad, self._sumsq)
+            grads = [p.grad if p.grad.is_contiguous() else p.grad.contiguous()
+                     for p in self.model.parameters() if p.grad is not None]
+            _launch.grad_sumsq_multi(grads, self._sumsq)
             if ex is not None:
                 self._sumsq.add_(ft_sumsq)
             _launch.clip_coef(self._sumsq, self.clip, self._coef, self.grad_prescale)

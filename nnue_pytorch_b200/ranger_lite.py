@@ -191,15 +191,27 @@ class RangerLite(torch.optim.Optimizer):
                 self.param_size = count
             var_norm = torch.sqrt(total / self.param_size).clamp_min(self.eps).item()
 
+        small = []  # tensors without row flags share launches
         for p, group in active:
             st = self.state[p]
             wd = group.get("weight_decay", 0.0)
             wd_keep = 1.0 - (wd * group["lr"] / var_norm) if (wd and var_norm is not None) else 1.0
             hp = self._hparams(group, st["step"], merge, phase=2 if decayed else 0, wd_keep=wd_keep)
             rows = self._rows_flag(p, group)
-            _launch.ranger_update(p.data, self._grad(p), st["grad_ma"], st.get("neg_grad_ma"), st["variance_ma"],
-                                  st.get("lookahead_params"), rows, self.grad_scale, hp)
+            args = (p.data, self._grad(p), st["grad_ma"], st.get("neg_grad_ma"), st["variance_ma"],
+                    st.get("lookahead_params"))
+            if rows is None and p.numel() <= self.MULTI_TENSOR_LIMIT and p.data.is_contiguous():
+                small.append(args + (hp,))
+            else:
+                _launch.ranger_update(*args, rows, self.grad_scale, hp)
+        by_device: dict = {}
+        for item in small:
+            by_device.setdefault(item[0].device, []).append(item)
+        for items in by_device.values():
+            _launch.ranger_update_multi(items, self.grad_scale)
         return loss
+
+    MULTI_TENSOR_LIMIT = 1 << 22  # elements; larger tensors get a launch of their own
 
     @staticmethod
     def _grad(p):
