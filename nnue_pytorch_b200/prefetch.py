@@ -19,11 +19,12 @@ class DevicePrefetcher:
     """Wraps an iterable of tuples of pinned CPU tensors; yields tuples of CUDA
     tensors whose copy was issued one iteration earlier."""
 
-    def __init__(self, batches: Iterable[tuple[torch.Tensor, ...]], device: torch.device, depth: int = 2):
+    def __init__(self, batches: Iterable[tuple[torch.Tensor, ...]], device: torch.device, depth: int = 2,
+                 copy_stream: torch.cuda.Stream | None = None):
         self.batches = batches
         self.device = device
         self.depth = max(2, depth)
-        self.copy_stream = torch.cuda.Stream(device)
+        self.copy_stream = copy_stream if copy_stream is not None else torch.cuda.Stream(device)
 
     def _issue(self, host_batch, slot):
         compute = torch.cuda.current_stream(self.device)

@@ -70,6 +70,39 @@ class QuantizedNet:
         return cls(table, bias, l1_w, l1_b, ls.l2.linear.weight, ls.l2.linear.bias, ls.output.linear.weight,
                    ls.output.linear.bias, model.L1, count, model.quantization)
 
+    @classmethod
+    def from_integers(cls, nf, quantization: QuantizationManager | None = None,
+                      device: torch.device | str = "cuda") -> "QuantizedNet":
+        """From the integer tensors of a `.nnue` file (`serialize.NNUEFile`): nothing is rescaled
+        or rounded again, the kernel evaluates the stored numbers."""
+        import numpy as np
+
+        q = quantization or QuantizationManager()
+        dev = torch.device(device)
+        if dev.type != "cuda":
+            raise RuntimeError("QuantizedNet needs a CUDA device (there is no CPU path)")
+        self = cls.__new__(cls)
+        self.consts = q.integer_constants()
+        self.device = dev
+        self.L1, self.buckets, self.P = int(nf.L1), int(nf.buckets), int(nf.P)
+        self.L2, self.L3 = int(nf.L2), int(nf.L3)
+        self.N = int(nf.ft_weight.shape[0])
+
+        def put(a, dtype):
+            return torch.from_numpy(np.ascontiguousarray(a)).to(device=dev, dtype=dtype).contiguous()
+
+        self.ft_w = put(nf.ft_weight, torch.int16)
+        self.ft_psqt = put(nf.ft_psqt, torch.int32)
+        self.ft_b = put(nf.ft_bias.astype(np.int32), torch.int32)
+        self.l1_w = put(np.concatenate([b[0][0] for b in nf.fc]), torch.int8)
+        self.l1_b = put(np.concatenate([b[0][1] for b in nf.fc]), torch.int32)
+        self.l2_w = put(np.concatenate([b[1][0] for b in nf.fc]), torch.int8)
+        self.l2_b = put(np.concatenate([b[1][1] for b in nf.fc]), torch.int32)
+        self.out_w = put(np.concatenate([b[2][0] for b in nf.fc]), torch.int8)
+        self.out_b = put(np.concatenate([b[2][1] for b in nf.fc]), torch.int32)
+        self._qp = _lib.QuantParams(**self.consts)
+        return self
+
     @torch.no_grad()
     def evaluate(self, white_indices, black_indices, stm_white, piece_count) -> torch.Tensor:
         """int32 [B]: the evaluation in units of 1/(2 * nnue2score * weight_scale_out)

@@ -10,7 +10,9 @@ only reads them, so it runs where the reference checkout does not exist.
 Two tiny stand-ins let `import model` work without optional packages the
 reference imports at module scope: `chess` (only piece constants and a
 `Piece(type, color)` record are used, for initial PSQT values) and
-`torchmetrics` (running means of the loss).
+`torchmetrics` (running means of the loss); `numba`, when absent, is replaced
+by an identity `njit` decorator (the reference's LEB128 loops then run as
+plain Python).
 """
 
 from __future__ import annotations
@@ -217,6 +219,28 @@ def main(ref_root: str):
     vals = [calculate_sf_loss(sn, sc, oc, LossParams(), lam) for lam in (1.0, 0.6)]
     np.savez_compressed(os.path.join(HERE, "sf_loss.npz"), scorenet=sn.numpy(), score=sc.numpy(), outcome=oc.numpy(),
                         loss_lambda_1=vals[0].numpy(), loss_lambda_06=vals[1].numpy())
+    # 7. `.nnue` file of the model of section 5, written by the reference's own serializer
+    #    (a few MB: only its SHA-256, length and first bytes are kept)
+    import hashlib
+
+    if "numba" not in sys.modules:
+        try:
+            import numba  # noqa: F401
+        except ImportError:  # the reference only uses numba.njit, as a plain decorator
+            nb = types.ModuleType("numba")
+            nb.njit = lambda f: f
+            sys.modules["numba"] = nb
+    ser = importlib.import_module("model.utils.serialize")
+    rec = {}
+    with torch.no_grad():
+        for comp in ("none", "leb128"):
+            data = bytes(ser.NNUEWriter(m, ft_compression=comp, verbose=False).buf)
+            rec[f"sha256_{comp}"] = np.frombuffer(hashlib.sha256(data).digest(), dtype=np.uint8)
+            rec[f"length_{comp}"] = len(data)
+            rec[f"head_{comp}"] = np.frombuffer(data[:1024], dtype=np.uint8)
+            rec[f"tail_{comp}"] = np.frombuffer(data[-1024:], dtype=np.uint8)
+    np.savez_compressed(os.path.join(HERE, "nnue_file.npz"), **rec)
+
     _ = QuantizationConfig
     print("golden fixtures written to", HERE)
 
