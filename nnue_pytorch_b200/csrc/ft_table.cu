@@ -5,6 +5,8 @@
 // (model/modules/features/halfka_v2_hm.py:68-69 `weight + virtual.repeat(32, 1)`,
 // model/modules/feature_transformer/composed_feature_transformer.py:61-76 with
 // model/quantize.py:47-56: round(x * scale) / scale, two scales, a concat).
+#include <math.h>
+
 #include <algorithm>
 
 #include "common.cuh"
@@ -14,40 +16,54 @@ namespace nnue {
 __device__ __forceinline__ float fq1(float x, float scale) {
     return __fdiv_rn(rintf(__fmul_rn(x, scale)), scale);  // rintf: half to even, like torch.round
 }
+// Same value when `scale` is a power of two: dividing by it and multiplying by
+// its reciprocal are both exact.
+__device__ __forceinline__ float fq1_pow2(float x, float scale, float inv_scale) {
+    return __fmul_rn(rintf(__fmul_rn(x, scale)), inv_scale);
+}
 
-// out[r, c] = fq(weight[r, c] + virtual[r % n_virtual, c]); thread = float4.
-template <bool VEC>
+// out[r, c] = fq(weight[r, c] + virtual[r % n_virtual, c]); thread = float4 (VEC) or float.
+// IDX = unsigned when the element count fits 32 bits (cheap index division), else int64_t.
+// inv_main > 0 marks a power-of-two main scale.
+template <bool VEC, typename IDX>
 __global__ void __launch_bounds__(kThreads)
     k_prepare_table(const float* __restrict__ weight, const float* __restrict__ virt,
                     float* __restrict__ out, int64_t N, int64_t n_virtual, int W, int L1,
-                    float scale_main, float scale_psqt) {
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    const int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+                    float scale_main, float scale_psqt, float inv_main) {
+    const IDX stride = (IDX)gridDim.x * blockDim.x;
+    const IDX t0 = (IDX)blockIdx.x * blockDim.x + threadIdx.x;
     if (VEC) {
-        const int W4 = W >> 2;
-        const int64_t n4 = N * W4;
+        const IDX W4 = (IDX)(W >> 2), L4 = (IDX)(L1 >> 2);  // a float4 never straddles the L1 | PSQT border
+        const IDX n4 = (IDX)N * W4, nv = (IDX)n_virtual;
         const float4* w4 = reinterpret_cast<const float4*>(weight);
         const float4* v4 = reinterpret_cast<const float4*>(virt);
         float4* o4 = reinterpret_cast<float4*>(out);
-        for (int64_t i = t0; i < n4; i += stride) {
-            const int64_t r = i / W4;
-            const int c4 = (int)(i - r * W4);
+        for (IDX i = t0; i < n4; i += stride) {
+            const IDX r = i / W4;
+            const IDX c4 = i - r * W4;
             float4 x = __ldcs(w4 + i);
-            if (virt) x = f4_add(x, __ldg(v4 + (r % n_virtual) * W4 + c4));
+            if (virt) x = f4_add(x, __ldg(v4 + (int64_t)(r % nv) * W4 + c4));
             if (scale_main > 0.f) {
-                // a float4 never straddles the L1 | PSQT border (L1 % 4 == 0)
-                const float s = (4 * c4 < L1) ? scale_main : scale_psqt;
-                x = make_float4(fq1(x.x, s), fq1(x.y, s), fq1(x.z, s), fq1(x.w, s));
+                if (c4 >= L4) {
+                    x = make_float4(fq1(x.x, scale_psqt), fq1(x.y, scale_psqt), fq1(x.z, scale_psqt),
+                                    fq1(x.w, scale_psqt));
+                } else if (inv_main > 0.f) {
+                    x = make_float4(fq1_pow2(x.x, scale_main, inv_main), fq1_pow2(x.y, scale_main, inv_main),
+                                    fq1_pow2(x.z, scale_main, inv_main), fq1_pow2(x.w, scale_main, inv_main));
+                } else {
+                    x = make_float4(fq1(x.x, scale_main), fq1(x.y, scale_main), fq1(x.z, scale_main),
+                                    fq1(x.w, scale_main));
+                }
             }
             o4[i] = x;
         }
     } else {
-        const int64_t n = N * W;
-        for (int64_t i = t0; i < n; i += stride) {
-            const int64_t r = i / W;
-            const int c = (int)(i - r * W);
+        const IDX n = (IDX)N * (IDX)W, nv = (IDX)n_virtual;
+        for (IDX i = t0; i < n; i += stride) {
+            const IDX r = i / (IDX)W;
+            const int c = (int)(i - r * (IDX)W);
             float x = weight[i];
-            if (virt) x = __fadd_rn(x, virt[(r % n_virtual) * W + c]);
+            if (virt) x = __fadd_rn(x, virt[(int64_t)(r % nv) * W + c]);
             if (scale_main > 0.f) x = fq1(x, c < L1 ? scale_main : scale_psqt);
             out[i] = x;
         }
@@ -99,15 +115,22 @@ extern "C" int nnue_ft_prepare_table(const float* weight, const float* virtual_w
     const int W = L1 + P;
     const bool vec = (W % 4 == 0) && (L1 % 4 == 0) && aligned16(weight) && aligned16(out) &&
                      (!virtual_weight || aligned16(virtual_weight));
+    // power-of-two main scale (the usual 256): the division becomes an exact multiplication
+    int exp2 = 0;
+    const float inv_main = (scale_main > 0.f && frexpf(scale_main, &exp2) == 0.5f) ? 1.0f / scale_main : 0.f;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int64_t work = vec ? N * (W / 4) : N * (int64_t)W;
     const unsigned grid = (unsigned)std::min<int64_t>((work + kThreads - 1) / kThreads, (int64_t)sm_count() * 16);
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (vec)
-        k_prepare_table<true><<<grid, kThreads, 0, s>>>(weight, virtual_weight, out, N, n_virtual ? n_virtual : 1,
-                                                       W, L1, scale_main, scale_psqt);
-    else
-        k_prepare_table<false><<<grid, kThreads, 0, s>>>(weight, virtual_weight, out, N, n_virtual ? n_virtual : 1,
-                                                        W, L1, scale_main, scale_psqt);
+    const bool narrow = work + (int64_t)grid * kThreads < 0x7fffffffLL;  // index + stride stays below 2^31
+    const int64_t nv = n_virtual ? n_virtual : 1;
+#define LAUNCH_PREP(VV, II)                                                                              \
+    k_prepare_table<VV, II><<<grid, kThreads, 0, s>>>(weight, virtual_weight, out, N, nv, W, L1, scale_main, \
+                                                      scale_psqt, inv_main)
+    if (vec && narrow) LAUNCH_PREP(true, unsigned);
+    else if (vec) LAUNCH_PREP(true, int64_t);
+    else if (narrow) LAUNCH_PREP(false, unsigned);
+    else LAUNCH_PREP(false, int64_t);
+#undef LAUNCH_PREP
     NNUE_CUDA_TRY(cudaGetLastError());
     note_launches(1);
     return NNUE_OK;

@@ -63,6 +63,8 @@ __global__ void __launch_bounds__(kThreads)
     if (__any_sync(kFullMask, nz) && lane == 0) row_active[row] = 1;
 }
 
+// IDX = unsigned when the float4 count (plus one grid stride) fits 32 bits: cheap row lookup
+template <typename IDX>
 __global__ void __launch_bounds__(kThreads)
     k_ranger_rows(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ gm,
                   float* __restrict__ ngm, float* __restrict__ vm, float* __restrict__ slow,
@@ -70,11 +72,12 @@ __global__ void __launch_bounds__(kThreads)
                   int64_t width4, RangerConst c) {
     const float scale = d_scale ? __ldg(d_scale) : 1.f;
     const float4* g4 = reinterpret_cast<const float4*>(g);
-    const int64_t n4 = rows * width4;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-        if (!__ldg(row_active + i / width4)) continue;
-        ranger_vec4(c, scale, i, g4, reinterpret_cast<float4*>(p), reinterpret_cast<float4*>(gm),
+    const IDX w4 = (IDX)width4;
+    const IDX n4 = (IDX)rows * w4;
+    const IDX stride = (IDX)gridDim.x * blockDim.x;
+    for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
+        if (!__ldg(row_active + i / w4)) continue;
+        ranger_vec4(c, scale, (int64_t)i, g4, reinterpret_cast<float4*>(p), reinterpret_cast<float4*>(gm),
                     reinterpret_cast<float4*>(ngm), reinterpret_cast<float4*>(vm),
                     reinterpret_cast<float4*>(slow), __ldg(g4 + i));
     }
@@ -135,8 +138,12 @@ extern "C" int nnue_rangerlite_update(float* p, const float* grad, float* grad_m
         k_rows_activate<<<(unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta), kThreads, 0, s>>>(
             grad, row_active, rows, width / 4);
         const unsigned grid = (unsigned)std::min<int64_t>((n / 4 + kThreads - 1) / kThreads, (int64_t)sms * 8);
-        k_ranger_rows<<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma, slow,
-                                               row_active, d_grad_scale, rows, width / 4, c);
+        if (n / 4 + (int64_t)grid * kThreads < 0x7fffffffLL)
+            k_ranger_rows<unsigned><<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma, slow,
+                                                             row_active, d_grad_scale, rows, width / 4, c);
+        else
+            k_ranger_rows<int64_t><<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma, slow,
+                                                            row_active, d_grad_scale, rows, width / 4, c);
         note_launches(1);
     } else {
         const int64_t work = al ? (n / 4 + 1) : n;

@@ -53,15 +53,42 @@ def _time(fn, iters, warmup, flush):
     return total / iters
 
 
-def run_point(l1: int, batch: int, active: int, mode: str, iters: int, warmup: int, flush: bool, dev):
+FULL_ROWS, FULL_K, FULL_MEAN = 88944, 288, 52  # the reference's default feature set (threats + pawn patterns + HalfKA)
+
+
+def _full_feature_lists(batch: int, seed: int):
+    """Stand-in lists with the default feature set's shape: 88944 rows, up to
+    288 active per perspective, about 52 on average, rows uniform at random."""
+    import numpy as np
+
+    rng = np.random.default_rng(seed)
+    n_act = np.clip(np.rint(rng.normal(FULL_MEAN, 14, size=(2, batch))), 4, FULL_K).astype(np.int64)
+    lists = []
+    for side in range(2):
+        idx = rng.integers(0, FULL_ROWS, size=(batch, FULL_K), dtype=np.int32)
+        idx[np.arange(FULL_K)[None, :] >= n_act[side][:, None]] = -1
+        lists.append(idx)
+    us = rng.integers(0, 2, size=(batch, 1)).astype(np.float32)
+    pc = rng.integers(2, 33, size=batch)
+    return us, 1.0 - us, lists[0], lists[1], pc, float(n_act.mean())
+
+
+def run_point(l1: int, batch: int, active: int, mode: str, iters: int, warmup: int, flush: bool, dev,
+              features: str = "halfka"):
     P = 8
     W = l1 + P
-    b = positions.generate_batch(batch, 0, layout="baseline", fixed_count=active if active else None)
-    rows_per_persp = 2.0 * (active if active else float(b.piece_count.mean()))
-    us, them, wi, bi = (torch.from_numpy(x).to(dev) for x in (b.us, b.them, b.white, b.black))
-    ps = torch.from_numpy((b.piece_count - 1) // 4).to(dev)
+    n_rows, k_max = (N_ROWS, K) if features == "halfka" else (FULL_ROWS, FULL_K)
+    if features == "halfka":
+        b = positions.generate_batch(batch, 0, layout="baseline", fixed_count=active if active else None)
+        rows_per_persp = 2.0 * (active if active else float(b.piece_count.mean()))
+        arrays, piece_count = (b.us, b.them, b.white, b.black), b.piece_count
+    else:
+        u, t_, wl, bl, piece_count, rows_per_persp = _full_feature_lists(batch, 0)
+        arrays = (u, t_, wl, bl)
+    us, them, wi, bi = (torch.from_numpy(x).to(dev) for x in arrays)
+    ps = torch.from_numpy((piece_count - 1) // 4).to(dev)
     g = torch.Generator(device=dev).manual_seed(1)
-    w = torch.randn(N_ROWS, W, generator=g, device=dev) * 0.01
+    w = torch.randn(n_rows, W, generator=g, device=dev) * 0.01
     bias = torch.randn(W, generator=g, device=dev) * 0.01
     gl0 = torch.randn(batch, l1, generator=g, device=dev)
     gp = torch.randn(batch, 1, generator=g, device=dev)
@@ -74,18 +101,19 @@ def run_point(l1: int, batch: int, active: int, mode: str, iters: int, warmup: i
         saved[0] = _launch.fused_forward(us, them, wi, bi, ps, w, bias, max_act, l1)[3]
 
     def bwd():
-        _launch.fused_backward(us, them, wi, bi, ps, max_act, l1, N_ROWS, W, gl0, gp, gp, saved[0], mode)
+        _launch.fused_backward(us, them, wi, bi, ps, max_act, l1, n_rows, W, gl0, gp, gp, saved[0], mode)
 
     t_f = _time(fwd, iters, warmup, fl)
     t_b = _time(bwd, iters, warmup, fl)
     _launch.device_status(dev)
-    common = batch * (2 * rows_per_persp * W * 4 + 2 * K * 4 + 24 + 3 * l1 * 4 + 8)
+    common = batch * (2 * rows_per_persp * W * 4 + 2 * k_max * 4 + 24 + 3 * l1 * 4 + 8)
     peak, kind = _peak()
     out = {
         "l1": l1, "batch": batch, "active_real_per_perspective": active or "U[2,32]", "rows_per_perspective": rows_per_persp,
         "fwd_ms": t_f, "fwd_algorithmic_GBps": common / t_f / 1e6, "fwd_frac_of_hbm": common / t_f / 1e6 / peak,
-        "bwd_ms": t_b, "bwd_algorithmic_GBps": (common + N_ROWS * W * 4) / t_b / 1e6,
-        "bwd_frac_of_hbm": (common + N_ROWS * W * 4) / t_b / 1e6 / peak,
+        "bwd_ms": t_b, "bwd_algorithmic_GBps": (common + n_rows * W * 4) / t_b / 1e6,
+        "bwd_frac_of_hbm": (common + n_rows * W * 4) / t_b / 1e6 / peak,
+        "rows": n_rows, "max_active": k_max,
         "bwd_mode": mode, "hbm_peak_GBps": peak, "peak_source": kind, "l2_flushed": bool(flush),
     }
     return out
@@ -100,6 +128,9 @@ def main():
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
+    ap.add_argument("--features", default="halfka", choices=["halfka", "full"],
+                    help="full = the shape of the reference's default feature set (88944 rows, K = 288, ~52 active); "
+                         "--active is ignored")
     ap.add_argument("--tune", action="append", default=[], help="key=value, passed to nnue_b200_tune")
     a = ap.parse_args()
     if not torch.cuda.is_available():
@@ -114,7 +145,7 @@ def main():
     for l1 in a.l1:
         for batch in a.batch:
             for act in a.active:
-                r = run_point(l1, batch, act, a.mode, a.iters, a.warmup, not a.no_flush, dev)
+                r = run_point(l1, batch, act, a.mode, a.iters, a.warmup, not a.no_flush, dev, a.features)
                 if tuned:
                     r["tune"] = tuned
                 print(json.dumps(r), flush=True)

@@ -186,6 +186,7 @@ CASES = [
     (40, 300, 33, 1024, 8, True, 255.0 / 256.0, 0.06),   # K not a multiple of 32
     (24, 200, 70, 3072, 8, True, 255.0 / 256.0, 0.04),   # K > 64, headline width
     (9, 50, 12, 6, 3, True, 255.0 / 256.0, 0.4),         # scalar kernels: l1 % 8 != 0, P % 4 != 0
+    (48, 88944, 288, 256, 8, True, 255.0 / 256.0, 0.03),  # the default feature set's table: 88944 rows, K = 288
 ]
 
 
