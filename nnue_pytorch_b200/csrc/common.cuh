@@ -178,6 +178,19 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, unsigned parity
     return false;
 }
 
+// ---- per-thread 16-byte asynchronous copies (global -> shared) -------------
+// `pred` false writes 16 zero bytes instead (nothing is read from `src`).
+__device__ __forceinline__ void cp_async16(void* dst_smem, const void* src_gmem, bool pred) {
+    const unsigned n = pred ? 16u : 0u;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst_smem)), "l"(src_gmem), "r"(n)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
 #endif  // __CUDACC__
 
 }  // namespace nnue

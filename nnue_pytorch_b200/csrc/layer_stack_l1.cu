@@ -18,21 +18,37 @@ __device__ __forceinline__ float dot4(float acc, float4 a, float4 b) {
     return __fmaf_rn(a.w, b.w, acc);
 }
 
-// ---- forward: tile = 64 positions x 32 outputs, K = L1 in chunks of 32 -----
-// 128 threads, each a 4 x 4 register tile (positions ty + 16 i, outputs tx + 8 j):
-// 8 shared float4 loads feed 64 FMA.
-__global__ void __launch_bounds__(128)
+// ---- forward: tile = 64 positions x 32 outputs -----------------------------
+// Shared-memory bandwidth is the limit of an fp32 FMA tile kernel here (one
+// 16-byte shared load per lane costs 4 cycles of the SM's single shared-memory
+// pipe, 4 FMA pipes retire 4 warp instructions per cycle), so every thread
+// holds an 8 x 8 register tile: 16 shared float4 loads feed 256 FMA.
+// A 64 x 32 tile is then ONE warp; the kWarpsL1 warps of a CTA split K between
+// them (contiguous ranges, walked in chunks of 8 through a kStagesL1-deep
+// cp.async pipeline in buffers private to the warp: warp-level barriers only)
+// and their tiles are added in warp order at the end.
+constexpr int kWarpsL1 = 4;
+constexpr int kStagesL1 = 4;
+constexpr int kKC8 = 8;            // K chunk of a warp
+constexpr int kPad8 = kKC8 + 4;    // row stride 48 B: float4 aligned, conflict-free for the access patterns below
+constexpr int kFwdStage = (kTP + kLsOut) * kPad8;  // floats per stage: A [64][12] + W [32][12]
+constexpr int kFwdSmemFloats = kWarpsL1 * kStagesL1 * kFwdStage;  // >= the (kWarpsL1 - 1) partial tiles [64][33]
+static_assert(kFwdSmemFloats >= (kWarpsL1 - 1) * kTP * (kLsOut + 1), "partial tiles alias the staging buffers");
+__global__ void __launch_bounds__(32 * kWarpsL1, 2)
     k_ls_l1_fwd(const float* __restrict__ x, const float* __restrict__ W1, const float* __restrict__ b1,
                 LsPlanView plan, float* __restrict__ o1, int L1) {
-    __shared__ __align__(16) float As[kTP][kPadK];
-    __shared__ __align__(16) float Ws[kLsOut][kPadK];
+    extern __shared__ __align__(16) float smem[];
     const int t = blockIdx.x;
     if (t >= *plan.n_tiles) return;
     const int cnt = plan.tile_count[t], bk = plan.tile_bucket[t];
     const int32_t* perm = plan.perm + plan.tile_start[t];
-    const int tid = threadIdx.x;
-    const int lr = tid >> 3, lc = tid & 7;  // loader: rows lr + 16 i of A, rows lr + 16 i of W; float4 column lc
-    const float4 z = f4_zero();
+    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+    float* stage0 = smem + g * kStagesL1 * kFwdStage;
+    // this warp's K range, in chunks of 8
+    const int nc = L1 / kKC8;
+    const int c_beg = (int)((int64_t)nc * g / kWarpsL1), c_end = (int)((int64_t)nc * (g + 1) / kWarpsL1);
+    // loader: A rows (lane >> 1) + 16 i (i < 4), W rows (lane >> 1) + 16 i (i < 2); float4 (lane & 1) of the chunk
+    const int lr = lane >> 1, lc = lane & 1;
     const float4* xa[4];
     bool live[4];
 #pragma unroll
@@ -42,50 +58,71 @@ __global__ void __launch_bounds__(128)
     }
     const float4* wr0 = reinterpret_cast<const float4*>(W1 + ((int64_t)bk * kLsOut + lr) * L1) + lc;
     const float4* wr1 = reinterpret_cast<const float4*>(W1 + ((int64_t)bk * kLsOut + lr + 16) * L1) + lc;
-    const int ty = tid >> 3, tx = tid & 7;
-    float acc[4][4];
+    auto issue = [&](int c, int st) {  // chunk c into stage st; chunks past the range copy nothing
+        if (c < c_end) {
+            float (*As)[kPad8] = reinterpret_cast<float (*)[kPad8]>(stage0 + st * kFwdStage);
+            float (*Ws)[kPad8] = As + kTP;
+            const int o = c * (kKC8 / 4);
 #pragma unroll
-    for (int i = 0; i < 4; ++i)
-#pragma unroll
-        for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
-    float4 ra[4], rw0 = __ldg(wr0), rw1 = __ldg(wr1);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) ra[i] = live[i] ? __ldg(xa[i]) : z;
-    const int nk = L1 / kKC;
-    for (int kc = 0; kc < nk; ++kc) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(&As[lr + 16 * i][4 * lc]) = ra[i];
-        *reinterpret_cast<float4*>(&Ws[lr][4 * lc]) = rw0;
-        *reinterpret_cast<float4*>(&Ws[lr + 16][4 * lc]) = rw1;
-        __syncthreads();
-        if (kc + 1 < nk) {  // next chunk travels while this one is multiplied
-            const int o = (kc + 1) * (kKC / 4);
-#pragma unroll
-            for (int i = 0; i < 4; ++i) ra[i] = live[i] ? __ldg(xa[i] + o) : z;
-            rw0 = __ldg(wr0 + o);
-            rw1 = __ldg(wr1 + o);
+            for (int i = 0; i < 4; ++i) cp_async16(&As[lr + 16 * i][4 * lc], xa[i] + o, live[i]);
+            cp_async16(&Ws[lr][4 * lc], wr0 + o, true);
+            cp_async16(&Ws[lr + 16][4 * lc], wr1 + o, true);
         }
+        cp_async_commit();  // one group per call, empty or not: the wait below counts groups
+    };
+    const int pg = lane >> 2, og = lane & 3;  // positions pg + 8 i, outputs og + 4 j
+    float acc[8][8];
 #pragma unroll
-        for (int k4 = 0; k4 < kKC / 4; ++k4) {
-            float4 a[4], w[4];
+    for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int i = 0; i < 4; ++i) a[i] = *reinterpret_cast<const float4*>(&As[ty + 16 * i][4 * k4]);
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 #pragma unroll
-            for (int j = 0; j < 4; ++j) w[j] = *reinterpret_cast<const float4*>(&Ws[tx + 8 * j][4 * k4]);
+    for (int st = 0; st < kStagesL1 - 1; ++st) issue(c_beg + st, st);
+    int st = 0;
+    for (int c = c_beg; c < c_end; ++c) {
+        cp_async_wait<kStagesL1 - 2>();  // this lane's part of chunk c has landed
+        __syncwarp();                    // ... and every other lane's; the stage refilled next was read last iteration
+        issue(c + kStagesL1 - 1, (st + kStagesL1 - 1) % kStagesL1);
+        float (*As)[kPad8] = reinterpret_cast<float (*)[kPad8]>(stage0 + st * kFwdStage);
+        float (*Ws)[kPad8] = As + kTP;
 #pragma unroll
-            for (int i = 0; i < 4; ++i)
+        for (int k4 = 0; k4 < kKC8 / 4; ++k4) {
+            float4 a[8];
 #pragma unroll
-                for (int j = 0; j < 4; ++j) acc[i][j] = dot4(acc[i][j], a[i], w[j]);
+            for (int i = 0; i < 8; ++i) a[i] = *reinterpret_cast<const float4*>(&As[pg + 8 * i][4 * k4]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const float4 w = *reinterpret_cast<const float4*>(&Ws[og + 4 * j][4 * k4]);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i][j] = dot4(acc[i][j], a[i], w);
+            }
         }
-        __syncthreads();
+        st = (st + 1) % kStagesL1;
     }
+    cp_async_wait<0>();
+    __syncthreads();  // every warp is done with its staging buffers
+    float (*red)[kTP][kLsOut + 1] = reinterpret_cast<float (*)[kTP][kLsOut + 1]>(smem);
+    if (g > 0) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        const int pos = ty + 16 * i;
-        if (pos < cnt) {
-            float* dst = o1 + (int64_t)perm[pos] * kLsOut;
+        for (int i = 0; i < 8; ++i)
 #pragma unroll
-            for (int j = 0; j < 4; ++j) dst[tx + 8 * j] = __fadd_rn(acc[i][j], __ldg(b1 + bk * kLsOut + tx + 8 * j));
+            for (int j = 0; j < 8; ++j) red[g - 1][pg + 8 * i][og + 4 * j] = acc[i][j];
+    }
+    __syncthreads();
+    if (g == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int pos = pg + 8 * i;
+            if (pos < cnt) {
+                float* dst = o1 + (int64_t)perm[pos] * kLsOut;
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    float v = acc[i][j];
+#pragma unroll
+                    for (int q = 0; q < kWarpsL1 - 1; ++q) v = __fadd_rn(v, red[q][pos][og + 4 * j]);
+                    dst[og + 4 * j] = __fadd_rn(v, __ldg(b1 + bk * kLsOut + og + 4 * j));
+                }
+            }
         }
     }
 }
@@ -149,91 +186,148 @@ __global__ void __launch_bounds__(256)
 }
 
 // ---- weight gradient: dW1[bucket, o, c] = sum_p d_o1[p, o] * x[p, c] -------
-// CTA = (bucket, 64 columns), 128 threads, each a 4 x 4 register tile (units
-// 4 ty .. 4 ty + 3, columns 4 tx .. 4 tx + 3); walks the bucket's positions 32
-// at a time with the next 32 prefetched into registers.
+// CTA = (bucket, 64 columns).  As in the forward, one warp holds the whole
+// 32 x 64 output tile as 8 x 8 register tiles (units 4 og + {0..3} and
+// 16 + 4 og + {0..3}, columns 4 cg + {0..3} and 32 + 4 cg + {0..3}); the
+// kWarpsL1 warps take every kWarpsL1-th block of 8 positions of the bucket
+// (kStagesL1-deep cp.async pipeline in buffers private to the warp, warp-level
+// barriers only) and their tiles are added in warp order at the end.
 constexpr int kDwCols = 64;
 constexpr int kPadC = kDwCols + 4;
-__global__ void __launch_bounds__(128)
+constexpr int kDwBlock = 8;  // positions per block
+constexpr int kDwStage = kDwBlock * (kPadC + kPadK);  // floats per stage: X [8][68] + D [8][36]
+constexpr int kDwSmemFloats = kWarpsL1 * kStagesL1 * kDwStage;
+static_assert(kDwSmemFloats >= (kWarpsL1 - 1) * kLsOut * (kDwCols + 4), "partial tiles alias the staging buffers");
+__global__ void __launch_bounds__(32 * kWarpsL1, 2)
     k_ls_l1_dw(const float* __restrict__ x, const float* __restrict__ d_o1, LsPlanView plan,
                float* __restrict__ dW1, float* __restrict__ db1, int L1, int n_col_chunks) {
-    __shared__ __align__(16) float Xs[32][kPadC];
-    __shared__ __align__(16) float Ds[32][kPadK];
+    extern __shared__ __align__(16) float smem[];
     const int bk = blockIdx.x / n_col_chunks, cc = blockIdx.x % n_col_chunks;
     const int t0 = plan.bucket_tile[bk], t1 = plan.bucket_tile[bk + 1];
     const int beg = t0 < t1 ? plan.tile_start[t0] : 0;
     const int end = t0 < t1 ? plan.tile_start[t1 - 1] + plan.tile_count[t1 - 1] : 0;
-    const int tid = threadIdx.x;
-    const int tx = tid & 15, ty = tid >> 4;  // ty 0..7
+    const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
+    float* stage0 = smem + g * kStagesL1 * kDwStage;
     const int c0 = cc * kDwCols;
-    float4 acc[4];
+    const int cg = lane & 7, og = lane >> 3;
+    float acc[8][8];  // [unit][column]
 #pragma unroll
-    for (int j = 0; j < 4; ++j) acc[j] = f4_zero();
+    for (int i = 0; i < 8; ++i)
+#pragma unroll
+        for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
     float bsum = 0.f;
-    // loader roles: X rows xr + 8 i (i < 4), float4 column tx; D rows dr + 16 i (i < 2), float4 column dc
-    const int xr = tid >> 4, dr = tid >> 3, dc = tid & 7;
-    const bool col_ok = c0 + 4 * tx < L1;
-    float4 rx[4], rd[2];
-    auto fetch = [&](int s) {
-        const int m = min(32, end - s);
+    // loader: X rows (lane >> 4) + 2 i (i < 4), float4 column lane & 15; D rows (lane >> 3) + 4 i (i < 2), float4 lane & 7
+    const int xr = lane >> 4, xc = lane & 15, dr = lane >> 3, dc = lane & 7;
+    const bool col_ok = c0 + 4 * xc < L1;
+    auto issue = [&](int s, int st) {  // the block of positions starting at s into stage st; past the end: nothing
+        if (s < end) {
+            float (*Xs)[kPadC] = reinterpret_cast<float (*)[kPadC]>(stage0 + st * kDwStage);
+            float (*Ds)[kPadK] = reinterpret_cast<float (*)[kPadK]>(stage0 + st * kDwStage + kDwBlock * kPadC);
+            const int m = min(kDwBlock, end - s);
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-            const int r = xr + 8 * i;
-            rx[i] = (r < m && col_ok)
-                        ? __ldg(reinterpret_cast<const float4*>(x + (int64_t)plan.perm[s + r] * L1 + c0) + tx)
-                        : f4_zero();
-        }
+            for (int i = 0; i < 4; ++i) {
+                const int r = xr + 2 * i;
+                const bool ok = r < m && col_ok;
+                cp_async16(&Xs[r][4 * xc], x + (int64_t)(ok ? plan.perm[s + r] : 0) * L1 + c0 + (ok ? 4 * xc : 0), ok);
+            }
 #pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int r = dr + 16 * i;
-            rd[i] = r < m ? __ldg(reinterpret_cast<const float4*>(d_o1 + (int64_t)plan.perm[s + r] * kLsOut) + dc)
-                          : f4_zero();
-        }
-    };
-    if (beg < end) fetch(beg);
-    for (int s = beg; s < end; s += 32) {
-        const int m = min(32, end - s);
-        __syncthreads();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) *reinterpret_cast<float4*>(&Xs[xr + 8 * i][4 * tx]) = rx[i];
-#pragma unroll
-        for (int i = 0; i < 2; ++i) *reinterpret_cast<float4*>(&Ds[dr + 16 * i][4 * dc]) = rd[i];
-        __syncthreads();
-        if (s + 32 < end) fetch(s + 32);
-#pragma unroll 8
-        for (int pp = 0; pp < 32; ++pp) {
-            const float4 xv = *reinterpret_cast<const float4*>(&Xs[pp][4 * tx]);
-            const float4 dv = *reinterpret_cast<const float4*>(&Ds[pp][4 * ty]);
-            const float d[4] = {dv.x, dv.y, dv.z, dv.w};
-#pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                acc[j].x = __fmaf_rn(d[j], xv.x, acc[j].x);
-                acc[j].y = __fmaf_rn(d[j], xv.y, acc[j].y);
-                acc[j].z = __fmaf_rn(d[j], xv.z, acc[j].z);
-                acc[j].w = __fmaf_rn(d[j], xv.w, acc[j].w);
+            for (int i = 0; i < 2; ++i) {
+                const int r = dr + 4 * i;
+                const bool ok = r < m;
+                cp_async16(&Ds[r][4 * dc], d_o1 + (int64_t)(ok ? plan.perm[s + r] : 0) * kLsOut + 4 * dc, ok);
             }
         }
-        if (cc == 0 && tid < kLsOut) {
-            for (int pp = 0; pp < m; ++pp) bsum = __fadd_rn(bsum, Ds[pp][tid]);
+        cp_async_commit();  // one group per call, empty or not: the wait below counts groups
+    };
+    const int step = kDwBlock * kWarpsL1;
+    const int s0 = beg + kDwBlock * g;
+#pragma unroll
+    for (int st = 0; st < kStagesL1 - 1; ++st) issue(s0 + st * step, st);
+    int st = 0;
+    for (int s = s0; s < end; s += step) {
+        const int m = min(kDwBlock, end - s);
+        cp_async_wait<kStagesL1 - 2>();  // this lane's part of the block has landed
+        __syncwarp();                    // ... and every other lane's; the stage refilled next was read last iteration
+        issue(s + (kStagesL1 - 1) * step, (st + kStagesL1 - 1) % kStagesL1);
+        float (*Xs)[kPadC] = reinterpret_cast<float (*)[kPadC]>(stage0 + st * kDwStage);
+        float (*Ds)[kPadK] = reinterpret_cast<float (*)[kPadK]>(stage0 + st * kDwStage + kDwBlock * kPadC);
+#pragma unroll
+        for (int pp = 0; pp < kDwBlock; ++pp) {
+            const float4 x0 = *reinterpret_cast<const float4*>(&Xs[pp][4 * cg]);
+            const float4 x1 = *reinterpret_cast<const float4*>(&Xs[pp][32 + 4 * cg]);
+            const float4 d0 = *reinterpret_cast<const float4*>(&Ds[pp][4 * og]);
+            const float4 d1 = *reinterpret_cast<const float4*>(&Ds[pp][16 + 4 * og]);
+            const float xv[8] = {x0.x, x0.y, x0.z, x0.w, x1.x, x1.y, x1.z, x1.w};
+            const float dv[8] = {d0.x, d0.y, d0.z, d0.w, d1.x, d1.y, d1.z, d1.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+#pragma unroll
+                for (int j = 0; j < 8; ++j) acc[i][j] = __fmaf_rn(dv[i], xv[j], acc[i][j]);
+        }
+        if (cc == 0) {
+            for (int pp = 0; pp < m; ++pp) bsum = __fadd_rn(bsum, Ds[pp][lane]);
+        }
+        st = (st + 1) % kStagesL1;
+    }
+    cp_async_wait<0>();
+    __syncthreads();  // every warp is done with its staging buffers
+    float (*red)[kLsOut][kDwCols + 4] = reinterpret_cast<float (*)[kLsOut][kDwCols + 4]>(smem);
+    if (g > 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int o = (i < 4 ? 4 * og + i : 16 + 4 * og + (i - 4));
+            *reinterpret_cast<float4*>(&red[g - 1][o][4 * cg]) = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            *reinterpret_cast<float4*>(&red[g - 1][o][32 + 4 * cg]) = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+        }
+        red[g - 1][lane][kDwCols] = bsum;  // row `lane`, first padding column
+    }
+    __syncthreads();
+    if (g == 0) {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int o = (i < 4 ? 4 * og + i : 16 + 4 * og + (i - 4));
+            float4 lo = make_float4(acc[i][0], acc[i][1], acc[i][2], acc[i][3]);
+            float4 hi = make_float4(acc[i][4], acc[i][5], acc[i][6], acc[i][7]);
+#pragma unroll
+            for (int q = 0; q < kWarpsL1 - 1; ++q) {
+                lo = f4_add(lo, *reinterpret_cast<const float4*>(&red[q][o][4 * cg]));
+                hi = f4_add(hi, *reinterpret_cast<const float4*>(&red[q][o][32 + 4 * cg]));
+            }
+            float* row = dW1 + ((int64_t)bk * kLsOut + o) * L1 + c0;
+            if (c0 + 4 * cg < L1) *reinterpret_cast<float4*>(row + 4 * cg) = lo;
+            if (c0 + 32 + 4 * cg < L1) *reinterpret_cast<float4*>(row + 32 + 4 * cg) = hi;
+        }
+        if (cc == 0) {
+#pragma unroll
+            for (int q = 0; q < kWarpsL1 - 1; ++q) bsum = __fadd_rn(bsum, red[q][lane][kDwCols]);
+            db1[bk * kLsOut + lane] = bsum;
         }
     }
-    if (col_ok) {
-#pragma unroll
-        for (int j = 0; j < 4; ++j)
-            *reinterpret_cast<float4*>(dW1 + ((int64_t)bk * kLsOut + 4 * ty + j) * L1 + c0 + 4 * tx) = acc[j];
-    }
-    if (cc == 0 && tid < kLsOut) db1[bk * kLsOut + tid] = bsum;
 }
 
 }  // namespace nnue
 
 using namespace nnue;
 
+// More than 48 KB of dynamic shared memory needs an opt-in per kernel and device.
+static int ls_l1_opt_in() {
+    static bool done[64] = {};
+    int dev = 0;
+    NNUE_CUDA_TRY(cudaGetDevice(&dev));
+    if (dev >= 0 && dev < 64 && done[dev]) return NNUE_OK;
+    NNUE_CUDA_TRY(cudaFuncSetAttribute(k_ls_l1_fwd, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(kFwdSmemFloats * sizeof(float))));
+    NNUE_CUDA_TRY(cudaFuncSetAttribute(k_ls_l1_dw, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                       (int)(kDwSmemFloats * sizeof(float))));
+    if (dev >= 0 && dev < 64) done[dev] = true;
+    return NNUE_OK;
+}
+
 static int ls_check(const char* who, int64_t B, int32_t L1, int32_t C, const void* plan) {
     NNUE_REQUIRE(B >= 0 && L1 > 0 && L1 % 32 == 0 && C > 0 && C <= 16, NNUE_ERR_UNSUPPORTED,
                  "%s: needs L1 %% 32 == 0 and 1..16 buckets (B=%lld L1=%d C=%d)", who, (long long)B, L1, C);
     NNUE_REQUIRE(plan != nullptr && aligned16(plan), NNUE_ERR_ARG, "%s: null or unaligned plan", who);
-    return NNUE_OK;
+    return ls_l1_opt_in();
 }
 
 extern "C" int nnue_ls_l1_fwd(const float* x, const float* W1, const float* b1, const void* plan, float* o1,
@@ -243,7 +337,7 @@ extern "C" int nnue_ls_l1_fwd(const float* x, const float* W1, const float* b1, 
     if (B == 0) return NNUE_OK;
     NNUE_REQUIRE(x && W1 && b1 && o1 && aligned16(x) && aligned16(W1) && aligned16(o1), NNUE_ERR_ARG,
                  "nnue_ls_l1_fwd: null or unaligned tensor");
-    k_ls_l1_fwd<<<(unsigned)ls_max_tiles(B, C), 128, 0, static_cast<cudaStream_t>(stream)>>>(
+    k_ls_l1_fwd<<<(unsigned)ls_max_tiles(B, C), 32 * kWarpsL1, kFwdSmemFloats * sizeof(float), static_cast<cudaStream_t>(stream)>>>(
         x, W1, b1, ls_view(plan, B, C), o1, L1);
     NNUE_CUDA_TRY(cudaGetLastError());
     note_launches(1);
@@ -270,7 +364,7 @@ extern "C" int nnue_ls_l1_bwd(const float* x, const float* W1, const float* d_o1
         note_launches(1);
     }
     const int chunks = (L1 + kDwCols - 1) / kDwCols;
-    k_ls_l1_dw<<<(unsigned)(C * chunks), 128, 0, s>>>(x, d_o1, v, dW1, db1, L1, chunks);
+    k_ls_l1_dw<<<(unsigned)(C * chunks), 32 * kWarpsL1, kDwSmemFloats * sizeof(float), s>>>(x, d_o1, v, dW1, db1, L1, chunks);
     NNUE_CUDA_TRY(cudaGetLastError());
     note_launches(1);
     return NNUE_OK;
