@@ -8,8 +8,9 @@ Shapes: HalfKAv2_hm^ as 22528 real + 704 factor rows (N = 23232, K = 64),
 L1 in {1024, 2048, 3072}, batch in {4096, 16384, 65536}, `active` real
 features per perspective fixed at 2, 8, 16 or 32 (0 = piece count ~ U[2,32]),
 fp32 weights ~ N(0, 0.01).  Each point prints one JSON line with the mean
-kernel time (CUDA events on the launching stream, L2 flushed between
-iterations unless --no-flush) and the algorithmic GB/s: every (position,
+kernel time over 50 launches after 10 warm-ups (CUDA events on the launching
+stream): "cold" with the L2 flushed between launches (the headline figures;
+--no-flush skips it) and "steady" back to back and the algorithmic GB/s: every (position,
 active row) counts one full row, as in an embedding bag; bytes served by the
 L2 are therefore counted too and the figure can exceed the DRAM bandwidth.
 """
@@ -105,6 +106,9 @@ def run_point(l1: int, batch: int, active: int, mode: str, iters: int, warmup: i
 
     t_f = _time(fwd, iters, warmup, fl)
     t_b = _time(bwd, iters, warmup, fl)
+    warm = None
+    if flush:  # the steady-state figures as well: same launches back to back, nothing evicted in between
+        warm = (_time(fwd, iters, warmup, None), _time(bwd, iters, warmup, None))
     _launch.device_status(dev)
     common = batch * (2 * rows_per_persp * W * 4 + 2 * k_max * 4 + 24 + 3 * l1 * 4 + 8)
     peak, kind = _peak()
@@ -114,6 +118,7 @@ def run_point(l1: int, batch: int, active: int, mode: str, iters: int, warmup: i
         "bwd_ms": t_b, "bwd_algorithmic_GBps": (common + n_rows * W * 4) / t_b / 1e6,
         "bwd_frac_of_hbm": (common + n_rows * W * 4) / t_b / 1e6 / peak,
         "rows": n_rows, "max_active": k_max,
+        "fwd_ms_steady": warm[0] if warm else None, "bwd_ms_steady": warm[1] if warm else None,
         "bwd_mode": mode, "hbm_peak_GBps": peak, "peak_source": kind, "l2_flushed": bool(flush),
     }
     return out
@@ -125,8 +130,8 @@ def main():
     ap.add_argument("--batch", type=int, nargs="*", default=[4096, 16384, 65536])
     ap.add_argument("--active", type=int, nargs="*", default=[2, 8, 16, 32])
     ap.add_argument("--mode", default="auto", choices=["auto", "atomic", "segment"])
-    ap.add_argument("--iters", type=int, default=10)
-    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--iters", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--no-flush", action="store_true")
     ap.add_argument("--features", default="halfka", choices=["halfka", "full"],
                     help="full = the shape of the reference's default feature set (88944 rows, K = 288, ~52 active); "

@@ -121,9 +121,11 @@ def test_model_forward_and_gradients_match_oracle(dev):
 
 
 def test_training_steps_track_the_oracle(dev):
-    """Five optimizer steps (one lookahead merge) of the whole model on the
-    baseline layout: loss curve and the touched part of the table follow the
-    CPU oracle (forward + autograd + RangerLite restatement)."""
+    """Twenty optimizer steps (four lookahead merges) of the whole model on the
+    baseline layout: the loss of every step and the parameters after 1, 5 and
+    20 steps follow the CPU oracle (forward + autograd + RangerLite
+    restatement).  Rounding differences in the gradients grow through the
+    normalised update, hence the looser bound at 20 steps."""
     from oracle import model_oracle, ranger_lite_oracle
     from nnue_pytorch_b200 import positions
     from nnue_pytorch_b200.model import ModelConfig, NNUEModel, TrainStep
@@ -143,7 +145,8 @@ def test_training_steps_track_the_oracle(dev):
     state = ranger_lite_oracle.RangerLiteState([cpu[k] for k in order])
     m.to(dev)
     step = TrainStep(m, lr=8.75e-4, clip=2.0)
-    for i in range(5):
+    worst = {}
+    for i in range(20):
         b = positions.generate_batch(512, 100 + i, layout="baseline")
         batch = tuple(t(a) for a in b.as_tuple())
         params = {k: v.clone().requires_grad_(True) for k, v in cpu.items()}
@@ -155,8 +158,10 @@ def test_training_steps_track_the_oracle(dev):
         ranger_lite_oracle.ranger_lite_step([cpu[k] for k in order], [g_ * coef for g_ in grads], state, lr=8.75e-4)
         loss = step(tuple(x.to(dev) for x in batch))
         assert abs(float(loss) - float(loss_ref)) <= 2e-5 * abs(float(loss_ref)), i
-    for k in order:
-        assert max_rel_err(names[k].detach().cpu(), cpu[k]) <= 1e-4, k
+        if i in (0, 4, 19):  # after 1, 5 and 20 optimizer steps (four lookahead merges by then)
+            worst[i + 1] = max(max_rel_err(names[k].detach().cpu(), cpu[k]) for k in order)
+    print("max-norm relative parameter error after 1 / 5 / 20 steps:", worst)
+    assert worst[1] <= 1e-5 and worst[5] <= 1e-4 and worst[20] <= 1e-3, worst
 
 
 @pytest.mark.parametrize("B,L1,fq", [(300, 64, True), (2000, 256, True), (777, 96, False), (5, 32, True)])
