@@ -124,8 +124,7 @@ def test_training_steps_track_the_oracle(dev):
     """Twenty optimizer steps (four lookahead merges) of the whole model on the
     baseline layout: the loss of every step and the parameters after 1, 5 and
     20 steps follow the CPU oracle (forward + autograd + RangerLite
-    restatement).  Rounding differences in the gradients grow through the
-    normalised update, hence the looser bound at 20 steps."""
+    restatement), each within 1e-5 of the tensor's max-norm."""
     from oracle import model_oracle, ranger_lite_oracle
     from nnue_pytorch_b200 import positions
     from nnue_pytorch_b200.model import ModelConfig, NNUEModel, TrainStep
@@ -161,7 +160,7 @@ def test_training_steps_track_the_oracle(dev):
         if i in (0, 4, 19):  # after 1, 5 and 20 optimizer steps (four lookahead merges by then)
             worst[i + 1] = max(max_rel_err(names[k].detach().cpu(), cpu[k]) for k in order)
     print("max-norm relative parameter error after 1 / 5 / 20 steps:", worst)
-    assert worst[1] <= 1e-5 and worst[5] <= 1e-4 and worst[20] <= 1e-3, worst
+    assert all(v <= 1e-5 for v in worst.values()), worst  # measured on B200: 8.8e-6, 6.3e-6, 5.2e-6
 
 
 @pytest.mark.parametrize("B,L1,fq", [(300, 64, True), (2000, 256, True), (777, 96, False), (5, 32, True)])
