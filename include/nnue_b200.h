@@ -181,6 +181,16 @@ int nnue_ft_prepare_table(const float* weight, const float* virtual_weight,
 int nnue_ft_virtual_grad(const float* grad, float* out, int64_t N,
                          int64_t n_virtual, int32_t W, void* stream);
 
+/* Row slices for the segment-mode nnue_ft_fused_bwd calls that follow (process-wide
+ * setting; n_slices <= 0 clears it).  h_row_bounds holds n_slices + 1 non-decreasing
+ * rows, the first 0; calls whose N equals the last bound produce grad_weight slice
+ * by slice (rows [bounds[i], bounds[i+1]) final, then h_events[i], a cudaEvent_t
+ * or NULL, recorded on the call's stream), so that a consumer on another stream
+ * can start on the first rows while the later ones are still computed.  The
+ * values written are those of the unsliced call.  n_slices <= 16. */
+int nnue_ft_fused_bwd_slices(const int64_t* h_row_bounds, void* const* h_events,
+                             int32_t n_slices);
+
 /* ---- A12: RangerLite (Adam + positive-negative momentum + lookahead) ---
  * One fused pass over a parameter tensor viewed as [rows, width]:
  *   g  = grad * (*d_grad_scale if given) ;

@@ -125,6 +125,7 @@ PROTOTYPES = {
         [_P, _P, _P, _P, _P, C.c_float, C.c_float, _P, _P, _P, _P, _P, _P, _I64, _I32, _I64, _I32, _I32,
          _P, _SZ, _I32, _P],
     ),
+    "nnue_ft_fused_bwd_slices": (C.c_int, [C.POINTER(C.c_int64), C.POINTER(C.c_void_p), _I32]),
     "nnue_ft_prepare_table": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, C.c_float, C.c_float, _P]),
     "nnue_ft_virtual_grad": (C.c_int, [_P, _P, _I64, _I64, _I32, _P]),
     "nnue_rangerlite_update": (

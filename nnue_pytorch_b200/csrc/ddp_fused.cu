@@ -31,23 +31,37 @@ struct PeerPtrs {
     float* p[kMaxRanks];
 };
 
+// UN float4 per thread and trip, every rank's copy of them loaded before the first add: with few
+// ranks (few loads per float4) the unroll keeps enough bytes in flight to fill the links even when
+// the grid is capped to leave SMs to a kernel running beside it.
+// WMAX bounds the world size of the instantiation (registers: UN * WMAX float4).
+template <int UN, int WMAX>
 __global__ void __launch_bounds__(kThreads)
     k_ddp_reduce_shard(PeerPtrs grads, int world, int rank, int64_t beg4, int64_t end4,
                        float* __restrict__ sumsq) {
     __shared__ float s_w[kWarpsPerCta];
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     float acc = 0.f;
-    for (int64_t i = beg4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < end4; i += stride) {
-        float4 v[kMaxRanks];
+    for (int64_t i0 = beg4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < end4; i0 += stride * UN) {
+        float4 v[UN][WMAX];
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r)
-            if (r < world) v[r] = __ldcs(reinterpret_cast<const float4*>(grads.p[r]) + i);
-        float4 s = v[0];
+        for (int u = 0; u < UN; ++u) {
+            const int64_t i = i0 + u * stride;
 #pragma unroll
-        for (int r = 1; r < kMaxRanks; ++r)
-            if (r < world) s = f4_add(s, v[r]);
-        reinterpret_cast<float4*>(grads.p[rank])[i] = s;
-        acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+            for (int r = 0; r < WMAX; ++r)
+                if (r < world && i < end4) v[u][r] = __ldcs(reinterpret_cast<const float4*>(grads.p[r]) + i);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const int64_t i = i0 + u * stride;
+            if (i >= end4) break;
+            float4 s = v[u][0];
+#pragma unroll
+            for (int r = 1; r < WMAX; ++r)
+                if (r < world) s = f4_add(s, v[u][r]);
+            reinterpret_cast<float4*>(grads.p[rank])[i] = s;
+            acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+        }
     }
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(kFullMask, acc, d);
@@ -124,9 +138,18 @@ extern "C" int nnue_ddp_reduce_shard(float* const* h_grad_ptrs, int32_t world, i
     PeerPtrs pp{};
     for (int r = 0; r < world; ++r) pp.p[r] = h_grad_ptrs[r];
     const int64_t n4 = (elem_end - elem_begin) / 4;
-    const unsigned grid = (unsigned)std::min<int64_t>((n4 + kThreads - 1) / kThreads, (int64_t)sm_count() * 8);
-    k_ddp_reduce_shard<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq);
+    const int cap = tuning().ddp_reduce_ctas > 0 ? tuning().ddp_reduce_ctas : sm_count() * 8;
+    const unsigned grid = (unsigned)std::min<int64_t>((n4 + kThreads - 1) / kThreads, (int64_t)cap);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (world <= 2)
+        k_ddp_reduce_shard<4, 2><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq);
+    else if (world <= 4)
+        k_ddp_reduce_shard<2, 4><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq);
+    else if (world <= 8)
+        k_ddp_reduce_shard<1, 8><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq);
+    else
+        k_ddp_reduce_shard<1, kMaxRanks><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4,
+                                                                  d_sumsq);
     NNUE_CUDA_TRY(cudaGetLastError());
     note_launches(1);
     return NNUE_OK;

@@ -538,6 +538,19 @@ static bool fused_vec_ok(int L1, int P, const void* a, const void* b, const void
            aligned16(d) && aligned16(e);
 }
 
+// Row slices of the next segment-mode backward calls (process-wide; one process drives one GPU
+// under data parallelism).  See nnue_ft_fused_bwd_slices.
+constexpr int kMaxBwdSlices = 16;
+struct BwdSlices {
+    int n = 0;
+    int64_t bounds[kMaxBwdSlices + 1] = {};
+    cudaEvent_t events[kMaxBwdSlices] = {};
+};
+static BwdSlices& bwd_slices() {
+    static BwdSlices s;
+    return s;
+}
+
 extern "C" int nnue_ft_fused_fwd(const float* us, const float* them, const int32_t* white_idx,
                                  const int32_t* black_idx, const int64_t* psqt_idx,
                                  const float* weight, const float* bias, float max_act,
@@ -738,5 +751,34 @@ extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32
     if (launch_err != cudaSuccess) return cuda_fail(launch_err, "backward prologue launch");
     if (rc != NNUE_OK) return rc;
     if (rj != NNUE_OK) return rj;
+    const BwdSlices& sl = bwd_slices();
+    if (sl.n > 0 && sl.bounds[sl.n] == N && sl.bounds[0] == 0) {
+        // the gradient in row slices, an event after each: a consumer on another stream (the
+        // data-parallel reduce) starts on slice i while slice i + 1 is computed
+        for (int i = 0; i < sl.n; ++i) {
+            rc = csr_reduce(plan, G, (int)W, grad_weight, s, sl.bounds[i], sl.bounds[i + 1]);
+            if (rc != NNUE_OK) return rc;
+            if (sl.events[i]) NNUE_CUDA_TRY(cudaEventRecord(sl.events[i], s));
+        }
+        return NNUE_OK;
+    }
     return csr_reduce(plan, G, (int)W, grad_weight, s);
+}
+
+extern "C" int nnue_ft_fused_bwd_slices(const int64_t* h_row_bounds, void* const* h_events, int32_t n_slices) {
+    BwdSlices& sl = bwd_slices();
+    if (n_slices <= 0) {
+        sl.n = 0;
+        return NNUE_OK;
+    }
+    NNUE_REQUIRE(n_slices <= kMaxBwdSlices && h_row_bounds != nullptr, NNUE_ERR_ARG,
+                 "nnue_ft_fused_bwd_slices: 1..%d slices with their row bounds", kMaxBwdSlices);
+    NNUE_REQUIRE(h_row_bounds[0] == 0, NNUE_ERR_ARG, "nnue_ft_fused_bwd_slices: the first slice starts at row 0");
+    for (int i = 0; i < n_slices; ++i)
+        NNUE_REQUIRE(h_row_bounds[i] <= h_row_bounds[i + 1], NNUE_ERR_ARG,
+                     "nnue_ft_fused_bwd_slices: row bounds must not decrease");
+    for (int i = 0; i <= n_slices; ++i) sl.bounds[i] = h_row_bounds[i];
+    for (int i = 0; i < n_slices; ++i) sl.events[i] = h_events ? static_cast<cudaEvent_t>(h_events[i]) : nullptr;
+    sl.n = n_slices;
+    return NNUE_OK;
 }

@@ -323,6 +323,21 @@ __global__ void __launch_bounds__(kThreads)
 // or `partial[chunk][1]` (piece that runs on into the next chunk);
 // k_segment_fixup adds them in chunk order, k_zero_empty_rows writes the rows
 // nobody touched.  Every order is fixed, so the result is reproducible.
+// Rows [begin, end) whose gradient a launch has to finish (a slice of the
+// table; the whole table by default).  A chunk takes part when any of its
+// entries can belong to such a row: its first row lies before `end` and the
+// next chunk's first row (>= this chunk's last row) not before `begin`.  A
+// chunk on a slice border runs in both slices and writes the same values twice.
+struct RowRange {
+    int begin, end, max_chunks;
+};
+__device__ __forceinline__ bool chunk_in_range(const int32_t* __restrict__ chunk_row, int c, const RowRange& rr) {
+    if (__ldg(chunk_row + c) >= rr.end) return false;
+    if (c + 1 >= rr.max_chunks) return true;
+    const int next = __ldg(chunk_row + c + 1);  // -1: no entries beyond this chunk
+    return next < 0 || next >= rr.begin;
+}
+
 __global__ void __launch_bounds__(kThreads)
     k_chunk_rows(const int32_t* __restrict__ offsets, int64_t N, int S, int max_chunks,
                  int32_t* __restrict__ chunk_row) {
@@ -348,13 +363,14 @@ __global__ void __launch_bounds__(kThreads, MINB)
                      const int32_t* __restrict__ offsets, const int32_t* __restrict__ entries,
                      const int32_t* __restrict__ chunk_row, float4* __restrict__ out,
                      float4* __restrict__ partial, int64_t N, int n_chunk_groups, int S,
-                     unsigned long long* status) {
+                     unsigned long long* status, RowRange rr) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x / n_chunk_groups;
     const int c = (blockIdx.x % n_chunk_groups) * kWarpsPerCta + warp;
     const int E = __ldg(offsets + N);
     const int e_beg = c * S;
     if (e_beg >= E) return;  // warp-uniform
+    if (!chunk_in_range(chunk_row, c, rr)) return;
     const int e_end = min(E, e_beg + S);
 
     int col[U];
@@ -373,7 +389,10 @@ __global__ void __launch_bounds__(kThreads, MINB)
     auto flush = [&](int pe) {  // piece [piece_beg, pe) of `row`
         if (next_b == row_beg) return;  // empty row: k_zero_empty_rows owns it
         float4* dst;
-        if (piece_beg == row_beg && pe == next_b) dst = out + (int64_t)row * W4;
+        if (piece_beg == row_beg && pe == next_b) {
+            if (row < rr.begin || row >= rr.end) return;  // a border chunk: that row belongs to another slice
+            dst = out + (int64_t)row * W4;
+        }
         else if (piece_beg == e_beg && row_beg < e_beg) dst = partial + ((int64_t)c * 2 + 0) * W4;
         else dst = partial + ((int64_t)c * 2 + 1) * W4;
 #pragma unroll
@@ -406,7 +425,7 @@ template <int U>
 __global__ void __launch_bounds__(kThreads)
     k_segment_fixup(const int32_t* __restrict__ offsets, const int32_t* __restrict__ chunk_row,
                     const float4* __restrict__ partial, float4* __restrict__ out, int64_t W4,
-                    int64_t N, int n_chunk_groups, int S) {
+                    int64_t N, int n_chunk_groups, int S, RowRange rr) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int tile = blockIdx.x / n_chunk_groups;
     const int c = (blockIdx.x % n_chunk_groups) * kWarpsPerCta + warp;
@@ -414,6 +433,7 @@ __global__ void __launch_bounds__(kThreads)
     const int e_beg = c * S;
     if (e_beg >= E) return;
     const int r = __ldg(chunk_row + c);
+    if (r < rr.begin || r >= rr.end) return;  // the row this warp would finish belongs to another slice
     const int rb = __ldg(offsets + r), re = __ldg(offsets + r + 1);
     if (rb >= e_beg) return;        // the opening row starts here: it has no earlier piece
     if (re > e_beg + S) return;     // it runs on: a later chunk finishes it
@@ -431,9 +451,9 @@ __global__ void __launch_bounds__(kThreads)
 // One warp per row: rows without a single entry get zeros.
 __global__ void __launch_bounds__(kThreads)
     k_zero_empty_rows(const int32_t* __restrict__ offsets, float4* __restrict__ out, int64_t W4,
-                      int64_t N) {
+                      int64_t row0, int64_t N) {
     const int lane = threadIdx.x & 31;
-    const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    const int64_t row = row0 + (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     if (row >= N) return;
     if (__ldg(offsets + row) != __ldg(offsets + row + 1)) return;
     for (int64_t c = lane; c < W4; c += 32) out[row * W4 + c] = f4_zero();
@@ -623,9 +643,15 @@ int csr_build(const CsrPlan& plan, const int32_t* const* lists, cudaStream_t s) 
     return NNUE_OK;
 }
 
-int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStream_t s) {
+int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStream_t s, int64_t row_begin,
+               int64_t row_end) {
     const int64_t N = plan.N, src_rows = plan.B * plan.n_lists;
     if (N == 0) return NNUE_OK;
+    if (row_end < 0 || row_end > N) row_end = N;
+    NNUE_REQUIRE(row_begin >= 0 && row_begin <= row_end, NNUE_ERR_ARG, "csr: bad row range");
+    if (row_begin == row_end) return NNUE_OK;
+    const bool whole = row_begin == 0 && row_end == N;
+    const RowRange rr{(int)row_begin, (int)row_end, (int)plan.max_chunks};
     unsigned long long* status = device_status_ptr();
     NNUE_REQUIRE(status, NNUE_ERR_CUDA, "csr: no device status word");
     const int64_t row_groups = (N + kWarpsPerCta - 1) / kWarpsPerCta;
@@ -644,13 +670,14 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
             NNUE_REQUIRE(tiles * groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
             const unsigned grid = (unsigned)(tiles * groups);
             float4* p4 = reinterpret_cast<float4*>(plan.partial);
-            k_zero_empty_rows<<<(unsigned)row_groups, kThreads, 0, s>>>(plan.offsets, o4, W4, N);
+            k_zero_empty_rows<<<(unsigned)((row_end - row_begin + kWarpsPerCta - 1) / kWarpsPerCta), kThreads, 0, s>>>(
+                plan.offsets, o4, W4, row_begin, row_end);
             // variant = rows per register buffer (R) and CTAs per SM the register budget must allow
             const int v = tuning().bwd_r;
 #define LAUNCH_CHUNKS(UU, RR, MB)                                                                  \
     k_segment_chunks<UU, RR, MB><<<grid, kThreads, 0, s>>>(s4, W4, src_rows, plan.offsets,         \
                                                            plan.entries, plan.chunk_row, o4, p4, N, \
-                                                           (int)groups, S, status)
+                                                           (int)groups, S, status, rr)
             if (U == 1) {
                 if (v == 1) LAUNCH_CHUNKS(1, 2, 6); else if (v == 2) LAUNCH_CHUNKS(1, 4, 4);
                 else LAUNCH_CHUNKS(1, 2, 4);
@@ -662,11 +689,12 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
                 if (v == 1) LAUNCH_CHUNKS(4, 1, 3); else LAUNCH_CHUNKS(4, 1, 4);
             }
 #undef LAUNCH_CHUNKS
-            if (U == 1) k_segment_fixup<1><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S);
-            else if (U == 2) k_segment_fixup<2><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S);
-            else k_segment_fixup<4><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S);
+            if (U == 1) k_segment_fixup<1><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);
+            else if (U == 2) k_segment_fixup<2><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);
+            else k_segment_fixup<4><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);
             note_launches(3);
         } else {
+            NNUE_REQUIRE(whole, NNUE_ERR_UNSUPPORTED, "csr: row slices need the chunked reduction (seg_chunk > 0)");
             NNUE_REQUIRE(tiles * row_groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
             const unsigned grid = (unsigned)(tiles * row_groups);
             const int long_row = tuning().long_row;
@@ -682,6 +710,7 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
             note_launches(1);
         }
     } else {
+        NNUE_REQUIRE(whole, NNUE_ERR_UNSUPPORTED, "csr: row slices need 16-byte aligned rows");
         const int64_t tiles = (W + 31) / 32;
         NNUE_REQUIRE(tiles * row_groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
         k_segment_reduce_scalar<<<(unsigned)(tiles * row_groups), kThreads, 0, s>>>(

@@ -47,6 +47,9 @@ int csr_build_overlapped(const CsrPlan& plan, const int32_t* const* lists, cudaS
 int csr_join(CsrJoin& join, cudaStream_t s);
 
 // out[r, :] = sum of the source rows named by the entries of r, for every r < N.
-int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStream_t s);
+// Rows [row_begin, row_end) only (row_end < 0: to the last row); the chunked
+// vector path supports any range, the fallbacks only the whole table.
+int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStream_t s, int64_t row_begin = 0,
+               int64_t row_end = -1);
 
 }  // namespace nnue

@@ -91,23 +91,46 @@ def shard_range(n_rows: int, width: int, world: int, rank: int) -> tuple[int, in
     return r0 * width, r1 * width
 
 
+def shard_ranges(bounds: list[int], width: int, world: int, rank: int) -> list[tuple[int, int]]:
+    """One element range per row slice [bounds[i], bounds[i+1]): rank's ceil-split
+    share of that slice.  Every rank owns a part of every slice, so all ranks
+    reduce a slice at the same time."""
+    out = []
+    for b0, b1 in zip(bounds[:-1], bounds[1:]):
+        e0, e1 = shard_range(b1 - b0, width, world, rank)
+        out.append((b0 * width + e0, b0 * width + e1))
+    return out
+
+
 class ShardedTableExchange:
     """Owner of the feature-transformer table under data parallelism.
 
     Every rank keeps the full table (the forward gathers from anywhere) but
-    optimizer state only for its own shard of rows.  Per step:
+    optimizer state only for its own share of the rows.  Per step:
       reduce()  peer-load reduce-scatter of the gradient + squared norm,
-      update()  RangerLite on the shard + peer-store all-gather of the rows.
+      update()  RangerLite on the share + peer-store all-gather of the rows.
     The table parameter's storage and the gradient buffer live in memory all
-    ranks have mapped; `install()` points the kernels' gradient sink at it."""
+    ranks have mapped; `install()` points the kernels' gradient sink at it.
 
-    def __init__(self, param: torch.nn.Parameter, group=None, pnm: bool = True, lookahead: bool = True):
+    `slices` (row bounds, first 0, last the row count) makes the backward
+    deliver the gradient slice by slice (`nnue_ft_fused_bwd_slices`) and the
+    reduce of slice i run on a second stream while slice i + 1 is still being
+    computed.  With the flat HalfKAv2_hm^ table, [0, 22528, 23232] puts the 704
+    factor rows, which collect half of all entries, last: nearly the whole
+    reduce traffic then hides behind their computation."""
+
+    def __init__(self, param: torch.nn.Parameter, group=None, pnm: bool = True, lookahead: bool = True,
+                 slices: list[int] | None = None):
         assert param.is_cuda and param.dim() == 2 and param.dtype == torch.float32
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
         self.param = param
         n, w = param.shape
         assert w % 4 == 0, "table width must be a multiple of 4 floats"
+        self.bounds = [0, n] if not slices else [int(b) for b in slices]
+        assert self.bounds[0] == 0 and self.bounds[-1] == n and all(
+            a <= b for a, b in zip(self.bounds[:-1], self.bounds[1:])), "slices must run from 0 to the row count"
+        assert len(self.bounds) - 1 <= 16
         dev = param.device
         self.table = _alloc_shared(n * w, dev, self.group)
         self.grad = _alloc_shared(n * w, dev, self.group)
@@ -115,52 +138,111 @@ class ShardedTableExchange:
         param.data = self.table.view(n, w)  # the model now reads the shared table
         self.table_ptrs, self._keep_t = _map_peers(self.table, self.group)
         self.grad_ptrs, self._keep_g = _map_peers(self.grad, self.group)
-        self.begin, self.end = shard_range(n, w, self.world, self.rank)
-        m = self.end - self.begin
+        self.ranges = shard_ranges(self.bounds, w, self.world, self.rank)
+        self.begin, self.end = self.ranges[0][0], self.ranges[-1][1]  # extent (one slice: the shard itself)
+        sizes = [e1 - e0 for e0, e1 in self.ranges]
+        self.state_at = [0]
+        for m_ in sizes:
+            self.state_at.append(self.state_at[-1] + m_)
+        m = self.state_at[-1]
         self.grad_ma = torch.zeros(m, device=dev)
         self.variance_ma = torch.zeros(m, device=dev)
         self.neg_grad_ma = torch.zeros(m, device=dev) if pnm else None
-        self.slow = self.table[self.begin : self.end].clone() if lookahead else None
+        self.slow = torch.cat([self.table[e0:e1] for e0, e1 in self.ranges]).clone() if lookahead else None
         self.step = 0
         self.ft_sumsq = torch.zeros(1, device=dev)
         self._token = torch.zeros(1, device=dev)
         self.grad_view = self.grad.view(n, w)
+        self.sliced = len(self.ranges) > 1
+        if self.sliced:
+            self.comm_stream = torch.cuda.Stream(dev)
+            self.slice_events = [torch.cuda.Event() for _ in self.ranges]
+            for e in self.slice_events:
+                e.record()  # creates the CUDA event the library will record
+            self._reduced = torch.cuda.Event()
+            self._zeroed = torch.cuda.Event()
+            self._zeroed.record()
 
     def install(self) -> None:
-        from . import _launch
+        import ctypes as C
+
+        from . import _launch, _lib
 
         _launch.GRAD_SINK = self.grad_view
+        lib = _lib.load()
+        if self.sliced:
+            arr = (C.c_int64 * len(self.bounds))(*self.bounds)
+            evs = (C.c_void_p * len(self.slice_events))(*[e.cuda_event for e in self.slice_events])
+            _lib.check(lib.nnue_ft_fused_bwd_slices(arr, evs, len(self.slice_events)), "nnue_ft_fused_bwd_slices")
+        else:
+            _lib.check(lib.nnue_ft_fused_bwd_slices(None, None, 0), "nnue_ft_fused_bwd_slices")
+
+    def uninstall(self) -> None:
+        """Back to plain gradients: no sink, no slices."""
+        from . import _launch, _lib
+
+        _launch.GRAD_SINK = None
+        _lib.check(_lib.load().nnue_ft_fused_bwd_slices(None, None, 0), "nnue_ft_fused_bwd_slices")
 
     def reduce(self) -> torch.Tensor:
-        """After every rank's backward (the caller has put a collective in between):
-        sums this rank's shard over the ranks.  Returns the squared norm of the whole
-        summed gradient (all-reduced scalar), which also fences the phase."""
+        """After every rank's backward has been ENQUEUED: sums this rank's share over the
+        ranks.  Returns the squared norm of the whole summed gradient (all-reduced scalar),
+        which also fences the phase.  One slice: the caller has put a collective between the
+        backward and this call.  Several: a tiny collective per slice, on the second stream,
+        tells that every rank has finished that slice."""
         from . import _launch
 
-        self.ft_sumsq.zero_()
-        _launch.ddp_reduce_shard(self.grad_ptrs, self.rank, self.begin, self.end, self.ft_sumsq)
+        if not self.sliced:
+            self.ft_sumsq.zero_()
+            e0, e1 = self.ranges[0]
+            _launch.ddp_reduce_shard(self.grad_ptrs, self.rank, e0, e1, self.ft_sumsq)
+        else:
+            cur = torch.cuda.current_stream(self.table.device)
+            comm = self.comm_stream
+            comm.wait_event(self._zeroed)  # ft_sumsq was cleared after its last reader
+            with torch.cuda.stream(comm):
+                for ev, (e0, e1) in zip(self.slice_events, self.ranges):
+                    comm.wait_event(ev)                           # this rank has finished the slice ...
+                    dist.all_reduce(self._token, group=self.group)  # ... and so has every other rank
+                    _launch.ddp_reduce_shard(self.grad_ptrs, self.rank, e0, e1, self.ft_sumsq)
+                self._reduced.record(comm)
+            cur.wait_event(self._reduced)
         dist.all_reduce(self.ft_sumsq, group=self.group)
         return self.ft_sumsq
 
     def update(self, hp, grad_scale: torch.Tensor | None) -> None:
         from . import _launch
 
-        _launch.ddp_update_shard(self.table_ptrs, self.rank, self.begin, self.end, self.grad, self.grad_ma,
-                                 self.neg_grad_ma, self.variance_ma, self.slow, grad_scale, hp)
-        # nobody may read its table before every rank has stored its shard into it
+        for (e0, e1), o0, o1 in zip(self.ranges, self.state_at[:-1], self.state_at[1:]):
+            if e1 == e0:
+                continue
+            _launch.ddp_update_shard(
+                self.table_ptrs, self.rank, e0, e1, self.grad, self.grad_ma[o0:o1],
+                None if self.neg_grad_ma is None else self.neg_grad_ma[o0:o1], self.variance_ma[o0:o1],
+                None if self.slow is None else self.slow[o0:o1], grad_scale, hp)
+        # nobody may read its table before every rank has stored its share into it
         dist.all_reduce(self._token, group=self.group)
+        if self.sliced:
+            self.ft_sumsq.zero_()
+            self._zeroed.record()
 
     def state_dict(self) -> dict:
-        """Full-size optimizer state of the table, gathered from the shards (same keys as RangerLite)."""
+        """Full-size optimizer state of the table, gathered from the shares (same keys as RangerLite)."""
         out = {"step": self.step}
+        n, w = self.param.shape
         for key, t in (("grad_ma", self.grad_ma), ("variance_ma", self.variance_ma),
                        ("neg_grad_ma", self.neg_grad_ma), ("lookahead_params", self.slow)):
             if t is None:
                 continue
-            per = (self.param.shape[0] + self.world - 1) // self.world * self.param.shape[1]
-            padded = torch.zeros(per, device=t.device)
-            padded[: t.numel()] = t
-            parts = [torch.empty_like(padded) for _ in range(self.world)]
-            dist.all_gather(parts, padded, group=self.group)
-            out[key] = torch.cat(parts)[: self.param.numel()].view_as(self.param).clone()
+            full = torch.zeros(n * w, device=t.device)
+            for (b0, b1), o0, o1 in zip(zip(self.bounds[:-1], self.bounds[1:]), self.state_at[:-1], self.state_at[1:]):
+                per = (b1 - b0 + self.world - 1) // self.world * w
+                if per == 0:
+                    continue
+                padded = torch.zeros(per, device=t.device)
+                padded[: o1 - o0] = t[o0:o1]
+                parts = [torch.empty_like(padded) for _ in range(self.world)]
+                dist.all_gather(parts, padded, group=self.group)
+                full[b0 * w : b1 * w] = torch.cat(parts)[: (b1 - b0) * w]
+            out[key] = full.view(n, w).clone()
         return out

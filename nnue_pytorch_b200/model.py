@@ -273,9 +273,13 @@ class TrainStep:
         ex = self.table_exchange
         if ex is not None:
             ex.param.grad = None  # its gradient lives in the exchange's buffer
+        if ex is not None and ex.sliced:
+            # slice by slice on the exchange's own stream, beside the rest of the backward; issued before
+            # the dense-gradient collective so that the per-slice collectives are not queued behind it
+            ft_sumsq = ex.reduce()
         if self.grad_hook is not None:
             self.grad_hook(self.model)  # a collective: every rank's backward is complete after it
-        if ex is not None:
+        if ex is not None and not ex.sliced:
             ft_sumsq = ex.reduce()
         if self._clipping:
             self._sumsq.zero_()

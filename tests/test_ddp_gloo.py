@@ -58,3 +58,21 @@ def test_single_rank_needs_no_hook():
     from nnue_pytorch_b200 import ddp
 
     assert ddp.make_grad_hook(torch.nn.Linear(2, 2), 1) is None
+
+
+def test_sliced_shares_tile_every_slice_exactly():
+    """Every rank owns a part of every row slice; the parts are whole rows, disjoint,
+    in rank order, and together cover the slice."""
+    from nnue_pytorch_b200.ddp import shard_ranges
+
+    width = 12
+    for bounds in ([0, 23232], [0, 22528, 23232], [0, 7, 7, 10, 1001], [0, 3, 5]):
+        for world in (1, 2, 3, 8):
+            per_rank = [shard_ranges(bounds, width, world, r) for r in range(world)]
+            for s, (b0, b1) in enumerate(zip(bounds[:-1], bounds[1:])):
+                at = b0 * width
+                for r in range(world):
+                    e0, e1 = per_rank[r][s]
+                    assert e0 == at and e1 >= e0 and e0 % width == 0 and e1 % width == 0
+                    at = e1
+                assert at == b1 * width

@@ -398,3 +398,44 @@ def test_fused_epilogue_matches_separate_ops(dev):
         assert torch.equal(outs[0][1], outs[1][1])
         assert torch.equal(outs[0][2], outs[1][2])
         assert len(torch.unique(outs[0][0] * 128 / corr)) <= 129
+
+
+@pytest.mark.parametrize("bounds", [[0, 23232], [0, 5000, 23232], [0, 7509, 15018, 22528, 23232], [0, 0, 1, 23231, 23232, 23232]])
+def test_sliced_backward_is_bitwise_the_unsliced_one(dev, bounds):
+    """The gradient produced slice by slice (what the data-parallel exchange
+    consumes while later slices are still computed) has the bits of the
+    one-launch gradient, and the slice events are recorded."""
+    import ctypes as C
+
+    from nnue_pytorch_b200 import _lib, positions
+
+    b = positions.generate_batch(2048, 11, layout="baseline")
+    c = {"us": t(b.us), "them": t(b.them), "white": t(b.white), "black": t(b.black),
+         "psqt": t((b.piece_count - 1) // 4), "max_act": 255.0 / 256.0, "l1": 256}
+    gen = torch.Generator().manual_seed(2)
+    c["weight"] = torch.randn(positions.NUM_INPUTS_BASELINE, 264, generator=gen) * 0.05
+    c["bias"] = torch.randn(264, generator=gen) * 0.05
+    c["grad_l0"] = torch.randn(2048, 256, generator=gen)
+    c["grad_wpsqt"] = torch.randn(2048, 1, generator=gen)
+    c["grad_bpsqt"] = torch.randn(2048, 1, generator=gen)
+    lib = _lib.load()
+    ref = _run_fused(dev, c, "segment")
+    events = [torch.cuda.Event() for _ in range(len(bounds) - 1)]
+    probe = torch.cuda.Event()
+    probe.record()
+    torch.cuda.synchronize()
+    arr = (C.c_int64 * len(bounds))(*bounds)
+    evs = (C.c_void_p * len(events))(*[e.cuda_event for e in events]) if events else None
+    # a torch event has no CUDA handle until it is first recorded
+    for e in events:
+        e.record()
+    evs = (C.c_void_p * len(events))(*[e.cuda_event for e in events])
+    _lib.check(lib.nnue_ft_fused_bwd_slices(arr, evs, len(events)), "nnue_ft_fused_bwd_slices")
+    try:
+        got = _run_fused(dev, c, "segment")
+    finally:
+        _lib.check(lib.nnue_ft_fused_bwd_slices(None, None, 0), "nnue_ft_fused_bwd_slices")
+    torch.cuda.synchronize()
+    assert all(e.query() for e in events)
+    assert torch.equal(got["grad_weight"], ref["grad_weight"])
+    assert torch.equal(got["grad_bias"], ref["grad_bias"])

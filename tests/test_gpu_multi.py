@@ -52,32 +52,40 @@ def _worker(rank, world, port, out_dir):
         ref_state = {k: v.clone() for k, v in step_ref.optimizer.state[ref.input.features[0].weight].items()
                      if torch.is_tensor(v)}
 
-        fused = build()
-        table = fused.input.features[0].weight
-        ex = ShardedTableExchange(table)
-        step = TrainStep(fused, clip=2.0, grad_hook=make_grad_hook(fused, world, average=False, skip=[table]),
-                         grad_prescale=1.0 / world, table_exchange=ex)
-        losses = [float(step(b)) for b in batches]
-        _launch.GRAD_SINK = None
-        _launch.device_status(dev)
-        sd = ex.state_dict()
-
         def rel(a, b):
             return float((a - b).abs().max()) / max(float(b.abs().max()), 1e-30)
 
+        def run(slices):
+            fused = build()
+            table = fused.input.features[0].weight
+            ex = ShardedTableExchange(table, slices=slices)
+            step = TrainStep(fused, clip=2.0, grad_hook=make_grad_hook(fused, world, average=False, skip=[table]),
+                             grad_prescale=1.0 / world, table_exchange=ex)
+            losses = [float(step(b)) for b in batches]
+            ex.uninstall()
+            _launch.device_status(dev)
+            sd = ex.state_dict()
+            rep = {
+                "loss": max(abs(a - b) / abs(b) for a, b in zip(losses, losses_ref)),
+                "table": rel(table.detach(), ref_table),
+                "small": max(rel(p.detach(), q.detach()) for (n, p), (_, q) in
+                             zip(fused.named_parameters(), ref.named_parameters()) if "features" not in n),
+                "state": max(rel(sd[k], ref_state[k]) for k in ("grad_ma", "neg_grad_ma", "variance_ma", "lookahead_params")),
+                "step": sd["step"],
+            }
+            # every rank must hold the same table after the all-gather
+            mine = table.detach().clone()
+            other = mine.clone()
+            dist.broadcast(other, src=0)
+            rep["ranks_agree"] = bool(torch.equal(mine, other))
+            return rep
+
+        n_rows = ref_table.shape[0]
         report = {
-            "loss": max(abs(a - b) / abs(b) for a, b in zip(losses, losses_ref)),
-            "table": rel(table.detach(), ref_table),
-            "small": max(rel(p.detach(), q.detach()) for (n, p), (_, q) in
-                         zip(fused.named_parameters(), ref.named_parameters()) if "features" not in n),
-            "state": max(rel(sd[k], ref_state[k]) for k in ("grad_ma", "neg_grad_ma", "variance_ma", "lookahead_params")),
-            "step": sd["step"],
+            "one_slice": run(None),
+            "two_slices": run([0, n_rows - 704, n_rows]),           # factor rows last, reduce overlapped
+            "four_slices": run([0, 9001, 9001, n_rows - 704, n_rows]),  # an empty slice and ragged shares
         }
-        # every rank must hold the same table after the all-gather
-        mine = table.detach().clone()
-        other = mine.clone()
-        dist.broadcast(other, src=0)
-        report["ranks_agree"] = bool(torch.equal(mine, other))
         torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
@@ -92,8 +100,9 @@ def test_sharded_table_exchange_matches_allreduce(tmp_path):
 
     mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
     for r in range(2):
-        rep = torch.load(tmp_path / f"rank{r}.pt")
-        assert rep["ranks_agree"], rep
-        assert rep["step"] == 6
-        assert rep["loss"] <= 1e-5, rep
-        assert rep["table"] <= 1e-5 and rep["small"] <= 1e-5 and rep["state"] <= 1e-5, rep
+        report = torch.load(tmp_path / f"rank{r}.pt")
+        for name, rep in report.items():
+            assert rep["ranks_agree"], (name, rep)
+            assert rep["step"] == 6
+            assert rep["loss"] <= 1e-5, (name, rep)
+            assert rep["table"] <= 1e-5 and rep["small"] <= 1e-5 and rep["state"] <= 1e-5, (name, rep)
