@@ -155,7 +155,7 @@ class ShardedTableExchange:
         self.grad_view = self.grad.view(n, w)
         self.sliced = len(self.ranges) > 1
         if self.sliced:
-            self.comm_stream = torch.cuda.Stream(dev)
+            self.comm_stream = torch.cuda.Stream(dev, priority=-1)  # its CTAs go first when an SM frees up
             self.slice_events = [torch.cuda.Event() for _ in self.ranges]
             for e in self.slice_events:
                 e.record()  # creates the CUDA event the library will record
