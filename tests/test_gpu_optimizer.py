@@ -153,3 +153,52 @@ def test_clip_coefficient_matches_torch(dev):
         _launch.clip_coef(sumsq, max_norm, coef, 0.25)
         want = 0.25 * torch.clamp(max_norm / (0.25 * total + 1e-6), max=1.0)
         assert abs(float(coef) - float(want)) <= 1e-5 * float(want)
+
+
+def test_multi_tensor_norm_matches_per_tensor_calls(dev):
+    from nnue_pytorch_b200 import _launch
+
+    gen = torch.Generator().manual_seed(9)
+    shapes = [(3072,), (32, 3072), (32,), (256, 3072), (256,), (256, 64), (256,), (8, 128), (8,), (5001, 264), (3,)] * 2
+    gs = [torch.randn(*sh, generator=gen).to(dev) for sh in shapes]  # 22 tensors: more than one launch's worth
+    gs.append(torch.randn(17, generator=gen).to(dev)[1:])             # not 16-byte aligned
+    multi = torch.zeros(1, device=dev)
+    _launch.grad_sumsq_multi(gs, multi)
+    want = sum(float((g.double() ** 2).sum()) for g in gs)
+    assert abs(float(multi) - want) <= 1e-5 * want
+    _launch.grad_sumsq_multi([], multi)  # nothing to add
+    assert abs(float(multi) - want) <= 1e-5 * want
+
+
+def test_multi_tensor_update_is_bitwise_the_single_tensor_update(dev):
+    """Nine small tensors with different constants in one launch = nine launches."""
+    from nnue_pytorch_b200 import _launch
+
+    gen = torch.Generator().manual_seed(4)
+    shapes = [(3080,), (32, 3072), (32,), (256, 3072), (255,), (256, 64), (7,), (8, 128), (1,)]
+
+    def state():
+        g2 = torch.Generator().manual_seed(5)
+        out = []
+        for sh in shapes:
+            out.append([torch.randn(*sh, generator=g2).to(dev) * s for s in (0.1, 0.01, 0.02, 0.02)] +
+                       [torch.rand(*sh, generator=g2).to(dev) * 1e-3, torch.randn(*sh, generator=g2).to(dev) * 0.1])
+        return out  # p, grad, grad_ma, neg_grad_ma, variance_ma, slow
+
+    scale = torch.full((1,), 0.37, device=dev)
+    for step_no, merge in ((1, 0), (2, 0), (5, 1)):
+        hps = []
+        for i in range(len(shapes)):
+            hps.append(_launch.hparams_struct(
+                beta2=0.999, one_minus_beta2=0.001, mom=0.81, one_minus_mom=0.19, one_plus_f=2.0, f=1.0,
+                noise_norm_inv=5.0 ** -0.5, step_size=8.75e-4 * (1 + 0.1 * i), bc2_sqrt=(1 - 0.999 ** step_no) ** 0.5,
+                eps=1e-7, wd_keep=1.0 if i % 2 else 0.999, alpha=0.5, one_minus_alpha=0.5, use_pnm=1,
+                step_is_odd=step_no % 2, do_merge=merge, phase=0))
+        a, b = state(), state()
+        for (p, g, gm, ngm, vm, slow), hp in zip(a, hps):
+            _launch.ranger_update(p, g, gm, ngm, vm, slow, None, scale, hp)
+        _launch.ranger_update_multi([(p, g, gm, ngm, vm, slow, hp) for (p, g, gm, ngm, vm, slow), hp in zip(b, hps)], scale)
+        for ta, tb in zip(a, b):
+            for x, y in zip(ta, tb):
+                assert torch.equal(x, y), (step_no, x.shape)
+    _ = gen

@@ -163,7 +163,8 @@ def test_training_steps_track_the_oracle(dev):
     assert all(v <= 1e-5 for v in worst.values()), worst  # measured on B200: 8.8e-6, 6.3e-6, 5.2e-6
 
 
-@pytest.mark.parametrize("B,L1,fq", [(300, 64, True), (2000, 256, True), (777, 96, False), (5, 32, True)])
+@pytest.mark.parametrize("B,L1,fq", [(300, 64, True), (2000, 256, True), (777, 96, False), (5, 32, True),
+                                     (1, 32, False), (4097, 3072, False)])
 def test_fused_layer_stack_matches_torch_layers(dev, B, L1, fq):
     """Bucket-aware layer-stack kernels against the plain torch layers of the same
     module (F.linear over all buckets + selection): output and every gradient."""
@@ -179,6 +180,8 @@ def test_fused_layer_stack_matches_torch_layers(dev, B, L1, fq):
     bucket = torch.randint(0, 8, (B,), device=dev)
     if B > 100:
         bucket[bucket == 5] = 4  # an empty bucket
+    if B == 777:
+        bucket[:] = 6            # everything in one bucket
     gy = torch.randn(B, 1, device=dev)
     res = []
     for fused in (True, False):
