@@ -91,15 +91,16 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-def test_sharded_table_exchange_matches_allreduce(tmp_path):
+@pytest.mark.parametrize("world", [2, 4])
+def test_sharded_table_exchange_matches_allreduce(tmp_path, world):
     if not torch.cuda.is_available():
         pytest.fail("GPU tests need a CUDA device")
-    if torch.cuda.device_count() < 2:
-        pytest.skip("needs two GPUs")
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
     import torch.multiprocessing as mp
 
-    mp.spawn(_worker, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
-    for r in range(2):
+    mp.spawn(_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
         report = torch.load(tmp_path / f"rank{r}.pt")
         for name, rep in report.items():
             assert rep["ranks_agree"], (name, rep)
