@@ -49,7 +49,11 @@ enum {
 
 /* Scatter strategy of the backward kernels. */
 enum {
-    NNUE_BWD_AUTO = 0,     /* library picks (segment reduction today) */
+    NNUE_BWD_AUTO = 0,     /* segment reduction, except that nnue_ft_fused_bwd switches to
+                              atomics while the lists it saw on its previous auto call of the
+                              same batch size held fewer than 6 active rows on average
+                              (nearly empty boards; the count reaches the host without a
+                              synchronisation, one call late) */
     NNUE_BWD_ATOMIC = 1,   /* vector red.global.add into a zeroed gradient */
     NNUE_BWD_SEGMENT = 2   /* CSR by row + gather-sum; every row written once */
 };

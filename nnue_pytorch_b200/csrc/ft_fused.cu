@@ -641,13 +641,13 @@ extern "C" size_t nnue_ft_fused_bwd_workspace_bytes(int64_t B, int32_t K, int64_
     return bytes + 256;
 }
 
-extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32_t* white_idx,
-                                 const int32_t* black_idx, const int64_t* psqt_idx, float max_act,
-                                 float out_scale, const float* grad_l0, const float* grad_wpsqt,
-                                 const float* grad_bpsqt, const float* saved, float* grad_weight,
-                                 float* grad_bias, int64_t B, int32_t K, int64_t N, int32_t L1,
-                                 int32_t P, void* workspace, size_t workspace_bytes, int32_t mode,
-                                 void* stream) {
+static int fused_bwd_impl(const float* us, const float* them, const int32_t* white_idx,
+                          const int32_t* black_idx, const int64_t* psqt_idx, float max_act,
+                          float out_scale, const float* grad_l0, const float* grad_wpsqt,
+                          const float* grad_bpsqt, const float* saved, float* grad_weight,
+                          float* grad_bias, int64_t B, int32_t K, int64_t N, int32_t L1,
+                          int32_t P, void* workspace, size_t workspace_bytes, int32_t mode,
+                          void* stream) {
     const FtAct act{max_act, 0.f, 0.f, out_scale, 0.f};
     NNUE_REQUIRE(B >= 0 && K >= 0 && N >= 0 && L1 > 0 && P >= 0, NNUE_ERR_ARG,
                  "nnue_ft_fused_bwd: negative size");
@@ -763,6 +763,117 @@ extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32
         return NNUE_OK;
     }
     return csr_reduce(plan, G, (int)W, grad_weight, s);
+}
+
+// ---- mode = auto: which scatter strategy ---------------------------------------------------------
+// The segment reduction wins as soon as a position activates more than a handful of rows; on nearly
+// empty boards its fixed costs (one gradient row per (position, perspective) written and read, the
+// CSR) exceed the whole atomic scatter.  Which case applies is a property of the data, known only on
+// the device, and the host must not wait for it: every auto call leaves the number of active entries
+// of its lists in pinned host memory (a tiny kernel after the real work), and the NEXT auto call of
+// the same batch size reads whatever count has arrived by then.  Training data (about 34 rows per
+// list) always take the segment route; mode = segment forces it (and its reproducible sums).
+struct DensityProbe {
+    long long* h = nullptr;        // pinned, mapped: [0] active entries, [1] lists counted (2 B)
+    long long* h_dev = nullptr;    // device view of h
+    unsigned long long* d = nullptr;  // device: [0] running entry count, [1] CTAs done
+    unsigned calls = 0;
+};
+static DensityProbe* density_probe() {
+    static DensityProbe table[64];
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return nullptr;
+    DensityProbe& t = table[dev];
+    if (!t.h) {
+        if (cudaHostAlloc(reinterpret_cast<void**>(&t.h), 2 * sizeof(long long), cudaHostAllocMapped) != cudaSuccess) {
+            t.h = nullptr;
+            cudaGetLastError();
+            return nullptr;
+        }
+        t.h[0] = t.h[1] = 0;
+        if (cudaHostGetDevicePointer(reinterpret_cast<void**>(&t.h_dev), t.h, 0) != cudaSuccess ||
+            cudaMalloc(reinterpret_cast<void**>(&t.d), 2 * sizeof(unsigned long long)) != cudaSuccess ||
+            cudaMemset(t.d, 0, 2 * sizeof(unsigned long long)) != cudaSuccess) {
+            cudaGetLastError();
+            cudaFreeHost(t.h);
+            t.h = nullptr;
+            return nullptr;
+        }
+    }
+    return &t;
+}
+
+namespace nnue {
+// warp per position: active entries of its two lists; the CTA that finishes last publishes the total
+__global__ void __launch_bounds__(kThreads)
+    k_density_probe(const int32_t* __restrict__ wi, const int32_t* __restrict__ bi, int64_t B, int K,
+                    unsigned long long* __restrict__ d, long long* __restrict__ h_out) {
+    __shared__ int s_n[kWarpsPerCta];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    int n = 0;
+    for (int64_t p = (int64_t)blockIdx.x * kWarpsPerCta + warp; p < B; p += (int64_t)gridDim.x * kWarpsPerCta)
+        n += count_active(wi + p * K, K, lane) + count_active(bi + p * K, K, lane);
+    if (lane == 0) s_n[warp] = n;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int t = 0;
+        for (int w = 0; w < kWarpsPerCta; ++w) t += s_n[w];
+        atomicAdd(d, (unsigned long long)t);
+        __threadfence();
+        if (atomicAdd(d + 1, 1ULL) == gridDim.x - 1) {
+            __threadfence();
+            h_out[0] = (long long)atomicExch(d, 0ULL);
+            h_out[1] = 2 * B;
+            d[1] = 0;
+            __threadfence_system();
+        }
+    }
+}
+}  // namespace nnue
+
+constexpr long long kAtomicBelowRowsPerList = 6;
+
+extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32_t* white_idx,
+                                 const int32_t* black_idx, const int64_t* psqt_idx, float max_act,
+                                 float out_scale, const float* grad_l0, const float* grad_wpsqt,
+                                 const float* grad_bpsqt, const float* saved, float* grad_weight,
+                                 float* grad_bias, int64_t B, int32_t K, int64_t N, int32_t L1,
+                                 int32_t P, void* workspace, size_t workspace_bytes, int32_t mode,
+                                 void* stream) {
+    int run_mode = mode;
+    DensityProbe* probe = nullptr;
+    if (mode == NNUE_BWD_AUTO && B > 0 && K > 0 && white_idx && black_idx && bwd_slices().n == 0) {
+        probe = density_probe();
+        if (probe) {
+            const volatile long long* h = probe->h;
+            const long long entries = h[0], lists = h[1];
+            const bool known = lists == 2 * B;
+            if (known && entries < kAtomicBelowRowsPerList * lists) run_mode = NNUE_BWD_ATOMIC;
+            // dense data of a known batch size (training): look again only every fourth call
+            if (known && run_mode != NNUE_BWD_ATOMIC && (++probe->calls & 3) != 0) probe = nullptr;
+        }
+    }
+    // the count for the next call runs on the helper stream, beside the real work
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    SideStreamView side;
+    bool probing = false;
+    if (probe && side_stream_get(side)) {
+        NNUE_CUDA_TRY(cudaEventRecord(side.fork, s));
+        NNUE_CUDA_TRY(cudaStreamWaitEvent(side.stream, side.fork, 0));
+        const unsigned grid = (unsigned)((B + kWarpsPerCta - 1) / kWarpsPerCta);  // a warp per position: 4 loads deep
+        k_density_probe<<<grid, kThreads, 0, side.stream>>>(white_idx, black_idx, B, K, probe->d, probe->h_dev);
+        NNUE_CUDA_TRY(cudaGetLastError());
+        note_launches(1);
+        probing = true;
+    }
+    const int rc = fused_bwd_impl(us, them, white_idx, black_idx, psqt_idx, max_act, out_scale, grad_l0,
+                                  grad_wpsqt, grad_bpsqt, saved, grad_weight, grad_bias, B, K, N, L1, P,
+                                  workspace, workspace_bytes, run_mode, stream);
+    if (probing) {  // the caller's stream must not outrun a reader of its index lists
+        NNUE_CUDA_TRY(cudaEventRecord(side.join, side.stream));
+        NNUE_CUDA_TRY(cudaStreamWaitEvent(s, side.join, 0));
+    }
+    return rc;
 }
 
 extern "C" int nnue_ft_fused_bwd_slices(const int64_t* h_row_bounds, void* const* h_events, int32_t n_slices) {

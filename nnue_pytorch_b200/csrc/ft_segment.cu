@@ -741,6 +741,15 @@ static SideStream* side_stream() {
     return &t;
 }
 
+bool side_stream_get(SideStreamView& out) {
+    SideStream* side = side_stream();
+    if (!side) return false;
+    out.stream = side->stream;
+    out.fork = side->fork;
+    out.join = side->join;
+    return true;
+}
+
 int csr_build_overlapped(const CsrPlan& plan, const int32_t* const* lists, cudaStream_t s,
                          CsrJoin& join) {
     join.pending = false;

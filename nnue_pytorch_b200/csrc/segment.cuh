@@ -46,6 +46,15 @@ int csr_build_overlapped(const CsrPlan& plan, const int32_t* const* lists, cudaS
                          CsrJoin& join);
 int csr_join(CsrJoin& join, cudaStream_t s);
 
+// The library's per-device helper stream with its fork / join events, for work that may run
+// beside the caller's stream: record `fork` on the caller's stream, make `stream` wait for it,
+// enqueue, record `join` on `stream`, make the caller's stream wait for `join`.
+struct SideStreamView {
+    cudaStream_t stream = nullptr;
+    cudaEvent_t fork = nullptr, join = nullptr;
+};
+bool side_stream_get(SideStreamView& out);
+
 // out[r, :] = sum of the source rows named by the entries of r, for every r < N.
 // Rows [row_begin, row_end) only (row_end < 0: to the last row); the chunked
 // vector path supports any range, the fallbacks only the whole table.

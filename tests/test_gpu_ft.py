@@ -439,3 +439,48 @@ def test_sliced_backward_is_bitwise_the_unsliced_one(dev, bounds):
     assert all(e.query() for e in events)
     assert torch.equal(got["grad_weight"], ref["grad_weight"])
     assert torch.equal(got["grad_bias"], ref["grad_bias"])
+
+
+def test_auto_mode_switches_to_atomics_on_nearly_empty_boards(dev):
+    """mode=auto learns the density of the lists from its previous call (no
+    synchronisation): dense boards stay on the segment route, boards with two
+    pieces move to the atomic scatter within a few calls; the gradients
+    agree with the segment route either way."""
+    from nnue_pytorch_b200 import _lib, positions
+
+    lib = _lib.load()
+
+    def case(fixed):
+        b = positions.generate_batch(3000, 5, layout="baseline", fixed_count=fixed)
+        c = {"us": t(b.us), "them": t(b.them), "white": t(b.white), "black": t(b.black),
+             "psqt": t((b.piece_count - 1) // 4), "max_act": 255.0 / 256.0, "l1": 256}
+        gen = torch.Generator().manual_seed(2)
+        c["weight"] = torch.randn(positions.NUM_INPUTS_BASELINE, 264, generator=gen) * 0.05
+        c["bias"] = torch.randn(264, generator=gen) * 0.05
+        c["grad_l0"] = torch.randn(3000, 256, generator=gen)
+        c["grad_wpsqt"] = torch.randn(3000, 1, generator=gen)
+        c["grad_bpsqt"] = torch.randn(3000, 1, generator=gen)
+        return c
+
+    def launches_of_auto(c):
+        torch.cuda.synchronize()
+        n0 = lib.nnue_b200_launch_count()
+        r = _run_fused(dev, c, "auto")
+        torch.cuda.synchronize()
+        return lib.nnue_b200_launch_count() - n0, r
+
+    sparse, dense = case(2), case(None)
+    ref_sparse, ref_dense = _run_fused(dev, sparse, "segment"), _run_fused(dev, dense, "segment")
+    launches_of_auto(dense)            # the probe of this call describes dense boards
+    n_dense, r = launches_of_auto(dense)
+    n_dense = max(n_dense, launches_of_auto(dense)[0])  # with or without the count kernel
+    assert torch.equal(r["grad_weight"], ref_dense["grad_weight"])  # still the segment route, bit for bit
+    for _ in range(4):                 # dense data are re-counted every fourth call: at most four calls late
+        launches_of_auto(sparse)
+    n_sparse, r = launches_of_auto(sparse)
+    assert n_sparse < n_dense - 5, (n_sparse, n_dense)  # one scatter kernel instead of the CSR pipeline
+    assert max_rel_err(r["grad_weight"].cpu(), ref_sparse["grad_weight"].cpu()) <= TOL
+    assert max_rel_err(r["grad_bias"].cpu(), ref_sparse["grad_bias"].cpu()) <= TOL
+    launches_of_auto(dense)
+    n_again, r = launches_of_auto(dense)  # and back (sparse data are counted on every call)
+    assert n_again >= n_dense - 1 and torch.equal(r["grad_weight"], ref_dense["grad_weight"])
