@@ -50,6 +50,20 @@ def test_host_side_argument_validation(lib):
                                  4, 4, 4, 8, 8, None, 0, 9, None) == -1  # unknown mode
     assert lib.nnue_b200_tune(b"no_such_knob", 1) == -1
     assert lib.nnue_rangerlite_update(None, None, None, None, None, None, None, None, 1, 1, None, None) == -1
+    # newer entry points: the same convention
+    i64 = lambda *v: (C.c_int64 * len(v))(*v)  # noqa: E731
+    assert lib.nnue_ft_fused_bwd_slices(i64(0, 10, 5), None, 2) == -1           # bounds decrease
+    assert lib.nnue_ft_fused_bwd_slices(i64(1, 10), None, 1) == -1              # does not start at row 0
+    assert lib.nnue_ft_fused_bwd_slices(None, None, 3) == -1                    # slices without bounds
+    assert lib.nnue_ft_fused_bwd_slices(i64(0, 4, 9), None, 2) == 0 and lib.nnue_ft_fused_bwd_slices(None, None, 0) == 0
+    assert lib.nnue_batch_build_halfka(None, 4, 7, 64, None, None, None, None, None, None, None, None, None) == -1  # layout
+    assert lib.nnue_batch_build_halfka(None, 4, 1, 32, None, None, None, None, None, None, None, None, None) == -1  # K < 64
+    assert lib.nnue_batch_build_halfka(None, 0, 0, 32, None, None, None, None, None, None, None, None, None) == 0
+    assert lib.nnue_sf_loss(None, None, None, None, None, None, None, None, None, None, None, None, 4, None) == -1
+    assert lib.nnue_grad_sumsq_multi(None, None, 3, None, None) == -1 and lib.nnue_grad_sumsq_multi(None, None, 0, None, None) == 0
+    assert lib.nnue_rangerlite_update_multi(None, 2, None, None) == -1 and lib.nnue_rangerlite_update_multi(None, 0, None, None) == 0
+    assert lib.nnue_ls_effective_weights(*([None] * 15), 0, 8, None) == -1       # L1 = 0
+    assert lib.nnue_ls_plan(None, 4, 99, None, 0, None) == -4                    # too many buckets
     # empty batches are a no-op that needs no device
     assert lib.nnue_ft_sparse_fwd(None, None, None, None, 0, 4, 4, 4, None) == 0
     assert lib.nnue_ft_fused_fwd(None, None, None, None, None, None, None, 1.0, 0.0, 0.0, 1.0, None, None, None, None,
