@@ -410,6 +410,26 @@ int nnue_quant_eval(const int32_t* white_idx, const int32_t* black_idx,
                     int32_t L3, int32_t P, int32_t buckets,
                     const nnue_quant_params* h_qp, void* stream);
 
+/* The same evaluation in two kernels: the feature-transformer part as a gather
+ * whose table slice stays in the L2 (column tiles are the slow grid dimension,
+ * as in nnue_ft_fused_fwd), then the layers.  Results are bit-identical to
+ * nnue_quant_eval; it needs nnue_quant_eval_workspace_bytes(B, L1) bytes of
+ * scratch (less is accepted: the batch is then processed in more passes) and
+ * ft_b 16-byte aligned. */
+size_t nnue_quant_eval_workspace_bytes(int64_t B, int32_t L1);
+int nnue_quant_eval_tiled(const int32_t* white_idx, const int32_t* black_idx,
+                          const uint8_t* stm_white, const int32_t* bucket,
+                          const int16_t* ft_w, const int32_t* ft_psqt,
+                          const int32_t* ft_b,
+                          const int8_t* l1_w, const int32_t* l1_b,
+                          const int8_t* l2_w, const int32_t* l2_b,
+                          const int8_t* out_w, const int32_t* out_b,
+                          int32_t* out,
+                          int64_t B, int32_t K, int64_t N, int32_t L1, int32_t L2,
+                          int32_t L3, int32_t P, int32_t buckets,
+                          const nnue_quant_params* h_qp, void* workspace,
+                          size_t workspace_bytes, void* stream);
+
 /* ---- L: training loss and its gradient, one launch ------------------------
  * `calculate_sf_loss` with `remap_tablebase_score` (model/nnue.py:18-69), fused
  * with the PSQT term of the model output (model/model.py:107-133) and the

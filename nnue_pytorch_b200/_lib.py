@@ -160,6 +160,11 @@ PROTOTYPES = {
     "nnue_ls_fold_grads": (C.c_int, [_P, _P, _P, _P, _I32, _I32, _P]),
     "nnue_sf_loss_workspace_bytes": (_SZ, []),
     "nnue_sf_loss": (C.c_int, [_P] * 6 + [C.POINTER(LossParams), _P, _P, _P, _P, _P, _I64, _P]),
+    "nnue_quant_eval_workspace_bytes": (_SZ, [_I64, _I32]),
+    "nnue_quant_eval_tiled": (
+        C.c_int,
+        [_P] * 14 + [_I64, _I32, _I64, _I32, _I32, _I32, _I32, _I32, C.POINTER(QuantParams), _P, _SZ, _P],
+    ),
     "nnue_batch_build_halfka": (C.c_int, [_P, _I64, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
 }
 

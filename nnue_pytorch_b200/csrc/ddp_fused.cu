@@ -146,7 +146,7 @@ extern "C" int nnue_ddp_reduce_shard(float* const* h_grad_ptrs, int32_t world, i
     else if (world <= 4)
         k_ddp_reduce_shard<2, 4><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq);
     else if (world <= 8)
-        k_ddp_reduce_shard<1, 8><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq);
+        k_ddp_reduce_shard<2, 8><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq);
     else
         k_ddp_reduce_shard<1, kMaxRanks><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4,
                                                                   d_sumsq);

@@ -104,9 +104,10 @@ class QuantizedNet:
         return self
 
     @torch.no_grad()
-    def evaluate(self, white_indices, black_indices, stm_white, piece_count) -> torch.Tensor:
+    def evaluate(self, white_indices, black_indices, stm_white, piece_count, tiled: bool = True) -> torch.Tensor:
         """int32 [B]: the evaluation in units of 1/(2 * nnue2score * weight_scale_out)
-        (= 1/19200 by default) of the float model output."""
+        (= 1/19200 by default) of the float model output.  `tiled=False` runs the
+        one-kernel form (no scratch memory, slower); the results are the same bits."""
         dev = self.device
         assert white_indices.dtype == torch.int32 and black_indices.dtype == torch.int32
         assert white_indices.is_cuda and white_indices.is_contiguous() and black_indices.is_contiguous()
@@ -115,6 +116,20 @@ class QuantizedNet:
         stm = stm_white.reshape(-1).to(device=dev, dtype=torch.uint8).contiguous()
         bucket = ((piece_count.reshape(-1) - 1) // 4).to(device=dev, dtype=torch.int32).contiguous()
         out = torch.empty(B, dtype=torch.int32, device=dev)
+        lib = _lib.load()
+        if tiled and B > 0:
+            ws = torch.empty(lib.nnue_quant_eval_workspace_bytes(B, self.L1), dtype=torch.uint8, device=dev)
+            with torch.cuda.device(dev):
+                st = lib.nnue_quant_eval_tiled(
+                    white_indices.data_ptr(), black_indices.data_ptr(), stm.data_ptr(), bucket.data_ptr(),
+                    self.ft_w.data_ptr(), self.ft_psqt.data_ptr(), self.ft_b.data_ptr(),
+                    self.l1_w.data_ptr(), self.l1_b.data_ptr(), self.l2_w.data_ptr(), self.l2_b.data_ptr(),
+                    self.out_w.data_ptr(), self.out_b.data_ptr(), out.data_ptr(),
+                    B, K, self.N, self.L1, self.L2, self.L3, self.P, self.buckets,
+                    C.byref(self._qp), ws.data_ptr(), ws.numel(), torch.cuda.current_stream(dev).cuda_stream,
+                )
+            _lib.check(st, "nnue_quant_eval_tiled")
+            return out
         with torch.cuda.device(dev):
             st = _lib.load().nnue_quant_eval(
                 white_indices.data_ptr(), black_indices.data_ptr(), stm.data_ptr(), bucket.data_ptr(),

@@ -82,3 +82,25 @@ def test_empty_batch_and_bad_arguments(dev):
         batch_build.build_batch(torch.zeros(4, 72, dtype=torch.uint8, device=dev), "baseline", max_active=32)
     with pytest.raises(_lib.NnueB200Error):
         batch_build.build_batch(torch.zeros(4, 72, dtype=torch.uint8), "baseline")
+
+
+def test_prefetcher_delivers_every_batch_in_order(dev):
+    """Side-stream staging: every batch arrives once, in order, with the bytes
+    of its pinned source, also when the consumer overwrites its inputs and the
+    source list is shorter than the pipeline depth."""
+    from nnue_pytorch_b200.prefetch import DevicePrefetcher
+
+    gen = torch.Generator().manual_seed(0)
+    for n in (0, 1, 2, 7):
+        host = [(torch.randint(0, 255, (4096, 72), generator=gen, dtype=torch.uint8).pin_memory(),
+                 torch.randn(513, generator=gen).pin_memory()) for _ in range(n)]
+        seen = 0
+        for i, (a, b) in enumerate(DevicePrefetcher(iter(host), dev)):
+            assert a.is_cuda and b.is_cuda
+            big = torch.empty(1 << 24, device=dev).normal_()  # keep the compute stream busy
+            assert torch.equal(a.cpu(), host[i][0]) and torch.equal(b.cpu(), host[i][1])
+            a.zero_()
+            b.zero_()
+            del big
+            seen += 1
+        assert seen == n

@@ -72,9 +72,48 @@ def test_integer_eval_matches_integer_oracle(dev, L1, layout, B):
     want = quant_oracle.integer_eval(quant_oracle.quantize_params(p, L1), b.white, b.black, b.us[:, 0] > 0.5,
                                      (b.piece_count - 1) // 4, consts)
     net = _net_from_params(p, L1, dev)
-    got = net.evaluate(t(b.white).to(dev), t(b.black).to(dev), t(b.us[:, 0] > 0.5), t(b.piece_count))
+    args = (t(b.white).to(dev), t(b.black).to(dev), t(b.us[:, 0] > 0.5), t(b.piece_count))
+    got = net.evaluate(*args)                    # gather kernel with an L2-resident slice + layer kernel
+    single = net.evaluate(*args, tiled=False)    # one kernel per position
     assert np.array_equal(got.cpu().numpy().astype(np.int64), want)
+    assert torch.equal(got, single)
     assert len(np.unique(want)) > B // 4  # the outputs are not degenerate
+
+
+def test_tiled_integer_eval_in_several_passes(dev):
+    """A workspace smaller than the batch needs: the batch is walked in passes; same bits."""
+    import ctypes as C
+
+    from nnue_pytorch_b200 import _lib, positions
+
+    L1, B = 256, 1000
+    p = _random_quant_params(L1, positions.NUM_INPUTS_BASELINE, np.random.default_rng(3))
+    net = _net_from_params(p, L1, dev)
+    b = positions.generate_batch(B, 5, layout="baseline")
+    white, black = t(b.white).to(dev), t(b.black).to(dev)
+    stm = t(b.us[:, 0] > 0.5).to(device=dev, dtype=torch.uint8)
+    bucket = ((t(b.piece_count) - 1) // 4).to(device=dev, dtype=torch.int32)
+    want = net.evaluate(white, black, t(b.us[:, 0] > 0.5), t(b.piece_count), tiled=False)
+    lib = _lib.load()
+    for positions_per_pass in (1, 37, 160, 5000):
+        ws = torch.empty(256 + positions_per_pass * (L1 + 4) + 255, dtype=torch.uint8, device=dev)
+        out = torch.full((B,), -7, dtype=torch.int32, device=dev)
+        st = lib.nnue_quant_eval_tiled(
+            white.data_ptr(), black.data_ptr(), stm.data_ptr(), bucket.data_ptr(), net.ft_w.data_ptr(),
+            net.ft_psqt.data_ptr(), net.ft_b.data_ptr(), net.l1_w.data_ptr(), net.l1_b.data_ptr(), net.l2_w.data_ptr(),
+            net.l2_b.data_ptr(), net.out_w.data_ptr(), net.out_b.data_ptr(), out.data_ptr(), B, white.shape[1], net.N,
+            L1, net.L2, net.L3, net.P, net.buckets, C.byref(net._qp), ws.data_ptr(), ws.numel(),
+            torch.cuda.current_stream(dev).cuda_stream)
+        _lib.check(st, "nnue_quant_eval_tiled")
+        assert torch.equal(out, want), positions_per_pass
+    tiny = torch.empty(64, dtype=torch.uint8, device=dev)
+    st = lib.nnue_quant_eval_tiled(
+        white.data_ptr(), black.data_ptr(), stm.data_ptr(), bucket.data_ptr(), net.ft_w.data_ptr(),
+        net.ft_psqt.data_ptr(), net.ft_b.data_ptr(), net.l1_w.data_ptr(), net.l1_b.data_ptr(), net.l2_w.data_ptr(),
+        net.l2_b.data_ptr(), net.out_w.data_ptr(), net.out_b.data_ptr(), out.data_ptr(), B, white.shape[1], net.N,
+        L1, net.L2, net.L3, net.P, net.buckets, C.byref(net._qp), tiny.data_ptr(), tiny.numel(),
+        torch.cuda.current_stream(dev).cuda_stream)
+    assert st == -3  # workspace too small
 
 
 def test_quantization_refuses_out_of_range_weights(dev):
