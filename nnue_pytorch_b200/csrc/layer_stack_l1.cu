@@ -128,21 +128,32 @@ __global__ void __launch_bounds__(32 * kWarpsL1, 2)
 }
 
 // ---- input gradient: dx[p, c] = sum_o d_o1[p, o] * W1[bucket, o, c] --------
-// Tile of 64 positions; columns in chunks of 128.  Lane = 4 columns, warp = 8
-// positions: per output unit two broadcast float4 of d_o1 (stored transposed)
-// and one float4 of W feed 32 FMA.
+// Tile of 64 positions; columns in chunks of 128 (the bucket's weight chunk double
+// buffered through cp.async).  Lane = 4 columns, warp = 8 positions: per output
+// unit two broadcast float4 of d_o1 (stored transposed) and one float4 of W
+// feed 32 FMA.
 constexpr int kDxCols = 128;
 constexpr int kPadP = kTP + 4;
 __global__ void __launch_bounds__(256)
     k_ls_l1_dx(const float* __restrict__ d_o1, const float* __restrict__ W1, LsPlanView plan,
                float* __restrict__ dx, int L1) {
     __shared__ __align__(16) float Dt[kLsOut][kPadP];  // [unit][position]
-    __shared__ __align__(16) float Ws[kLsOut][kDxCols];
+    __shared__ __align__(16) float Ws[2][kLsOut][kDxCols];  // double buffer: chunk c + 1 lands while c is used
     const int t = blockIdx.x;
     if (t >= *plan.n_tiles) return;
     const int cnt = plan.tile_count[t], bk = plan.tile_bucket[t];
     const int32_t* perm = plan.perm + plan.tile_start[t];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const float* wbase = W1 + (int64_t)bk * kLsOut * L1;
+    auto issue = [&](int c0, int buf) {  // columns [c0, c0 + 128) of the bucket's 32 rows; past L1: zeros
+        for (int i = tid; i < kLsOut * (kDxCols / 4); i += 256) {
+            const int o = i / (kDxCols / 4), c4 = i % (kDxCols / 4);
+            const bool ok = c0 + 4 * c4 < L1;
+            cp_async16(&Ws[buf][o][4 * c4], wbase + (int64_t)o * L1 + (ok ? c0 + 4 * c4 : 0), ok);
+        }
+        cp_async_commit();
+    };
+    issue(0, 0);
     for (int i = tid; i < kTP * kLsOut; i += 256) {
         const int r = i >> 5, o = i & 31;  // coalesced read of a position's 32 units
         Dt[o][r] = r < cnt ? __ldg(d_o1 + (int64_t)perm[r] * kLsOut + o) : 0.f;
@@ -150,22 +161,17 @@ __global__ void __launch_bounds__(256)
     int64_t prow[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) prow[i] = 8 * warp + i < cnt ? (int64_t)perm[8 * warp + i] * L1 : -1;
-    const float* wbase = W1 + (int64_t)bk * kLsOut * L1;
-    for (int c0 = 0; c0 < L1; c0 += kDxCols) {
-        __syncthreads();  // Dt ready (first pass) / previous Ws consumed
-        for (int i = tid; i < kLsOut * (kDxCols / 4); i += 256) {
-            const int o = i / (kDxCols / 4), c4 = i % (kDxCols / 4);
-            float4 v = f4_zero();
-            if (c0 + 4 * c4 < L1) v = __ldg(reinterpret_cast<const float4*>(wbase + (int64_t)o * L1 + c0) + c4);
-            *reinterpret_cast<float4*>(&Ws[o][4 * c4]) = v;
-        }
-        __syncthreads();
+    int buf = 0;
+    for (int c0 = 0; c0 < L1; c0 += kDxCols, buf ^= 1) {
+        cp_async_wait<0>();
+        __syncthreads();  // chunk c0 (and, first pass, Dt) visible to all; the other buffer is free again
+        if (c0 + kDxCols < L1) issue(c0 + kDxCols, buf ^ 1);
         float4 acc[8];
 #pragma unroll
         for (int i = 0; i < 8; ++i) acc[i] = f4_zero();
 #pragma unroll 8
         for (int o = 0; o < kLsOut; ++o) {
-            const float4 w = *reinterpret_cast<const float4*>(&Ws[o][4 * lane]);
+            const float4 w = *reinterpret_cast<const float4*>(&Ws[buf][o][4 * lane]);
             const float4 da = *reinterpret_cast<const float4*>(&Dt[o][8 * warp]);
             const float4 db = *reinterpret_cast<const float4*>(&Dt[o][8 * warp + 4]);
             const float d[8] = {da.x, da.y, da.z, da.w, db.x, db.y, db.z, db.w};
