@@ -253,6 +253,10 @@ int nnue_lookahead_merge(float* p, float* slow, int64_t n, float alpha,
  * have to become means (the division rides in the coefficient). */
 int nnue_grad_sumsq(const float* grad, int64_t n, float* d_out_sumsq,
                     void* stream);
+/* Both norm entry points (and the norm inside nnue_ddp_reduce_shard) add their
+ * per-CTA partial sums in a fixed order, so the result is reproducible run to
+ * run; the partials live in a file-scope device array of the library, which
+ * calls overlapping on the GPU (different streams) must not share. */
 int nnue_clip_coef(const float* d_sumsq, float max_norm, float prescale,
                    float* d_coef, void* stream);
 

@@ -60,31 +60,6 @@ int sm_count() {
 }
 
 // ---- gradient norm helpers ------------------------------------------------
-// Partial sums per CTA in registers/shared memory, one atomicAdd per CTA.
-__global__ void __launch_bounds__(kThreads)
-    k_sumsq(const float* __restrict__ g, int64_t n, float* __restrict__ out) {
-    __shared__ float s_w[kWarpsPerCta];
-    float acc = 0.f;
-    const int64_t n4 = n >> 2;
-    const float4* g4 = reinterpret_cast<const float4*>(g);
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
-    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-        const float4 v = __ldg(g4 + i);
-        acc += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
-    }
-    for (int64_t i = (n4 << 2) + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += stride)
-        acc += g[i] * g[i];
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(kFullMask, acc, d);
-    if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = acc;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float t = 0.f;
-        for (int w = 0; w < kWarpsPerCta; ++w) t += s_w[w];
-        atomicAdd(out, t);
-    }
-}
-
 // The gradients the norm was taken over are `prescale` times the true ones
 // (data-parallel ranks sum before they average): the coefficient folds both.
 __global__ void k_clip_coef(const float* __restrict__ sumsq, float max_norm, float prescale,
@@ -152,13 +127,8 @@ extern "C" int nnue_grad_sumsq(const float* grad, int64_t n, float* d_out_sumsq,
     NNUE_REQUIRE(n >= 0 && d_out_sumsq, NNUE_ERR_ARG, "nnue_grad_sumsq: bad argument");
     if (n == 0) return NNUE_OK;
     NNUE_REQUIRE(grad, NNUE_ERR_ARG, "nnue_grad_sumsq: null gradient");
-    NNUE_REQUIRE(aligned16(grad), NNUE_ERR_ALIGN, "nnue_grad_sumsq: gradient not 16-byte aligned");
-    const int64_t want = (n / 4 + kThreads - 1) / kThreads + 1;
-    const unsigned grid = (unsigned)std::min<int64_t>(want, (int64_t)sm_count() * 8);
-    k_sumsq<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(grad, n, d_out_sumsq);
-    note_launches(1);
-    NNUE_CUDA_TRY(cudaGetLastError());
-    return NNUE_OK;
+    const float* grads[1] = {grad};
+    return nnue_grad_sumsq_multi(grads, &n, 1, d_out_sumsq, stream);  // one reproducible implementation
 }
 
 extern "C" int nnue_clip_coef(const float* d_sumsq, float max_norm, float prescale, float* d_coef,

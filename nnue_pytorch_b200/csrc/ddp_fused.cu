@@ -31,6 +31,12 @@ struct PeerPtrs {
     float* p[kMaxRanks];
 };
 
+// Per-CTA partial norms of the reduce kernel (file scope: reduce launches of one device are ordered
+// on one stream by the exchange).
+constexpr int kReduceMaxGrid = 2048;
+__device__ float g_reduce_partial[kReduceMaxGrid];
+__device__ unsigned int g_reduce_arrived;
+
 // UN float4 per thread and trip, every rank's copy of them loaded before the first add: with few
 // ranks (few loads per float4) the unroll keeps enough bytes in flight to fill the links even when
 // the grid is capped to leave SMs to a kernel running beside it.
@@ -40,6 +46,7 @@ __global__ void __launch_bounds__(kThreads)
     k_ddp_reduce_shard(PeerPtrs grads, int world, int rank, int64_t beg4, int64_t end4,
                        float* __restrict__ sumsq) {
     __shared__ float s_w[kWarpsPerCta];
+    __shared__ bool s_last;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     float acc = 0.f;
     for (int64_t i0 = beg4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i0 < end4; i0 += stride * UN) {
@@ -63,6 +70,7 @@ __global__ void __launch_bounds__(kThreads)
             acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
         }
     }
+    // reproducible norm: a slot per CTA, the CTA that arrives last adds the slots in index order
 #pragma unroll
     for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(kFullMask, acc, d);
     if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = acc;
@@ -70,7 +78,25 @@ __global__ void __launch_bounds__(kThreads)
     if (threadIdx.x == 0) {
         float t = 0.f;
         for (int w = 0; w < kWarpsPerCta; ++w) t += s_w[w];
-        atomicAdd(sumsq, t);
+        g_reduce_partial[blockIdx.x] = t;
+        __threadfence();
+        s_last = atomicAdd(&g_reduce_arrived, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float tot = 0.f;
+    for (unsigned i = threadIdx.x; i < gridDim.x; i += kThreads) tot += __ldcg(&g_reduce_partial[i]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) tot += __shfl_xor_sync(kFullMask, tot, d);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = tot;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < kWarpsPerCta; ++w) t += s_w[w];
+        *sumsq += t;
+        g_reduce_arrived = 0;
     }
 }
 
@@ -138,7 +164,7 @@ extern "C" int nnue_ddp_reduce_shard(float* const* h_grad_ptrs, int32_t world, i
     PeerPtrs pp{};
     for (int r = 0; r < world; ++r) pp.p[r] = h_grad_ptrs[r];
     const int64_t n4 = (elem_end - elem_begin) / 4;
-    const int cap = tuning().ddp_reduce_ctas > 0 ? tuning().ddp_reduce_ctas : sm_count() * 8;
+    const int cap = std::min(kReduceMaxGrid, tuning().ddp_reduce_ctas > 0 ? tuning().ddp_reduce_ctas : sm_count() * 8);
     const unsigned grid = (unsigned)std::min<int64_t>((n4 + kThreads - 1) / kThreads, (int64_t)cap);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     if (world <= 2)

@@ -15,13 +15,51 @@ struct SumsqJob {
     int64_t n[NNUE_MULTI_MAX];
 };
 
-__global__ void __launch_bounds__(kThreads) k_sumsq_multi(SumsqJob job, float* __restrict__ out) {
+// Reproducible: every CTA leaves its partial sum in a slot of its own; the CTA that arrives last adds
+// all slots in a fixed order (whichever CTA that is) and adds the total to *out.  The slots are a
+// file-scope array: calls that overlap on the GPU (different streams) would share it and must not.
+constexpr int kSumsqMaxGridX = 1024;
+__device__ float g_sumsq_partial[NNUE_MULTI_MAX * kSumsqMaxGridX];
+__device__ unsigned int g_sumsq_arrived;
+
+__device__ __forceinline__ void sumsq_finish(float mine, float* __restrict__ out) {
     __shared__ float s_w[kWarpsPerCta];
+    __shared__ bool s_last;
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) mine += __shfl_xor_sync(kFullMask, mine, d);
+    if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = mine;
+    __syncthreads();
+    const unsigned n_ctas = gridDim.x * gridDim.y;
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < kWarpsPerCta; ++w) t += s_w[w];
+        g_sumsq_partial[blockIdx.y * gridDim.x + blockIdx.x] = t;
+        __threadfence();
+        s_last = atomicAdd(&g_sumsq_arrived, 1u) == n_ctas - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float acc = 0.f;
+    for (unsigned i = threadIdx.x; i < n_ctas; i += kThreads) acc += __ldcg(&g_sumsq_partial[i]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(kFullMask, acc, d);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < kWarpsPerCta; ++w) t += s_w[w];
+        *out += t;
+        g_sumsq_arrived = 0;  // ready for the next launch
+    }
+}
+
+__global__ void __launch_bounds__(kThreads) k_sumsq_multi(SumsqJob job, float* __restrict__ out) {
     const float* g = job.g[blockIdx.y];
     const int64_t n = job.n[blockIdx.y];
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const int64_t t0 = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if ((int64_t)blockIdx.x * blockDim.x >= n) return;  // whole CTA beyond this tensor
     float acc = 0.f;
     int64_t done = 0;
     if ((reinterpret_cast<uintptr_t>(g) & 15u) == 0) {
@@ -34,15 +72,7 @@ __global__ void __launch_bounds__(kThreads) k_sumsq_multi(SumsqJob job, float* _
         done = n4 << 2;
     }
     for (int64_t i = done + t0; i < n; i += stride) acc += g[i] * g[i];
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(kFullMask, acc, d);
-    if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = acc;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float t = 0.f;
-        for (int w = 0; w < kWarpsPerCta; ++w) t += s_w[w];
-        atomicAdd(out, t);
-    }
+    sumsq_finish(acc, out);
 }
 
 struct RangerJob {
@@ -86,7 +116,7 @@ __global__ void __launch_bounds__(kThreads)
 
 static unsigned grid_x_for(int64_t max_n) {
     const int64_t want = (max_n / 4 + kThreads - 1) / kThreads + 1;
-    return (unsigned)std::min<int64_t>(want, (int64_t)sm_count() * 4);
+    return (unsigned)std::min<int64_t>(want, std::min<int64_t>((int64_t)sm_count() * 4, kSumsqMaxGridX));
 }
 
 }  // namespace nnue

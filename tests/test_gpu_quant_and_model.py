@@ -240,3 +240,31 @@ def test_fused_layer_stack_matches_torch_layers(dev, B, L1, fq):
     if not fq:
         for n in ga:
             assert max_rel_err(ga[n].cpu(), gb[n].cpu()) <= 1e-4, n
+
+
+def test_training_is_reproducible(dev):
+    """Two runs of eight optimizer steps from the same seed: every loss and every
+    parameter agree bit for bit (the reference's atomics make its runs differ)."""
+    from nnue_pytorch_b200 import batch_build, positions
+    from nnue_pytorch_b200.model import ModelConfig, NNUEModel, TrainStep
+
+    def run():
+        torch.manual_seed(0)
+        m = NNUEModel("HalfKAv2_hm^flat", ModelConfig(L1=256, L2=32, L3=32))
+        with torch.no_grad():
+            m.input.features[0].weight[:, :256].normal_(0, 0.05)
+        m.to(dev)
+        step = TrainStep(m, clip=2.0)
+        losses = []
+        for i in range(8):
+            pos = positions.generate_positions(2048, 40 + i)
+            score, outcome = positions.generate_targets(2048, 40 + i)
+            packed = batch_build.as_bytes(batch_build.pack_positions(pos, score, outcome)).to(dev)
+            losses.append(step(batch_build.build_batch(packed, "baseline")).clone())
+        return torch.stack(losses), [p.detach().clone() for p in m.parameters()]
+
+    la, pa = run()
+    lb, pb = run()
+    assert torch.equal(la, lb)
+    for a, b in zip(pa, pb):
+        assert torch.equal(a, b)
