@@ -24,15 +24,16 @@ __device__ __forceinline__ float dot4(float acc, float4 a, float4 b) {
 // pipe, 4 FMA pipes retire 4 warp instructions per cycle), so every thread
 // holds an 8 x 8 register tile: 16 shared float4 loads feed 256 FMA.
 // A 64 x 32 tile is then ONE warp; the kWarpsL1 warps of a CTA split K between
-// them (contiguous ranges, walked in chunks of 8 through a kStagesL1-deep
+// them (contiguous ranges, walked in chunks of 16 through a kFwdStages-deep
 // cp.async pipeline in buffers private to the warp: warp-level barriers only)
 // and their tiles are added in warp order at the end.
 constexpr int kWarpsL1 = 4;
-constexpr int kStagesL1 = 4;
-constexpr int kKC8 = 8;            // K chunk of a warp
-constexpr int kPad8 = kKC8 + 4;    // row stride 48 B: float4 aligned, conflict-free for the access patterns below
-constexpr int kFwdStage = (kTP + kLsOut) * kPad8;  // floats per stage: A [64][12] + W [32][12]
-constexpr int kFwdSmemFloats = kWarpsL1 * kStagesL1 * kFwdStage;  // >= the (kWarpsL1 - 1) partial tiles [64][33]
+constexpr int kStagesL1 = 4;       // pipeline depth of the weight-gradient kernel
+constexpr int kFwdStages = 3;      // ... and of the forward
+constexpr int kKC8 = 16;           // K chunk of a warp (64 B of every row per stage)
+constexpr int kPad8 = kKC8 + 4;    // row stride 80 B: float4 aligned, conflict-free for the access patterns below
+constexpr int kFwdStage = (kTP + kLsOut) * kPad8;  // floats per stage: A [64][20] + W [32][20]
+constexpr int kFwdSmemFloats = kWarpsL1 * kFwdStages * kFwdStage;  // >= the (kWarpsL1 - 1) partial tiles [64][33]
 static_assert(kFwdSmemFloats >= (kWarpsL1 - 1) * kTP * (kLsOut + 1), "partial tiles alias the staging buffers");
 __global__ void __launch_bounds__(32 * kWarpsL1, 2)
     k_ls_l1_fwd(const float* __restrict__ x, const float* __restrict__ W1, const float* __restrict__ b1,
@@ -43,30 +44,32 @@ __global__ void __launch_bounds__(32 * kWarpsL1, 2)
     const int cnt = plan.tile_count[t], bk = plan.tile_bucket[t];
     const int32_t* perm = plan.perm + plan.tile_start[t];
     const int lane = threadIdx.x & 31, g = threadIdx.x >> 5;
-    float* stage0 = smem + g * kStagesL1 * kFwdStage;
+    float* stage0 = smem + g * kFwdStages * kFwdStage;
     // this warp's K range, in chunks of 8
     const int nc = L1 / kKC8;
     const int c_beg = (int)((int64_t)nc * g / kWarpsL1), c_end = (int)((int64_t)nc * (g + 1) / kWarpsL1);
-    // loader: A rows (lane >> 1) + 16 i (i < 4), W rows (lane >> 1) + 16 i (i < 2); float4 (lane & 1) of the chunk
-    const int lr = lane >> 1, lc = lane & 1;
-    const float4* xa[4];
-    bool live[4];
+    // loader: kF4 lanes per row (one float4 each), kRowsPass rows per pass: A in kTP / kRowsPass passes, W in
+    // kLsOut / kRowsPass
+    constexpr int kF4 = kKC8 / 4, kRowsPass = 32 / kF4, kPassA = kTP / kRowsPass, kPassW = kLsOut / kRowsPass;
+    const int lr = lane / kF4, lc = lane % kF4;
+    const float4* xa[kPassA];
+    bool live[kPassA];
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-        live[i] = lr + 16 * i < cnt;
-        xa[i] = reinterpret_cast<const float4*>(x + (int64_t)(live[i] ? perm[lr + 16 * i] : 0) * L1) + lc;
+    for (int i = 0; i < kPassA; ++i) {
+        live[i] = lr + kRowsPass * i < cnt;
+        xa[i] = reinterpret_cast<const float4*>(x + (int64_t)(live[i] ? perm[lr + kRowsPass * i] : 0) * L1) + lc;
     }
-    const float4* wr0 = reinterpret_cast<const float4*>(W1 + ((int64_t)bk * kLsOut + lr) * L1) + lc;
-    const float4* wr1 = reinterpret_cast<const float4*>(W1 + ((int64_t)bk * kLsOut + lr + 16) * L1) + lc;
+    const float4* wr = reinterpret_cast<const float4*>(W1 + ((int64_t)bk * kLsOut + lr) * L1) + lc;
+    const int64_t w_pass = (int64_t)kRowsPass * (L1 / 4);  // float4 between the W rows of two passes
     auto issue = [&](int c, int st) {  // chunk c into stage st; chunks past the range copy nothing
         if (c < c_end) {
             float (*As)[kPad8] = reinterpret_cast<float (*)[kPad8]>(stage0 + st * kFwdStage);
             float (*Ws)[kPad8] = As + kTP;
-            const int o = c * (kKC8 / 4);
+            const int o = c * kF4;
 #pragma unroll
-            for (int i = 0; i < 4; ++i) cp_async16(&As[lr + 16 * i][4 * lc], xa[i] + o, live[i]);
-            cp_async16(&Ws[lr][4 * lc], wr0 + o, true);
-            cp_async16(&Ws[lr + 16][4 * lc], wr1 + o, true);
+            for (int i = 0; i < kPassA; ++i) cp_async16(&As[lr + kRowsPass * i][4 * lc], xa[i] + o, live[i]);
+#pragma unroll
+            for (int i = 0; i < kPassW; ++i) cp_async16(&Ws[lr + kRowsPass * i][4 * lc], wr + i * w_pass + o, true);
         }
         cp_async_commit();  // one group per call, empty or not: the wait below counts groups
     };
@@ -77,12 +80,12 @@ __global__ void __launch_bounds__(32 * kWarpsL1, 2)
 #pragma unroll
         for (int j = 0; j < 8; ++j) acc[i][j] = 0.f;
 #pragma unroll
-    for (int st = 0; st < kStagesL1 - 1; ++st) issue(c_beg + st, st);
+    for (int st = 0; st < kFwdStages - 1; ++st) issue(c_beg + st, st);
     int st = 0;
     for (int c = c_beg; c < c_end; ++c) {
-        cp_async_wait<kStagesL1 - 2>();  // this lane's part of chunk c has landed
+        cp_async_wait<kFwdStages - 2>();  // this lane's part of chunk c has landed
         __syncwarp();                    // ... and every other lane's; the stage refilled next was read last iteration
-        issue(c + kStagesL1 - 1, (st + kStagesL1 - 1) % kStagesL1);
+        issue(c + kFwdStages - 1, (st + kFwdStages - 1) % kFwdStages);
         float (*As)[kPad8] = reinterpret_cast<float (*)[kPad8]>(stage0 + st * kFwdStage);
         float (*Ws)[kPad8] = As + kTP;
 #pragma unroll
@@ -97,7 +100,7 @@ __global__ void __launch_bounds__(32 * kWarpsL1, 2)
                 for (int i = 0; i < 8; ++i) acc[i][j] = dot4(acc[i][j], a[i], w);
             }
         }
-        st = (st + 1) % kStagesL1;
+        st = (st + 1) % kFwdStages;
     }
     cp_async_wait<0>();
     __syncthreads();  // every warp is done with its staging buffers
