@@ -87,7 +87,7 @@ class ClockSampler:
               "clocks_event_reasons.sw_power_cap")
 
     def __init__(self, index: int):
-        self.index, self.proc, self.lines = index, None, []
+        self.index, self.proc, self.lines, self.skip = index, None, [], 0
 
     def __enter__(self):
         try:
@@ -96,6 +96,12 @@ class ClockSampler:
                  "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
+            # nvidia-smi needs a moment to start: wait for its first line, then count only what follows,
+            # so that every sample kept was taken while the timed region ran
+            t0 = time.time()
+            while not self.lines and time.time() - t0 < 3.0:
+                time.sleep(0.005)
+            self.skip = len(self.lines)
         except OSError:
             self.proc = None
         return self
@@ -115,7 +121,7 @@ class ClockSampler:
     def summary(self):
         sm, mx, reasons = [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines:
+        for ln in self.lines[self.skip:]:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 7:
                 continue
