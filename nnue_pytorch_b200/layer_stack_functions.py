@@ -43,9 +43,43 @@ def supported(x: torch.Tensor, l1: int, l2: int, l3: int, count: int) -> bool:
     return x.is_cuda and x.dtype == torch.float32 and l2 == 32 and l3 == 32 and l1 % 32 == 0 and 1 <= count <= 16
 
 
+_PLAN_STREAMS: dict[int, torch.cuda.Stream] = {}
+
+
+class PlanAhead:
+    """The bucket plan of a batch, built on a second stream.  It depends on
+    the bucket indices only, so a caller that knows them early (before the
+    feature transformer runs) gets the plan for free, beside that work."""
+
+    def __init__(self, bucket: torch.Tensor, count: int):
+        dev = _require_cuda(bucket)
+        key = dev.index if dev.index is not None else torch.cuda.current_device()
+        side = _PLAN_STREAMS.get(key)
+        if side is None:
+            side = _PLAN_STREAMS[key] = torch.cuda.Stream(dev)
+        lib = _lib.load()
+        self.bucket = bucket.reshape(-1).to(torch.int64).contiguous()
+        self.count, self.B = int(count), self.bucket.numel()
+        self.plan = torch.empty(lib.nnue_ls_plan_bytes(self.B, count) // 4 + 4, dtype=torch.int32, device=dev)
+        cur = torch.cuda.current_stream(dev)
+        side.wait_stream(cur)  # the bucket indices (and the plan's memory) are ready on the caller's stream
+        with torch.cuda.device(dev):
+            _lib.check(lib.nnue_ls_plan(_ptr(self.bucket), self.B, count, _ptr(self.plan), self.plan.numel() * 4,
+                                        side.cuda_stream), "nnue_ls_plan")
+        self.bucket.record_stream(side)
+        self.plan.record_stream(side)
+        self.ready = torch.cuda.Event()
+        self.ready.record(side)
+
+    def take(self, dev, B: int, count: int) -> torch.Tensor:
+        assert self.B == B and self.count == count, "the plan was built for another batch"
+        torch.cuda.current_stream(dev).wait_event(self.ready)
+        return self.plan
+
+
 class FusedLayerStackFunction(autograd.Function):
     @staticmethod
-    def forward(ctx, x, bucket, W1, b1, W2, b2, W3, b3, quantization, fake_quantize_acts):
+    def forward(ctx, x, bucket, W1, b1, W2, b2, W3, b3, quantization, fake_quantize_acts, plan_ahead=None):
         dev = _require_cuda(x, bucket, W1, b1, W2, b2, W3, b3)
         x, W1, b1, W2, b2, W3, b3 = (t.contiguous() for t in (x, W1, b1, W2, b2, W3, b3))
         bucket = bucket.reshape(-1).to(torch.int64).contiguous()
@@ -54,13 +88,17 @@ class FusedLayerStackFunction(autograd.Function):
         assert W1.shape == (count * 32, L1) and W2.shape == (count * 32, 64) and W3.shape == (count, 128)
         lib = _lib.load()
         params = _params(quantization, fake_quantize_acts)
-        plan = torch.empty(lib.nnue_ls_plan_bytes(B, count) // 4 + 4, dtype=torch.int32, device=dev)
+        if plan_ahead is not None:
+            plan = plan_ahead.take(dev, B, count)
+        else:
+            plan = torch.empty(lib.nnue_ls_plan_bytes(B, count) // 4 + 4, dtype=torch.int32, device=dev)
         o1 = torch.empty(B, 32, device=dev)
         o2 = torch.empty(B, 32, device=dev)
         y = torch.empty(B, 1, device=dev)
         s = _stream(dev)
         with torch.cuda.device(dev), _span("layer_stack_fwd", dev):
-            _lib.check(lib.nnue_ls_plan(_ptr(bucket), B, count, _ptr(plan), plan.numel() * 4, s), "nnue_ls_plan")
+            if plan_ahead is None:
+                _lib.check(lib.nnue_ls_plan(_ptr(bucket), B, count, _ptr(plan), plan.numel() * 4, s), "nnue_ls_plan")
             with _span("ls_l1_fwd", dev):
                 _lib.check(lib.nnue_ls_l1_fwd(_ptr(x), _ptr(W1), _ptr(b1), _ptr(plan), _ptr(o1), B, L1, count, s),
                            "nnue_ls_l1_fwd")
@@ -95,7 +133,7 @@ class FusedLayerStackFunction(autograd.Function):
             with _span("ls_l1_bwd", dev):
                 _lib.check(lib.nnue_ls_l1_bwd(_ptr(x), _ptr(W1), _ptr(d_o1), _ptr(plan), _ptr(dx), _ptr(dW1),
                                               _ptr(db1), B, L1, count, s), "nnue_ls_l1_bwd")
-        return dx, None, dW1, db1, dW2, db2, dW3, db3.view(ctx.b3_shape), None, None
+        return dx, None, dW1, db1, dW2, db2, dW3, db3.view(ctx.b3_shape), None, None, None
 
 
 class LayerStackWeightsFunction(autograd.Function):

@@ -94,7 +94,16 @@ class LayerStacks(nn.Module):
 
     fused = True  # use the bucket-aware kernels when the shapes allow it
 
-    def forward(self, x, ls_indices, fake_quantize_acts=True, fake_quantize_weights=True):
+    def plan_ahead(self, ls_indices):
+        """Starts the bucket plan of this batch on a second stream (CUDA only); pass the result to
+        `forward(..., plan_ahead=...)`.  None when the fused kernels do not apply."""
+        from . import layer_stack_functions as lsf
+
+        if self.fused and ls_indices.is_cuda and self.L2 == 32 and self.L3 == 32 and self.L1 % 32 == 0 and self.count <= 16:
+            return lsf.PlanAhead(ls_indices, self.count)
+        return None
+
+    def forward(self, x, ls_indices, fake_quantize_acts=True, fake_quantize_weights=True, plan_ahead=None):
         from . import layer_stack_functions as lsf
 
         if self.fused and lsf.supported(x, self.L1, self.L2, self.L3, self.count):
@@ -104,7 +113,7 @@ class LayerStacks(nn.Module):
                 l2.linear.weight, l2.linear.bias, out.linear.weight, out.linear.bias, self.quantization,
                 fake_quantize_weights)
             return lsf.FusedLayerStackFunction.apply(x, ls_indices, w1, b1, w2, b2, w3, b3, self.quantization,
-                                                     fake_quantize_acts)
+                                                     fake_quantize_acts, plan_ahead)
         o1 = self.l1(x, ls_indices, fake_quantize_weights)
         skip = o1[:, -2].view(-1, 1) - o1[:, -1].view(-1, 1)
         x1 = self._activate(o1, fake_quantize_acts)
@@ -141,8 +150,9 @@ class NNUEModel(nn.Module):
         """(layer-stack output, white PSQT, black PSQT), each [B, 1]: the three
         terms `forward` combines."""
         bucket = (piece_count - 1) // 4
+        ahead = self.layer_stacks.plan_ahead(bucket)  # built beside the feature transformer
         l0, wpsqt, bpsqt = self.input(us, them, white_indices, black_indices, bucket, fake_quantize_acts, fake_quantize_weights)
-        return self.layer_stacks(l0, bucket, fake_quantize_acts, fake_quantize_weights), wpsqt, bpsqt
+        return self.layer_stacks(l0, bucket, fake_quantize_acts, fake_quantize_weights, ahead), wpsqt, bpsqt
 
     def forward(self, us, them, white_indices, black_indices, piece_count, fake_quantize_acts=True, fake_quantize_weights=True):
         y, wpsqt, bpsqt = self.forward_parts(us, them, white_indices, black_indices, piece_count, fake_quantize_acts,
