@@ -39,11 +39,12 @@ def make_grad_hook(model: torch.nn.Module, world: int, average: bool = True, ski
             dist.all_reduce(flat)
             if inv != 1.0:
                 flat.mul_(inv)
-            at = 0
+            views, at = [], 0
             for g in small:
                 n = g.numel()
-                g.copy_(flat[at : at + n].view_as(g))
+                views.append(flat[at : at + n].view_as(g))
                 at += n
+            torch._foreach_copy_(small, views)  # one multi-tensor launch instead of one copy per tensor
 
     return hook
 
