@@ -58,9 +58,10 @@ def parse_args():
     ap.add_argument("--cpu-sample-batch", type=int, default=2048)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--tune", action="append", default=[], help="key=value, passed to nnue_b200_tune")
-    ap.add_argument("--slices", action="store_true",
-                    help="fused exchange with the backward delivered in two row slices and the reduce of the "
-                         "first one overlapped with the second (measured slower than the plain order at 2 GPUs)")
+    ap.add_argument("--slices", default="auto", choices=["auto", "on", "off"],
+                    help="fused exchange with the backward delivered in two row slices and the reduce of the first "
+                         "one overlapped with the second.  auto = on from 8 GPUs (measured there: 3.42 ms against "
+                         "3.55 ms per step; at 2 GPUs the two orders tie)")
     ap.add_argument("--feed", default="packed", choices=["packed", "lists"],
                     help="what the end-to-end run copies from pinned host memory every step: 72-byte packed "
                          "positions expanded on the GPU, or the expanded index lists")
@@ -198,9 +199,11 @@ def run_b200(args):
         dist.init_process_group("nccl", init_method="env://", device_id=dev)
     lib = _lib.load()
     _launch.set_backward_mode(args.bwd_mode)
+    tuned = {}
     for kv in args.tune:
         k, v = kv.split("=")
         _lib.tune(k, int(v))
+        tuned[k] = int(v)
 
     torch.manual_seed(1)
     model = NNUEModel("HalfKAv2_hm^flat", ModelConfig(L1=args.l1, L2=32, L3=32))
@@ -215,8 +218,9 @@ def run_b200(args):
 
             # --slices: the 704 factor rows (half of all entries) form the last slice, so the reduce of the
             # 22528 real rows can run while the factor rows' gradient is still being computed
-            slices = [0, table.shape[0] - 704, table.shape[0]] if args.slices else None
-            exchange = ShardedTableExchange(table, slices=slices)
+            sliced = args.slices == "on" or (args.slices == "auto" and world >= 8)
+            slices = [0, table.shape[0] - 704, table.shape[0]] if sliced else None
+            exchange = ShardedTableExchange(table, slices=slices, reduce_ctas=tuned.get("ddp_reduce_ctas", 32))
         hook = make_grad_hook(model, world, average=False, skip=[table] if exchange is not None else [])
     step = TrainStep(model, lr=8.75e-4, clip=2.0, lam=1.0, grad_hook=hook, grad_prescale=1.0 / world,
                      table_exchange=exchange)
@@ -333,6 +337,7 @@ def run_b200(args):
             "l1": args.l1,
             "parallelism": f"dp{world}",
             "table_exchange": (args.ddp if world > 1 else "none"),
+            "exchange_slices": (len(exchange.bounds) - 1) if exchange is not None else None,
             "backward": args.bwd_mode,
             "l2_policy": "working set per step (table 286 MB + gradient + moments + activations > 2 GB) exceeds the 126 MB L2; "
                          f"{args.pool} distinct batches cycled",
