@@ -310,13 +310,14 @@ def run_b200(args):
     fwd_gbs = fwd_bytes / (fwd_ms * 1e-3) / 1e9 if fwd_ms else None
     bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9 if bwd_ms else None
     opt_gbs = 32.0 * N_ROWS * (args.l1 + 8) / (opt_ms * 1e-3) / 1e9 if opt_ms else None
-    # dram__bytes_read.sum + dram__bytes_write.sum per launch of k_fused_fwd from the ncu capture summarised
-    # in profiles/ft_kernels_L3072_B4096_ncu_full.md (batch 4096: 0.300 GB read, 0.130 GB written), scaled to
-    # this batch: the table is read about once per launch, the outputs grow with the batch
+    # dram__bytes_read.sum + dram__bytes_write.sum per launch of k_fused_fwd.  At the headline shape: measured by
+    # ncu on this very workload (0.388 GB read + 0.562 GB written; profiles/ft_kernels_L3072_B4096_ncu_full.md has
+    # the command).  Other batch sizes at L1 = 3072: scaled from it, the table read (<= 286 MB) does not grow with
+    # the batch, the outputs do.
     traffic = None
     if args.l1 == 3072:
-        traffic = N_ROWS * (args.l1 + 8) * 4 + (0.300e9 - N_ROWS * (args.l1 + 8) * 4 + 0.130e9) * args.batch / 4096
-
+        table = N_ROWS * (args.l1 + 8) * 4
+        traffic = 0.950316288e9 if args.batch == 16384 else table + (0.950316288e9 - table) * args.batch / 16384
     line = {
         "metric": METRIC,
         "value": world * args.batch / (ms_resident * 1e-3),
