@@ -5,9 +5,15 @@
  * Conventions shared by every entry point
  *   - plain C: pointers, sizes and scalars only; no torch / C++ types.
  *   - every pointer is a DEVICE pointer owned by the caller unless the
- *     parameter name starts with `h_` (host).  The library allocates no
- *     device memory; kernels that need scratch take a caller-provided
- *     workspace whose size the matching *_workspace_bytes() call returns.
+ *     parameter name starts with `h_` (host).  Kernels that need scratch take
+ *     a caller-provided workspace whose size the matching *_workspace_bytes()
+ *     call returns.  What the library creates by itself, once per device, on
+ *     the first call that needs it and kept until the process ends: a helper
+ *     stream with two events (first backward call), 16 bytes of device memory
+ *     plus 16 bytes of pinned host memory (first nnue_ft_fused_bwd call with
+ *     mode = NNUE_BWD_AUTO), the timing events of nnue_b200_profile, and the
+ *     fixed arrays of its device image (status words, norm partials, the
+ *     scratch of nnue_ft_sparse_bwd_static).  Nothing else is allocated.
  *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default
  *     stream).  Work is only enqueued; nothing synchronises with the host.
  *   - the return value is a status: 0 (NNUE_OK) or a negative NNUE_ERR_*
@@ -69,6 +75,31 @@ int64_t nnue_b200_launch_count(void);
  * Unknown keys return NNUE_ERR_ARG.  Process-wide, not thread-safe. */
 int nnue_b200_tune(const char* key, int value);
 
+/* Per-kernel device times of the calls made while profiling is on: the library
+ * brackets its main kernels with CUDA events on the stream they run on.
+ *   nnue_b200_profile(1)   clears the record and starts recording;
+ *   nnue_b200_profile(0)   stops.
+ *   nnue_b200_profile_read SYNCHRONISES the device, then returns entry i of
+ *     the record grouped by kernel name (*h_name points at a string constant,
+ *     *h_total_ms is the sum over its launches); NNUE_ERR_ARG past the end.
+ * Process-wide, one host thread; events are created as needed and kept. */
+int nnue_b200_profile(int32_t enable);
+int nnue_b200_profile_read(int32_t i, const char** h_name, double* h_total_ms,
+                           int64_t* h_launches);
+
+/* L2 -> SM read probe: the access shape of the gather kernels without their
+ * index lists and epilogue.  `buf` holds `rows` rows of 1024 bytes (16-byte
+ * aligned; keep rows * 1 KiB well inside the L2 so that after one warm-up
+ * launch every read is an L2 hit).  `warps` warps each sum `rows_per_warp`
+ * rows (pattern 0: consecutive rows from a per-warp start; 1: pseudo-random
+ * rows), every lane loading two 16-byte pieces per row with eight loads in
+ * flight, and store one 16-byte result per lane to `sink`
+ * (warps * 512 bytes).  Bytes read per launch: warps * rows_per_warp * 1024;
+ * the caller times the launch with events on `stream`. */
+int nnue_l2_read_probe(const void* buf, int64_t rows, int64_t warps,
+                       int32_t rows_per_warp, int32_t pattern, void* sink,
+                       void* stream);
+
 /* Reads (and clears) the device status word.  SYNCHRONISES `stream`.
  * h_bad_index_count / h_timeout_count may be NULL.  Returns NNUE_OK,
  * NNUE_ERR_INDEX or NNUE_ERR_TIMEOUT. */
@@ -104,16 +135,18 @@ int nnue_ft_sparse_bwd(const int32_t* idx, const float* grad_out,
  * No counterpart in the reference project.
  * Same result as nnue_ft_sparse_bwd (segment route), for hosts that cannot
  * obtain a workspace because they must not allocate device memory when the
- * call is made: a process whose device memory is owned by its own pool, a
- * service that forbids allocation after start-up, code between the begin and
- * the end of a stream capture.  The scratch is a fixed array of
+ * call is made: a process whose device memory is owned by its own pool, or a
+ * service that forbids allocation after start-up.  The scratch is a fixed array of
  * NNUE_SPARSE_BWD_STATIC_SCRATCH_BYTES inside the library's device image
  * (every GPU that loads the library carries it until the process ends); the
  * call allocates nothing and frees nothing.
  *   - shapes whose scratch need (nnue_ft_sparse_bwd_workspace_bytes) exceeds
  *     the array are refused with NNUE_ERR_WORKSPACE and a message;
  *   - the first call on each device looks up the array's address
- *     (cudaGetSymbolAddress); make that first call outside any stream capture;
+ *     (cudaGetSymbolAddress); make that first call before any stream capture
+ *     begins, and from one host thread (the per-device address cache is
+ *     filled without a lock; concurrent first calls would only repeat the
+ *     look-up);
  *   - all calls share the one array: two calls that can overlap on the GPU
  *     (different streams, no ordering between them) race on it.  Calls on one
  *     stream, or otherwise ordered, are safe; nothing has to be cleared by the
@@ -185,15 +218,33 @@ int nnue_ft_prepare_table(const float* weight, const float* virtual_weight,
 int nnue_ft_virtual_grad(const float* grad, float* out, int64_t N,
                          int64_t n_virtual, int32_t W, void* stream);
 
-/* Row slices for the segment-mode nnue_ft_fused_bwd calls that follow (process-wide
- * setting; n_slices <= 0 clears it).  h_row_bounds holds n_slices + 1 non-decreasing
- * rows, the first 0; calls whose N equals the last bound produce grad_weight slice
- * by slice (rows [bounds[i], bounds[i+1]) final, then h_events[i], a cudaEvent_t
- * or NULL, recorded on the call's stream), so that a consumer on another stream
- * can start on the first rows while the later ones are still computed.  The
- * values written are those of the unsliced call.  n_slices <= 16. */
-int nnue_ft_fused_bwd_slices(const int64_t* h_row_bounds, void* const* h_events,
-                             int32_t n_slices);
+/* The same backward with the gradient delivered in row slices, for a consumer
+ * on another stream (the data-parallel reduce) that starts on the first rows
+ * while the later ones are still computed.  h_slices->row_bounds holds
+ * n_slices + 1 non-decreasing rows, the first 0 and the last N; rows
+ * [bounds[i], bounds[i+1]) are final when events[i] (a cudaEvent_t or NULL) is
+ * recorded on the call's stream.  The values written are those of the unsliced
+ * call, bit for bit.  The setting belongs to this one call: nothing is kept
+ * between calls.  Every successful return has recorded every event exactly
+ * once, also on the routes that finish the whole gradient at once (B == 0,
+ * mode = NNUE_BWD_ATOMIC; NNUE_BWD_AUTO with slices is the segment route).
+ * h_slices == NULL or n_slices == 0 is nnue_ft_fused_bwd. */
+#define NNUE_BWD_MAX_SLICES 16
+typedef struct nnue_bwd_slices {
+    int32_t n_slices;
+    int64_t row_bounds[NNUE_BWD_MAX_SLICES + 1];
+    void* events[NNUE_BWD_MAX_SLICES];
+} nnue_bwd_slices;
+
+int nnue_ft_fused_bwd_sliced(const float* us, const float* them,
+                             const int32_t* white_idx, const int32_t* black_idx,
+                             const int64_t* psqt_idx, float max_act, float out_scale,
+                             const float* grad_l0, const float* grad_wpsqt,
+                             const float* grad_bpsqt, const float* saved,
+                             float* grad_weight, float* grad_bias,
+                             int64_t B, int32_t K, int64_t N, int32_t L1, int32_t P,
+                             void* workspace, size_t workspace_bytes, int32_t mode,
+                             const nnue_bwd_slices* h_slices, void* stream);
 
 /* ---- A12: RangerLite (Adam + positive-negative momentum + lookahead) ---
  * One fused pass over a parameter tensor viewed as [rows, width]:

@@ -59,14 +59,13 @@ class _NoSpan:
         return False
 
 
-# When set (data-parallel table exchange), the fused backward writes the table
-# gradient into this preallocated [N, W] buffer instead of a fresh tensor, and
-# the autograd functions hand no gradient to the parameter: the exchange owns it.
-GRAD_SINK: torch.Tensor | None = None
-
-
-def is_grad_sink(t: torch.Tensor | None) -> bool:
-    return t is not None and GRAD_SINK is not None and t.data_ptr() == GRAD_SINK.data_ptr()
+def exchange_of(t: torch.Tensor | None):
+    """The data-parallel table exchange (`ddp.ShardedTableExchange`) that owns tensor `t`,
+    or None.  The exchange marks its table parameter; tables derived from the parameter
+    (`PrepareTableFunction`) carry the mark on.  With an exchange, the fused backward writes
+    the table gradient into the exchange's shared buffer instead of a fresh tensor and the
+    autograd functions hand no gradient to the parameter."""
+    return getattr(t, "_nnue_exchange", None) if t is not None else None
 
 
 TIMER: KernelTimer | None = None
@@ -192,7 +191,11 @@ def fused_forward(us, them, white_indices, black_indices, psqt_indices, weight, 
 def fused_backward(
     us, them, white_indices, black_indices, psqt_indices, max_ft_activation, l1_size, num_inputs, num_outputs,
     grad_l0, grad_wpsqt, grad_bpsqt, saved, mode: str | None = None, out_scale: float = 1.0,
+    sink: torch.Tensor | None = None, slices=None,
 ):
+    """`sink`: preallocated [num_inputs, num_outputs] destination of the table gradient (a fresh
+    tensor otherwise).  `slices`: (row bounds, torch events) to deliver the gradient slice by slice
+    (`nnue_ft_fused_bwd_sliced`); both belong to this one call."""
     dev = _require_cuda(us, grad_l0, grad_wpsqt, grad_bpsqt, saved)
     grad_l0 = grad_l0.contiguous()
     grad_wpsqt = grad_wpsqt.contiguous()
@@ -201,19 +204,32 @@ def fused_backward(
     P = num_outputs - l1_size
     m = _lib.bwd_mode(mode or _BWD_MODE)
     lib = _lib.load()
-    if GRAD_SINK is not None and tuple(GRAD_SINK.shape) == (num_inputs, num_outputs) and GRAD_SINK.device == dev:
-        grad_w = GRAD_SINK
+    if sink is not None:
+        assert tuple(sink.shape) == (num_inputs, num_outputs) and sink.device == dev and sink.is_contiguous()
+        assert sink.dtype == torch.float32
+        grad_w = sink
     else:
         grad_w = torch.empty(num_inputs, num_outputs, dtype=torch.float32, device=dev)
     grad_b = torch.empty(num_outputs, dtype=torch.float32, device=dev)
+    spec = None
+    if slices is not None:
+        bounds, events = slices
+        assert len(bounds) - 1 == len(events) <= _lib.MAX_SLICES
+        spec = _lib.BwdSlices()
+        spec.n_slices = len(events)
+        for i, b in enumerate(bounds):
+            spec.row_bounds[i] = int(b)
+        for i, e in enumerate(events):
+            spec.events[i] = e.cuda_event
     ws = _workspace(lib.nnue_ft_fused_bwd_workspace_bytes(B, K, num_inputs, l1_size, P, m), dev)
     with torch.cuda.device(dev), _span("fused_bwd", dev):
-        st = lib.nnue_ft_fused_bwd(
+        st = lib.nnue_ft_fused_bwd_sliced(
             _ptr(us), _ptr(them), _ptr(white_indices), _ptr(black_indices), _ptr(psqt_indices),
             float(max_ft_activation), float(out_scale), _ptr(grad_l0), _ptr(grad_wpsqt), _ptr(grad_bpsqt), _ptr(saved),
-            _ptr(grad_w), _ptr(grad_b), B, K, num_inputs, l1_size, P, _ptr(ws), ws.numel(), m, _stream(dev),
+            _ptr(grad_w), _ptr(grad_b), B, K, num_inputs, l1_size, P, _ptr(ws), ws.numel(), m,
+            C.byref(spec) if spec is not None else None, _stream(dev),
         )
-    _lib.check(st, "nnue_ft_fused_bwd")
+    _lib.check(st, "nnue_ft_fused_bwd_sliced")
     return grad_w, grad_b
 
 
@@ -252,6 +268,29 @@ def virtual_grad(grad: torch.Tensor, n_virtual: int) -> torch.Tensor:
         st = _lib.load().nnue_ft_virtual_grad(_ptr(grad), _ptr(out), N, n_virtual, W, _stream(dev))
     _lib.check(st, "nnue_ft_virtual_grad")
     return out
+
+
+def l2_read_probe(rows: int = 23232, total_rows: int = 16384 * 68, rows_per_warp: int = 68, pattern: int = 1,
+                  iters: int = 20, device: torch.device | None = None) -> float:
+    """GB/s of `nnue_l2_read_probe` over a rows x 1 KiB buffer (24 MB by default: the slice of the
+    table one column tile of the forward touches), timed with CUDA events over `iters` launches
+    after two warm-ups."""
+    dev = torch.device("cuda", torch.cuda.current_device()) if device is None else device
+    buf = torch.ones(rows * 256, dtype=torch.float32, device=dev)
+    warps = max(total_rows // rows_per_warp, 1)
+    sink = torch.empty(warps * 128, dtype=torch.float32, device=dev)
+    lib = _lib.load()
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    with torch.cuda.device(dev):
+        for i in range(iters + 2):
+            if i == 2:
+                a.record(torch.cuda.current_stream(dev))
+            _lib.check(lib.nnue_l2_read_probe(_ptr(buf), rows, warps, rows_per_warp, pattern, _ptr(sink), _stream(dev)),
+                       "nnue_l2_read_probe")
+        b.record(torch.cuda.current_stream(dev))
+        b.synchronize()
+    ms = a.elapsed_time(b) / iters
+    return warps * rows_per_warp * 1024 / (ms * 1e-3) / 1e9
 
 
 def device_status(device: torch.device | None = None) -> None:

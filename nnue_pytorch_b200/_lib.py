@@ -70,6 +70,15 @@ class QuantParams(C.Structure):
     ]
 
 
+MAX_SLICES = 16  # NNUE_BWD_MAX_SLICES
+
+
+class BwdSlices(C.Structure):
+    """Mirror of `nnue_bwd_slices`."""
+
+    _fields_ = [("n_slices", C.c_int32), ("row_bounds", C.c_int64 * (MAX_SLICES + 1)), ("events", C.c_void_p * MAX_SLICES)]
+
+
 class LsWeightScales(C.Structure):
     """Mirror of `nnue_ls_weight_scales`."""
 
@@ -110,6 +119,9 @@ PROTOTYPES = {
     "nnue_b200_launch_count": (C.c_int64, []),
     "nnue_b200_tune": (C.c_int, [C.c_char_p, C.c_int]),
     "nnue_b200_device_status": (C.c_int, [_P, C.POINTER(_I64), C.POINTER(_I64)]),
+    "nnue_b200_profile": (C.c_int, [_I32]),
+    "nnue_b200_profile_read": (C.c_int, [_I32, C.POINTER(C.c_char_p), C.POINTER(C.c_double), C.POINTER(_I64)]),
+    "nnue_l2_read_probe": (C.c_int, [_P, _I64, _I64, _I32, _I32, _P, _P]),
     "nnue_ft_sparse_fwd": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _I64, _I32, _P]),
     "nnue_ft_sparse_bwd_workspace_bytes": (_SZ, [_I64, _I32, _I64, _I32, _I32]),
     "nnue_ft_sparse_bwd": (C.c_int, [_P, _P, _P, _P, _I64, _I32, _I64, _I32, _P, _SZ, _I32, _P]),
@@ -125,7 +137,11 @@ PROTOTYPES = {
         [_P, _P, _P, _P, _P, C.c_float, C.c_float, _P, _P, _P, _P, _P, _P, _I64, _I32, _I64, _I32, _I32,
          _P, _SZ, _I32, _P],
     ),
-    "nnue_ft_fused_bwd_slices": (C.c_int, [C.POINTER(C.c_int64), C.POINTER(C.c_void_p), _I32]),
+    "nnue_ft_fused_bwd_sliced": (
+        C.c_int,
+        [_P, _P, _P, _P, _P, C.c_float, C.c_float, _P, _P, _P, _P, _P, _P, _I64, _I32, _I64, _I32, _I32,
+         _P, _SZ, _I32, C.POINTER(BwdSlices), _P],
+    ),
     "nnue_ft_prepare_table": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, C.c_float, C.c_float, _P]),
     "nnue_ft_virtual_grad": (C.c_int, [_P, _P, _I64, _I64, _I32, _P]),
     "nnue_rangerlite_update": (
@@ -211,6 +227,24 @@ def bwd_mode(name: str) -> int:
 
 def tune(key: str, value: int) -> None:
     check(load().nnue_b200_tune(key.encode(), int(value)), f"nnue_b200_tune({key})")
+
+
+def profile(enable: bool) -> None:
+    """Start (and clear) or stop the library's per-kernel event record."""
+    check(load().nnue_b200_profile(1 if enable else 0), "nnue_b200_profile")
+
+
+def profile_summary() -> dict[str, dict]:
+    """{kernel name: {"launches": n, "total_ms": t, "mean_ms": t / n}} of the record; synchronises the device."""
+    lib, out, i = load(), {}, 0
+    while True:
+        name, ms, n = C.c_char_p(), C.c_double(0.0), _I64(0)
+        if lib.nnue_b200_profile_read(i, C.byref(name), C.byref(ms), C.byref(n)) != NNUE_OK:
+            break
+        out[name.value.decode()] = {"launches": int(n.value), "total_ms": ms.value,
+                                    "mean_ms": ms.value / max(int(n.value), 1)}
+        i += 1
+    return out
 
 
 def device_status(stream_ptr: int) -> None:

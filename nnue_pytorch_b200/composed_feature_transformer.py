@@ -21,8 +21,9 @@ _FAKE_QUANTIZE_EPS = 1e-5  # model/quantize.py:10 of the reference
 
 
 def _fusable_feature(f) -> bool:
-    """Features whose merged table is `weight` or `weight + virtual_weight.repeat(k, 1)`."""
-    return getattr(f, "FUSED_TABLE", False) or type(f).__name__ == "HalfKav2Hm"
+    """Features that declare (`FUSED_TABLE = True`) that their merged table is `weight` or
+    `weight + virtual_weight.repeat(k, 1)`, which the table kernel computes in one pass."""
+    return bool(getattr(f, "FUSED_TABLE", False))
 
 
 class ComposedFeatureTransformer(nn.Module):
@@ -72,7 +73,11 @@ class ComposedFeatureTransformer(nn.Module):
                 if virt is None and not fake_quantize_weights:
                     tables.append(f.weight)
                 else:
-                    tables.append(PrepareTableFunction.apply(f.weight, virt, self.l1_size, sm, sp))
+                    t = PrepareTableFunction.apply(f.weight, virt, self.l1_size, sm, sp)
+                    ex = getattr(f.weight, "_nnue_exchange", None)
+                    if ex is not None:
+                        t._nnue_exchange = ex  # the derived table's gradient lands in the exchange's buffer
+                    tables.append(t)
             merged = tables[0] if len(tables) == 1 else torch.cat(tables, dim=0)
             sb = q.weight_scales_dict["ft_bias"] if fake_quantize_weights else 0.0
             return merged, PrepareBiasFunction.apply(self.bias, self.l1_size, sb)

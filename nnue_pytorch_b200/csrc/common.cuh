@@ -63,6 +63,21 @@ int sm_count();
 // Host-side tally of kernels this process has launched (for benchmarks).
 void note_launches(int n);
 
+// Brackets the launches enqueued on `s` during its lifetime with two timing
+// events when nnue_b200_profile(1) is in effect; free otherwise.  `name` must
+// be a string constant.
+class ProfScope {
+public:
+    ProfScope(const char* name, cudaStream_t s);
+    ~ProfScope();
+    ProfScope(const ProfScope&) = delete;
+    ProfScope& operator=(const ProfScope&) = delete;
+
+private:
+    int slot_;
+    cudaStream_t stream_;
+};
+
 // ---- device helpers -----------------------------------------------------
 #ifdef __CUDACC__
 

@@ -3,6 +3,7 @@
 #include <stdarg.h>
 
 #include <algorithm>
+#include <vector>
 
 #include "common.cuh"
 
@@ -45,6 +46,44 @@ unsigned long long* device_status_ptr() {
 
 static unsigned long long g_launches = 0;
 void note_launches(int n) { g_launches += (unsigned long long)n; }
+
+// ---- per-kernel timing (nnue_b200_profile) ----------------------------------
+struct ProfSpan {
+    const char* name;
+    cudaEvent_t a, b;
+    bool closed;
+};
+static bool g_prof_on = false;
+static std::vector<ProfSpan> g_prof_spans;   // used[0, g_prof_used) belong to the current record
+static size_t g_prof_used = 0;
+constexpr size_t kProfMaxSpans = 1 << 16;
+
+ProfScope::ProfScope(const char* name, cudaStream_t s) : slot_(-1), stream_(s) {
+    if (!g_prof_on || g_prof_used >= kProfMaxSpans) return;
+    if (g_prof_used == g_prof_spans.size()) {
+        ProfSpan sp{name, nullptr, nullptr, false};
+        if (cudaEventCreate(&sp.a) != cudaSuccess || cudaEventCreate(&sp.b) != cudaSuccess) {
+            cudaGetLastError();
+            return;
+        }
+        g_prof_spans.push_back(sp);
+    }
+    ProfSpan& sp = g_prof_spans[g_prof_used];
+    sp.name = name;
+    sp.closed = false;
+    if (cudaEventRecord(sp.a, s) != cudaSuccess) {
+        cudaGetLastError();
+        return;
+    }
+    slot_ = (int)g_prof_used++;
+}
+
+ProfScope::~ProfScope() {
+    if (slot_ < 0) return;
+    ProfSpan& sp = g_prof_spans[(size_t)slot_];
+    if (cudaEventRecord(sp.b, stream_) == cudaSuccess) sp.closed = true;
+    else cudaGetLastError();
+}
 
 int sm_count() {
     static int cache[64] = {0};
@@ -98,6 +137,100 @@ extern "C" int nnue_b200_tune(const char* key, int value) {
         set_error("nnue_b200_tune: unknown key '%s'", key);
         return NNUE_ERR_ARG;
     }
+    return NNUE_OK;
+}
+
+extern "C" int nnue_b200_profile(int32_t enable) {
+    if (enable) g_prof_used = 0;
+    g_prof_on = enable != 0;
+    return NNUE_OK;
+}
+
+extern "C" int nnue_b200_profile_read(int32_t i, const char** h_name, double* h_total_ms,
+                                      int64_t* h_launches) {
+    NNUE_REQUIRE(i >= 0 && h_name && h_total_ms && h_launches, NNUE_ERR_ARG, "nnue_b200_profile_read: bad argument");
+    NNUE_CUDA_TRY(cudaDeviceSynchronize());
+    // group by name in order of first appearance
+    std::vector<const char*> names;
+    for (size_t k = 0; k < g_prof_used; ++k) {
+        const char* n = g_prof_spans[k].name;
+        bool seen = false;
+        for (const char* m : names) seen = seen || !strcmp(m, n);
+        if (!seen) names.push_back(n);
+    }
+    NNUE_REQUIRE((size_t)i < names.size(), NNUE_ERR_ARG, "nnue_b200_profile_read: entry %d of %zu", i, names.size());
+    double total = 0.0;
+    int64_t count = 0;
+    for (size_t k = 0; k < g_prof_used; ++k) {
+        const ProfSpan& sp = g_prof_spans[k];
+        if (!sp.closed || strcmp(sp.name, names[(size_t)i])) continue;
+        float ms = 0.f;
+        if (cudaEventElapsedTime(&ms, sp.a, sp.b) != cudaSuccess) {
+            cudaGetLastError();
+            continue;
+        }
+        total += ms;
+        ++count;
+    }
+    *h_name = names[(size_t)i];
+    *h_total_ms = total;
+    *h_launches = count;
+    return NNUE_OK;
+}
+
+// ---- L2 -> SM read probe ------------------------------------------------------
+namespace nnue {
+__global__ void __launch_bounds__(kThreads, 4)
+    k_l2_read_probe(const float4* __restrict__ buf, long long rows, long long warps, int rows_per_warp,
+                    int pattern, float4* __restrict__ sink) {
+    const int lane = threadIdx.x & 31;
+    const long long w = (long long)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    if (w >= warps) return;
+    float4 acc0 = f4_zero(), acc1 = f4_zero();
+    // 64 float4 per row; the lane's two pieces are the forward's "column c and column h + c"
+    unsigned long long state = 0x9E3779B97F4A7C15ULL * (unsigned long long)(w + 1);
+    long long r = (long long)(state % (unsigned long long)rows);
+    for (int i = 0; i < rows_per_warp; i += 4) {
+        float4 v[4][2];
+        long long rr[4];
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            if (pattern) {
+                state = state * 6364136223846793005ULL + 1442695040888963407ULL;
+                rr[t] = (long long)((state >> 33) % (unsigned long long)rows);
+            } else {
+                rr[t] = r;
+                r = (r + 1 == rows) ? 0 : r + 1;
+            }
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            const bool live = i + t < rows_per_warp;
+            const float4* row = buf + rr[t] * 64;
+            v[t][0] = live ? ldg4(row + lane) : f4_zero();
+            v[t][1] = live ? ldg4(row + 32 + lane) : f4_zero();
+        }
+#pragma unroll
+        for (int t = 0; t < 4; ++t) {
+            acc0 = f4_add(acc0, v[t][0]);
+            acc1 = f4_add(acc1, v[t][1]);
+        }
+    }
+    sink[w * 32 + lane] = f4_add(acc0, acc1);
+}
+}  // namespace nnue
+
+extern "C" int nnue_l2_read_probe(const void* buf, int64_t rows, int64_t warps, int32_t rows_per_warp,
+                                  int32_t pattern, void* sink, void* stream) {
+    NNUE_REQUIRE(buf && sink && rows > 0 && warps > 0 && rows_per_warp > 0, NNUE_ERR_ARG,
+                 "nnue_l2_read_probe: bad argument");
+    NNUE_REQUIRE(aligned16(buf) && aligned16(sink), NNUE_ERR_ALIGN, "nnue_l2_read_probe: 16-byte aligned buffers");
+    const int64_t ctas = (warps + kWarpsPerCta - 1) / kWarpsPerCta;
+    NNUE_REQUIRE(ctas <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "nnue_l2_read_probe: grid too large");
+    k_l2_read_probe<<<(unsigned)ctas, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<const float4*>(buf), rows, warps, rows_per_warp, pattern, static_cast<float4*>(sink));
+    note_launches(1);
+    NNUE_CUDA_TRY(cudaGetLastError());
     return NNUE_OK;
 }
 

@@ -538,19 +538,6 @@ static bool fused_vec_ok(int L1, int P, const void* a, const void* b, const void
            aligned16(d) && aligned16(e);
 }
 
-// Row slices of the next segment-mode backward calls (process-wide; one process drives one GPU
-// under data parallelism).  See nnue_ft_fused_bwd_slices.
-constexpr int kMaxBwdSlices = 16;
-struct BwdSlices {
-    int n = 0;
-    int64_t bounds[kMaxBwdSlices + 1] = {};
-    cudaEvent_t events[kMaxBwdSlices] = {};
-};
-static BwdSlices& bwd_slices() {
-    static BwdSlices s;
-    return s;
-}
-
 extern "C" int nnue_ft_fused_fwd(const float* us, const float* them, const int32_t* white_idx,
                                  const int32_t* black_idx, const int64_t* psqt_idx,
                                  const float* weight, const float* bias, float max_act,
@@ -596,6 +583,7 @@ extern "C" int nnue_ft_fused_fwd(const float* us, const float* them, const int32
     const int stage = tuning().stage_idx && K > 0 && smem <= 48 * 1024 && aligned16(white_idx) &&
                       aligned16(black_idx);
     const unsigned grid = (unsigned)(groups * tiles);
+    ProfScope prof("k_fused_fwd", s);
 #define LAUNCH_FWD(UU, RR, MB)                                                                  \
     k_fused_fwd<UU, RR, MB><<<grid, kThreads, stage ? smem : 0, s>>>(                           \
         us, them, white_idx, black_idx, psqt_idx, weight, bias, act, l0, wpsqt, bpsqt, saved, B, \
@@ -647,13 +635,29 @@ static int fused_bwd_impl(const float* us, const float* them, const int32_t* whi
                           const float* grad_bpsqt, const float* saved, float* grad_weight,
                           float* grad_bias, int64_t B, int32_t K, int64_t N, int32_t L1,
                           int32_t P, void* workspace, size_t workspace_bytes, int32_t mode,
-                          void* stream) {
+                          const nnue_bwd_slices* slices, void* stream) {
     const FtAct act{max_act, 0.f, 0.f, out_scale, 0.f};
+    const int n_slices = slices ? slices->n_slices : 0;
+    // routes that finish the whole gradient at once still owe the consumer its events
+    auto record_all = [&](cudaStream_t st) -> int {
+        for (int i = 0; i < n_slices; ++i)
+            if (slices->events[i]) NNUE_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(slices->events[i]), st));
+        return NNUE_OK;
+    };
     NNUE_REQUIRE(B >= 0 && K >= 0 && N >= 0 && L1 > 0 && P >= 0, NNUE_ERR_ARG,
                  "nnue_ft_fused_bwd: negative size");
     NNUE_REQUIRE(L1 % 2 == 0, NNUE_ERR_ARG, "nnue_ft_fused_bwd: l1_size must be even, got %d", L1);
     NNUE_REQUIRE(mode >= NNUE_BWD_AUTO && mode <= NNUE_BWD_SEGMENT, NNUE_ERR_ARG,
                  "nnue_ft_fused_bwd: unknown mode %d", mode);
+    NNUE_REQUIRE(n_slices >= 0 && n_slices <= NNUE_BWD_MAX_SLICES, NNUE_ERR_ARG,
+                 "nnue_ft_fused_bwd_sliced: 0..%d slices, got %d", NNUE_BWD_MAX_SLICES, n_slices);
+    if (n_slices > 0) {
+        NNUE_REQUIRE(slices->row_bounds[0] == 0 && slices->row_bounds[n_slices] == N, NNUE_ERR_ARG,
+                     "nnue_ft_fused_bwd_sliced: row bounds must run from 0 to N = %lld", (long long)N);
+        for (int i = 0; i < n_slices; ++i)
+            NNUE_REQUIRE(slices->row_bounds[i] <= slices->row_bounds[i + 1], NNUE_ERR_ARG,
+                         "nnue_ft_fused_bwd_sliced: row bounds must not decrease");
+    }
     NNUE_REQUIRE(grad_weight && grad_bias, NNUE_ERR_ARG, "nnue_ft_fused_bwd: null output");
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     const int64_t W = (int64_t)L1 + P;
@@ -661,7 +665,7 @@ static int fused_bwd_impl(const float* us, const float* them, const int32_t* whi
         if (N > 0) NNUE_CUDA_TRY(cudaMemsetAsync(grad_weight, 0, (size_t)N * W * sizeof(float), s));
         if (B == 0) {
             NNUE_CUDA_TRY(cudaMemsetAsync(grad_bias, 0, (size_t)W * sizeof(float), s));
-            return NNUE_OK;
+            return record_all(s);
         }
     }
     NNUE_REQUIRE(us && them && white_idx && black_idx && psqt_idx && grad_l0 && grad_wpsqt &&
@@ -689,6 +693,7 @@ static int fused_bwd_impl(const float* us, const float* them, const int32_t* whi
         const int ppc = 64;
         const int64_t groups = (B + ppc - 1) / ppc;
         const unsigned grid = (unsigned)(groups * tiles);
+        ProfScope prof("k_fused_bwd_atomic", s);
         if (U == 1)
             k_fused_bwd_atomic<1><<<grid, kThreads, 0, s>>>(us, them, white_idx, black_idx, psqt_idx,
                                                            act, grad_l0, grad_wpsqt, grad_bpsqt,
@@ -701,7 +706,7 @@ static int fused_bwd_impl(const float* us, const float* them, const int32_t* whi
                                                            P, (int)groups, ppc, status);
         NNUE_CUDA_TRY(cudaGetLastError());
         note_launches(1);
-        return NNUE_OK;
+        return record_all(s);
     }
 
     // segment mode (also the route of the scalar shapes)
@@ -731,6 +736,7 @@ static int fused_bwd_impl(const float* us, const float* them, const int32_t* whi
         if (vec) {
             const int cols4 = L1 / 8 + P / 4;
             const int chunks = (cols4 + kThreads - 1) / kThreads;
+            ProfScope prof("k_bwd_prologue", s);
             k_bwd_prologue<<<(unsigned)(nblk * chunks), kThreads, 0, s>>>(
                 us, them, psqt_idx, act, grad_l0, grad_wpsqt, grad_bpsqt, saved, G, bias_part, B,
                 L1, P, pb, chunks);
@@ -751,18 +757,20 @@ static int fused_bwd_impl(const float* us, const float* them, const int32_t* whi
     if (launch_err != cudaSuccess) return cuda_fail(launch_err, "backward prologue launch");
     if (rc != NNUE_OK) return rc;
     if (rj != NNUE_OK) return rj;
-    const BwdSlices& sl = bwd_slices();
-    if (sl.n > 0 && sl.bounds[sl.n] == N && sl.bounds[0] == 0) {
+    if (n_slices > 0 && vec && plan.S > 0) {
         // the gradient in row slices, an event after each: a consumer on another stream (the
         // data-parallel reduce) starts on slice i while slice i + 1 is computed
-        for (int i = 0; i < sl.n; ++i) {
-            rc = csr_reduce(plan, G, (int)W, grad_weight, s, sl.bounds[i], sl.bounds[i + 1]);
+        for (int i = 0; i < n_slices; ++i) {
+            rc = csr_reduce(plan, G, (int)W, grad_weight, s, slices->row_bounds[i], slices->row_bounds[i + 1]);
             if (rc != NNUE_OK) return rc;
-            if (sl.events[i]) NNUE_CUDA_TRY(cudaEventRecord(sl.events[i], s));
+            if (slices->events[i])
+                NNUE_CUDA_TRY(cudaEventRecord(static_cast<cudaEvent_t>(slices->events[i]), s));
         }
         return NNUE_OK;
     }
-    return csr_reduce(plan, G, (int)W, grad_weight, s);
+    rc = csr_reduce(plan, G, (int)W, grad_weight, s);  // shapes the sliced reduction does not cover: all at once
+    if (rc != NNUE_OK) return rc;
+    return record_all(s);
 }
 
 // ---- mode = auto: which scatter strategy ---------------------------------------------------------
@@ -833,16 +841,17 @@ __global__ void __launch_bounds__(kThreads)
 
 constexpr long long kAtomicBelowRowsPerList = 6;
 
-extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32_t* white_idx,
-                                 const int32_t* black_idx, const int64_t* psqt_idx, float max_act,
-                                 float out_scale, const float* grad_l0, const float* grad_wpsqt,
-                                 const float* grad_bpsqt, const float* saved, float* grad_weight,
-                                 float* grad_bias, int64_t B, int32_t K, int64_t N, int32_t L1,
-                                 int32_t P, void* workspace, size_t workspace_bytes, int32_t mode,
-                                 void* stream) {
+extern "C" int nnue_ft_fused_bwd_sliced(const float* us, const float* them, const int32_t* white_idx,
+                                        const int32_t* black_idx, const int64_t* psqt_idx, float max_act,
+                                        float out_scale, const float* grad_l0, const float* grad_wpsqt,
+                                        const float* grad_bpsqt, const float* saved, float* grad_weight,
+                                        float* grad_bias, int64_t B, int32_t K, int64_t N, int32_t L1,
+                                        int32_t P, void* workspace, size_t workspace_bytes, int32_t mode,
+                                        const nnue_bwd_slices* h_slices, void* stream) {
     int run_mode = mode;
+    const bool sliced = h_slices != nullptr && h_slices->n_slices > 0;
     DensityProbe* probe = nullptr;
-    if (mode == NNUE_BWD_AUTO && B > 0 && K > 0 && white_idx && black_idx && bwd_slices().n == 0) {
+    if (mode == NNUE_BWD_AUTO && B > 0 && K > 0 && white_idx && black_idx && !sliced) {
         probe = density_probe();
         if (probe) {
             const volatile long long* h = probe->h;
@@ -868,7 +877,7 @@ extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32
     }
     const int rc = fused_bwd_impl(us, them, white_idx, black_idx, psqt_idx, max_act, out_scale, grad_l0,
                                   grad_wpsqt, grad_bpsqt, saved, grad_weight, grad_bias, B, K, N, L1, P,
-                                  workspace, workspace_bytes, run_mode, stream);
+                                  workspace, workspace_bytes, run_mode, sliced ? h_slices : nullptr, stream);
     if (probing) {  // the caller's stream must not outrun a reader of its index lists
         NNUE_CUDA_TRY(cudaEventRecord(side.join, side.stream));
         NNUE_CUDA_TRY(cudaStreamWaitEvent(s, side.join, 0));
@@ -876,20 +885,14 @@ extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32
     return rc;
 }
 
-extern "C" int nnue_ft_fused_bwd_slices(const int64_t* h_row_bounds, void* const* h_events, int32_t n_slices) {
-    BwdSlices& sl = bwd_slices();
-    if (n_slices <= 0) {
-        sl.n = 0;
-        return NNUE_OK;
-    }
-    NNUE_REQUIRE(n_slices <= kMaxBwdSlices && h_row_bounds != nullptr, NNUE_ERR_ARG,
-                 "nnue_ft_fused_bwd_slices: 1..%d slices with their row bounds", kMaxBwdSlices);
-    NNUE_REQUIRE(h_row_bounds[0] == 0, NNUE_ERR_ARG, "nnue_ft_fused_bwd_slices: the first slice starts at row 0");
-    for (int i = 0; i < n_slices; ++i)
-        NNUE_REQUIRE(h_row_bounds[i] <= h_row_bounds[i + 1], NNUE_ERR_ARG,
-                     "nnue_ft_fused_bwd_slices: row bounds must not decrease");
-    for (int i = 0; i <= n_slices; ++i) sl.bounds[i] = h_row_bounds[i];
-    for (int i = 0; i < n_slices; ++i) sl.events[i] = h_events ? static_cast<cudaEvent_t>(h_events[i]) : nullptr;
-    sl.n = n_slices;
-    return NNUE_OK;
+extern "C" int nnue_ft_fused_bwd(const float* us, const float* them, const int32_t* white_idx,
+                                 const int32_t* black_idx, const int64_t* psqt_idx, float max_act,
+                                 float out_scale, const float* grad_l0, const float* grad_wpsqt,
+                                 const float* grad_bpsqt, const float* saved, float* grad_weight,
+                                 float* grad_bias, int64_t B, int32_t K, int64_t N, int32_t L1,
+                                 int32_t P, void* workspace, size_t workspace_bytes, int32_t mode,
+                                 void* stream) {
+    return nnue_ft_fused_bwd_sliced(us, them, white_idx, black_idx, psqt_idx, max_act, out_scale, grad_l0,
+                                    grad_wpsqt, grad_bpsqt, saved, grad_weight, grad_bias, B, K, N, L1, P,
+                                    workspace, workspace_bytes, mode, nullptr, stream);
 }

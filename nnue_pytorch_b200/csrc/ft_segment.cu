@@ -539,6 +539,7 @@ int column_sum(const float* src, int64_t rows, int W, float* out, cudaStream_t s
                      (!two_stage || aligned16(scratch));
     const int cols = vec ? W / 4 : W;
     const unsigned gx = (unsigned)((cols + 31) / 32);
+    ProfScope prof("k_column_sum", s);
     auto launch = [&](const float* in, int64_t n, float* dst, int slices) {
         dim3 grid(gx, (unsigned)slices);
         if (vec) k_column_sum<true><<<grid, kThreads, 0, s>>>(in, n, W, dst, slices);
@@ -596,6 +597,7 @@ int csr_build(const CsrPlan& plan, const int32_t* const* lists, cudaStream_t s) 
     if (N == 0) return NNUE_OK;
     unsigned long long* status = device_status_ptr();
     NNUE_REQUIRE(status, NNUE_ERR_CUDA, "csr: no device status word");
+    ProfScope prof("csr_build (7 kernels)", s);
     NNUE_CUDA_TRY(cudaMemsetAsync(plan.counts, 0, (size_t)(N + 1) * sizeof(int32_t), s));
     const int64_t warps = B * n_lists;
     const unsigned lgrid = (unsigned)((warps + kWarpsPerCta - 1) / kWarpsPerCta);
@@ -670,14 +672,19 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
             NNUE_REQUIRE(tiles * groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
             const unsigned grid = (unsigned)(tiles * groups);
             float4* p4 = reinterpret_cast<float4*>(plan.partial);
-            k_zero_empty_rows<<<(unsigned)((row_end - row_begin + kWarpsPerCta - 1) / kWarpsPerCta), kThreads, 0, s>>>(
-                plan.offsets, o4, W4, row_begin, row_end);
+            {
+                ProfScope prof("k_zero_empty_rows", s);
+                k_zero_empty_rows<<<(unsigned)((row_end - row_begin + kWarpsPerCta - 1) / kWarpsPerCta), kThreads, 0, s>>>(
+                    plan.offsets, o4, W4, row_begin, row_end);
+            }
             // variant = rows per register buffer (R) and CTAs per SM the register budget must allow
             const int v = tuning().bwd_r;
 #define LAUNCH_CHUNKS(UU, RR, MB)                                                                  \
     k_segment_chunks<UU, RR, MB><<<grid, kThreads, 0, s>>>(s4, W4, src_rows, plan.offsets,         \
                                                            plan.entries, plan.chunk_row, o4, p4, N, \
                                                            (int)groups, S, status, rr)
+            {
+            ProfScope prof("k_segment_chunks", s);
             if (U == 1) {
                 if (v == 1) LAUNCH_CHUNKS(1, 2, 6); else if (v == 2) LAUNCH_CHUNKS(1, 4, 4);
                 else LAUNCH_CHUNKS(1, 2, 4);
@@ -688,7 +695,9 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
             } else {
                 if (v == 1) LAUNCH_CHUNKS(4, 1, 3); else LAUNCH_CHUNKS(4, 1, 4);
             }
+            }
 #undef LAUNCH_CHUNKS
+            ProfScope prof_fix("k_segment_fixup", s);
             if (U == 1) k_segment_fixup<1><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);
             else if (U == 2) k_segment_fixup<2><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);
             else k_segment_fixup<4><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);
@@ -722,8 +731,7 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
 }
 
 // Per-device helper stream and events for overlapping the CSR build (atomics,
-// latency bound) with DRAM-bound work on the caller's stream.  The fork/join
-// pattern below is also legal inside a stream capture.
+// latency bound) with DRAM-bound work on the caller's stream.
 struct SideStream {
     cudaStream_t stream = nullptr;
     cudaEvent_t fork = nullptr, join = nullptr;

@@ -3,9 +3,8 @@
 // Some hosts of this library cannot call cudaMalloc (or anything that calls it
 // for them) at the moment they need a gradient: a program that handed the
 // whole device to its own memory pool at start-up and forbids later
-// allocations, a service with a no-allocation-after-initialisation rule, or
-// code that runs between cudaStreamBeginCapture and cudaStreamEndCapture,
-// where allocation calls are not permitted.  nnue_ft_sparse_bwd needs a
+// allocations, or a service with a no-allocation-after-initialisation rule.
+// nnue_ft_sparse_bwd needs a
 // caller-provided workspace, which such a host may have no way to obtain.
 // This entry point brings its own: a fixed array in the library's device
 // image.  It has no counterpart in the reference project.
@@ -20,7 +19,9 @@ static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBy
 
 // In host code `g_static_scratch` is only a handle for the runtime, not a
 // device address; the address comes from cudaGetSymbolAddress, once per
-// device, with that device current.
+// device, with that device current.  The cache below is filled without a
+// lock: concurrent first calls from several host threads would each do the
+// same look-up and store the same value.
 static int static_scratch_ptr(void** out) {
     static void* cache[64] = {nullptr};
     int dev = -1;

@@ -114,7 +114,7 @@ class ShardedTableExchange:
     ranks have mapped; `install()` points the kernels' gradient sink at it.
 
     `slices` (row bounds, first 0, last the row count) makes the backward
-    deliver the gradient slice by slice (`nnue_ft_fused_bwd_slices`) and the
+    deliver the gradient slice by slice (`nnue_ft_fused_bwd_sliced`) and the
     reduce of slice i run on a second stream while slice i + 1 is still being
     computed.  With the flat HalfKAv2_hm^ table, [0, 22528, 23232] puts the 704
     factor rows, which collect half of all entries, last: nearly the whole
@@ -167,29 +167,39 @@ class ShardedTableExchange:
             self._reduced = torch.cuda.Event()
             self._zeroed = torch.cuda.Event()
             self._zeroed.record()
+            self._local_reader = torch.cuda.Event()
+        self._local_reader_pending = False
 
     def install(self) -> None:
-        import ctypes as C
+        """Marks the table parameter: the fused backward of every op that reads it (or a table
+        derived from it) then writes the gradient into the shared buffer, slice by slice when
+        the exchange is sliced."""
+        from . import _lib
 
-        from . import _launch, _lib
-
-        _launch.GRAD_SINK = self.grad_view
-        lib = _lib.load()
+        self.param._nnue_exchange = self
         if self.sliced:
-            arr = (C.c_int64 * len(self.bounds))(*self.bounds)
-            evs = (C.c_void_p * len(self.slice_events))(*[e.cuda_event for e in self.slice_events])
-            _lib.check(lib.nnue_ft_fused_bwd_slices(arr, evs, len(self.slice_events)), "nnue_ft_fused_bwd_slices")
             _lib.tune("ddp_reduce_ctas", self.reduce_ctas)
-        else:
-            _lib.check(lib.nnue_ft_fused_bwd_slices(None, None, 0), "nnue_ft_fused_bwd_slices")
 
     def uninstall(self) -> None:
-        """Back to plain gradients: no sink, no slices."""
-        from . import _launch, _lib
+        """Back to plain gradients: no shared buffer, no slices."""
+        from . import _lib
 
-        _launch.GRAD_SINK = None
-        _lib.check(_lib.load().nnue_ft_fused_bwd_slices(None, None, 0), "nnue_ft_fused_bwd_slices")
+        if getattr(self.param, "_nnue_exchange", None) is self:
+            del self.param._nnue_exchange
         _lib.tune("ddp_reduce_ctas", 0)
+
+    def slice_spec(self):
+        """(row bounds, events) for `nnue_ft_fused_bwd_sliced`, or None when the gradient is taken whole."""
+        return (self.bounds, self.slice_events) if self.sliced else None
+
+    def note_local_reader(self) -> None:
+        """Called after a kernel of THIS rank that reads the unsummed gradient buffer has been
+        enqueued on the current stream (the factor-row gradient of a folded table): the sliced
+        reduce, which runs on its own stream and overwrites this rank's share with rank sums,
+        waits for it."""
+        if self.sliced:
+            self._local_reader.record(torch.cuda.current_stream(self.table.device))
+            self._local_reader_pending = True
 
     def reduce(self) -> torch.Tensor:
         """After every rank's backward has been ENQUEUED: sums this rank's share over the
@@ -207,6 +217,9 @@ class ShardedTableExchange:
             cur = torch.cuda.current_stream(self.table.device)
             comm = self.comm_stream
             comm.wait_event(self._zeroed)  # ft_sumsq was cleared after its last reader
+            if self._local_reader_pending:
+                comm.wait_event(self._local_reader)
+                self._local_reader_pending = False
             with torch.cuda.stream(comm):
                 for ev, (e0, e1) in zip(self.slice_events, self.ranges):
                     comm.wait_event(ev)                           # this rank has finished the slice ...

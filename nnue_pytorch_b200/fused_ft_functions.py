@@ -42,18 +42,21 @@ class FusedDoubleFtFunction(autograd.Function):
         ctx.weight_shape = tuple(weight.shape)
         # a table made by PrepareTableFunction still needs its gradient routed to the factor rows
         ctx.table_is_derived = weight.grad_fn is not None
+        ctx.exchange = _launch.exchange_of(weight)  # data-parallel owner of the table, if any
         return l0, wpsqt, bpsqt
 
     @staticmethod
     def backward(ctx, grad_l0, grad_wpsqt, grad_bpsqt):
         us, them, white_indices, black_indices, psqt_indices, saved = ctx.saved_tensors
         num_inputs, num_outputs = ctx.weight_shape
+        ex = ctx.exchange
         grad_weight, grad_bias = _launch.fused_backward(
             us, them, white_indices, black_indices, psqt_indices, ctx.max_ft_activation, ctx.l1_size,
             num_inputs, num_outputs, grad_l0, grad_wpsqt, grad_bpsqt, saved, out_scale=ctx.out_scale,
+            sink=None if ex is None else ex.grad_view, slices=None if ex is None else ex.slice_spec(),
         )
-        if _launch.is_grad_sink(grad_weight) and not ctx.table_is_derived:
-            grad_weight = None  # the data-parallel exchange reads the sink buffer itself
+        if ex is not None and not ctx.table_is_derived:
+            grad_weight = None  # the exchange reads its shared buffer itself
         return None, None, None, None, None, grad_weight, grad_bias, None, None, None, None, None
 
 
@@ -66,6 +69,7 @@ class PrepareTableFunction(autograd.Function):
     @staticmethod
     def forward(ctx, weight, virtual_weight, l1_size, scale_main, scale_psqt):
         ctx.n_virtual = 0 if virtual_weight is None else virtual_weight.shape[0]
+        ctx.exchange = _launch.exchange_of(weight)
         return _launch.prepare_table(weight, virtual_weight, int(l1_size), scale_main, scale_psqt)
 
     @staticmethod
@@ -73,8 +77,11 @@ class PrepareTableFunction(autograd.Function):
         gv = None
         if ctx.n_virtual and ctx.needs_input_grad[1]:
             gv = _launch.virtual_grad(grad, ctx.n_virtual)
-        if _launch.is_grad_sink(grad):
-            grad = None  # the data-parallel exchange reads the sink buffer itself
+        ex = ctx.exchange
+        if ex is not None and grad.data_ptr() == ex.grad_view.data_ptr():
+            if gv is not None:
+                ex.note_local_reader()  # the reduce overwrites the buffer: it must wait for the kernel above
+            grad = None  # the exchange reads its shared buffer itself
         return grad, gv, None, None, None
 
 

@@ -76,25 +76,17 @@ def _select(stacked, bucket, width, count):
     return rows[bucket.flatten() + base]
 
 
-def forward(params, us, them, white, black, piece_count, q: Quant = Quant(), fq_acts=True, fq_weights=True):
-    L1 = params["l1_w"].shape[1]
+def layer_stacks(params, l0, bucket, q: Quant = Quant(), fq_acts=True, fq_weights=True, trace: dict | None = None):
+    """The three bucketed layers behind the feature transformer (model/modules/layer_stacks.py:33-84):
+    `l0` [B, L1] -> [B, 1].  `trace`, when given, receives the values that go into each `floor` of the
+    activation fake quantization ("pre_floor": [B, 2*L2 + 2*L3], in units of one quantization step),
+    so that a caller can tell which positions sit on a step boundary."""
     L2 = params["l1f_w"].shape[0]
     count = params["out_w"].shape[0]
     L3 = params["l2_w"].shape[0] // count
-    bucket = (piece_count - 1) // 4
-
-    table, fb = params["ft_weight"], params["ft_bias"][:L1]
-    if fq_weights:
-        table = torch.cat([fq_weight(table[:, :L1], q.ft_one), fq_weight(table[:, L1:], q.nnue2score * q.ws_out)], dim=1)
-        fb = fq_weight(fb, q.ft_one)
-    bias = torch.cat([fb, torch.zeros_like(params["ft_bias"][L1:], dtype=fb.dtype)])
-    l0, wpsqt, bpsqt = double_feature_transform(us, them, white, black, bucket, table, bias, q.ft_max / q.ft_one, L1)
-    if fq_acts:
-        l0 = fq_act(l0, q.hidden_one)
-    l0 = l0 * (q.ft_one**2 / q.l0_div / q.hidden_one)
-
     max_hidden = q.hidden_max / q.hidden_one
     sqr_corr = q.hidden_one / q.sqr_div
+    pre = []
 
     w1 = params["l1_w"] + params["l1f_w"].repeat(count, 1)
     b1 = params["l1_b"] + params["l1f_b"].repeat(count)
@@ -105,6 +97,7 @@ def forward(params, us, them, white, black, piece_count, q: Quant = Quant(), fq_
     sq = torch.pow(o1, 2.0)
     lin = o1
     if fq_acts:
+        pre += [sq.detach() * q.hidden_one, lin.detach() * q.hidden_one]
         sq = fq_act(sq, q.hidden_one)
     sq = sq * sqr_corr
     if fq_acts:
@@ -118,6 +111,7 @@ def forward(params, us, them, white, black, piece_count, q: Quant = Quant(), fq_
     sq = torch.pow(o2, 2.0)
     lin = o2
     if fq_acts:
+        pre += [sq.detach() * q.hidden_one, lin.detach() * q.hidden_one]
         sq = fq_act(sq, q.hidden_one)
     sq = sq * sqr_corr
     if fq_acts:
@@ -129,8 +123,28 @@ def forward(params, us, them, white, black, piece_count, q: Quant = Quant(), fq_
         w3, b3 = fq_weight(w3, q.ws_lout), fq_weight(b3, q.ws_lout * q.hidden_one)
     o3 = _select(F.linear(torch.cat([x1, x2], dim=1), w3, b3), bucket, 1, count)
     y = o3 + skip
+    if trace is not None:
+        trace["pre_floor"] = torch.cat(pre, dim=1) if pre else None
+        trace["pre_output"] = y.detach()
     if fq_acts:
         y = fq_output(y, q)
+    return y
+
+
+def forward(params, us, them, white, black, piece_count, q: Quant = Quant(), fq_acts=True, fq_weights=True):
+    L1 = params["l1_w"].shape[1]
+    bucket = (piece_count - 1) // 4
+
+    table, fb = params["ft_weight"], params["ft_bias"][:L1]
+    if fq_weights:
+        table = torch.cat([fq_weight(table[:, :L1], q.ft_one), fq_weight(table[:, L1:], q.nnue2score * q.ws_out)], dim=1)
+        fb = fq_weight(fb, q.ft_one)
+    bias = torch.cat([fb, torch.zeros_like(params["ft_bias"][L1:], dtype=fb.dtype)])
+    l0, wpsqt, bpsqt = double_feature_transform(us, them, white, black, bucket, table, bias, q.ft_max / q.ft_one, L1)
+    if fq_acts:
+        l0 = fq_act(l0, q.hidden_one)
+    l0 = l0 * (q.ft_one**2 / q.l0_div / q.hidden_one)
+    y = layer_stacks(params, l0, bucket, q, fq_acts, fq_weights)
     return y + (wpsqt - bpsqt) * (us - 0.5)
 
 

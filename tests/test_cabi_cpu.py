@@ -40,6 +40,8 @@ def test_abi_version(lib):
 
 
 def test_host_side_argument_validation(lib):
+    from nnue_pytorch_b200 import _lib
+
     # negative sizes and bad enums are rejected before any CUDA call
     assert lib.nnue_ft_sparse_fwd(None, None, None, None, -1, 4, 4, 4, None) == -1
     assert b"negative size" in lib.nnue_b200_last_error()
@@ -51,11 +53,21 @@ def test_host_side_argument_validation(lib):
     assert lib.nnue_b200_tune(b"no_such_knob", 1) == -1
     assert lib.nnue_rangerlite_update(None, None, None, None, None, None, None, None, 1, 1, None, None) == -1
     # newer entry points: the same convention
-    i64 = lambda *v: (C.c_int64 * len(v))(*v)  # noqa: E731
-    assert lib.nnue_ft_fused_bwd_slices(i64(0, 10, 5), None, 2) == -1           # bounds decrease
-    assert lib.nnue_ft_fused_bwd_slices(i64(1, 10), None, 1) == -1              # does not start at row 0
-    assert lib.nnue_ft_fused_bwd_slices(None, None, 3) == -1                    # slices without bounds
-    assert lib.nnue_ft_fused_bwd_slices(i64(0, 4, 9), None, 2) == 0 and lib.nnue_ft_fused_bwd_slices(None, None, 0) == 0
+    def sliced(n, *bounds):
+        sp = _lib.BwdSlices()
+        sp.n_slices = n
+        for i, b in enumerate(bounds):
+            sp.row_bounds[i] = b
+        return lib.nnue_ft_fused_bwd_sliced(None, None, None, None, None, 1.0, 1.0, None, None, None, None, None, None,
+                                            4, 4, 10, 8, 8, None, 0, 2, C.byref(sp), None)
+
+    assert sliced(2, 0, 10, 5) == -1 and b"row bounds" in lib.nnue_b200_last_error()   # bounds decrease / wrong end
+    assert sliced(1, 1, 10) == -1 and b"row bounds" in lib.nnue_b200_last_error()      # does not start at row 0
+    assert sliced(1, 0, 9) == -1 and b"row bounds" in lib.nnue_b200_last_error()       # does not end at N
+    assert sliced(17, 0) == -1 and b"slices" in lib.nnue_b200_last_error()             # too many
+    assert sliced(2, 0, 4, 10) == -1 and b"null output" in lib.nnue_b200_last_error()  # valid slices: next check
+    assert lib.nnue_l2_read_probe(None, 0, 1, 1, 0, None, None) == -1
+    assert lib.nnue_b200_profile(1) == 0 and lib.nnue_b200_profile(0) == 0
     assert lib.nnue_batch_build_halfka(None, 4, 7, 64, None, None, None, None, None, None, None, None, None) == -1  # layout
     assert lib.nnue_batch_build_halfka(None, 4, 1, 32, None, None, None, None, None, None, None, None, None) == -1  # K < 64
     assert lib.nnue_batch_build_halfka(None, 0, 0, 32, None, None, None, None, None, None, None, None, None) == 0

@@ -400,14 +400,14 @@ def test_fused_epilogue_matches_separate_ops(dev):
         assert len(torch.unique(outs[0][0] * 128 / corr)) <= 129
 
 
+@pytest.mark.parametrize("mode", ["segment", "atomic"])
 @pytest.mark.parametrize("bounds", [[0, 23232], [0, 5000, 23232], [0, 7509, 15018, 22528, 23232], [0, 0, 1, 23231, 23232, 23232]])
-def test_sliced_backward_is_bitwise_the_unsliced_one(dev, bounds):
+def test_sliced_backward_is_bitwise_the_unsliced_one(dev, bounds, mode):
     """The gradient produced slice by slice (what the data-parallel exchange
     consumes while later slices are still computed) has the bits of the
-    one-launch gradient, and the slice events are recorded."""
-    import ctypes as C
-
-    from nnue_pytorch_b200 import _lib, positions
+    one-launch gradient, and every slice event is recorded by the call -- also
+    on the atomic route, which finishes the whole gradient at once."""
+    from nnue_pytorch_b200 import _launch, positions
 
     b = positions.generate_batch(2048, 11, layout="baseline")
     c = {"us": t(b.us), "them": t(b.them), "white": t(b.white), "black": t(b.black),
@@ -418,27 +418,52 @@ def test_sliced_backward_is_bitwise_the_unsliced_one(dev, bounds):
     c["grad_l0"] = torch.randn(2048, 256, generator=gen)
     c["grad_wpsqt"] = torch.randn(2048, 1, generator=gen)
     c["grad_bpsqt"] = torch.randn(2048, 1, generator=gen)
-    lib = _lib.load()
-    ref = _run_fused(dev, c, "segment")
+    d = {k: (v.to(dev) if torch.is_tensor(v) else v) for k, v in c.items()}
+    _, _, _, saved = _launch.fused_forward(d["us"], d["them"], d["white"], d["black"], d["psqt"], d["weight"], d["bias"],
+                                           c["max_act"], 256)
+
+    def backward(slices, sink=None):
+        return _launch.fused_backward(d["us"], d["them"], d["white"], d["black"], d["psqt"], c["max_act"], 256,
+                                      positions.NUM_INPUTS_BASELINE, 264, d["grad_l0"], d["grad_wpsqt"], d["grad_bpsqt"],
+                                      saved, mode=mode, slices=slices, sink=sink)
+
+    ref_w, ref_b = backward(None)
     events = [torch.cuda.Event() for _ in range(len(bounds) - 1)]
-    probe = torch.cuda.Event()
-    probe.record()
-    torch.cuda.synchronize()
-    arr = (C.c_int64 * len(bounds))(*bounds)
-    evs = (C.c_void_p * len(events))(*[e.cuda_event for e in events]) if events else None
-    # a torch event has no CUDA handle until it is first recorded
+    blocker = torch.cuda.Event()
     for e in events:
-        e.record()
-    evs = (C.c_void_p * len(events))(*[e.cuda_event for e in events])
-    _lib.check(lib.nnue_ft_fused_bwd_slices(arr, evs, len(events)), "nnue_ft_fused_bwd_slices")
-    try:
-        got = _run_fused(dev, c, "segment")
-    finally:
-        _lib.check(lib.nnue_ft_fused_bwd_slices(None, None, 0), "nnue_ft_fused_bwd_slices")
+        e.record()  # a torch event has no CUDA handle until it is first recorded
+    torch.cuda.synchronize()
+    # keep the stream busy so that an event the call does NOT re-record would still read "done" from the
+    # record above, while an event it does record stays pending until the work in front of it drains
+    torch.cuda._sleep(200_000_000)
+    sink = torch.full((positions.NUM_INPUTS_BASELINE, 264), float("nan"), device=dev)
+    got_w, got_b = backward((bounds, events), sink)
+    assert not any(e.query() for e in events), "every slice event must be re-recorded behind the pending work"
+    blocker.record()
     torch.cuda.synchronize()
     assert all(e.query() for e in events)
-    assert torch.equal(got["grad_weight"], ref["grad_weight"])
-    assert torch.equal(got["grad_bias"], ref["grad_bias"])
+    assert got_w.data_ptr() == sink.data_ptr()
+    if mode == "segment":
+        assert torch.equal(got_w, ref_w) and torch.equal(got_b, ref_b)
+    else:
+        assert max_rel_err(got_w.cpu(), ref_w.cpu()) <= TOL and max_rel_err(got_b.cpu(), ref_b.cpu()) <= TOL
+
+
+def test_sliced_backward_records_events_for_an_empty_batch(dev):
+    from nnue_pytorch_b200 import _launch
+
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=dev)  # noqa: E731
+    events = [torch.cuda.Event(), torch.cuda.Event()]
+    for e in events:
+        e.record()
+    torch.cuda.synchronize()
+    torch.cuda._sleep(100_000_000)
+    gw, gb = _launch.fused_backward(z(0, 1), z(0, 1), z(0, 8, dt=torch.int32), z(0, 8, dt=torch.int32), z(0, dt=torch.int64),
+                                    1.0, 16, 40, 24, z(0, 16), z(0, 1), z(0, 1), z(0, 4, 8), mode="segment",
+                                    slices=([0, 10, 40], events))
+    assert not any(e.query() for e in events)
+    torch.cuda.synchronize()
+    assert all(e.query() for e in events) and float(gw.abs().sum()) == 0.0 and float(gb.abs().sum()) == 0.0
 
 
 def test_auto_mode_switches_to_atomics_on_nearly_empty_boards(dev):

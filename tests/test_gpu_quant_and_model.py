@@ -151,12 +151,30 @@ def test_model_forward_and_gradients_match_oracle(dev):
     loss = sf_loss(y * 600.0, score, outcome, LossParams(), 1.0)
     loss.backward()
     assert abs(float(loss) - float(g["loss"])) <= 1e-5 * float(g["loss"])
+    # float64 run of the same graph: tells the kernels' error from the fp32 reference's own rounding
+    p64 = {k: t(np.asarray(v), torch.float64).requires_grad_(True) for k, v in p.items()
+           if k not in ("ft_real", "ft_virtual")}
+    cpu_batch = tuple(t(a) for a in b.as_tuple())
+    cpu_batch = tuple(x.double() if x.is_floating_point() else x for x in cpu_batch)
+    model_oracle.training_loss(p64, cpu_batch).backward()
+    g64 = {"g_ft_weight": p64["ft_weight"].grad, "g_ft_virtual": p64["ft_weight"].grad.view(32, 768, -1).sum(0),
+           "g_ft_bias": p64["ft_bias"].grad, "g_l1_w": p64["l1_w"].grad, "g_out_w": p64["out_w"].grad}
     f = m.input.features[0]
     for ours, key in ((f.weight.grad, "g_ft_weight"), (f.virtual_weight.grad, "g_ft_virtual"),
                       (m.input.bias.grad, "g_ft_bias"), (m.layer_stacks.l1.linear.weight.grad, "g_l1_w"),
                       (m.layer_stacks.output.linear.weight.grad, "g_out_w")):
-        assert max_rel_err(ours.cpu(), t(g[key])) <= 2e-5, key
-    _ = model_oracle
+        ref32, ref64 = t(g[key]), g64[key]
+        if key == "g_ft_bias":
+            ref64 = ref64.clone()
+            ref64[64:] = 0  # the reference drops the PSQT part of the bias from the graph
+        err = max_rel_err(ours.cpu(), ref32)
+        scale = float(ref32.abs().max())
+        e_ours = float((ours.cpu().double() - ref64).abs().max())
+        e_ref = float((ref32.double() - ref64).abs().max())
+        print(f"{key}: vs fp32 reference {err:.2e}; vs float64: ours {e_ours / scale:.2e}, fp32 reference {e_ref / scale:.2e}")
+        # the bar is 1e-5 against the fp32 reference; where two fp32 evaluations of a sum this long differ by
+        # more, the float64 run decides: ours may be no further from it than twice the reference's own error
+        assert err <= 1e-5 or e_ours <= 2 * e_ref + 1e-7 * scale, key
 
 
 def test_training_steps_track_the_oracle(dev):
@@ -195,7 +213,7 @@ def test_training_steps_track_the_oracle(dev):
         coef = torch.clamp(2.0 / (total + 1e-6), max=1.0)
         ranger_lite_oracle.ranger_lite_step([cpu[k] for k in order], [g_ * coef for g_ in grads], state, lr=8.75e-4)
         loss = step(tuple(x.to(dev) for x in batch))
-        assert abs(float(loss) - float(loss_ref)) <= 2e-5 * abs(float(loss_ref)), i
+        assert abs(float(loss) - float(loss_ref)) <= 1e-5 * abs(float(loss_ref)), i
         if i in (0, 4, 19):  # after 1, 5 and 20 optimizer steps (four lookahead merges by then)
             worst[i + 1] = max(max_rel_err(names[k].detach().cpu(), cpu[k]) for k in order)
     print("max-norm relative parameter error after 1 / 5 / 20 steps:", worst)
@@ -203,43 +221,89 @@ def test_training_steps_track_the_oracle(dev):
 
 
 @pytest.mark.parametrize("B,L1,fq", [(300, 64, True), (2000, 256, True), (777, 96, False), (5, 32, True),
-                                     (1, 32, False), (4097, 3072, False)])
-def test_fused_layer_stack_matches_torch_layers(dev, B, L1, fq):
-    """Bucket-aware layer-stack kernels against the plain torch layers of the same
-    module (F.linear over all buckets + selection): output and every gradient."""
+                                     (1, 32, False), (4097, 3072, False), (4097, 3072, True)])
+def test_fused_layer_stack_matches_oracle(dev, B, L1, fq):
+    """Bucket-aware layer-stack kernels against the CPU oracle of the layer stacks (fp32 and
+    float64): output, input gradient and every parameter gradient.
+
+    With fake quantization on, an activation is floor(v * 128 + 1e-5) / 128.  The first-layer sums are
+    exact in fp32 (inputs and quantized weights are small multiples of 1/128; the test's parameters
+    sit on a 2^-12 grid so that the factor merge is exact too), but the SQUARE of a sum is rounded.
+    Where the float64 value of v * 128 + 1e-5 lies within fp32 rounding distance of an integer without
+    v * 128 being that integer exactly, an fp32 evaluation may land on either side of the step; the
+    same holds for the rounding of the output.  Such positions are identified FROM THE FLOAT64 RUN
+    (not from the disagreement), take no part in the gradient comparison (their cotangent is zeroed
+    for every implementation) and are the only ones allowed to differ in the output."""
+    from oracle import model_oracle
     from nnue_pytorch_b200.model import LayerStacks
     from nnue_pytorch_b200.quantize import QuantizationManager
 
     torch.manual_seed(B)
-    ls = LayerStacks(8, L1, 32, 32, QuantizationManager()).to(dev)
+    ls = LayerStacks(8, L1, 32, 32, QuantizationManager())
     with torch.no_grad():
         for p in ls.parameters():
             p.add_(torch.randn_like(p) * 0.05)
-    x0 = (torch.rand(B, L1, device=dev) * 0.9).div(1 / 128).floor().div(128)  # quantized activations in [0, 0.9]
-    bucket = torch.randint(0, 8, (B,), device=dev)
+            p.copy_((p * 4096).round() / 4096)
+    x0 = (torch.rand(B, L1) * 0.9).div(1 / 128).floor().div(128)  # quantized activations in [0, 0.9]
+    bucket = torch.randint(0, 8, (B,))
     if B > 100:
         bucket[bucket == 5] = 4  # an empty bucket
     if B == 777:
         bucket[:] = 6            # everything in one bucket
-    gy = torch.randn(B, 1, device=dev)
-    res = []
-    for fused in (True, False):
-        ls.fused = fused
-        ls.zero_grad(set_to_none=True)
-        x = x0.clone().requires_grad_(True)
-        y = ls(x, bucket, fq, fq)
-        y.backward(gy)
-        res.append((y.detach(), x.grad, {n: p.grad.clone() for n, p in ls.named_parameters()}))
-    (ya, xa, ga), (yb, xb, gb) = res
-    # the floor() of the fake quantization turns last-bit differences of the dot products into 1/128 steps
-    # on a few units, so the comparison allows a small fraction of outliers on y and exact parity elsewhere
-    close = (ya - yb).abs() <= 1e-4 + 1e-4 * yb.abs()
-    assert close.float().mean() >= (0.97 if fq else 1.0)
-    good = close[:, 0]
-    assert max_rel_err(xa[good].cpu(), xb[good].cpu()) <= 1e-4
-    if not fq:
-        for n in ga:
-            assert max_rel_err(ga[n].cpu(), gb[n].cpu()) <= 1e-4, n
+    gy = torch.randn(B, 1)
+    keys = {"l1_w": ls.l1.linear.weight, "l1_b": ls.l1.linear.bias, "l1f_w": ls.l1.factorized_linear.weight,
+            "l1f_b": ls.l1.factorized_linear.bias, "l2_w": ls.l2.linear.weight, "l2_b": ls.l2.linear.bias,
+            "out_w": ls.output.linear.weight, "out_b": ls.output.linear.bias}
+
+    def oracle(dtype, cot, trace=None):
+        params = {k: v.detach().to(dtype).requires_grad_(True) for k, v in keys.items()}
+        x = x0.to(dtype).requires_grad_(True)
+        y = model_oracle.layer_stacks(params, x, bucket, model_oracle.Quant(), fq, fq, trace)
+        y.backward(cot.to(dtype))
+        return y.detach(), x.grad, {k: v.grad for k, v in params.items()}
+
+    trace = {}
+    y64, _, _ = oracle(torch.float64, gy, trace)
+    on_step = torch.zeros(B, dtype=torch.bool)
+    if fq:
+        # distance of every value that enters a floor() to the nearest integer, within eight fp32 ulp of the
+        # value (exact integers excepted: fp32 holds them exactly), and of the scaled output to the nearest
+        # half-integer (its round())
+        v = trace["pre_floor"]
+        dist = ((v + model_oracle.EPS) - (v + model_oracle.EPS).round()).abs()
+        near = dist < 8 * 2.0**-23 * v.abs().clamp(min=1.0)
+        on_step = (near & (v != v.round())).any(dim=1)
+        z = trace["pre_output"][:, 0] * 32768.0
+        on_step |= ((z - z.floor()) - 0.5).abs() < 1e-4
+    cot = gy * (~on_step).float()[:, None]
+    y32, dx32, g32 = oracle(torch.float32, cot)
+    y64, dx64, g64 = oracle(torch.float64, cot)
+
+    ls.to(dev)
+    ls.fused = True
+    ls.zero_grad(set_to_none=True)
+    x = x0.to(dev).requires_grad_(True)
+    y = ls(x, bucket.to(dev), fq, fq)
+    y.backward(cot.to(dev))
+    ya, xa = y.detach().cpu(), x.grad.cpu()
+    ga = {k: v.grad.cpu() for k, v in keys.items()}
+
+    def parity(ours, r32, r64, what):
+        scale = max(float(r32.abs().max()), 1e-30)
+        err = float((ours.double() - r32.double()).abs().max()) / scale
+        e_ours = float((ours.double() - r64).abs().max())
+        e_ref = float((r32.double() - r64).abs().max())
+        assert err <= 1e-5 or e_ours <= 2 * e_ref + 1e-7 * scale, (what, err, e_ours / scale, e_ref / scale)
+
+    ok = ~on_step
+    differing = int(((ya - y32).abs() > 1e-5 * max(float(y32.abs().max()), 1e-30))[:, 0].sum())
+    print(f"B={B} L1={L1} fq={fq}: {int(on_step.sum())} positions on a quantization step, {differing} outputs differ")
+    assert float(on_step.float().mean()) <= 0.01  # the explanation must stay an exception
+    if ok.any():
+        parity(ya[ok], y32[ok], y64[ok], "y")
+        parity(xa[ok], dx32[ok], dx64[ok], "dx")
+    for k in keys:
+        parity(ga[k], g32[k], g64[k], k)
 
 
 def test_training_is_reproducible(dev):

@@ -1,9 +1,9 @@
 """The allocation-free sparse-linear backward (`nnue_ft_sparse_bwd_static`).
 
 Some programs that embed this library may not allocate device memory when
-they need the gradient (their own pool owns the device, allocation is banned
-after start-up, or the call sits inside a stream capture), so they cannot
-hand over the workspace `nnue_ft_sparse_bwd` asks for.  The variant carries
+they need the gradient (their own pool owns the device, or allocation is banned
+after start-up), so they cannot hand over the workspace `nnue_ft_sparse_bwd`
+asks for.  The variant carries
 its scratch as a fixed 32 MiB array in the library image.  Here it is called
 straight through the C ABI, twice in a row on different inputs, and compared
 with the workspace-taking entry point; shapes beyond the array are refused.
@@ -17,8 +17,6 @@ import pytest
 import torch
 
 pytestmark = pytest.mark.gpu
-
-TOL = 1e-5  # relative to the tensor's max-norm, as in the other GPU tests
 
 
 def _case(seed, B, K, N, W, dev):
@@ -59,16 +57,19 @@ def test_static_scratch_backward_matches_workspace_backward():
         want_w, want_b = _reference(lib, idx, go, N)
         gw = torch.full((N, W), float("nan"), device=dev)
         gb = torch.full((W,), float("nan"), device=dev)
-        before = torch.cuda.memory_allocated(dev)
+        torch.cuda.synchronize()
+        # the driver's own count of free device memory (torch's allocator statistics would not see an
+        # allocation made inside the library); the workspace call above has already created the
+        # library's helper stream, so nothing is left to set up except the array's address
+        free_before, _ = torch.cuda.mem_get_info(dev)
         st = lib.nnue_ft_sparse_bwd_static(idx.data_ptr(), go.data_ptr(), gw.data_ptr(), gb.data_ptr(),
                                            B, K, N, W, stream)
         assert st == 0, lib.nnue_b200_last_error()
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated(dev) == before
-        for ours, want in ((gw, want_w), (gb, want_b)):
-            scale = max(float(want.abs().max()), 1e-30)
-            assert float((ours - want).abs().max()) <= TOL * scale
-        assert torch.isfinite(gw).all()
+        free_after, _ = torch.cuda.mem_get_info(dev)
+        assert free_after == free_before, "the call changed the amount of free device memory"
+        # both entry points take the same deterministic segment route: the bits agree
+        assert torch.equal(gw, want_w) and torch.equal(gb, want_b)
 
 
 def test_static_scratch_refuses_shapes_beyond_its_array():
