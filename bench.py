@@ -3,21 +3,35 @@
 
     python bench.py --gpus N --steps K --warmup W            (this repository's arm)
     python bench.py --impl reference --steps K --warmup W     (CPU arm, host cores)
+    python bench.py --workload sweep [--l1 ... --batch ... --active ...]   forward / backward kernel sweep
+    python bench.py --workload step-native                    the same step in the reference's own table layout
 
-Workload (the headline configuration): HalfKAv2_hm^ as one table of
-22528 real + 704 factor rows, feature transformer 23232 -> 3072 for both
-perspectives, pairwise clipped product, eight layer-stack buckets, fp32, batch
-16384 per GPU, RangerLite, gradient-norm clip at 2.0, sigmoid-scaled loss with
-lambda 1.0, synthetic positions (piece count ~ U[2,32]).  A step is one
-forward + backward + optimizer update over one batch.
+Workload of the default run (the headline configuration): HalfKAv2_hm^ as one
+table of 22528 real + 704 factor rows, feature transformer 23232 -> 3072 for
+both perspectives, pairwise clipped product, eight layer-stack buckets, fp32,
+batch 16384 per GPU, RangerLite, gradient-norm clip at 2.0, sigmoid-scaled
+loss with lambda 1.0, synthetic positions (piece count ~ U[2,32]).  A step is
+one forward + backward + optimizer update over one batch.
 
-One JSON line is printed by rank 0.  `value` is positions/s with the batches
-already resident in HBM; `e2e` repeats the measurement with the batch copied
-from pinned host memory on a side stream (one batch ahead) and the loss of
-every step copied back to the host, which reads it one step later.  With
-`--feed packed` (default) the host copy is the 72-byte packed position records
-and the index lists are written on the GPU inside the timed region; with
-`--feed lists` it is the expanded lists, as the reference's loader ships them.
+One JSON line is printed by rank 0.
+  value       positions/s over exactly K steps with the batches resident in HBM, CUDA events, max over
+              ranks, no per-call timers running.
+  e2e         the same with every batch copied from pinned host memory on a side stream (one batch
+              ahead) and the loss of every step copied back to the host, which reads it one step later.
+              `--feed packed` (default): the host copy is the 72-byte packed position records and the
+              index lists are written on the GPU inside the timed region; `--feed lists`: the expanded
+              lists, as the reference's loader ships them.
+  spans_ms / kernels / roofline   a separate pass with the per-call and per-kernel event timers on.
+              `roofline` describes the kernel with the largest share of the step.  The gather kernels
+              run out of the L2 (the table slice a column tile touches stays resident), so the bound
+              is the L2 -> SM path: `peak` is measured in the same run by `nnue_l2_read_probe`.  The
+              figure against the HBM copy peak (`hbm_algorithmic_frac`, embedding-bag accounting) and
+              the DRAM utilisation from the recorded ncu traffic (`dram_frac`) stand beside it.
+  sustained   a few seconds of back-to-back steps with the clock sampler running: the step time and
+              SM clock the GPU settles at under its power limit.
+  quant_eval  integer evaluation throughput of the same architecture (calls of one batch).
+  exchange_check (N > 1)  untimed, after the timed loops: the fused table exchange against a plain
+              all-reduce + full update from the same initial state, and whether all ranks hold the same table.
 """
 
 from __future__ import annotations
@@ -44,6 +58,16 @@ N_ROWS = 23232
 K_ACTIVE = 64
 MEAN_ACTIVE = 34.0  # expected rows per perspective: 2 * E[k], k ~ U{2..32}
 
+# dram__bytes_read.sum + dram__bytes_write.sum per launch at the headline shape (L1 = 3072, batch 16384), from
+# ncu captures summarised under profiles/.  Recorded, not re-measured by a run of this file: the entry names
+# the summary it comes from, and a kernel that changed since then has no entry.
+RECORDED_DRAM_TRAFFIC = {
+    "k_segment_chunks": (1.084e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
+    "k_bwd_prologue": (1.008e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
+    "k_ranger_rows": (2.29e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
+    "k_fused_fwd": (0.950316288e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
+}
+
 
 def parse_args():
     ap = argparse.ArgumentParser()
@@ -51,23 +75,39 @@ def parse_args():
     ap.add_argument("--steps", type=int, default=50)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--l1", type=int, default=3072)
-    ap.add_argument("--batch", type=int, default=16384, help="positions per GPU per step")
+    ap.add_argument("--workload", default="step", choices=["step", "sweep", "step-native"])
+    ap.add_argument("--l1", type=int, nargs="*", default=None, help="L1 (step: one value, default 3072; sweep: a list)")
+    ap.add_argument("--batch", type=int, nargs="*", default=None,
+                    help="positions per GPU per step (step: one value, default 16384; sweep: a list)")
+    ap.add_argument("--active", type=int, nargs="*", default=[2, 8, 16, 32],
+                    help="sweep: real features per perspective (0 = piece count ~ U[2,32])")
+    ap.add_argument("--features", default="halfka", choices=["halfka", "full"],
+                    help="sweep: full = the table shape of the reference's default feature set (88944 rows, K = 288)")
+    ap.add_argument("--skew", default="uniform", choices=["uniform", "zipf"],
+                    help="sweep: zipf = king squares and piece placement drawn from a skewed distribution, so that "
+                         "a few dozen rows collect a third of all entries, as real positions do")
+    ap.add_argument("--no-flush", action="store_true", help="sweep: do not evict the L2 between launches")
     ap.add_argument("--pool", type=int, default=4, help="distinct synthetic batches cycled through")
     ap.add_argument("--bwd-mode", default="auto", choices=["auto", "atomic", "segment"])
     ap.add_argument("--cpu-sample-batch", type=int, default=2048)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sustain-seconds", type=float, default=3.0, help="0 = skip the sustained block")
+    ap.add_argument("--no-extras", action="store_true",
+                    help="only the timed loops: no spans pass, sustained block, L2 probe, quant_eval, exchange check")
     ap.add_argument("--tune", action="append", default=[], help="key=value, passed to nnue_b200_tune")
     ap.add_argument("--slices", default="auto", choices=["auto", "on", "off"],
                     help="fused exchange with the backward delivered in two row slices and the reduce of the first "
-                         "one overlapped with the second.  auto = on from 8 GPUs (measured there: 3.42 ms against "
-                         "3.55 ms per step; at 2 GPUs the two orders tie)")
+                         "one overlapped with the second.  auto = on from 8 GPUs")
     ap.add_argument("--feed", default="packed", choices=["packed", "lists"],
                     help="what the end-to-end run copies from pinned host memory every step: 72-byte packed "
                          "positions expanded on the GPU, or the expanded index lists")
     ap.add_argument("--ddp", default="fused", choices=["fused", "allreduce"],
                     help="table exchange at N > 1: peer-memory reduce-scatter/update/all-gather kernels, or NCCL all-reduce")
-    return ap.parse_args()
+    a = ap.parse_args()
+    if a.workload != "sweep":
+        a.l1 = (a.l1 or [3072])[0]
+        a.batch = (a.batch or [16384])[0]
+    return a
 
 
 def measured_peak_gbs():
@@ -120,7 +160,7 @@ class ClockSampler:
                 self.proc.kill()
 
     def summary(self):
-        sm, mx, reasons = [], [], set()
+        sm, mx, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         for ln in self.lines[self.skip:]:
             parts = [p.strip() for p in ln.split(",")]
@@ -129,6 +169,7 @@ class ClockSampler:
             try:
                 sm.append(float(parts[0]))
                 mx.append(float(parts[1]))
+                power.append(float(parts[2]))
             except ValueError:
                 continue
             for name, val in zip(names, parts[3:7]):
@@ -136,27 +177,35 @@ class ClockSampler:
                     reasons.add(name)
         if not sm:
             return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
-        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(mx), "reasons": sorted(reasons), "samples": len(sm),
+                "power_w_max": max(power) if power else None}
 
 
 # ---------------------------------------------------------------------------
-def algorithmic_bytes_fwd(batch: int, l1: int, rows_per_persp: float) -> float:
+def algorithmic_bytes_fwd(batch: int, l1: int, rows_per_persp: float, k_max: int = K_ACTIVE) -> float:
     """Embedding-bag accounting: every (position, active row) counts a full row."""
     W = l1 + 8
-    return batch * (2 * rows_per_persp * W * 4 + 2 * K_ACTIVE * 4 + 24 + 3 * l1 * 4 + 8)
+    return batch * (2 * rows_per_persp * W * 4 + 2 * k_max * 4 + 24 + 3 * l1 * 4 + 8)
 
 
-def algorithmic_bytes_bwd(batch: int, l1: int, rows_per_persp: float) -> float:
-    return algorithmic_bytes_fwd(batch, l1, rows_per_persp) + N_ROWS * (l1 + 8) * 4
+def algorithmic_bytes_bwd(batch: int, l1: int, rows_per_persp: float, n_rows: int = N_ROWS, k_max: int = K_ACTIVE) -> float:
+    return algorithmic_bytes_fwd(batch, l1, rows_per_persp, k_max) + n_rows * (l1 + 8) * 4
 
 
-def make_pool(args, rank: int, n: int, batch: int):
+def algorithmic_bytes_segment(batch: int, l1: int, rows_per_persp: float, n_rows: int = N_ROWS) -> float:
+    """The segment gather-sum alone: one scratch-gradient row and one entry id per (position, perspective,
+    active row), one write of the dense gradient."""
+    W = l1 + 8
+    return batch * 2 * rows_per_persp * (W * 4 + 4) + n_rows * W * 4
+
+
+def make_pool(rank: int, n: int, batch: int):
     from nnue_pytorch_b200 import positions
 
     return [positions.generate_batch(batch, 1000 * rank + i, layout="baseline") for i in range(n)]
 
 
-def make_packed_pool(args, rank: int, n: int, batch: int):
+def make_packed_pool(rank: int, n: int, batch: int):
     """The same positions as `make_pool`, as pinned [B, 72] byte records."""
     from nnue_pytorch_b200 import batch_build, positions
 
@@ -177,13 +226,112 @@ def to_pinned(b):
     return tuple(out)
 
 
+def build_model(l1: int, dev, feature: str = "HalfKAv2_hm^flat"):
+    from nnue_pytorch_b200.model import ModelConfig, NNUEModel
+
+    torch.manual_seed(1)
+    model = NNUEModel(feature, ModelConfig(L1=l1, L2=32, L3=32))
+    with torch.no_grad():  # config: weights ~ N(0, 0.01) (standard deviation), PSQT columns keep their material init
+        model.input.features[0].weight[:, :l1].normal_(0.0, 0.01)
+    return model.to(dev)
+
+
+def build_step(model, world: int, ddp: str, slices, reduce_ctas: int):
+    """(TrainStep, exchange or None) for `world` ranks."""
+    from nnue_pytorch_b200.ddp import ShardedTableExchange, make_grad_hook
+    from nnue_pytorch_b200.model import TrainStep
+
+    hook = exchange = None
+    if world > 1:
+        table = model.input.features[0].weight
+        if ddp == "fused":
+            exchange = ShardedTableExchange(table, slices=slices, reduce_ctas=reduce_ctas)
+        hook = make_grad_hook(model, world, average=False, skip=[table] if exchange is not None else [])
+    step = TrainStep(model, lr=8.75e-4, clip=2.0, lam=1.0, grad_hook=hook, grad_prescale=1.0 / world,
+                     table_exchange=exchange)
+    return step, exchange
+
+
 # ---------------------------------------------------------------------------
-def run_b200(args):
+def exchange_check(args, dev, rank: int, world: int, bench_table: torch.Tensor, slices, reduce_ctas: int) -> dict:
+    """Untimed correctness evidence for N > 1, at the benchmark's size: two optimizer steps of the fused
+    exchange (peer-load reduce, sharded update, peer-store gather) against NCCL all-reduce + the full update on
+    every rank, both from the same seeded state and on the same per-rank batches; and whether every rank holds
+    the same table, both after those steps and in the table the timed loops left behind."""
+    import torch.distributed as dist
+
+    def agree(t: torch.Tensor) -> bool:
+        other = t.detach().clone()
+        dist.broadcast(other, src=0)
+        flag = torch.tensor([0.0 if torch.equal(other, t.detach()) else 1.0], device=dev)
+        dist.all_reduce(flag)
+        return float(flag) == 0.0
+
+    def rel(a, b):
+        return float((a - b).abs().max()) / max(float(b.abs().max()), 1e-30)
+
+    out = {"bench_table_ranks_agree": agree(bench_table)}
+    batches = [tuple(torch.from_numpy(np.ascontiguousarray(a)).to(dev) for a in b.as_tuple())
+               for b in make_pool(rank + 100, 2, args.batch)]
+    ref = build_model(args.l1, dev)
+    step_ref, _ = build_step(ref, world, "allreduce", None, reduce_ctas)
+    losses_ref = [float(step_ref(b)) for b in batches]
+    fused = build_model(args.l1, dev)
+    step_fused, ex = build_step(fused, world, "fused", slices, reduce_ctas)
+    losses = [float(step_fused(b)) for b in batches]
+    ex.uninstall()
+    t_ref, t_fused = ref.input.features[0].weight.detach(), fused.input.features[0].weight.detach()
+    small = max(rel(p.detach(), q.detach()) for (n, p), (_, q) in zip(fused.named_parameters(), ref.named_parameters())
+                if "features" not in n)
+    out.update({
+        "ranks_agree": agree(t_fused),
+        "table_rel_err": rel(t_fused, t_ref),
+        "table_step_rel_err": None,
+        "small_params_rel_err": small,
+        "loss_rel_err": max(abs(a - b) / abs(b) for a, b in zip(losses, losses_ref)),
+        "steps": len(batches),
+        "reference": "NCCL all-reduce of the table gradient + full RangerLite update on every rank",
+    })
+    init = build_model(args.l1, dev).input.features[0].weight.detach()
+    d_ref, d_fused = t_ref - init, t_fused - init
+    out["table_step_rel_err"] = float((d_fused - d_ref).abs().max()) / max(float(d_ref.abs().max()), 1e-30)
+    return out
+
+
+def quant_eval_block(model, args, dev) -> dict:
+    """Integer evaluation of the benchmark's architecture: positions/s in calls of one batch (index lists
+    resident on the device), CUDA events, after warm-up."""
+    from nnue_pytorch_b200 import _launch, _lib
+    from nnue_pytorch_b200.quantized_eval import QuantizedNet
+
+    net = QuantizedNet.from_model(model)
+    pool = make_pool(7, 4, args.batch)
+    dev_pool = [(torch.from_numpy(b.white).to(dev), torch.from_numpy(b.black).to(dev),
+                 torch.from_numpy(b.us[:, 0] > 0.5).to(dev), torch.from_numpy(b.piece_count).to(dev)) for b in pool]
+    for i in range(4):
+        net.evaluate(*dev_pool[i % 4])
+    iters = 40
+    _lib.profile(True)
+    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a.record()
+    for i in range(iters):
+        out = net.evaluate(*dev_pool[i % 4])
+    b.record()
+    b.synchronize()
+    _lib.profile(False)
+    prof = _lib.profile_summary()
+    _launch.device_status(dev)
+    ms = a.elapsed_time(b) / iters
+    return {"value": args.batch / (ms * 1e-3), "unit": "positions/s", "ms_per_call": ms, "batch": args.batch,
+            "dtype": "int16 table, int32 accumulation, int8 layers", "checksum": int(out.sum()),
+            "kernels_ms": {k: round(v["mean_ms"], 4) for k, v in prof.items()}}
+
+
+# ---------------------------------------------------------------------------
+def run_step(args):
     import torch.distributed as dist
 
     from nnue_pytorch_b200 import _launch, _lib
-    from nnue_pytorch_b200.ddp import make_grad_hook
-    from nnue_pytorch_b200.model import ModelConfig, NNUEModel, TrainStep
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -205,32 +353,26 @@ def run_b200(args):
         _lib.tune(k, int(v))
         tuned[k] = int(v)
 
-    torch.manual_seed(1)
-    model = NNUEModel("HalfKAv2_hm^flat", ModelConfig(L1=args.l1, L2=32, L3=32))
-    with torch.no_grad():  # config: weights ~ N(0, 0.01) (standard deviation), PSQT columns keep their material init
-        model.input.features[0].weight[:, : args.l1].normal_(0.0, 0.01)
-    model.to(dev)
-    hook = exchange = None
-    if world > 1:
-        table = model.input.features[0].weight
-        if args.ddp == "fused":
-            from nnue_pytorch_b200.ddp import ShardedTableExchange
+    native = args.workload == "step-native"
+    layout = "native" if native else "baseline"
+    model = build_model(args.l1, dev, "HalfKAv2_hm^" if native else "HalfKAv2_hm^flat")
+    n_rows = model.input.features[0].weight.shape[0]
+    # --slices: the 704 factor rows (half of all entries) form the last slice, so the reduce of the
+    # 22528 real rows can run while the factor rows' gradient is still being computed
+    sliced = world > 1 and args.ddp == "fused" and not native and (
+        args.slices == "on" or (args.slices == "auto" and world >= 8))
+    slices = [0, n_rows - 704, n_rows] if sliced else None
+    reduce_ctas = tuned.get("ddp_reduce_ctas", 32)
+    step, exchange = build_step(model, world, args.ddp, slices, reduce_ctas)
 
-            # --slices: the 704 factor rows (half of all entries) form the last slice, so the reduce of the
-            # 22528 real rows can run while the factor rows' gradient is still being computed
-            sliced = args.slices == "on" or (args.slices == "auto" and world >= 8)
-            slices = [0, table.shape[0] - 704, table.shape[0]] if sliced else None
-            exchange = ShardedTableExchange(table, slices=slices, reduce_ctas=tuned.get("ddp_reduce_ctas", 32))
-        hook = make_grad_hook(model, world, average=False, skip=[table] if exchange is not None else [])
-    step = TrainStep(model, lr=8.75e-4, clip=2.0, lam=1.0, grad_hook=hook, grad_prescale=1.0 / world,
-                     table_exchange=exchange)
+    from nnue_pytorch_b200 import positions
 
-    pool_host = [to_pinned(b) for b in make_pool(args, rank, args.pool, args.batch)]
+    pool_host = [to_pinned(positions.generate_batch(args.batch, 1000 * rank + i, layout=layout)) for i in range(args.pool)]
     pool_dev = [tuple(x.to(dev) for x in b) for b in pool_host]
     if args.feed == "packed":
         from nnue_pytorch_b200.batch_build import build_batch
 
-        feed_host = make_packed_pool(args, rank, args.pool, args.batch)
+        feed_host = make_packed_pool(rank, args.pool, args.batch)
     else:
         feed_host = pool_host
     h2d_bytes = sum(x.numel() * x.element_size() for x in feed_host[0])
@@ -247,7 +389,7 @@ def run_b200(args):
     copy_stream = torch.cuda.Stream(dev)
 
     def timed(n_steps, resident: bool):
-        """Returns (ms per step over this rank, last loss)."""
+        """Returns (ms per step, max over ranks; last loss)."""
         from nnue_pytorch_b200.prefetch import DevicePrefetcher
 
         barrier()
@@ -265,7 +407,7 @@ def run_b200(args):
             host_iter = (feed_host[i % len(feed_host)] for i in range(n_steps))
             for i, batch in enumerate(DevicePrefetcher(host_iter, dev, copy_stream=copy_stream)):
                 if args.feed == "packed":
-                    batch = build_batch(batch[0], "baseline")  # index lists and targets written on the GPU
+                    batch = build_batch(batch[0], layout)  # index lists and targets written on the GPU
                 loss = step(batch)
                 slots[i % 2].copy_(loss.reshape(1), non_blocking=True)  # device -> host, every step
                 done[i % 2].record()
@@ -283,18 +425,41 @@ def run_b200(args):
             ms = float(t)
         return ms, (loss_host if not resident else float(loss))
 
-    timed(max(args.warmup, 3), True)  # warm-up (also builds allocator pools, lazy attributes)
+    warm = max(args.warmup, 3)
+    timed(warm, True)  # warm-up (also builds allocator pools, lazy attributes)
 
     launches0 = lib.nnue_b200_launch_count()
-    _launch.TIMER = _launch.KernelTimer()
     with ClockSampler(local) as clocks:
         ms_resident, loss_val = timed(args.steps, True)
-    spans = _launch.TIMER.summary()
-    _launch.TIMER = None
     launches = (lib.nnue_b200_launch_count() - launches0) // max(args.steps, 1)
-    timed(max(args.warmup, 3), False)  # warm-up of the end-to-end path (copy-stream allocations, pinned slots)
+    timed(warm, False)  # warm-up of the end-to-end path (copy-stream allocations, pinned slots)
     ms_e2e, loss_e2e = timed(args.steps, False)
     _launch.device_status(dev)
+
+    extras = not args.no_extras
+    spans, kprof = {}, {}
+    if extras:
+        # separate pass with the timers on: per C-ABI call (torch events around the call) and per kernel (the
+        # library's own events around its main launches)
+        _launch.TIMER = _launch.KernelTimer()
+        _lib.profile(True)
+        timed(min(args.steps, 20), True)
+        _lib.profile(False)
+        spans = _launch.TIMER.summary()
+        _launch.TIMER = None
+        kprof = _lib.profile_summary()
+
+    sustained = None
+    if extras and args.sustain_seconds > 0:
+        n_sus = max(int(args.sustain_seconds * 1e3 / ms_resident), args.steps)
+        with ClockSampler(local) as sus_clocks:
+            ms_sus, _ = timed(n_sus, True)
+        sustained = {"steps": n_sus, "ms_per_step": ms_sus, "value": world * args.batch / (ms_sus * 1e-3), "unit": UNIT,
+                     "seconds": n_sus * ms_sus * 1e-3, "clocks": sus_clocks.summary()}
+
+    check = None
+    if extras and world > 1 and exchange is not None:
+        check = exchange_check(args, dev, rank, world, model.input.features[0].weight, slices, reduce_ctas)
 
     if rank != 0:
         if world > 1:
@@ -302,29 +467,82 @@ def run_b200(args):
         return
 
     peak, peak_kind = measured_peak_gbs()
+    l2 = None
+    if extras:
+        seq = _launch.l2_read_probe(pattern=0, device=dev)
+        rnd = _launch.l2_read_probe(pattern=1, device=dev)
+        l2 = {"random_rows_gbs": rnd, "sequential_rows_gbs": seq,
+              "how": "nnue_l2_read_probe: 1.14 GB read per launch from a 24 MB buffer (23232 rows x 1 KiB), 8 x 16-byte "
+                     "loads in flight per lane, 20 launches after 2 warm-ups, CUDA events"}
+    l2_peak = max(l2["random_rows_gbs"], l2["sequential_rows_gbs"]) if l2 else None
+
+    rows_pp = MEAN_ACTIVE if not native else MEAN_ACTIVE / 2
+    k_max = 32 if native else K_ACTIVE
+    alg = {
+        "k_fused_fwd": algorithmic_bytes_fwd(args.batch, args.l1, rows_pp, k_max),
+        "k_segment_chunks": algorithmic_bytes_segment(args.batch, args.l1, rows_pp, n_rows),
+        "k_bwd_prologue": args.batch * (5 * args.l1 * 4 + 2 * (args.l1 + 8) * 4 + 24),
+        "k_ranger_rows": 32.0 * n_rows * (args.l1 + 8),
+    }
+    bound_of = {"k_fused_fwd": "l2", "k_segment_chunks": "l2", "k_bwd_prologue": "hbm", "k_ranger_rows": "hbm"}
+    kernels = {}
+    for name, rec in kprof.items():
+        ms = rec["total_ms"] / max(min(args.steps, 20), 1)  # per step (a step may launch a kernel more than once)
+        entry = {"ms_per_step": round(ms, 4), "launches_per_step": rec["launches"] / max(min(args.steps, 20), 1)}
+        if name in alg and ms > 0:
+            gbs = alg[name] / (ms * 1e-3) / 1e9
+            entry.update({"algorithmic_bytes": alg[name], "algorithmic_GBps": gbs, "bound": bound_of[name],
+                          "hbm_algorithmic_frac": gbs / peak})
+            if l2_peak and bound_of[name] == "l2":
+                entry["l2_frac"] = gbs / l2_peak
+            if name in RECORDED_DRAM_TRAFFIC and args.l1 == 3072 and args.batch == 16384 and not native and not tuned:
+                traffic, src = RECORDED_DRAM_TRAFFIC[name]
+                entry.update({"dram_traffic": traffic, "dram_frac": traffic / (ms * 1e-3) / 1e9 / peak,
+                              "traffic_source": src + " (recorded, not re-measured by this run)"})
+        kernels[name] = entry
+    roofline = None
+    timed_kernels = {k: v for k, v in kernels.items() if "algorithmic_GBps" in v}
+    if timed_kernels:
+        top = max(timed_kernels, key=lambda k: timed_kernels[k]["ms_per_step"])
+        e = timed_kernels[top]
+        use_l2 = e["bound"] == "l2" and l2_peak
+        roofline = {
+            "kernel": top,
+            "share_of_step": e["ms_per_step"] / ms_resident,
+            "bound": "l2" if use_l2 else "hbm",
+            "achieved": e["algorithmic_GBps"],
+            "peak": l2_peak if use_l2 else peak,
+            "peak_source": ("L2 -> SM read rate measured in this run (nnue_l2_read_probe)" if use_l2
+                            else f"{peak_kind} copy bandwidth"),
+            "unit": "GB/s",
+            "frac": e["algorithmic_GBps"] / (l2_peak if use_l2 else peak),
+            "hbm_peak": peak,
+            "hbm_peak_source": f"{peak_kind} copy bandwidth",
+            "hbm_algorithmic_frac": e["hbm_algorithmic_frac"],
+            "traffic": e.get("dram_traffic"),
+            "traffic_source": e.get("traffic_source"),
+            "dram_frac": e.get("dram_frac"),
+            "algorithmic_bytes_per_launch": e["algorithmic_bytes"],
+            "ms_per_launch": e["ms_per_step"] / max(e["launches_per_step"], 1),
+            "l2_probe": l2,
+        }
     fwd_ms = spans.get("fused_fwd", {}).get("mean_ms")
     bwd_ms = spans.get("fused_bwd", {}).get("mean_ms")
-    opt_ms = spans.get("ranger_table", {}).get("mean_ms")
-    fwd_bytes = algorithmic_bytes_fwd(args.batch, args.l1, MEAN_ACTIVE)
-    bwd_bytes = algorithmic_bytes_bwd(args.batch, args.l1, MEAN_ACTIVE)
-    fwd_gbs = fwd_bytes / (fwd_ms * 1e-3) / 1e9 if fwd_ms else None
-    bwd_gbs = bwd_bytes / (bwd_ms * 1e-3) / 1e9 if bwd_ms else None
-    opt_gbs = 32.0 * N_ROWS * (args.l1 + 8) / (opt_ms * 1e-3) / 1e9 if opt_ms else None
-    # dram__bytes_read.sum + dram__bytes_write.sum per launch of k_fused_fwd.  At the headline shape: measured by
-    # ncu on this very workload (0.388 GB read + 0.562 GB written; profiles/ft_kernels_L3072_B4096_ncu_full.md has
-    # the command).  Other batch sizes at L1 = 3072: scaled from it, the table read (<= 286 MB) does not grow with
-    # the batch, the outputs do.
-    traffic = None
-    if args.l1 == 3072:
-        table = N_ROWS * (args.l1 + 8) * 4
-        traffic = 0.950316288e9 if args.batch == 16384 else table + (0.950316288e9 - table) * args.batch / 16384
+    calls = {}
+    if fwd_ms:
+        g = algorithmic_bytes_fwd(args.batch, args.l1, rows_pp, k_max) / (fwd_ms * 1e-3) / 1e9
+        calls["fused_fwd"] = {"ms": fwd_ms, "algorithmic_GBps": g, "hbm_algorithmic_frac": g / peak}
+    if bwd_ms:
+        g = algorithmic_bytes_bwd(args.batch, args.l1, rows_pp, n_rows, k_max) / (bwd_ms * 1e-3) / 1e9
+        calls["fused_bwd"] = {"ms": bwd_ms, "algorithmic_GBps": g, "hbm_algorithmic_frac": g / peak,
+                              "note": "one C-ABI call: prologue + CSR build + segment gather-sum + bias column sum"}
     line = {
         "metric": METRIC,
         "value": world * args.batch / (ms_resident * 1e-3),
         "unit": UNIT,
         "n_gpus": world,
         "steps": args.steps,
-        "warmup": max(args.warmup, 3),
+        "warmup": warm,
         "ms_per_step": ms_resident,
         "higher_is_better": True,
         "scaling": "weak",
@@ -332,8 +550,10 @@ def run_b200(args):
         "dtype": "f32",
         "data": "synthetic",
         "config": {
-            "workload": f"full training step: FT {N_ROWS}->{args.l1} x2 perspectives, 8 layer-stack buckets (L2=32, L3=32), "
-                        f"RangerLite, clip 2.0, batch {args.batch}/GPU, HalfKAv2_hm^ real+factor indices (K=64)",
+            "workload": f"full training step: FT {n_rows}->{args.l1} x2 perspectives, 8 layer-stack buckets (L2=32, L3=32), "
+                        f"RangerLite, clip 2.0, batch {args.batch}/GPU, "
+                        + ("HalfKAv2_hm^ native layout (factor rows folded in weight space, K=32)" if native
+                           else "HalfKAv2_hm^ real+factor indices (K=64)"),
             "global_batch": world * args.batch,
             "l1": args.l1,
             "parallelism": f"dp{world}",
@@ -350,28 +570,19 @@ def run_b200(args):
         "host_enqueue_ms_per_step": round(host_ms[0], 3),
         "loss": loss_val,
         "clocks": clocks.summary(),
-        "roofline": {
-            "kernel": "k_fused_fwd (fused double-FT forward gather)",
-            "bound": "hbm",
-            "achieved": fwd_gbs,
-            "peak": peak,
-            "peak_source": f"{peak_kind} copy bandwidth",
-            "unit": "GB/s",
-            "frac": (fwd_gbs / peak) if fwd_gbs else None,
-            "traffic": traffic,
-            "algorithmic_bytes_per_launch": fwd_bytes,
-            "ms_per_launch": fwd_ms,
-        },
-        "kernels": {
-            "fused_fwd": {"ms": fwd_ms, "algorithmic_GBps": fwd_gbs, "frac": (fwd_gbs / peak) if fwd_gbs else None},
-            "fused_bwd": {"ms": bwd_ms, "algorithmic_GBps": bwd_gbs, "frac": (bwd_gbs / peak) if bwd_gbs else None,
-                          "note": "prologue + CSR build + segment gather-sum + bias column sum"},
-            "ranger_table": {"ms": opt_ms, "GBps_at_32B_per_element": opt_gbs,
-                             "frac": (opt_gbs / peak) if opt_gbs else None},
-        },
+        "roofline": roofline,
+        "kernels": kernels,
+        "calls": calls,
         "spans_ms": {k: round(v["mean_ms"], 4) for k, v in sorted(spans.items())},
+        "sustained": sustained,
     }
-    if not args.no_cpu_baseline and world == 1:
+    if tuned:
+        line["config"]["tune"] = tuned
+    if check is not None:
+        line["exchange_check"] = check
+    if extras and world == 1 and not native:
+        line["quant_eval"] = quant_eval_block(model, args, dev)
+    if not args.no_cpu_baseline and world == 1 and not native:
         line["cpu_baseline"] = cpu_reference_steps(args, steps=2, warmup=1)
     print(json.dumps(line), flush=True)
     if world > 1:
@@ -379,49 +590,150 @@ def run_b200(args):
 
 
 # ---------------------------------------------------------------------------
-def cpu_reference_steps(args, steps: int, warmup: int):
-    """The CPU restatement of the reference's own path (oracle/: embedding-bag
-    feature transformer, torch layer stacks, loss, autograd, RangerLite Python
-    path) timed on this host's cores on a bounded sample of the workload."""
-    from oracle import model_oracle, ranger_lite_oracle
-    from nnue_pytorch_b200 import positions
+# kernel sweep: forward and backward of the fused double feature transformer, separately
+FULL_ROWS, FULL_K, FULL_MEAN = 88944, 288, 52  # the reference's default feature set (threats + pawn patterns + HalfKA)
 
+
+def _full_feature_lists(batch: int, seed: int):
+    """Stand-in lists with the default feature set's shape: 88944 rows, up to
+    288 active per perspective, about 52 on average, rows uniform at random."""
+    rng = np.random.default_rng(seed)
+    n_act = np.clip(np.rint(rng.normal(FULL_MEAN, 14, size=(2, batch))), 4, FULL_K).astype(np.int64)
+    lists = []
+    for side in range(2):
+        idx = rng.integers(0, FULL_ROWS, size=(batch, FULL_K), dtype=np.int32)
+        idx[np.arange(FULL_K)[None, :] >= n_act[side][:, None]] = -1
+        lists.append(idx)
+    us = rng.integers(0, 2, size=(batch, 1)).astype(np.float32)
+    pc = rng.integers(2, 33, size=batch)
+    return us, 1.0 - us, lists[0], lists[1], pc, float(n_act.mean())
+
+
+def _time_launches(fn, iters, warmup, flush):
+    for _ in range(warmup):
+        fn()
+    total = 0.0
+    for _ in range(iters):
+        if flush is not None:
+            flush.add_(1.0)  # 512 MB read-modify-write evicts the 126 MB L2
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        b.synchronize()
+        total += a.elapsed_time(b)
+    return total / iters
+
+
+def sweep_point(l1, batch, active, mode, iters, warmup, flush, dev, features, skew):
+    from nnue_pytorch_b200 import _launch, positions
+
+    P = 8
+    W = l1 + P
+    n_rows, k_max = (N_ROWS, K_ACTIVE) if features == "halfka" else (FULL_ROWS, FULL_K)
+    stats = None
+    if features == "halfka":
+        b = positions.generate_batch(batch, 0, layout="baseline", fixed_count=active if active else None,
+                                     **({"skew": "zipf"} if skew == "zipf" else {}))
+        rows_per_persp = 2.0 * (active if active else float(b.piece_count.mean()))
+        arrays, piece_count = (b.us, b.them, b.white, b.black), b.piece_count
+        hits = np.bincount(np.concatenate([b.white[b.white >= 0], b.black[b.black >= 0]]), minlength=n_rows)
+        top = np.sort(hits[: positions.NUM_REAL_BASELINE])[::-1]
+        stats = {"max_hits_real_row": int(top[0]), "top64_share_real_rows": float(top[:64].sum() / max(top.sum(), 1))}
+    else:
+        u, t_, wl, bl, piece_count, rows_per_persp = _full_feature_lists(batch, 0)
+        arrays = (u, t_, wl, bl)
+    us, them, wi, bi = (torch.from_numpy(x).to(dev) for x in arrays)
+    ps = torch.from_numpy((piece_count - 1) // 4).to(dev)
+    g = torch.Generator(device=dev).manual_seed(1)
+    w = torch.randn(n_rows, W, generator=g, device=dev) * 0.01
+    bias = torch.randn(W, generator=g, device=dev) * 0.01
+    gl0 = torch.randn(batch, l1, generator=g, device=dev)
+    gp = torch.randn(batch, 1, generator=g, device=dev)
+    fl = torch.zeros(128 * 1024 * 1024, device=dev) if flush else None
+    max_act = 255.0 / 256.0
+    saved = [None]
+
+    def fwd():
+        saved[0] = _launch.fused_forward(us, them, wi, bi, ps, w, bias, max_act, l1)[3]
+
+    def bwd():
+        _launch.fused_backward(us, them, wi, bi, ps, max_act, l1, n_rows, W, gl0, gp, gp, saved[0], mode)
+
+    t_f = _time_launches(fwd, iters, warmup, fl)
+    t_b = _time_launches(bwd, iters, warmup, fl)
+    warm = None
+    if flush:  # the steady-state figures as well: same launches back to back, nothing evicted in between
+        warm = (_time_launches(fwd, iters, warmup, None), _time_launches(bwd, iters, warmup, None))
+    _launch.device_status(dev)
+    common = algorithmic_bytes_fwd(batch, l1, rows_per_persp, k_max)
+    peak, kind = measured_peak_gbs()
+    return {
+        "l1": l1, "batch": batch, "active_real_per_perspective": active or "U[2,32]", "rows_per_perspective": rows_per_persp,
+        "skew": skew, "list_stats": stats,
+        "fwd_ms": t_f, "fwd_algorithmic_GBps": common / t_f / 1e6, "fwd_frac_of_hbm": common / t_f / 1e6 / peak,
+        "bwd_ms": t_b, "bwd_algorithmic_GBps": (common + n_rows * W * 4) / t_b / 1e6,
+        "bwd_frac_of_hbm": (common + n_rows * W * 4) / t_b / 1e6 / peak,
+        "rows": n_rows, "max_active": k_max,
+        "fwd_ms_steady": warm[0] if warm else None, "bwd_ms_steady": warm[1] if warm else None,
+        "bwd_mode": mode, "hbm_peak_GBps": peak, "peak_source": kind, "l2_flushed": bool(flush),
+    }
+
+
+def run_sweep(args):
+    """BASELINE config 3: L1 x batch x active features; one JSON line per point.  Mean kernel time over
+    `--steps` launches after `--warmup` (CUDA events on the launching stream): "cold" with the L2 flushed
+    between launches (the headline figures) and "steady" back to back."""
+    from nnue_pytorch_b200 import _lib
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU path for the kernels")
+    dev = torch.device("cuda", torch.cuda.current_device())
+    _lib.load()
+    tuned = {}
+    for kv in args.tune:
+        k, v = kv.split("=")
+        _lib.tune(k, int(v))
+        tuned[k] = int(v)
+    for l1 in (args.l1 or [1024, 2048, 3072]):
+        for batch in (args.batch or [4096, 16384, 65536]):
+            for act in (args.active if args.features == "halfka" else [0]):
+                r = sweep_point(l1, batch, act, args.bwd_mode, args.steps, max(args.warmup, 3), not args.no_flush, dev,
+                                args.features, args.skew)
+                if tuned:
+                    r["tune"] = tuned
+                print(json.dumps(r), flush=True)
+                torch.cuda.empty_cache()
+
+
+# ---------------------------------------------------------------------------
+def cpu_reference_steps(args, steps: int, warmup: int):
+    """The reference's own path of the step on this host's cores, on a bounded sample of the workload.
+    With the reference's `model/` tree present under oracle/_ref (see oracle/make_ref.py) this is the
+    reference's `NNUEModel` forward, loss, autograd, `clip_grad_norm_` and `RangerLite.step`, unmodified
+    (kind "reference"); otherwise the oracle's restatement of the same path (kind "port")."""
     cores = os.cpu_count() or 1
     torch.set_num_threads(cores)
     B = min(args.cpu_sample_batch, args.batch)
-    g = torch.Generator().manual_seed(1)
-    L1 = args.l1
-    p = {
-        "ft_weight": torch.randn(N_ROWS, L1 + 8, generator=g) * 0.01,
-        "ft_bias": torch.randn(L1 + 8, generator=g) * 0.01,
-        "l1_w": torch.randn(256, L1, generator=g) * 0.02, "l1_b": torch.zeros(256),
-        "l1f_w": torch.zeros(32, L1), "l1f_b": torch.zeros(32),
-        "l2_w": torch.randn(256, 64, generator=g) * 0.1, "l2_b": torch.zeros(256),
-        "out_w": torch.randn(8, 128, generator=g) * 0.1, "out_b": torch.zeros(8),
-    }
-    order = list(p)
-    state = ranger_lite_oracle.RangerLiteState([p[k] for k in order])
+    from oracle import ref_runner
+
+    runner = ref_runner.make_cpu_step(args.l1, N_ROWS)
+    from nnue_pytorch_b200 import positions
+
     times = []
     for i in range(warmup + steps):
-        b = positions.generate_batch(B, 5000 + i, layout="baseline")
+        b = positions.generate_batch(B, 5000 + i, layout=runner.layout)
         batch = tuple(torch.from_numpy(np.ascontiguousarray(a)) for a in b.as_tuple())
         t0 = time.perf_counter()
-        params = {k: v.requires_grad_(True) for k, v in p.items()}
-        loss = model_oracle.training_loss(params, batch)
-        grads = torch.autograd.grad(loss, [params[k] for k in order])
-        total = torch.linalg.vector_norm(torch.stack([torch.linalg.vector_norm(x) for x in grads]))
-        coef = torch.clamp(2.0 / (total + 1e-6), max=1.0)
-        for v in p.values():
-            v.requires_grad_(False)
-        ranger_lite_oracle.ranger_lite_step([p[k] for k in order], [x * coef for x in grads], state, lr=8.75e-4)
+        runner.step(batch)
         dt = time.perf_counter() - t0
         if i >= warmup:
             times.append(dt)
     sec = statistics.median(times)
     return {
-        "value": B / sec, "unit": UNIT, "cores": cores, "kind": "port",
+        "value": B / sec, "unit": UNIT, "cores": cores, "kind": runner.kind,
         "sample": f"{warmup} warm-up + {steps} timed optimizer steps at batch {B} (the bench batch is {args.batch}), "
-                  f"same model (L1={L1}), torch {torch.__version__} CPU ops, {cores} threads",
+                  f"{runner.describe}, torch {torch.__version__} CPU ops, {cores} threads",
         "ms_per_step": sec * 1e3,
     }
 
@@ -454,12 +766,28 @@ def run_reference(args):
         "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
+    if torch.cuda.is_available():
+        line["reference_gpu"] = ref_gpu_kernels(args)
     print(json.dumps(line), flush=True)
+
+
+def ref_gpu_kernels(args) -> dict:
+    """The reference's own CUDA kernels (its fused double-FT forward and backward) on this GPU at the
+    benchmark's shape, compiled at run time from the sources under oracle/_ref through the NVRTC stand-in for
+    CuPy that oracle/cupy_shim.py provides; or the reason why they could not be run."""
+    try:
+        from oracle import ref_runner
+
+        return ref_runner.time_reference_gpu_kernels(args.l1, args.batch, N_ROWS)
+    except Exception as e:  # noqa: BLE001 - reported, never fatal for the CPU arm
+        return {"unavailable": f"{type(e).__name__}: {e}"[:300]}
 
 
 if __name__ == "__main__":
     a = parse_args()
     if a.impl == "reference":
         run_reference(a)
+    elif a.workload == "sweep":
+        run_sweep(a)
     else:
-        run_b200(a)
+        run_step(a)

@@ -17,6 +17,15 @@ Two index layouts are produced from the same positions:
              rows, at most 64 active indices, reals first, then virtuals.
 
 Lists are int32, padded with -1 on the right.
+
+`skew="zipf"` draws king squares and (type, colour, square) of the other
+pieces from Zipf-like distributions instead of uniform ones.  Real games put
+about a third of all active features on a few dozen table rows (castled
+kings, pawns on their home squares: on one batch of 16384 real positions the
+reference's loader, data_loader/cpp/training_data_loader.cpp:487-544, fills a
+single row more than 12000 times); the skewed generator reproduces that
+concentration, which is what decides between atomics and a segment reduction
+in the backward pass.
 """
 
 from __future__ import annotations
@@ -52,7 +61,39 @@ class PositionBatch:
     stm_white: np.ndarray    # [B] bool
 
 
-def generate_positions(batch: int, seed: int, fixed_count: int | None = None) -> PositionBatch:
+def _zipf_weights(n: int, exponent: float, perm_seed: int) -> np.ndarray:
+    """Probabilities proportional to 1 / rank^exponent over a fixed (seeded) ranking of n items."""
+    ranks = np.random.default_rng(perm_seed).permutation(n) + 1
+    w = 1.0 / ranks.astype(np.float64) ** exponent
+    return w / w.sum()
+
+
+def _skewed_slots(rng, batch: int):
+    """Distinct squares per row with both kings and the other pieces drawn from skewed distributions:
+    squares come out as the order of `weight / Exp(1)` keys (a weighted permutation), the kings from a steeper
+    ranking of their own, and (type, colour) of a piece from a ranking tied to its square."""
+    king_w = _zipf_weights(64, 2.0, 101)
+    sq_w = _zipf_weights(64, 1.1, 202)
+    keys = sq_w[None, :] / rng.exponential(1.0, size=(batch, 64))
+    order = np.argsort(-keys, axis=1).astype(np.int64)          # likely squares first
+    wk = rng.choice(64, size=batch, p=king_w)
+    bk = rng.choice(64, size=batch, p=king_w[::-1])
+    bk = np.where(bk == wk, (bk + 8) % 64, bk)
+    squares = np.empty((batch, 32), dtype=np.int64)
+    squares[:, 0], squares[:, 1] = wk, bk
+    # the other slots: the row's likely squares in order, skipping the two king squares
+    free = (order != wk[:, None]) & (order != bk[:, None])
+    rank_among_free = np.cumsum(free, axis=1) - 1
+    take = free & (rank_among_free < 30)
+    squares[:, 2:] = order[take].reshape(batch, 30)
+    # piece on a square: one dominant (type, colour) per square, the rest uniform
+    combo_of_sq = np.random.default_rng(303).integers(0, 10, size=64)
+    dominant = rng.random((batch, 32)) < 0.8
+    combo = np.where(dominant, combo_of_sq[squares], rng.integers(0, 10, size=(batch, 32)))
+    return squares, combo // 2 + 1, (combo % 2).astype(bool)
+
+
+def generate_positions(batch: int, seed: int, fixed_count: int | None = None, skew: str = "uniform") -> PositionBatch:
     rng = np.random.default_rng(seed)
     if fixed_count is None:
         k = rng.integers(2, 33, size=batch)
@@ -60,9 +101,14 @@ def generate_positions(batch: int, seed: int, fixed_count: int | None = None) ->
         if not 2 <= fixed_count <= 32:
             raise ValueError("fixed_count must be in 2..32")
         k = np.full(batch, fixed_count, dtype=np.int64)
-    squares = np.argsort(rng.random((batch, 64)), axis=1)[:, :32].astype(np.int64)
-    piece_type = rng.integers(1, 6, size=(batch, 32))
-    is_white = rng.integers(0, 2, size=(batch, 32)).astype(bool)
+    if skew == "zipf":
+        squares, piece_type, is_white = _skewed_slots(rng, batch)
+    elif skew == "uniform":
+        squares = np.argsort(rng.random((batch, 64)), axis=1)[:, :32].astype(np.int64)
+        piece_type = rng.integers(1, 6, size=(batch, 32))
+        is_white = rng.integers(0, 2, size=(batch, 32)).astype(bool)
+    else:
+        raise ValueError(f"unknown skew {skew!r}; expected 'uniform' or 'zipf'")
     piece_type[:, 0] = 6
     piece_type[:, 1] = 6
     is_white[:, 0] = True
@@ -132,8 +178,9 @@ def generate_targets(batch: int, seed: int) -> tuple[np.ndarray, np.ndarray]:
     return score, outcome
 
 
-def generate_batch(batch: int, seed: int, layout: str = "baseline", fixed_count: int | None = None) -> TrainingBatch:
-    pos = generate_positions(batch, seed, fixed_count)
+def generate_batch(batch: int, seed: int, layout: str = "baseline", fixed_count: int | None = None,
+                   skew: str = "uniform") -> TrainingBatch:
+    pos = generate_positions(batch, seed, fixed_count, skew)
     fn = {"baseline": baseline_indices, "native": native_indices}[layout]
     score, outcome = generate_targets(batch, seed)
     us = pos.stm_white.astype(np.float32)[:, None]

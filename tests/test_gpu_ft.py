@@ -509,3 +509,54 @@ def test_auto_mode_switches_to_atomics_on_nearly_empty_boards(dev):
     launches_of_auto(dense)
     n_again, r = launches_of_auto(dense)  # and back (sparse data are counted on every call)
     assert n_again >= n_dense - 1 and torch.equal(r["grad_weight"], ref_dense["grad_weight"])
+
+
+def test_skewed_lists_with_rows_hit_thousands_of_times(dev):
+    """Real positions concentrate a third of all entries on a few dozen rows; the skewed generator
+    does the same (one real row collects more than 4096 entries in a batch of 8192).  Both scatter
+    routes against the oracle, and the segment route bit for bit run to run: the long rows go
+    through the per-row bitmap ordering of the CSR builder."""
+    from nnue_pytorch_b200 import positions
+
+    B, L1, P = 8192, 256, 8
+    b = positions.generate_batch(B, 4, layout="baseline", skew="zipf")
+    hits = np.bincount(np.concatenate([b.white[b.white >= 0], b.black[b.black >= 0]]),
+                       minlength=positions.NUM_INPUTS_BASELINE)
+    assert hits[: positions.NUM_REAL_BASELINE].max() > 4096
+    gen = torch.Generator().manual_seed(2)
+    c = {
+        "us": t(b.us), "them": t(b.them), "white": t(b.white), "black": t(b.black),
+        "psqt": t((b.piece_count - 1) // 4),
+        "weight": torch.randn(positions.NUM_INPUTS_BASELINE, L1 + P, generator=gen) * 0.02,
+        "bias": torch.randn(L1 + P, generator=gen) * 0.02,
+        "grad_l0": torch.randn(B, L1, generator=gen), "grad_wpsqt": torch.randn(B, 1, generator=gen),
+        "grad_bpsqt": torch.randn(B, 1, generator=gen), "max_act": 255.0 / 256.0, "l1": L1,
+    }
+    r32, r64 = _oracle(c, torch.float32), _oracle(c, torch.float64)
+    a = _run_fused(dev, c, "segment")
+    again = _run_fused(dev, c, "segment")
+    assert torch.equal(a["grad_weight"], again["grad_weight"]) and torch.equal(a["grad_bias"], again["grad_bias"])
+    for mode, r in (("segment", a), ("atomic", _run_fused(dev, c, "atomic"))):
+        for k in ("l0", "wpsqt", "bpsqt", "grad_weight", "grad_bias"):
+            _check(r[k], r32[k], r64[k], f"zipf.{k}[{mode}]")
+
+
+def test_row_named_twice_by_many_positions(dev):
+    """The one documented exception to the ordered sums: a row that single positions name twice
+    and that collects more than 4096 entries keeps its fill order (the per-row bitmap cannot
+    hold duplicates and the shared-memory sort stops at 4096).  The sums are still right; only
+    their order, hence the last bits, may differ between runs."""
+    from nnue_pytorch_b200 import _launch
+
+    B, N, K, L1, P = 3000, 500, 8, 64, 8
+    c = _random_case(B, N, K, L1, P, seed=31, wscale=0.1)
+    for key in ("white", "black"):
+        c[key][:, 0] = 7
+        c[key][:, 1] = 7        # every position names row 7 twice: 12000 entries, all duplicated
+        c[key][:, 2:] = torch.where(c[key][:, 2:] == 7, torch.full_like(c[key][:, 2:], 8), c[key][:, 2:])
+        c[key][::3, 4:] = -1
+    r32, r64 = _oracle(c, torch.float32), _oracle(c, torch.float64)
+    r = _run_fused(dev, c, "segment")
+    for k in ("l0", "grad_weight", "grad_bias"):
+        _check(r[k], r32[k], r64[k], f"dup.{k}")
+    _launch.device_status(dev)

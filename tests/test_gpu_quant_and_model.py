@@ -257,7 +257,7 @@ def test_fused_layer_stack_matches_oracle(dev, B, L1, fq):
 
     def oracle(dtype, cot, trace=None):
         params = {k: v.detach().to(dtype).requires_grad_(True) for k, v in keys.items()}
-        x = x0.to(dtype).requires_grad_(True)
+        x = x0.detach().clone().to(dtype).requires_grad_(True)
         y = model_oracle.layer_stacks(params, x, bucket, model_oracle.Quant(), fq, fq, trace)
         y.backward(cot.to(dtype))
         return y.detach(), x.grad, {k: v.grad for k, v in params.items()}
@@ -282,7 +282,7 @@ def test_fused_layer_stack_matches_oracle(dev, B, L1, fq):
     ls.to(dev)
     ls.fused = True
     ls.zero_grad(set_to_none=True)
-    x = x0.to(dev).requires_grad_(True)
+    x = x0.detach().clone().to(dev).requires_grad_(True)
     y = ls(x, bucket.to(dev), fq, fq)
     y.backward(cot.to(dev))
     ya, xa = y.detach().cpu(), x.grad.cpu()
