@@ -126,6 +126,7 @@ class ComposedFeatureTransformer(nn.Module):
         for f in self.features:
             f.clip_weights(quantization)
 
+    @torch.compiler.disable  # ctypes launches: runs eagerly inside a compiled model
     def forward(
         self,
         us: torch.Tensor,

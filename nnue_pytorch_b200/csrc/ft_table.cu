@@ -126,6 +126,7 @@ extern "C" int nnue_ft_prepare_table(const float* weight, const float* virtual_w
 #define LAUNCH_PREP(VV, II)                                                                              \
     k_prepare_table<VV, II><<<grid, kThreads, 0, s>>>(weight, virtual_weight, out, N, nv, W, L1, scale_main, \
                                                       scale_psqt, inv_main)
+    ProfScope prof("k_prepare_table", s);
     if (vec && narrow) LAUNCH_PREP(true, unsigned);
     else if (vec) LAUNCH_PREP(true, int64_t);
     else if (narrow) LAUNCH_PREP(false, unsigned);

@@ -440,10 +440,14 @@ extern "C" int nnue_quant_eval_tiled(const int32_t* white_idx, const int32_t* bl
         int32_t* psq = reinterpret_cast<int32_t*>(ws + (size_t)chunk * L1);
         const int64_t groups = (p1 - p0 + kWarpsPerCta - 1) / kWarpsPerCta;
         NNUE_REQUIRE(groups * tiles <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "nnue_quant_eval_tiled: grid too large");
-        k_quant_gather<<<(unsigned)(groups * tiles), kThreads, 0, s>>>(white_idx, black_idx, stm_white, bucket, ft_w,
-                                                                      ft_psqt, ft_b, x0, psq, p0, p1, d, *qp,
-                                                                      (int)groups, status);
+        {
+            ProfScope prof("k_quant_gather", s);
+            k_quant_gather<<<(unsigned)(groups * tiles), kThreads, 0, s>>>(white_idx, black_idx, stm_white, bucket,
+                                                                          ft_w, ft_psqt, ft_b, x0, psq, p0, p1, d,
+                                                                          *qp, (int)groups, status);
+        }
         const unsigned grid = (unsigned)std::min<int64_t>(p1 - p0, (int64_t)sm_count() * 16);
+        ProfScope prof("k_quant_layers", s);
         k_quant_layers<<<grid, kQLayerThreads, smem, s>>>(x0, psq, bucket, l1_w, l1_b, l2_w, l2_b, out_w, out_b, out,
                                                          p0, p1, d, *qp, status);
         NNUE_CUDA_TRY(cudaGetLastError());

@@ -138,6 +138,7 @@ extern "C" int nnue_rangerlite_update(float* p, const float* grad, float* grad_m
         k_rows_activate<<<(unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta), kThreads, 0, s>>>(
             grad, row_active, rows, width / 4);
         const unsigned grid = (unsigned)std::min<int64_t>((n / 4 + kThreads - 1) / kThreads, (int64_t)sms * 8);
+        ProfScope prof("k_ranger_rows", s);
         if (n / 4 + (int64_t)grid * kThreads < 0x7fffffffLL)
             k_ranger_rows<unsigned><<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma, slow,
                                                              row_active, d_grad_scale, rows, width / 4, c);

@@ -103,6 +103,35 @@ def shard_ranges(bounds: list[int], width: int, world: int, rank: int) -> list[t
     return out
 
 
+def gather_sharded(local: torch.Tensor, bounds: list[int], width: int, group) -> torch.Tensor:
+    """Full [bounds[-1] * width] tensor from every rank's shares.  `local` is this rank's shares of all
+    slices back to back (the layout of `ShardedTableExchange`'s optimizer state); collective."""
+    world, rank = dist.get_world_size(group), dist.get_rank(group)
+    full = torch.zeros(bounds[-1] * width, dtype=local.dtype, device=local.device)
+    at = 0
+    for b0, b1 in zip(bounds[:-1], bounds[1:]):
+        per = (b1 - b0 + world - 1) // world * width  # the largest share of this slice
+        e0, e1 = shard_range(b1 - b0, width, world, rank)
+        if per == 0:
+            continue
+        padded = torch.zeros(per, dtype=local.dtype, device=local.device)
+        padded[: e1 - e0] = local[at : at + (e1 - e0)]
+        at += e1 - e0
+        parts = [torch.empty_like(padded) for _ in range(world)]
+        dist.all_gather(parts, padded, group=group)
+        # shares are ceil-split: every rank but the last ones holds `per` elements, so the padded
+        # concatenation has the slice's elements in front
+        full[b0 * width : b1 * width] = torch.cat(parts)[: (b1 - b0) * width]
+    return full
+
+
+def scatter_full(full: torch.Tensor, bounds: list[int], width: int, world: int, rank: int) -> torch.Tensor:
+    """This rank's shares of `full` ([bounds[-1] * width] or [rows, width]), slice after slice: the
+    inverse of `gather_sharded`; no communication."""
+    flat = full.reshape(-1)
+    return torch.cat([flat[e0:e1] for e0, e1 in shard_ranges(bounds, width, world, rank)])
+
+
 class ShardedTableExchange:
     """Owner of the feature-transformer table under data parallelism.
 
@@ -246,23 +275,37 @@ class ShardedTableExchange:
             self.ft_sumsq.zero_()
             self._zeroed.record()
 
+    _STATE_KEYS = (("grad_ma", "grad_ma"), ("variance_ma", "variance_ma"), ("neg_grad_ma", "neg_grad_ma"),
+                   ("lookahead_params", "slow"))
+
     def state_dict(self) -> dict:
-        """Full-size optimizer state of the table, gathered from the shares (same keys as RangerLite)."""
+        """Full-size optimizer state of the table, gathered from the shares: the keys and shapes the
+        reference's RangerLite keeps per parameter (model/optimizers/ranger_lite.py:268-278), so a checkpoint
+        written under the exchange resumes without it and the other way round.  Collective."""
         out = {"step": self.step}
         n, w = self.param.shape
-        for key, t in (("grad_ma", self.grad_ma), ("variance_ma", self.variance_ma),
-                       ("neg_grad_ma", self.neg_grad_ma), ("lookahead_params", self.slow)):
+        for key, attr in self._STATE_KEYS:
+            t = getattr(self, attr)
+            if t is not None:
+                out[key] = gather_sharded(t, self.bounds, w, self.group).view(n, w)
+        return out
+
+    def load_state_dict(self, state: dict) -> None:
+        """Inverse of `state_dict`: every rank keeps its shares of the full-size tensors (any device;
+        missing moments start from zero as in a fresh optimizer, a missing lookahead copy from the table).
+        The table itself is the model parameter and is loaded with the model's state dict; call this after it."""
+        n, w = self.param.shape
+        self.step = int(state.get("step", 0))
+        for key, attr in self._STATE_KEYS:
+            t = getattr(self, attr)
             if t is None:
                 continue
-            full = torch.zeros(n * w, device=t.device)
-            for (b0, b1), o0, o1 in zip(zip(self.bounds[:-1], self.bounds[1:]), self.state_at[:-1], self.state_at[1:]):
-                per = (b1 - b0 + self.world - 1) // self.world * w
-                if per == 0:
-                    continue
-                padded = torch.zeros(per, device=t.device)
-                padded[: o1 - o0] = t[o0:o1]
-                parts = [torch.empty_like(padded) for _ in range(self.world)]
-                dist.all_gather(parts, padded, group=self.group)
-                full[b0 * w : b1 * w] = torch.cat(parts)[: (b1 - b0) * w]
-            out[key] = full.view(n, w).clone()
-        return out
+            if key in state and state[key] is not None:
+                src = state[key]
+                if tuple(src.shape) != (n, w) and src.numel() != n * w:
+                    raise ValueError(f"{key}: expected {n} x {w} elements, got {tuple(src.shape)}")
+                t.copy_(scatter_full(src.to(device=t.device, dtype=t.dtype), self.bounds, w, self.world, self.rank))
+            elif attr == "slow":
+                t.copy_(scatter_full(self.table, self.bounds, w, self.world, self.rank))
+            else:
+                t.zero_()

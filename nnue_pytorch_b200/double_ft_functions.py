@@ -15,6 +15,7 @@ from .fused_ft_functions import _HAS_CUPY_KERNELS, FusedDoubleFtFunction  # noqa
 from .sparse_linear_functions import SparseLinearFunction
 
 
+@torch.compiler.disable  # ctypes launches: runs eagerly inside a compiled model, as the reference's kernels do
 def double_feature_transform(
     us: torch.Tensor,
     them: torch.Tensor,

@@ -94,6 +94,7 @@ class LayerStacks(nn.Module):
 
     fused = True  # use the bucket-aware kernels when the shapes allow it
 
+    @torch.compiler.disable  # ctypes launches: runs eagerly inside a compiled model
     def plan_ahead(self, ls_indices):
         """Starts the bucket plan of this batch on a second stream (CUDA only); pass the result to
         `forward(..., plan_ahead=...)`.  None when the fused kernels do not apply."""
@@ -103,17 +104,23 @@ class LayerStacks(nn.Module):
             return lsf.PlanAhead(ls_indices, self.count)
         return None
 
+    @torch.compiler.disable  # ctypes launches: runs eagerly inside a compiled model
+    def _fused_forward(self, x, ls_indices, fake_quantize_acts, fake_quantize_weights, plan_ahead):
+        from . import layer_stack_functions as lsf
+
+        l1, l2, out = self.l1, self.l2, self.output
+        w1, b1, w2, b2, w3, b3 = lsf.LayerStackWeightsFunction.apply(
+            l1.linear.weight, l1.linear.bias, l1.factorized_linear.weight, l1.factorized_linear.bias,
+            l2.linear.weight, l2.linear.bias, out.linear.weight, out.linear.bias, self.quantization,
+            fake_quantize_weights)
+        return lsf.FusedLayerStackFunction.apply(x, ls_indices, w1, b1, w2, b2, w3, b3, self.quantization,
+                                                 fake_quantize_acts, plan_ahead)
+
     def forward(self, x, ls_indices, fake_quantize_acts=True, fake_quantize_weights=True, plan_ahead=None):
         from . import layer_stack_functions as lsf
 
         if self.fused and lsf.supported(x, self.L1, self.L2, self.L3, self.count):
-            l1, l2, out = self.l1, self.l2, self.output
-            w1, b1, w2, b2, w3, b3 = lsf.LayerStackWeightsFunction.apply(
-                l1.linear.weight, l1.linear.bias, l1.factorized_linear.weight, l1.factorized_linear.bias,
-                l2.linear.weight, l2.linear.bias, out.linear.weight, out.linear.bias, self.quantization,
-                fake_quantize_weights)
-            return lsf.FusedLayerStackFunction.apply(x, ls_indices, w1, b1, w2, b2, w3, b3, self.quantization,
-                                                     fake_quantize_acts, plan_ahead)
+            return self._fused_forward(x, ls_indices, fake_quantize_acts, fake_quantize_weights, plan_ahead)
         o1 = self.l1(x, ls_indices, fake_quantize_weights)
         skip = o1[:, -2].view(-1, 1) - o1[:, -1].view(-1, 1)
         x1 = self._activate(o1, fake_quantize_acts)

@@ -39,7 +39,11 @@ class _CudaSparseLinearFunction(autograd.Function):
 
 
 class SparseLinearFunction:
+    # The kernels are reached through ctypes with raw device pointers, which a tracing compiler cannot
+    # follow: like the reference's kernel factories (sparse_linear_kernel.py:50,172), the operator is
+    # excluded from torch.compile and runs eagerly inside a compiled model.
     @staticmethod
+    @torch.compiler.disable
     def apply(feature_indices, weight, bias, backend: str = "auto"):
         if backend in ("auto", "sparse"):
             if not (feature_indices.is_cuda and weight.is_cuda and bias.is_cuda):

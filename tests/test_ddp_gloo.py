@@ -76,3 +76,34 @@ def test_sliced_shares_tile_every_slice_exactly():
                     assert e0 == at and e1 >= e0 and e0 % width == 0 and e1 % width == 0
                     at = e1
                 assert at == b1 * width
+
+
+def _state_worker(rank, world, port, out_dir):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        from nnue_pytorch_b200.ddp import gather_sharded, scatter_full
+
+        width = 12
+        report = {}
+        for bounds in ([0, 101], [0, 64, 101], [0, 7, 7, 10, 101], [0, 1]):
+            full = torch.arange(bounds[-1] * width, dtype=torch.float32) * 0.5 + 3.0
+            mine = scatter_full(full.view(bounds[-1], width), bounds, width, world, rank)
+            back = gather_sharded(mine, bounds, width, dist.group.WORLD)
+            report[str(bounds)] = (mine.numel(), bool(torch.equal(back, full)))
+        torch.save(report, os.path.join(out_dir, f"state{rank}.pt"))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_optimizer_state_round_trip(tmp_path):
+    """Checkpoint layout of the sharded table exchange: scattering a full-size state tensor into the
+    per-rank shares (what `load_state_dict` does) and gathering it again (what `state_dict` does) is
+    the identity, the shares partition the tensor, for one and several slices, ragged and empty ones."""
+    for world in (2, 3):
+        mp.spawn(_state_worker, args=(world, _free_port(), str(tmp_path)), nprocs=world, join=True)
+        reports = [torch.load(tmp_path / f"state{r}.pt") for r in range(world)]
+        for key in reports[0]:
+            rows = eval(key)[-1]  # noqa: S307 - the key is the bounds list this test wrote
+            assert sum(rep[key][0] for rep in reports) == rows * 12, key
+            assert all(rep[key][1] for rep in reports), key
