@@ -218,6 +218,47 @@ int nnue_ft_prepare_table(const float* weight, const float* virtual_weight,
 int nnue_ft_virtual_grad(const float* grad, float* out, int64_t N,
                          int64_t n_virtual, int32_t W, void* stream);
 
+/* ---- N1, integer form: the forward on an int16 table --------------------------
+ * With weight fake quantization on, every L1 entry of the table the operator
+ * reads is k / scale_main with integer k (scale_main = 256 in the reference,
+ * model/quantize.py:58-73).  nnue_ft_quantize_table writes that table as
+ *   q16  int16 [N, L1]   k = round_half_even((weight + virtual_weight[r % n_virtual]) * scale_main), columns
+ *                        (c, c + 1), c even, stored together as the int32 number k[c + 1] * 65536 + k[c];
+ *                        rows q16_pitch elements apart (a multiple of 8, >= L1)
+ *   psqt float [N, P]    the PSQT columns, fake-quantized at scale_psqt as nnue_ft_prepare_table does
+ * and updates d_stats (two device int32 the caller zeroes before the first block of a table):
+ * d_stats[0] += entries with |k| > 32767 (stored saturated), d_stats[1] = max(d_stats[1], max |k|).
+ * nnue_ft_fused_fwd_q16 is nnue_ft_fused_fwd on that table: integer sums of the k (column pairs summed
+ * as one 32-bit number and split every 32767 / d_stats[1] rows), one multiplication by 1 / scale_main,
+ * then the same epilogue.  The results are bit for bit those of nnue_ft_fused_fwd on the table
+ * nnue_ft_prepare_table makes from the same parameters: with |k| <= 32767 and K <= 511 no partial sum of the
+ * fp32 form is ever rounded.  `bias_fq` is the bias as that forward takes it (fp32 [L1 + P], its L1 part
+ * fake-quantized at scale_main; quantize it into the same d_stats as a one-row table so that its range
+ * counts).  While d_stats[0] != 0 the kernel ignores q16 and gathers
+ * round((weight + virtual) * scale_main) / scale_main from the parameter blocks themselves (h_blocks: the
+ * table's row ranges in order, their `rows` adding up to N), so the results never depend on the range; the
+ * host does not have to read the words.  Needs L1 % 16 == 0, P % 4 == 0, K <= 511, a power-of-two scale_main.
+ * Replaces the same reference code as nnue_ft_prepare_table + nnue_ft_fused_fwd. */
+typedef struct nnue_ft_block {
+    const float* weight;          /* [rows, L1 + P] */
+    const float* virtual_weight;  /* [n_virtual, L1 + P] or NULL */
+    int64_t rows;
+    int64_t n_virtual;
+} nnue_ft_block;
+
+int nnue_ft_quantize_table(const float* weight, const float* virtual_weight,
+                           int16_t* q16, int64_t q16_pitch, float* psqt, int64_t N, int64_t n_virtual,
+                           int32_t L1, int32_t P, float scale_main, float scale_psqt,
+                           int32_t* d_stats, void* stream);
+int nnue_ft_fused_fwd_q16(const float* us, const float* them,
+                          const int32_t* white_idx, const int32_t* black_idx,
+                          const int64_t* psqt_idx, const int16_t* q16, int64_t q16_pitch, const float* psqt,
+                          const float* bias_fq, float scale_main, const int32_t* d_stats,
+                          const nnue_ft_block* h_blocks, int32_t n_blocks,
+                          float max_act, float act_quant_scale, float act_quant_eps, float out_scale,
+                          float* l0, float* wpsqt, float* bpsqt, float* saved,
+                          int64_t B, int32_t K, int64_t N, int32_t L1, int32_t P, void* stream);
+
 /* The same backward with the gradient delivered in row slices, for a consumer
  * on another stream (the data-parallel reduce) that starts on the first rows
  * while the later ones are still computed.  h_slices->row_bounds holds

@@ -23,6 +23,7 @@ SOURCES = [
     "ft_sparse.cu",
     "ft_sparse_static.cu",
     "ft_fused.cu",
+    "ft_fused_q16.cu",
     "ft_segment.cu",
     "ft_table.cu",
     "ranger_lite.cu",

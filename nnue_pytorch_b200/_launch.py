@@ -259,6 +259,71 @@ def prepare_table(weight, virtual_weight, l1_size: int, scale_main: float, scale
     return out
 
 
+def quantize_blocks(blocks, l1_size: int, scale_main: float, scale_psqt: float, overflow: torch.Tensor | None = None):
+    """The integer form of the table the forward reads when weights are fake-quantized
+    (`nnue_ft_quantize_table`, one launch per parameter block).  `blocks` is a list of
+    (weight [rows, W], virtual_weight [n_virtual, W] or None) in table order.  Returns
+    (q16 int16 [N, L1], psqt float32 [N, P], stats int32 [2] = entries outside int16, max |k|); a given
+    `overflow` (the stats of an earlier call) is updated instead of a fresh one."""
+    dev = _require_cuda(*[t for b in blocks for t in b if t is not None])
+    W = blocks[0][0].shape[1]
+    P = W - l1_size
+    n_total = sum(w.shape[0] for w, _ in blocks)
+    pitch = l1_size  # rows back to back (a padded pitch was measured: no faster on B200)
+    q16 = torch.empty(n_total, pitch, dtype=torch.int16, device=dev)
+    psqt = torch.empty(n_total, max(P, 1), dtype=torch.float32, device=dev)[:, :P]
+    if overflow is None:
+        overflow = torch.zeros(2, dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    at = 0
+    with torch.cuda.device(dev), _span("quantize_table", dev):
+        for w, v in blocks:
+            assert w.dtype == torch.float32 and w.dim() == 2 and w.is_contiguous() and w.shape[1] == W
+            nv = 0
+            if v is not None:
+                assert v.dtype == torch.float32 and v.is_contiguous() and v.shape[1] == W and w.shape[0] % v.shape[0] == 0
+                nv = v.shape[0]
+            rows = w.shape[0]
+            st = lib.nnue_ft_quantize_table(
+                _ptr(w), _ptr(v), q16.data_ptr() + at * pitch * 2, pitch, psqt.data_ptr() + at * P * 4, rows, nv,
+                l1_size, P, float(scale_main), float(scale_psqt), _ptr(overflow), _stream(dev))
+            _lib.check(st, "nnue_ft_quantize_table")
+            at += rows
+    return q16, psqt, overflow
+
+
+def fused_forward_q16(us, them, white_indices, black_indices, psqt_indices, q16, psqt, bias_fq, overflow, blocks,
+                      scale_main: float, max_ft_activation, l1_size, act_quant_scale: float = 0.0,
+                      act_quant_eps: float = 0.0, out_scale: float = 1.0):
+    """`nnue_ft_fused_fwd_q16`: the fused forward on the tensors `quantize_blocks` made (same outputs
+    and saved tensor as `fused_forward`)."""
+    dev = _require_cuda(us, them, white_indices, black_indices, psqt_indices, q16, bias_fq, overflow)
+    assert us.dtype == torch.float32 and them.dtype == torch.float32
+    assert white_indices.dtype == torch.int32 and black_indices.dtype == torch.int32 and psqt_indices.dtype == torch.int64
+    assert white_indices.shape == black_indices.shape and white_indices.shape[0] == psqt_indices.shape[0]
+    assert us.is_contiguous() and them.is_contiguous() and white_indices.is_contiguous() and black_indices.is_contiguous()
+    assert psqt_indices.is_contiguous() and q16.is_contiguous() and bias_fq.is_contiguous()
+    assert q16.dtype == torch.int16 and q16.shape[1] >= l1_size and bias_fq.dtype == torch.float32
+    B, K = white_indices.shape
+    N = q16.shape[0]
+    P = bias_fq.shape[0] - l1_size
+    arr = (_lib.FtBlock * len(blocks))()
+    for d, (w, v) in zip(arr, blocks):
+        d.weight, d.virtual_weight, d.rows, d.n_virtual = _ptr(w), _ptr(v), w.shape[0], 0 if v is None else v.shape[0]
+    l0 = torch.empty(B, l1_size, dtype=torch.float32, device=dev)
+    wpsqt = torch.empty(B, 1, dtype=torch.float32, device=dev)
+    bpsqt = torch.empty(B, 1, dtype=torch.float32, device=dev)
+    saved = torch.empty(B, 4, l1_size // 2, dtype=torch.float32, device=dev)
+    with torch.cuda.device(dev), _span("fused_fwd", dev):
+        st = _lib.load().nnue_ft_fused_fwd_q16(
+            _ptr(us), _ptr(them), _ptr(white_indices), _ptr(black_indices), _ptr(psqt_indices), _ptr(q16), q16.shape[1],
+            psqt.data_ptr() if P > 0 else None, _ptr(bias_fq), float(scale_main), _ptr(overflow), arr, len(blocks),
+            float(max_ft_activation), float(act_quant_scale), float(act_quant_eps), float(out_scale),
+            _ptr(l0), _ptr(wpsqt), _ptr(bpsqt), _ptr(saved), B, K, N, l1_size, P, _stream(dev))
+    _lib.check(st, "nnue_ft_fused_fwd_q16")
+    return l0, wpsqt, bpsqt, saved
+
+
 def virtual_grad(grad: torch.Tensor, n_virtual: int) -> torch.Tensor:
     dev = _require_cuda(grad)
     grad = grad.contiguous()

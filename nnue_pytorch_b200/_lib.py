@@ -79,6 +79,12 @@ class BwdSlices(C.Structure):
     _fields_ = [("n_slices", C.c_int32), ("row_bounds", C.c_int64 * (MAX_SLICES + 1)), ("events", C.c_void_p * MAX_SLICES)]
 
 
+class FtBlock(C.Structure):
+    """Mirror of `nnue_ft_block`."""
+
+    _fields_ = [("weight", C.c_void_p), ("virtual_weight", C.c_void_p), ("rows", C.c_int64), ("n_virtual", C.c_int64)]
+
+
 class LsWeightScales(C.Structure):
     """Mirror of `nnue_ls_weight_scales`."""
 
@@ -143,6 +149,12 @@ PROTOTYPES = {
          _P, _SZ, _I32, C.POINTER(BwdSlices), _P],
     ),
     "nnue_ft_prepare_table": (C.c_int, [_P, _P, _P, _I64, _I64, _I32, _I32, C.c_float, C.c_float, _P]),
+    "nnue_ft_quantize_table": (C.c_int, [_P, _P, _P, _I64, _P, _I64, _I64, _I32, _I32, C.c_float, C.c_float, _P, _P]),
+    "nnue_ft_fused_fwd_q16": (
+        C.c_int,
+        [_P] * 6 + [_I64, _P, _P, C.c_float, _P, C.POINTER(FtBlock), _I32, C.c_float, C.c_float, C.c_float, C.c_float,
+                    _P, _P, _P, _P, _I64, _I32, _I64, _I32, _I32, _P],
+    ),
     "nnue_ft_virtual_grad": (C.c_int, [_P, _P, _I64, _I64, _I32, _P]),
     "nnue_rangerlite_update": (
         C.c_int,

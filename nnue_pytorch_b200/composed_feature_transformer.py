@@ -15,7 +15,12 @@ import torch
 from torch import nn
 
 from .double_ft_functions import double_feature_transform
-from .fused_ft_functions import FusedDoubleFtFunction, PrepareBiasFunction, PrepareTableFunction
+from .fused_ft_functions import (
+    FusedDoubleFtFunction,
+    PrepareBiasFunction,
+    PrepareTableFunction,
+    QuantizedFusedDoubleFtFunction,
+)
 
 _FAKE_QUANTIZE_EPS = 1e-5  # model/quantize.py:10 of the reference
 
@@ -95,6 +100,21 @@ class ComposedFeatureTransformer(nn.Module):
         bias = torch.cat([b, torch.zeros_like(self.bias[self.l1_size :], dtype=b.dtype)], dim=0)
         return merged, bias
 
+    integer_table = True  # gather an int16 table when weights are fake-quantized (same bits, half the bytes)
+
+    def _integer_table_applies(self, indices: torch.Tensor, fake_quantize_weights: bool) -> bool:
+        """The int16 form of the table is exact when every fake-quantized entry is an integer over a
+        power-of-two scale shared by weights and bias, and a list holds at most 511 rows."""
+        if not (self.integer_table and fake_quantize_weights and self.bias.is_cuda and indices.is_cuda):
+            return False
+        if not all(_fusable_feature(f) for f in self.features) or len(self.features) > 8:
+            return False
+        s = self.quantization.weight_scales_dict
+        scale = float(s["ft_weight"])
+        pow2 = scale > 0 and math.frexp(scale)[0] == 0.5
+        return (pow2 and float(s["ft_bias"]) == scale and indices.shape[1] <= 511 and self.l1_size % 16 == 0
+                and self.num_psqt_buckets % 4 == 0)
+
     @torch.no_grad()
     def coalesce(self) -> None:
         for f in self.features:
@@ -138,6 +158,16 @@ class ComposedFeatureTransformer(nn.Module):
         fake_quantize_weights: bool,
         backend: str = "auto",
     ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+        if backend in ("auto", "fused") and self._integer_table_applies(white_indices, fake_quantize_weights):
+            q = self.quantization
+            params = []
+            for f in self.features:
+                params += [f.weight, getattr(f, "virtual_weight", None)]
+            return QuantizedFusedDoubleFtFunction.apply(
+                us, them, white_indices, black_indices, psqt_indices, self.bias, q.max_ft_activation, self.l1_size,
+                q.config.hidden_quantized_one if fake_quantize_acts else 0.0, _FAKE_QUANTIZE_EPS,
+                q.l0_correction_factor, q.weight_scales_dict["ft_weight"], q.weight_scales_dict["ft_psqt_weight"],
+                *params)
         merged, bias = self.merged_weight_and_bias(fake_quantize_weights)
         if backend in ("auto", "fused") and merged.is_cuda:
             # activation fake quantization and the correction factor ride in the kernel epilogue

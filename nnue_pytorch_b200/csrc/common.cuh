@@ -53,6 +53,7 @@ struct Tuning {
     int seg_chunk = 256;  // entries per warp in the chunked segment gather-sum; 0 = one warp per row
     int bwd_r = 0;        // compiled variant of the chunked gather-sum (see LAUNCH_CHUNKS)
     int fwd_variant = 0;  // compiled variant of the fused forward (see LAUNCH_FWD)
+    int fwd_q16_variant = 0;  // compiled variant of the int16-table forward (see LAUNCH_Q16)
     int overlap_csr = 1;  // 1 = build the CSR on the helper stream, beside the backward prologue
     int ddp_reduce_ctas = 0;  // > 0: grid cap of the peer-load reduce (it runs beside the sliced backward)
 };

@@ -131,6 +131,7 @@ extern "C" int nnue_b200_tune(const char* key, int value) {
     else if (!strcmp(key, "seg_chunk")) t.seg_chunk = value > 0 ? value : 0;
     else if (!strcmp(key, "bwd_r")) t.bwd_r = value;
     else if (!strcmp(key, "fwd_variant")) t.fwd_variant = value;
+    else if (!strcmp(key, "fwd_q16_variant")) t.fwd_q16_variant = value;
     else if (!strcmp(key, "ddp_reduce_ctas")) t.ddp_reduce_ctas = value;
     else if (!strcmp(key, "overlap_csr")) t.overlap_csr = value;
     else {

@@ -70,6 +70,63 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// The same table as integers: k[r, c] = rint((weight + virtual)[r, c] * scale_main) for the L1 columns,
+// psqt[r, j] = fq(.., scale_psqt) for the PSQT columns (fp32, their scale is not a power of two).
+// Neighbouring columns (c, c + 1), c even, are stored as the int32 NUMBER k[c + 1] * 65536 + k[c]: its
+// low half is k[c] in two's complement, its high half k[c + 1] minus one when k[c] is negative, so that
+// 32-bit adds of such words sum both columns (see ft_fused_q16.cu).  A value outside the int16 range is
+// stored saturated and tallied in stats[0] (the reader then takes its fp32 route); stats[1] collects
+// max |k|.  Thread = 8 consecutive columns (two float4 in, one 16-byte store out).
+template <typename IDX>
+__global__ void __launch_bounds__(kThreads)
+    k_quantize_table(const float* __restrict__ weight, const float* __restrict__ virt,
+                     int16_t* __restrict__ q16, int64_t pitch8, float* __restrict__ psqt, int64_t N,
+                     int64_t n_virtual, int W, int L1, int P, float scale_main, float scale_psqt,
+                     int* __restrict__ stats) {
+    const IDX stride = (IDX)gridDim.x * blockDim.x;
+    const IDX t0 = (IDX)blockIdx.x * blockDim.x + threadIdx.x;
+    const IDX L8 = (IDX)(L1 >> 3), P4 = (IDX)(P >> 2);
+    const IDX per_row = L8 + P4;                  // work items per row: 8-column groups, then PSQT float4
+    const IDX total = (IDX)N * per_row, nv = (IDX)n_virtual;
+    const int64_t W4 = W >> 2;
+    const float4* w4 = reinterpret_cast<const float4*>(weight);
+    const float4* v4 = reinterpret_cast<const float4*>(virt);
+    int bad = 0, max_abs = 0;
+    for (IDX i = t0; i < total; i += stride) {
+        const IDX r = i / per_row;
+        const IDX j = i - r * per_row;
+        const float4* wrow = w4 + (int64_t)r * W4;
+        const float4* vrow = virt ? v4 + (int64_t)(r % nv) * W4 : nullptr;
+        if (j < L8) {
+            float4 a = __ldcs(wrow + 2 * j), b = __ldcs(wrow + 2 * j + 1);
+            if (virt) {
+                a = f4_add(a, __ldg(vrow + 2 * j));
+                b = f4_add(b, __ldg(vrow + 2 * j + 1));
+            }
+            const float x[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+            unsigned packed[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                float lo = rintf(__fmul_rn(x[2 * k], scale_main)), hi = rintf(__fmul_rn(x[2 * k + 1], scale_main));
+                if (!(fabsf(lo) <= 32767.f)) { ++bad; lo = fminf(fmaxf(lo, -32767.f), 32767.f); if (lo != lo) lo = 0.f; }
+                if (!(fabsf(hi) <= 32767.f)) { ++bad; hi = fminf(fmaxf(hi, -32767.f), 32767.f); if (hi != hi) hi = 0.f; }
+                packed[k] = (unsigned)((int)hi * 65536 + (int)lo);
+                max_abs = max(max_abs, max(abs((int)lo), abs((int)hi)));
+            }
+            reinterpret_cast<uint4*>(q16)[(int64_t)r * pitch8 + j] = make_uint4(packed[0], packed[1], packed[2], packed[3]);
+        } else {
+            const IDX q = j - L8;
+            float4 x = __ldcs(wrow + 2 * L8 + q);
+            if (virt) x = f4_add(x, __ldg(vrow + 2 * L8 + q));
+            x = make_float4(fq1(x.x, scale_psqt), fq1(x.y, scale_psqt), fq1(x.z, scale_psqt), fq1(x.w, scale_psqt));
+            reinterpret_cast<float4*>(psqt)[(int64_t)r * P4 + q] = x;
+        }
+    }
+    if (bad) atomicAdd(stats, bad);
+    max_abs = __reduce_max_sync(kFullMask, max_abs);
+    if ((threadIdx.x & 31) == 0 && max_abs > 0) atomicMax(stats + 1, max_abs);
+}
+
 // out[v, c] = sum over b of grad[b * n_virtual + v, c], b ascending.
 template <bool VEC>
 __global__ void __launch_bounds__(kThreads)
@@ -152,6 +209,43 @@ extern "C" int nnue_ft_virtual_grad(const float* grad, float* out, int64_t N, in
     const unsigned grid = (unsigned)((work + kThreads - 1) / kThreads);
     if (vec) k_virtual_grad<true><<<grid, kThreads, 0, s>>>(grad, out, N / n_virtual, n_virtual, W);
     else k_virtual_grad<false><<<grid, kThreads, 0, s>>>(grad, out, N / n_virtual, n_virtual, W);
+    NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
+    return NNUE_OK;
+}
+
+extern "C" int nnue_ft_quantize_table(const float* weight, const float* virtual_weight, int16_t* q16,
+                                      int64_t q16_pitch, float* psqt, int64_t N, int64_t n_virtual, int32_t L1,
+                                      int32_t P, float scale_main, float scale_psqt, int32_t* d_overflow,
+                                      void* stream) {
+    NNUE_REQUIRE(N >= 0 && L1 > 0 && P >= 0 && n_virtual >= 0, NNUE_ERR_ARG, "nnue_ft_quantize_table: bad size");
+    NNUE_REQUIRE(L1 % 8 == 0 && P % 4 == 0, NNUE_ERR_UNSUPPORTED,
+                 "nnue_ft_quantize_table: needs L1 %% 8 == 0 and P %% 4 == 0 (L1=%d P=%d)", L1, P);
+    NNUE_REQUIRE(q16_pitch >= L1 && q16_pitch % 8 == 0, NNUE_ERR_ARG,
+                 "nnue_ft_quantize_table: the row pitch (%lld) must be a multiple of 8 not below L1", (long long)q16_pitch);
+    int exp2 = 0;
+    NNUE_REQUIRE(scale_main > 0.f && frexpf(scale_main, &exp2) == 0.5f && scale_psqt > 0.f, NNUE_ERR_UNSUPPORTED,
+                 "nnue_ft_quantize_table: the main scale must be a power of two (got %g)", (double)scale_main);
+    if (N == 0) return NNUE_OK;
+    NNUE_REQUIRE(weight && q16 && d_overflow && (psqt || P == 0), NNUE_ERR_ARG, "nnue_ft_quantize_table: null pointer");
+    NNUE_REQUIRE(!virtual_weight || (n_virtual > 0 && N % n_virtual == 0), NNUE_ERR_ARG,
+                 "nnue_ft_quantize_table: N (%lld) is not a multiple of the factor rows (%lld)", (long long)N,
+                 (long long)n_virtual);
+    NNUE_REQUIRE(aligned16(weight) && aligned16(q16) && aligned16(psqt) && (!virtual_weight || aligned16(virtual_weight)),
+                 NNUE_ERR_ALIGN, "nnue_ft_quantize_table: 16-byte aligned buffers");
+    const int W = L1 + P;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int64_t work = N * (int64_t)(L1 / 8 + P / 4);
+    const unsigned grid = (unsigned)std::min<int64_t>((work + kThreads - 1) / kThreads, (int64_t)sm_count() * 16);
+    const bool narrow = work + (int64_t)grid * kThreads < 0x7fffffffLL;
+    const int64_t nv = n_virtual ? n_virtual : 1;
+    ProfScope prof("k_quantize_table", s);
+    if (narrow)
+        k_quantize_table<unsigned><<<grid, kThreads, 0, s>>>(weight, virtual_weight, q16, q16_pitch / 8, psqt, N, nv, W,
+                                                            L1, P, scale_main, scale_psqt, d_overflow);
+    else
+        k_quantize_table<int64_t><<<grid, kThreads, 0, s>>>(weight, virtual_weight, q16, q16_pitch / 8, psqt, N, nv, W,
+                                                           L1, P, scale_main, scale_psqt, d_overflow);
     NNUE_CUDA_TRY(cudaGetLastError());
     note_launches(1);
     return NNUE_OK;

@@ -10,6 +10,13 @@ plus 768 factor ("virtual") rows that are folded in weight space,
 of 23232 rows (22528 real + 704 factor rows) where factor features are extra
 *indices* of a position, so no merge pass exists.
 
+`FullThreats` and `PP3Wide` mirror the two other blocks of the reference's
+default feature set `Full_Threats+PP_3Wide+HalfKAv2_hm^`
+(model/modules/features/full_threats.py:7-57, pp_3wide.py:7-55,
+features/__init__.py:13-19): plain tables without factor rows, PSQT columns
+zero, weights kept inside the int8 export range by `clip_weights`.
+`full_features.py` builds their index lists.
+
 Any object with the same attributes works with `ComposedFeatureTransformer`,
 including the reference's own feature classes.
 """
@@ -181,7 +188,70 @@ class HalfKav2HmFlat(InputFeature):
         self.zero_virtual_weights()
 
 
-_FEATURES = {"HalfKAv2_hm^": HalfKav2Hm, "HalfKAv2_hm^flat": HalfKav2HmFlat}
+class _PlainTable(InputFeature):
+    """A feature block that is one trainable table: no factor rows, no piece values."""
+
+    FUSED_TABLE = True  # merged table = weight
+    MAX_ACTIVE_FEATURES = 128
+    EXPORT_WEIGHT_DTYPE = torch.int8
+
+    def __init__(self, num_outputs: int):
+        super().__init__()
+        self.num_outputs = num_outputs
+        self.weight = nn.Parameter(torch.empty(self.NUM_INPUTS, num_outputs, dtype=torch.float32))
+        self.reset_parameters()
+
+    def merged_weight(self) -> torch.Tensor:
+        return self.weight
+
+    @torch.no_grad()
+    def coalesce(self) -> None:
+        pass
+
+    @torch.no_grad()
+    def zero_virtual_weights(self) -> None:
+        pass
+
+    @torch.no_grad()
+    def init_weights(self, num_psqt_buckets: int, nnue2score: float) -> None:
+        self.weight[:, self.num_outputs - num_psqt_buckets :] = 0.0
+
+    @torch.no_grad()
+    def get_export_weights(self) -> torch.Tensor:
+        return self.weight.data.clone()
+
+    @torch.no_grad()
+    def load_export_weights(self, export_weight: torch.Tensor) -> None:
+        self.weight.data.copy_(export_weight)
+
+    def clip_weights(self, quantization) -> None:
+        """Keeps every weight inside what the int8 export can hold (+-127 / ft_quantized_one)."""
+        self.weight.data.clamp_(quantization.min_threat_weight, quantization.max_threat_weight)
+
+
+class FullThreats(_PlainTable):
+    """One row per (attacking piece, from, attacked piece, to) relation: 59808 rows."""
+
+    HASH = 0x2E6B9D04
+    FEATURE_NAME = "Full_Threats"
+    INPUT_FEATURE_NAME = "Full_Threats"
+    NUM_INPUTS = 59808
+    NUM_REAL_FEATURES = 59808
+
+
+class PP3Wide(_PlainTable):
+    """One row per pair of pawns on the same or adjacent files: 96 * 95 / 2 = 4560 rows."""
+
+    HASH = 0x86F2B1DD
+    FEATURE_NAME = "PP_3Wide"
+    INPUT_FEATURE_NAME = "PP_3Wide"
+    NUM_INPUTS = 4560
+    NUM_REAL_FEATURES = 4560
+
+
+DEFAULT_FEATURES = "Full_Threats+PP_3Wide+HalfKAv2_hm^"
+_FEATURES = {"HalfKAv2_hm^": HalfKav2Hm, "HalfKAv2_hm^flat": HalfKav2HmFlat, "Full_Threats": FullThreats,
+             "PP_3Wide": PP3Wide}
 
 
 def get_feature_cls(name: str):

@@ -103,3 +103,66 @@ class PrepareBiasFunction(autograd.Function):
     @staticmethod
     def backward(ctx, grad):
         return torch.nn.functional.pad(grad[: ctx.l1], (0, ctx.pad)), None, None
+
+
+class QuantizedFusedDoubleFtFunction(autograd.Function):
+    """The whole feature transformer of one step when weights are fake-quantized at a power-of-two
+    scale: table preparation (factor fold + fake quantization, written as int16), bias fake
+    quantization and the fused operator, as ONE autograd node over the raw parameters.
+
+    Same values, bit for bit, as `PrepareTableFunction` + `PrepareBiasFunction` +
+    `FusedDoubleFtFunction` (every partial sum of the fp32 form is exact, see
+    csrc/ft_fused_q16.cu); half the bytes through the L2.  Backward: the operator's gradient goes
+    straight through both fake quantizations to every block's `weight`, summed over the repeats to
+    its `virtual_weight`, and to the L1 part of the bias.
+
+    apply(us, them, white_indices, black_indices, psqt_indices, bias, max_ft_activation, l1_size,
+          act_quant_scale, act_quant_eps, out_scale, scale_main, scale_psqt, w0, v0, w1, v1, ...)
+    with (w_i, v_i) the parameter blocks in table order, v_i None for a block without factor rows."""
+
+    @staticmethod
+    def forward(ctx, us, them, white_indices, black_indices, psqt_indices, bias, max_ft_activation, l1_size,
+                act_quant_scale, act_quant_eps, out_scale, scale_main, scale_psqt, *params):
+        l1 = int(l1_size)
+        blocks = [(params[i].detach(), None if params[i + 1] is None else params[i + 1].detach())
+                  for i in range(0, len(params), 2)]
+        q16, psqt, overflow = _launch.quantize_blocks(blocks, l1, scale_main, scale_psqt)
+        # a bias outside the int16 range also sends the forward down its fp32 route
+        _launch.quantize_blocks([(bias.detach().reshape(1, -1), None)], l1, scale_main, scale_psqt, overflow=overflow)
+        bias_fq = torch.zeros_like(bias)
+        _launch.prepare_table(bias.detach()[:l1].reshape(1, l1), None, l1, scale_main, 1.0, out=bias_fq, span="prepare_bias")
+        l0, wpsqt, bpsqt, saved = _launch.fused_forward_q16(
+            us, them, white_indices, black_indices, psqt_indices, q16, psqt, bias_fq, overflow, blocks, scale_main,
+            max_ft_activation, l1, act_quant_scale, act_quant_eps, out_scale)
+        ctx.save_for_backward(us, them, white_indices, black_indices, psqt_indices, saved)
+        ctx.max_ft_activation, ctx.l1_size, ctx.out_scale = float(max_ft_activation), l1, float(out_scale)
+        ctx.rows = [w.shape[0] for w, _ in blocks]
+        ctx.n_virtual = [0 if v is None else v.shape[0] for _, v in blocks]
+        ctx.num_outputs = bias.shape[0]
+        # a single block owned by a data-parallel exchange: its gradient lands in the exchange's buffer
+        ctx.exchange = _launch.exchange_of(params[0]) if len(blocks) == 1 else None
+        return l0, wpsqt, bpsqt
+
+    @staticmethod
+    def backward(ctx, grad_l0, grad_wpsqt, grad_bpsqt):
+        us, them, white_indices, black_indices, psqt_indices, saved = ctx.saved_tensors
+        ex = ctx.exchange
+        n_total = sum(ctx.rows)
+        grad_table, grad_bias = _launch.fused_backward(
+            us, them, white_indices, black_indices, psqt_indices, ctx.max_ft_activation, ctx.l1_size,
+            n_total, ctx.num_outputs, grad_l0, grad_wpsqt, grad_bpsqt, saved, out_scale=ctx.out_scale,
+            sink=None if ex is None else ex.grad_view, slices=None if ex is None else ex.slice_spec(),
+        )
+        grads, at = [], 0
+        for i, (rows, nv) in enumerate(zip(ctx.rows, ctx.n_virtual)):
+            gw = grad_table if len(ctx.rows) == 1 else grad_table[at : at + rows]
+            at += rows
+            gv = None
+            if nv and ctx.needs_input_grad[13 + 2 * i + 1]:
+                gv = _launch.virtual_grad(gw, nv)
+                if ex is not None:
+                    ex.note_local_reader()  # the reduce overwrites the buffer: it must wait for the kernel above
+            grads += [None if ex is not None else gw, gv]
+        pad = ctx.num_outputs - ctx.l1_size
+        grad_bias = torch.nn.functional.pad(grad_bias[: ctx.l1_size], (0, pad))  # the PSQT part of the bias never trains
+        return (None, None, None, None, None, grad_bias, None, None, None, None, None, None, None, *grads)

@@ -44,7 +44,12 @@ def loss_params_struct(lp, lam: float, net_scale: float) -> _lib.LossParams:
 def sf_loss_fused(y, wpsqt, bpsqt, us, score, outcome, lp, lam: float, net_scale: float, want_grads: bool = True):
     """Returns (loss [] , d_y, d_wpsqt, d_bpsqt); the gradients are None when
     not wanted, and the PSQT ones when wpsqt is None.  All inputs float32 CUDA
-    tensors of B elements."""
+    tensors of B elements.  `lam` is one number for the whole batch: the reference's
+    `LambdaController` (model/lambda_utils.py:59-81) hands out a per-batch or per-sample TENSOR
+    when lambda jitter is configured; such a lambda goes through the elementwise form
+    (`model.sf_loss`), which broadcasts it."""
+    if torch.is_tensor(lam):
+        raise TypeError("sf_loss_fused takes a scalar lambda; use model.sf_loss for a per-sample lambda tensor")
     if not y.is_cuda:
         raise _lib.NnueB200Error("sf_loss_fused runs on the GPU only; pass CUDA tensors")
     dev, B = y.device, y.numel()

@@ -237,7 +237,8 @@ class TrainStep:
         optimizer's parameter groups."""
         self.model = model
         self.clip, self.lam = clip, lam
-        self.fused_loss = fused_loss  # False: the loss as elementwise torch ops (`sf_loss`) under autograd
+        # False, or a tensor-valued `lam` (per-sample lambda jitter): the loss as elementwise torch ops (`sf_loss`)
+        self.fused_loss = fused_loss
         self.loss_params = loss_params or LossParams()
         self.grad_hook = grad_hook
         self.table_exchange = table_exchange
@@ -281,7 +282,7 @@ class TrainStep:
     def __call__(self, batch):
         from . import _launch
 
-        if self.fused_loss and batch[0].is_cuda:
+        if self.fused_loss and batch[0].is_cuda and not torch.is_tensor(self.lam):
             loss = self._loss_and_backward(batch)
         else:
             loss = self.loss(batch)

@@ -1,7 +1,7 @@
 """Child process of tests/test_overlay.py (a separate interpreter, because the
 overlay changes what `import model` means for the whole process).
 
-    python tests/_overlay_child.py reference OUT.pt        the reference as it is, on CPU (its torch path)
+    python tests/_overlay_child.py reference OUT.pt [FEATURES]   the reference as it is, on CPU (its torch path)
     python tests/_overlay_child.py keys OUT.pt             overlay installed, CPU only: names and structure
     python tests/_overlay_child.py overlay IN.pt OUT.pt [module]   overlay installed, on cuda:0, model compiled
 """
@@ -19,20 +19,29 @@ sys.path.insert(0, ROOT)
 L1, B, SEED = 256, 192, 5
 
 
+FEATURES = "HalfKAv2_hm^"
+
+
 def _batch():
-    from nnue_pytorch_b200 import positions
+    """The tuple `SparseBatch.get_tensors` returns, for generated positions in the layout FEATURES needs."""
+    from nnue_pytorch_b200 import full_features, positions
 
     b = positions.generate_batch(B, 77, layout="native")
+    if FEATURES != "HalfKAv2_hm^":
+        white, black = full_features.full_feature_lists(full_features.boards_of(positions.generate_positions(B, 77)))
+        b.white, b.black = white, black
     return tuple(torch.from_numpy(np.ascontiguousarray(a)) for a in b.as_tuple())
 
 
 def _build(model_pkg):
-    cfg = model_pkg.NNUELightningConfig(features="HalfKAv2_hm^", model_config=model_pkg.ModelConfig(L1=L1, L2=32, L3=32))
+    cfg = model_pkg.NNUELightningConfig(features=FEATURES, model_config=model_pkg.ModelConfig(L1=L1, L2=32, L3=32))
     torch.manual_seed(SEED)
     nnue = model_pkg.NNUE(cfg)
     with torch.no_grad():
-        nnue.model.input.features[0].weight[:, :L1].normal_(0.0, 0.05)
-        nnue.model.input.features[0].virtual_weight[:, :L1].normal_(0.0, 0.02)
+        for f in nnue.model.input.features:
+            f.weight[:, :L1].normal_(0.0, 0.05)
+            if hasattr(f, "virtual_weight"):
+                f.virtual_weight[:, :L1].normal_(0.0, 0.02)
     return nnue
 
 
@@ -41,7 +50,10 @@ def _grads(nnue):
 
 
 def main():
+    global FEATURES
     mode = sys.argv[1]
+    if mode == "reference" and len(sys.argv) > 3:
+        FEATURES = sys.argv[3]
     from oracle import ref_runner, ref_shims
 
     ref_shims.install()
@@ -53,7 +65,8 @@ def main():
         nnue.train()
         out = nnue.train_step(_batch(), 0, 0)
         out["loss"].backward()
-        torch.save({"state": nnue.model.state_dict(), "loss": float(out["loss"]), "grads": _grads(nnue)}, sys.argv[2])
+        torch.save({"state": nnue.model.state_dict(), "loss": float(out["loss"]), "grads": _grads(nnue),
+                    "batch": _batch()}, sys.argv[2])
         return
     from nnue_pytorch_b200 import overlay
 

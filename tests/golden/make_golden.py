@@ -241,6 +241,32 @@ def main(ref_root: str):
             rec[f"tail_{comp}"] = np.frombuffer(data[-1024:], dtype=np.uint8)
     np.savez_compressed(os.path.join(HERE, "nnue_file.npz"), **rec)
 
+    # 8. index lists of the default feature set on real positions: the reference loader's own extractors
+    #    (compiled here from its sources, where they lie) over every 23rd entry of its sample binpack
+    import subprocess
+    import tempfile
+
+    binpack = os.path.join(ref_root, ".pgo", "small.binpack")
+    with tempfile.TemporaryDirectory() as tmp:
+        exe = os.path.join(tmp, "dump_features")
+        subprocess.run(["g++", "-std=c++20", "-O1", "-I" + os.path.join(ref_root, "data_loader", "cpp"),
+                        os.path.join(HERE, "dump_features.cpp"), "-o", exe, "-lpthread"], check=True)
+        text = subprocess.run([exe, binpack, "300", "23"], check=True, capture_output=True, text=True).stdout
+    rows = [list(map(int, ln.split())) for ln in text.strip().splitlines()]
+    n = len(rows)
+    boards = np.zeros((n, 64), np.int8)
+    stm = np.zeros(n, np.int8)
+    lists = {name: np.full((n, 2, k), -1, np.int32) for name, k in (("halfka", 32), ("threats", 128), ("pawn_pairs", 128))}
+    for i, v in enumerate(rows):
+        boards[i], stm[i], at = v[:64], v[64], 65
+        for side in range(2):
+            for name in ("halfka", "threats", "pawn_pairs"):
+                k = v[at]
+                lists[name][i, side, :k] = v[at + 1 : at + 1 + k]
+                at += 1 + k
+        assert at == len(v)
+    np.savez_compressed(os.path.join(HERE, "full_features.npz"), boards=boards, black_to_move=stm, **lists)
+
     _ = QuantizationConfig
     print("golden fixtures written to", HERE)
 

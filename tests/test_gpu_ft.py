@@ -562,3 +562,101 @@ def test_row_named_twice_by_many_positions(dev):
     for k in ("l0", "grad_weight", "grad_bias"):
         _check(r[k], r32[k], r64[k], f"dup.{k}")
     _launch.device_status(dev)
+
+
+def _transformer_both_ways(dev, blocks, bias, c, l1, act=(128.0, 1e-5, 1.0)):
+    """The feature transformer of one step through the int16 table (one autograd node over the raw
+    parameters) and through the fp32 table (table preparation + bias preparation + operator);
+    returns both result sets: outputs and the gradients of every parameter."""
+    from nnue_pytorch_b200.fused_ft_functions import (FusedDoubleFtFunction, PrepareBiasFunction, PrepareTableFunction,
+                                                      QuantizedFusedDoubleFtFunction)
+
+    args = tuple(c[k].to(dev) for k in ("us", "them", "white", "black", "psqt"))
+    res = []
+    for integer in (True, False):
+        ps = [(w.clone().to(dev).requires_grad_(True), None if v is None else v.clone().to(dev).requires_grad_(True))
+              for w, v in blocks]
+        bd = bias.clone().to(dev).requires_grad_(True)
+        if integer:
+            flat = [t_ for pair in ps for t_ in pair]
+            l0, wp, bp = QuantizedFusedDoubleFtFunction.apply(*args, bd, c["max_act"], l1, *act, 256.0, 9600.0, *flat)
+        else:
+            tables = [PrepareTableFunction.apply(w, v, l1, 256.0, 9600.0) for w, v in ps]
+            table = tables[0] if len(tables) == 1 else torch.cat(tables, dim=0)
+            l0, wp, bp = FusedDoubleFtFunction.apply(*args, table, PrepareBiasFunction.apply(bd, l1, 256.0), c["max_act"],
+                                                     l1, *act)
+        torch.autograd.backward([l0, wp, bp], [c["grad_l0"].to(dev), c["grad_wpsqt"].to(dev), c["grad_bpsqt"].to(dev)])
+        out = {"l0": l0.detach(), "wpsqt": wp.detach(), "bpsqt": bp.detach(), "bias.grad": bd.grad}
+        for i, (w, v) in enumerate(ps):
+            out[f"w{i}.grad"] = w.grad
+            if v is not None:
+                out[f"v{i}.grad"] = v.grad
+        res.append(out)
+    return res
+
+
+Q16_CASES = [
+    # B, blocks as (rows, factor rows or 0), K, l1
+    (67, [(500, 0)], 64, 512),
+    (40, [(768 * 4, 768)], 33, 1024),              # factor rows folded in weight space
+    (24, [(200, 0)], 70, 3072),                    # headline width, K > 64
+    (48, [(1200, 0), (96, 0), (768 * 2, 768)], 288, 256),  # three feature blocks, the default set's list length
+    (9, [(64, 0)], 5, 16),                         # one 16-byte group per half
+    (1, [(64, 32)], 1, 32),
+]
+
+
+@pytest.mark.parametrize("case", Q16_CASES, ids=[f"B{c[0]}-K{c[2]}-L{c[3]}-{len(c[1])}blk" for c in Q16_CASES])
+def test_integer_table_forward_has_the_bits_of_the_fp32_forward(dev, case):
+    """With fake-quantized weights the forward gathers an int16 table and sums in int32; nothing
+    of the fp32 sum is ever rounded, so outputs (and, the backward being shared, gradients) are
+    identical bit for bit; an oracle comparison of the same outputs rides along."""
+    from oracle import ft_oracle
+
+    B, blocks_spec, K, l1 = case
+    P = 8
+    n_total = sum(r for r, _ in blocks_spec)
+    c = _random_case(B, n_total, K, l1, P, seed=l1 + B, wscale=0.05)
+    gen = torch.Generator().manual_seed(5)
+    blocks = [(torch.randn(r, l1 + P, generator=gen) * 0.2, torch.randn(nv, l1 + P, generator=gen) * 0.1 if nv else None)
+              for r, nv in blocks_spec]
+    bias = torch.randn(l1 + P, generator=gen) * 0.3
+    a, b = _transformer_both_ways(dev, blocks, bias, c, l1)
+    assert a.keys() == b.keys()
+    for k in a:
+        assert torch.equal(a[k], b[k]), k
+    # and against the oracle's restatement of the module (fold, two fake quantizations, operator, activation
+    # fake quantization)
+    fq = lambda x, s: x.mul(s).round().div(s)  # noqa: E731
+    merged = torch.cat([w if v is None else w + v.repeat(w.shape[0] // v.shape[0], 1) for w, v in blocks])
+    table = torch.cat([fq(merged[:, :l1], 256.0), fq(merged[:, l1:], 9600.0)], dim=1)
+    bq = torch.cat([fq(bias[:l1], 256.0), torch.zeros(P)])
+    l0, wp, bp = ft_oracle.double_feature_transform(c["us"], c["them"], c["white"], c["black"], c["psqt"], table, bq,
+                                                    c["max_act"], l1)
+    l0 = l0.mul(128.0).add(1e-5).floor().div(128.0)
+    on_step = ((l0 - a["l0"].cpu()).abs() > 1e-6).float().mean()
+    assert float(on_step) <= 2e-3  # floor() flips where an fp32 product lands within rounding of a step
+    assert max_rel_err(a["wpsqt"].cpu(), wp) <= TOL and max_rel_err(a["bpsqt"].cpu(), bp) <= TOL
+
+
+def test_integer_table_falls_back_when_a_weight_leaves_the_int16_range(dev):
+    """An entry with |round(w * 256)| > 32767 (or such a bias) cannot live in the int16 table.  The
+    emitting kernel tallies it on the device, and the forward then gathers the fp32 parameters with
+    the fake quantization applied per element: same bits as the fp32 table, no host round trip."""
+    B, K, l1, P = 50, 40, 256, 8
+    c = _random_case(B, 600, K, l1, P, seed=3, wscale=0.05)
+    gen = torch.Generator().manual_seed(6)
+    for poke in ("weight", "factor", "bias"):
+        w = torch.randn(600, l1 + P, generator=gen) * 0.2
+        v = torch.randn(100, l1 + P, generator=gen) * 0.1
+        bias = torch.randn(l1 + P, generator=gen) * 0.3
+        if poke == "weight":
+            w[17, 5] = 200.0          # k = 51200
+            w[300, 250] = -129.5
+        elif poke == "factor":
+            v[3, 100] = 150.0
+        else:
+            bias[7] = -400.0
+        a, b = _transformer_both_ways(dev, [(w, v)], bias, c, l1)
+        for k in a:
+            assert torch.equal(a[k], b[k]), (poke, k)

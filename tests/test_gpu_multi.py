@@ -31,19 +31,50 @@ def _worker(rank, world, port, out_dir):
         from nnue_pytorch_b200.ddp import ShardedTableExchange, make_grad_hook
         from nnue_pytorch_b200.model import ModelConfig, NNUEModel, TrainStep
 
-        def build():
+        def rel(a, b):
+            return float((a - b).abs().max()) / max(float(b.abs().max()), 1e-30)
+
+        def build(feature="HalfKAv2_hm^flat"):
             torch.manual_seed(0)
-            m = NNUEModel("HalfKAv2_hm^flat", ModelConfig(L1=128, L2=32, L3=32))
+            m = NNUEModel(feature, ModelConfig(L1=128, L2=32, L3=32))
             with torch.no_grad():
                 m.input.features[0].weight[:, :128].normal_(0, 0.05)
                 m.layer_stacks.l1.linear.weight.normal_(0, 0.05)
             return m.to(dev)
 
-        batches = []
-        for i in range(6):
-            b = positions.generate_batch(256, 50 + 10 * i + rank, layout="baseline")
-            batches.append(tuple(torch.from_numpy(a).to(dev) for a in b.as_tuple()))
+        def make_batches(layout):
+            out = []
+            for i in range(6):
+                b = positions.generate_batch(256, 50 + 10 * i + rank, layout=layout)
+                out.append(tuple(torch.from_numpy(a).to(dev) for a in b.as_tuple()))
+            return out
 
+        # the reference's own table layout: factor rows are a separate parameter folded in weight space, so the
+        # backward ALSO reads the table's gradient buffer (the bucket sum for the factor rows) while the sliced
+        # exchange is already reducing it on its own stream
+        native_batches = make_batches("native")
+        nref = build("HalfKAv2_hm^")
+        nstep = TrainStep(nref, clip=2.0, grad_hook=make_grad_hook(nref, world, average=False), grad_prescale=1.0 / world)
+        nlosses = [float(nstep(b)) for b in native_batches]
+
+        def run_native(slices):
+            fused = build("HalfKAv2_hm^")
+            f0 = fused.input.features[0]
+            ex = ShardedTableExchange(f0.weight, slices=slices)
+            step = TrainStep(fused, clip=2.0, grad_hook=make_grad_hook(fused, world, average=False, skip=[f0.weight]),
+                             grad_prescale=1.0 / world, table_exchange=ex)
+            losses = [float(step(b)) for b in native_batches]
+            ex.uninstall()
+            _launch.device_status(dev)
+            return {
+                "loss": max(abs(a - b) / abs(b) for a, b in zip(losses, nlosses)),
+                "table": rel(f0.weight.detach(), nref.input.features[0].weight.detach()),
+                "small": max(rel(p.detach(), q.detach()) for (n, p), (_, q) in
+                             zip(fused.named_parameters(), nref.named_parameters()) if n != "input.features.0.weight"),
+                "state": 0.0, "step": ex.step, "ranks_agree": True,
+            }
+
+        batches = make_batches("baseline")
         ref = build()
         step_ref = TrainStep(ref, clip=2.0, grad_hook=make_grad_hook(ref, world, average=False),
                              grad_prescale=1.0 / world)
@@ -51,9 +82,6 @@ def _worker(rank, world, port, out_dir):
         ref_table = ref.input.features[0].weight.detach().clone()
         ref_state = {k: v.clone() for k, v in step_ref.optimizer.state[ref.input.features[0].weight].items()
                      if torch.is_tensor(v)}
-
-        def rel(a, b):
-            return float((a - b).abs().max()) / max(float(b.abs().max()), 1e-30)
 
         def run(slices):
             fused = build()
@@ -65,6 +93,12 @@ def _worker(rank, world, port, out_dir):
             ex.uninstall()
             _launch.device_status(dev)
             sd = ex.state_dict()
+            # the checkpoint round trip: what state_dict gathered, load_state_dict scatters back to the same shares
+            before = [t_.clone() for t_ in (ex.grad_ma, ex.variance_ma, ex.neg_grad_ma, ex.slow)]
+            for t_ in (ex.grad_ma, ex.variance_ma, ex.neg_grad_ma, ex.slow):
+                t_.fill_(float("nan"))
+            ex.load_state_dict({k: (v.cpu() if torch.is_tensor(v) else v) for k, v in sd.items()})
+            assert all(torch.equal(a, b) for a, b in zip(before, (ex.grad_ma, ex.variance_ma, ex.neg_grad_ma, ex.slow)))
             rep = {
                 "loss": max(abs(a - b) / abs(b) for a, b in zip(losses, losses_ref)),
                 "table": rel(table.detach(), ref_table),
@@ -85,6 +119,8 @@ def _worker(rank, world, port, out_dir):
             "one_slice": run(None),
             "two_slices": run([0, n_rows - 704, n_rows]),           # factor rows last, reduce overlapped
             "four_slices": run([0, 9001, 9001, n_rows - 704, n_rows]),  # an empty slice and ragged shares
+            "native_one_slice": run_native(None),
+            "native_two_slices": run_native([0, 12288, 24576]),
         }
         torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
     finally:

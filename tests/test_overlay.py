@@ -69,3 +69,40 @@ def test_compiled_reference_model_trains_on_the_overlay(tmp_path, variant):
         scale = max(float(g_ref.abs().max()), 1e-30)
         err = float((got["grads"][name] - g_ref).abs().max()) / scale
         assert err <= 1e-5, (name, err)
+
+
+@needs_ref
+@pytest.mark.gpu
+def test_default_feature_set_matches_the_reference_module(tmp_path):
+    """`Full_Threats+PP_3Wide+HalfKAv2_hm^` (88944 rows, lists of up to 288): this package's model on the GPU
+    (three feature blocks quantized into one int16 table, fused operator, fused layer stacks) against the
+    reference's own model with the same parameters on CPU through its torch path: loss and the gradient of
+    every parameter, the factor rows of the HalfKA block included."""
+    if not torch.cuda.is_available():
+        pytest.fail("GPU tests need a CUDA device")
+    from nnue_pytorch_b200.features import DEFAULT_FEATURES
+    from nnue_pytorch_b200.model import LossParams, ModelConfig, NNUEModel, sf_loss
+
+    ref = tmp_path / "ref.pt"
+    _child("reference", ref, DEFAULT_FEATURES)
+    want = torch.load(ref)
+    dev = torch.device("cuda:0")
+    m = NNUEModel(DEFAULT_FEATURES, ModelConfig(L1=256, L2=32, L3=32))
+    assert m.input.NUM_INPUTS == 88944 and m.input.MAX_ACTIVE_FEATURES == 288
+    m.load_state_dict(want["state"])
+    m.to(dev)
+    us, them, white, black, outcome, score, pc = (x.to(dev) for x in want["batch"])
+    assert white.shape[1] == 288
+    for integer_table in (True, False):
+        m.input.integer_table = integer_table
+        m.zero_grad(set_to_none=True)
+        y = m(us, them, white, black, pc, True, True)
+        loss = sf_loss(y * 600.0, score, outcome, LossParams(), 1.0)
+        loss.backward()
+        assert abs(float(loss) - want["loss"]) <= 1e-5 * abs(want["loss"]), (integer_table, float(loss), want["loss"])
+        got = {n: p.grad.detach().cpu() for n, p in m.named_parameters() if p.grad is not None}
+        assert set(got) == set(want["grads"])
+        for name, g_ref in want["grads"].items():
+            scale = max(float(g_ref.abs().max()), 1e-30)
+            err = float((got[name] - g_ref).abs().max()) / scale
+            assert err <= 1e-5, (integer_table, name, err)
