@@ -143,7 +143,9 @@ int nnue_ft_sparse_bwd(const int32_t* idx, const float* grad_out,
  *   - shapes whose scratch need (nnue_ft_sparse_bwd_workspace_bytes) exceeds
  *     the array are refused with NNUE_ERR_WORKSPACE and a message;
  *   - the first call on each device looks up the array's address
- *     (cudaGetSymbolAddress); make that first call before any stream capture
+ *     (cudaGetSymbolAddress; with the CUDA runtime's lazy module loading this is
+ *     also when the array's 32 MiB appear in device memory, the only time a
+ *     call changes the amount of free memory); make that first call before any stream capture
  *     begins, and from one host thread (the per-device address cache is
  *     filled without a lock; concurrent first calls would only repeat the
  *     look-up);
@@ -224,13 +226,15 @@ int nnue_ft_virtual_grad(const float* grad, float* out, int64_t N,
  * model/quantize.py:58-73).  nnue_ft_quantize_table writes that table as
  *   q16  int16 [N, L1]   k = round_half_even((weight + virtual_weight[r % n_virtual]) * scale_main), columns
  *                        (c, c + 1), c even, stored together as the int32 number k[c + 1] * 65536 + k[c];
- *                        rows q16_pitch elements apart (a multiple of 8, >= L1)
+ *                        rows q16_pitch elements apart (a multiple of 8, >= L1).  The forward wants ONE MORE
+ *                        row behind the table, row N, all zeros (the caller clears it): padding and
+ *                        out-of-range list entries read it, which keeps the gather loop free of branches
  *   psqt float [N, P]    the PSQT columns, fake-quantized at scale_psqt as nnue_ft_prepare_table does
  * and updates d_stats (two device int32 the caller zeroes before the first block of a table):
  * d_stats[0] += entries with |k| > 32767 (stored saturated), d_stats[1] = max(d_stats[1], max |k|).
  * nnue_ft_fused_fwd_q16 is nnue_ft_fused_fwd on that table: integer sums of the k (column pairs summed
  * as one 32-bit number and split every 32767 / d_stats[1] rows), one multiplication by 1 / scale_main,
- * then the same epilogue.  The results are bit for bit those of nnue_ft_fused_fwd on the table
+ * then the same epilogue (a table with d_stats[1] > 4095, weights above 16.0, also takes the fp32 route).  The results are bit for bit those of nnue_ft_fused_fwd on the table
  * nnue_ft_prepare_table makes from the same parameters: with |k| <= 32767 and K <= 511 no partial sum of the
  * fp32 form is ever rounded.  `bias_fq` is the bias as that forward takes it (fp32 [L1 + P], its L1 part
  * fake-quantized at scale_main; quantize it into the same d_stats as a one-row table so that its range
@@ -332,6 +336,26 @@ int nnue_rangerlite_update(float* p, const float* grad, float* grad_ma,
                            uint8_t* row_active, const float* d_grad_scale,
                            int64_t rows, int64_t width,
                            const nnue_ranger_hparams* h_hp, void* stream);
+
+/* The same update that also leaves the new parameter values as the integer table of
+ * nnue_ft_quantize_table (q16 with `rows` rows + the caller's zero row, psqt, d_stats: zeroed by this call,
+ * then the overflow count and max |k| of ALL rows, updated or not), for a [rows, L1 + P] table without
+ * factor rows.  The next forward then needs no pass of its own over the table. */
+typedef struct nnue_table_emit {
+    int16_t* q16;
+    int64_t q16_pitch;
+    float* psqt;
+    int32_t* d_stats;
+    int32_t L1, P;
+    float scale_main, scale_psqt;
+} nnue_table_emit;
+
+int nnue_rangerlite_update_emit(float* p, const float* grad, float* grad_ma,
+                                float* neg_grad_ma, float* variance_ma, float* slow,
+                                uint8_t* row_active, const float* d_grad_scale,
+                                int64_t rows, int64_t width,
+                                const nnue_ranger_hparams* h_hp, const nnue_table_emit* h_emit,
+                                void* stream);
 
 /* Standalone lookahead merge, model/optimizers/ranger_lite.py:746-768. */
 int nnue_lookahead_merge(float* p, float* slow, int64_t n, float alpha,

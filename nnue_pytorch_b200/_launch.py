@@ -259,6 +259,13 @@ def prepare_table(weight, virtual_weight, l1_size: int, scale_main: float, scale
     return out
 
 
+def quantize_bias_stats(bias: torch.Tensor, l1_size: int, scale_main: float, scale_psqt: float, stats: torch.Tensor) -> None:
+    """Adds the bias to the range statistics of a table (a bias outside the int16 range also sends the
+    forward down its fp32 route): the bias goes through `nnue_ft_quantize_table` as a one-row table whose
+    integer output is dropped."""
+    quantize_blocks([(bias.detach().reshape(1, -1), None)], l1_size, scale_main, scale_psqt, overflow=stats)
+
+
 def quantize_blocks(blocks, l1_size: int, scale_main: float, scale_psqt: float, overflow: torch.Tensor | None = None):
     """The integer form of the table the forward reads when weights are fake-quantized
     (`nnue_ft_quantize_table`, one launch per parameter block).  `blocks` is a list of
@@ -270,7 +277,8 @@ def quantize_blocks(blocks, l1_size: int, scale_main: float, scale_psqt: float, 
     P = W - l1_size
     n_total = sum(w.shape[0] for w, _ in blocks)
     pitch = l1_size  # rows back to back (a padded pitch was measured: no faster on B200)
-    q16 = torch.empty(n_total, pitch, dtype=torch.int16, device=dev)
+    q16 = torch.empty(n_total + 1, pitch, dtype=torch.int16, device=dev)
+    q16[n_total].zero_()  # the all-zero row that padding and out-of-range list entries read
     psqt = torch.empty(n_total, max(P, 1), dtype=torch.float32, device=dev)[:, :P]
     if overflow is None:
         overflow = torch.zeros(2, dtype=torch.int32, device=dev)
@@ -305,7 +313,7 @@ def fused_forward_q16(us, them, white_indices, black_indices, psqt_indices, q16,
     assert psqt_indices.is_contiguous() and q16.is_contiguous() and bias_fq.is_contiguous()
     assert q16.dtype == torch.int16 and q16.shape[1] >= l1_size and bias_fq.dtype == torch.float32
     B, K = white_indices.shape
-    N = q16.shape[0]
+    N = q16.shape[0] - 1  # the last row is the all-zero row
     P = bias_fq.shape[0] - l1_size
     arr = (_lib.FtBlock * len(blocks))()
     for d, (w, v) in zip(arr, blocks):
@@ -373,7 +381,53 @@ def hparams_struct(**kw) -> _lib.RangerHParams:
     return hp
 
 
-def ranger_update(p, grad, grad_ma, neg_grad_ma, variance_ma, slow, row_active, grad_scale, hp) -> None:
+class QuantTableCache:
+    """The integer table of ONE parameter block without factor rows, kept between steps.
+
+    The forward gathers `q16` / `psqt` (see `quantize_blocks`); writing them costs a pass over the
+    whole table.  When the optimizer is this package's RangerLite, its update kernel writes the new
+    table while it has the new weights in registers, and the forward finds the cache fresh.  Fresh
+    means: made from this very storage (`data_ptr`) at this very `_version` with the same scales.
+    Any in-place change through torch (clipping, `copy_`, loading a state dict) moves `_version`,
+    a swap of `.data` moves the pointer, and either makes the next forward quantize from scratch.
+    Code that writes the parameter through raw pointers must call `mark` (after re-emitting) or
+    `invalidate`."""
+
+    def __init__(self):
+        self.q16 = self.psqt = self.stats = None
+        self.key = None
+
+    @staticmethod
+    def _key(w, l1, scale_main, scale_psqt):
+        return (w.data_ptr(), w._version, tuple(w.shape), int(l1), float(scale_main), float(scale_psqt))
+
+    def fresh(self, w, l1, scale_main, scale_psqt) -> bool:
+        return self.q16 is not None and self.key == self._key(w, l1, scale_main, scale_psqt)
+
+    def store(self, w, l1, scale_main, scale_psqt, q16, psqt, stats) -> None:
+        self.q16, self.psqt, self.stats = q16, psqt, stats
+        self.key = self._key(w, l1, scale_main, scale_psqt)
+
+    def invalidate(self) -> None:
+        self.key = None
+
+    def emit_struct(self, w):
+        """`nnue_table_emit` for an optimizer update of `w`, or None when the cache does not describe
+        the tensor as it is now."""
+        if self.q16 is None or self.key is None or self.key[:3] != (w.data_ptr(), w._version, tuple(w.shape)):
+            return None
+        e = _lib.TableEmit()
+        e.q16, e.q16_pitch, e.psqt, e.d_stats = self.q16.data_ptr(), self.q16.shape[1], self.psqt.data_ptr(), self.stats.data_ptr()
+        e.L1, e.P, e.scale_main, e.scale_psqt = self.key[3], w.shape[1] - self.key[3], self.key[4], self.key[5]
+        return e
+
+    def mark(self, w) -> None:
+        """The buffers now hold the table of `w` as it is (an emitting update has just run)."""
+        self.key = (w.data_ptr(), w._version, tuple(w.shape)) + self.key[3:]
+
+
+def ranger_update(p, grad, grad_ma, neg_grad_ma, variance_ma, slow, row_active, grad_scale, hp, emit=None) -> None:
+    """`emit`: a `_lib.TableEmit` to have the kernel also write the integer table of the new weights."""
     dev = _require_cuda(p, grad, grad_ma, variance_ma)
     for t in (p, grad, grad_ma, neg_grad_ma, variance_ma, slow):
         if t is not None:
@@ -384,11 +438,12 @@ def ranger_update(p, grad, grad_ma, neg_grad_ma, variance_ma, slow, row_active, 
     else:
         rows, width = 1, p.numel()
     with torch.cuda.device(dev), _span("ranger_table" if row_active is not None or p.numel() > (1 << 22) else "ranger_small", dev):
-        st = _lib.load().nnue_rangerlite_update(
+        st = _lib.load().nnue_rangerlite_update_emit(
             _ptr(p), _ptr(grad), _ptr(grad_ma), _ptr(neg_grad_ma), _ptr(variance_ma), _ptr(slow),
-            _ptr(row_active), _ptr(grad_scale), rows, width, C.byref(hp), _stream(dev),
+            _ptr(row_active), _ptr(grad_scale), rows, width, C.byref(hp),
+            C.byref(emit) if emit is not None else None, _stream(dev),
         )
-    _lib.check(st, "nnue_rangerlite_update")
+    _lib.check(st, "nnue_rangerlite_update_emit")
 
 
 def ranger_update_multi(items, grad_scale) -> None:

@@ -85,6 +85,13 @@ class FtBlock(C.Structure):
     _fields_ = [("weight", C.c_void_p), ("virtual_weight", C.c_void_p), ("rows", C.c_int64), ("n_virtual", C.c_int64)]
 
 
+class TableEmit(C.Structure):
+    """Mirror of `nnue_table_emit`."""
+
+    _fields_ = [("q16", C.c_void_p), ("q16_pitch", C.c_int64), ("psqt", C.c_void_p), ("d_stats", C.c_void_p),
+                ("L1", C.c_int32), ("P", C.c_int32), ("scale_main", C.c_float), ("scale_psqt", C.c_float)]
+
+
 class LsWeightScales(C.Structure):
     """Mirror of `nnue_ls_weight_scales`."""
 
@@ -159,6 +166,10 @@ PROTOTYPES = {
     "nnue_rangerlite_update": (
         C.c_int,
         [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, C.POINTER(RangerHParams), _P],
+    ),
+    "nnue_rangerlite_update_emit": (
+        C.c_int,
+        [_P, _P, _P, _P, _P, _P, _P, _P, _I64, _I64, C.POINTER(RangerHParams), C.POINTER(TableEmit), _P],
     ),
     "nnue_ddp_reduce_shard": (C.c_int, [C.POINTER(_P), _I32, _I32, _I64, _I64, _P, _P]),
     "nnue_ddp_update_shard": (

@@ -102,6 +102,18 @@ class ComposedFeatureTransformer(nn.Module):
 
     integer_table = True  # gather an int16 table when weights are fake-quantized (same bits, half the bytes)
 
+    def _table_cache(self):
+        """One feature block without factor rows: its integer table is kept between steps (the optimizer
+        of this package refreshes it inside its update kernel)."""
+        if len(self.features) != 1 or getattr(self.features[0], "virtual_weight", None) is not None:
+            return None
+        cache = getattr(self, "_q16_cache", None)
+        if cache is None:
+            from ._launch import QuantTableCache
+
+            cache = self._q16_cache = QuantTableCache()
+        return cache
+
     def _integer_table_applies(self, indices: torch.Tensor, fake_quantize_weights: bool) -> bool:
         """The int16 form of the table is exact when every fake-quantized entry is an integer over a
         power-of-two scale shared by weights and bias, and a list holds at most 511 rows."""
@@ -167,7 +179,7 @@ class ComposedFeatureTransformer(nn.Module):
                 us, them, white_indices, black_indices, psqt_indices, self.bias, q.max_ft_activation, self.l1_size,
                 q.config.hidden_quantized_one if fake_quantize_acts else 0.0, _FAKE_QUANTIZE_EPS,
                 q.l0_correction_factor, q.weight_scales_dict["ft_weight"], q.weight_scales_dict["ft_psqt_weight"],
-                *params)
+                self._table_cache(), *params)
         merged, bias = self.merged_weight_and_bias(fake_quantize_weights)
         if backend in ("auto", "fused") and merged.is_cuda:
             # activation fake quantization and the correction factor ride in the kernel epilogue

@@ -57,47 +57,47 @@ __device__ __forceinline__ void split_pairs(int (&pk)[2][4], PairAcc& acc) {
     }
 }
 
-// acc += sum over the listed rows of the column pairs 4 * c8 .. 4 * c8 + 3 of both halves
+// acc += sum over the listed rows of this lane's column pairs in both halves.
+// The loop carries no predicates: the table has one more row than the feature set, all zeros
+// (row `zero_row`), and list entries that are padding, out of range or beyond the end of the list
+// read that row, so every batch of R rows is complete and is loaded and added unconditionally.
+// base0 / base1 point at this lane's 16-byte group in the first / second half of row 0.
 template <int R>
-__device__ __forceinline__ void gather_q16(const uint4* __restrict__ table, int64_t stride8, int64_t n_rows,
-                                           const int32_t* list, int n, int c8, int h8, bool ok, int rows_per_split,
-                                           PairAcc& acc, int lane, unsigned long long* status) {
+__device__ __forceinline__ void gather_q16(const uint4* __restrict__ base0, const uint4* __restrict__ base1,
+                                           int stride8, int zero_row, const int32_t* list, int n,
+                                           int rows_per_split, PairAcc& acc, int lane, unsigned long long* status) {
+    constexpr int kChunk = (32 / R) * R;  // list entries per pass: a multiple of R, so a batch never wraps the warp
     int pk[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
     int pending = 0;
-    for (int k0 = 0; k0 < n; k0 += 32) {
-        const int m = min(32, n - k0);
-        int mine = (lane < m) ? list[k0 + lane] : 0;
-        if ((unsigned)mine >= (unsigned long long)n_rows) {  // negative or too large
+    for (int k0 = 0; k0 < n; k0 += kChunk) {
+        const int m = min(kChunk, n - k0);
+        int mine = (lane < m) ? list[k0 + lane] : zero_row;
+        if ((unsigned)mine >= (unsigned)zero_row) {  // negative or too large (padding lanes hold zero_row itself)
             if (lane < m) note_bad_index(status);
-            mine = -1;
+            mine = zero_row;
         }
         for (int j = 0; j < m; j += R) {
             uint4 v[R][2];
-            bool live[R];
 #pragma unroll
             for (int t = 0; t < R; ++t) {
-                const int r = __shfl_sync(kFullMask, mine, (j + t) & 31);
-                live[t] = (j + t < m) && (r >= 0);
-                const uint4* row = table + (int64_t)(live[t] ? r : 0) * stride8;
-                const bool take = live[t] && ok;
-                v[t][0] = take ? __ldg(row + c8) : make_uint4(0u, 0u, 0u, 0u);
-                v[t][1] = take ? __ldg(row + h8 + c8) : make_uint4(0u, 0u, 0u, 0u);
+                const int off = __shfl_sync(kFullMask, mine, j + t) * stride8;
+                v[t][0] = __ldg(base0 + off);
+                v[t][1] = __ldg(base1 + off);
             }
 #pragma unroll
             for (int t = 0; t < R; ++t) {
-                if (live[t]) {  // warp-uniform
 #pragma unroll
-                    for (int h = 0; h < 2; ++h) {
-                        pk[h][0] += (int)v[t][h].x;
-                        pk[h][1] += (int)v[t][h].y;
-                        pk[h][2] += (int)v[t][h].z;
-                        pk[h][3] += (int)v[t][h].w;
-                    }
-                    if (++pending >= rows_per_split) {
-                        split_pairs(pk, acc);
-                        pending = 0;
-                    }
+                for (int h = 0; h < 2; ++h) {
+                    pk[h][0] += (int)v[t][h].x;
+                    pk[h][1] += (int)v[t][h].y;
+                    pk[h][2] += (int)v[t][h].z;
+                    pk[h][3] += (int)v[t][h].w;
                 }
+            }
+            pending += R;
+            if (pending + R > rows_per_split) {
+                split_pairs(pk, acc);
+                pending = 0;
             }
         }
     }
@@ -163,10 +163,14 @@ __device__ __forceinline__ void store_half(float u_, float t_, float4 mine_lo, f
 }
 
 constexpr int kPosPerCta = kWarpsPerCta / 2;  // a warp per (position, perspective)
+// Largest |k| the packed sums take: 32767 / 4095 = 8 rows per split, above the deepest batch (R <= 6).
+// A table beyond it (weights above 16.0) goes the fp32 route like one beyond the int16 range.
+constexpr int kMaxAbsPacked = 4095;
 
 // bias: fp32 [L1 + P], already fake-quantized at `scale` (its L1 part is k / scale), PSQT part as the op adds it.
 // psqt_tab: fp32 [N, P], the fake-quantized PSQT columns of the table.
 // stats: [0] entries outside the int16 range (non-zero: fp32 route), [1] max |k| of the table.
+// q16 holds N + 1 rows, the last one all zeros.
 // Warp 2q gathers the white list of the CTA's q-th position, warp 2q + 1 its black list (half the
 // accumulators per warp, twice the warps per position); the pair swaps its sums through shared memory
 // and each warp finishes one half of the outputs.
@@ -218,9 +222,9 @@ __global__ void __launch_bounds__(kThreads, MINB)
     const float4* bias4 = reinterpret_cast<const float4*>(bias);
 
     float4 f[4];  // this perspective: columns 2*c8, 2*c8+1 of the first half, then of the second half
-    if (__ldg(stats) == 0) {
-        const int max_abs = __ldg(stats + 1);
-        const int rows_per_split = max_abs > 0 ? min(32767 / max_abs, 512) : 512;
+    const int max_abs = __ldg(stats + 1);
+    if (__ldg(stats) == 0 && max_abs <= kMaxAbsPacked) {
+        const int rows_per_split = max_abs > 0 ? min(32767 / max_abs, 512) : 512;  // >= 8 > R
         PairAcc acc;
 #pragma unroll
         for (int hlf = 0; hlf < 2; ++hlf) {
@@ -233,8 +237,9 @@ __global__ void __launch_bounds__(kThreads, MINB)
                 acc.hi[hlf][w] = __float2int_rn(__fmul_rn(bv[2 * w + 1], scale));
             }
         }
-        gather_q16<R>(reinterpret_cast<const uint4*>(q16), pitch8, N, list, n, c8, h8, ok, rows_per_split, acc, lane,
-                      status);
+        // lanes beyond the last column read column group 0 (valid memory); their sums are never stored
+        const uint4* base0 = reinterpret_cast<const uint4*>(q16) + (ok ? c8 : 0);
+        gather_q16<R>(base0, base0 + h8, (int)pitch8, (int)N, list, n, rows_per_split, acc, lane, status);
         auto cv = [inv_scale](int a) { return __fmul_rn(__int2float_rn(a), inv_scale); };
 #pragma unroll
         for (int hlf = 0; hlf < 2; ++hlf) {
@@ -300,6 +305,8 @@ extern "C" int nnue_ft_fused_fwd_q16(const float* us, const float* them, const i
                  "nnue_ft_fused_fwd_q16: needs L1 %% 16 == 0 and P %% 4 == 0 (L1=%d P=%d)", L1, P);
     NNUE_REQUIRE(q16_pitch >= L1 && q16_pitch % 8 == 0, NNUE_ERR_ARG,
                  "nnue_ft_fused_fwd_q16: the row pitch (%lld) must be a multiple of 8 not below L1", (long long)q16_pitch);
+    NNUE_REQUIRE((N + 1) * (q16_pitch / 8) < 0x7fffffffLL, NNUE_ERR_UNSUPPORTED,
+                 "nnue_ft_fused_fwd_q16: table too large for 32-bit row offsets");
     NNUE_REQUIRE(K <= 511, NNUE_ERR_UNSUPPORTED,
                  "nnue_ft_fused_fwd_q16: at most 511 rows per list keep the integer sum exact (K=%d)", K);
     NNUE_REQUIRE(scale_main > 0.f && frexpf(scale_main, &sc_exp) == 0.5f, NNUE_ERR_UNSUPPORTED,

@@ -64,6 +64,9 @@ __device__ __forceinline__ void gather_sum(const float4* __restrict__ table, int
 // pre(i) runs before entry i (0-based position in `list`) is added, in order;
 // the segment kernel uses it to close a row when i crosses a row boundary.
 // Bad ids are tallied only when `count_bad`.
+// The loads carry no predicate: a slot past the end of the list, a bad id or a lane beyond the
+// last column reads row 0 / column 0 (valid memory) and the value is dropped, by the warp-uniform
+// test around the add or by the caller's masked store.
 template <int C, int R, class Pre>
 __device__ __forceinline__ void gather_sum_pipelined(const float4* __restrict__ table,
                                                      int64_t stride4, int64_t n_rows,
@@ -72,6 +75,9 @@ __device__ __forceinline__ void gather_sum_pipelined(const float4* __restrict__ 
                                                      float4 (&acc)[C], int lane,
                                                      unsigned long long* status, bool count_bad,
                                                      Pre pre) {
+    const float4* base[C];
+#pragma unroll
+    for (int c = 0; c < C; ++c) base[c] = table + (ok[c] ? col[c] : 0);
     int next_mine = (lane < min(32, n)) ? list[lane] : 0;
     for (int k0 = 0; k0 < n; k0 += 32) {
         const int m = min(32, n - k0);
@@ -83,26 +89,24 @@ __device__ __forceinline__ void gather_sum_pipelined(const float4* __restrict__ 
         }
         const int nb = (m + R - 1) / R;
         float4 va[R][C], vb[R][C];
+        int ra[R], rb[R];
 
-        auto issue = [&](float4 (&v)[R][C], int b) {
+        auto issue = [&](float4 (&v)[R][C], int (&rr)[R], int b) {
 #pragma unroll
             for (int t = 0; t < R; ++t) {
-                const int j = b * R + t;
-                const int r = __shfl_sync(kFullMask, mine, j & 31);
-                const bool live = (j < m) && (r >= 0);
-                const float4* row = table + (int64_t)(live ? r : 0) * stride4;
+                rr[t] = __shfl_sync(kFullMask, mine, (b * R + t) & 31);  // lanes >= m hold 0: row 0
+                const int64_t off = (int64_t)max(rr[t], 0) * stride4;
 #pragma unroll
-                for (int c = 0; c < C; ++c) v[t][c] = (live && ok[c]) ? ldg4(row + col[c]) : f4_zero();
+                for (int c = 0; c < C; ++c) v[t][c] = ldg4(base[c] + off);
             }
         };
-        auto consume = [&](float4 (&v)[R][C], int b) {
+        auto consume = [&](float4 (&v)[R][C], int (&rr)[R], int b) {
 #pragma unroll
             for (int t = 0; t < R; ++t) {
                 const int j = b * R + t;
                 if (j < m) {  // warp-uniform
-                    const int r = __shfl_sync(kFullMask, mine, j & 31);
                     pre(k0 + j);
-                    if (r >= 0) {
+                    if (rr[t] >= 0) {
 #pragma unroll
                         for (int c = 0; c < C; ++c) acc[c] = f4_add(acc[c], v[t][c]);
                     }
@@ -110,12 +114,12 @@ __device__ __forceinline__ void gather_sum_pipelined(const float4* __restrict__ 
             }
         };
 
-        issue(va, 0);
+        issue(va, ra, 0);
         for (int b = 0; b < nb; b += 2) {
-            if (b + 1 < nb) issue(vb, b + 1);
-            consume(va, b);
-            if (b + 2 < nb) issue(va, b + 2);
-            if (b + 1 < nb) consume(vb, b + 1);
+            if (b + 1 < nb) issue(vb, rb, b + 1);
+            consume(va, ra, b);
+            if (b + 2 < nb) issue(va, ra, b + 2);
+            if (b + 1 < nb) consume(vb, rb, b + 1);
         }
     }
 }

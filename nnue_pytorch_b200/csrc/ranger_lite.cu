@@ -63,23 +63,39 @@ __global__ void __launch_bounds__(kThreads)
     if (__any_sync(kFullMask, nz) && lane == 0) row_active[row] = 1;
 }
 
-// IDX = unsigned when the float4 count (plus one grid stride) fits 32 bits: cheap row lookup
-template <typename IDX>
+// IDX = unsigned when the float4 count (plus one grid stride) fits 32 bits: cheap row lookup.
+// EMIT: the new parameter values also leave the kernel as the integer table the next forward gathers
+// (nnue_ft_quantize_table's format), which saves that pass its read of the whole table; rows the update
+// skips are emitted from the values they hold.
+template <typename IDX, bool EMIT>
 __global__ void __launch_bounds__(kThreads)
     k_ranger_rows(float* __restrict__ p, const float* __restrict__ g, float* __restrict__ gm,
                   float* __restrict__ ngm, float* __restrict__ vm, float* __restrict__ slow,
                   const uint8_t* __restrict__ row_active, const float* __restrict__ d_scale, int64_t rows,
-                  int64_t width4, RangerConst c) {
+                  int64_t width4, RangerConst c, TableEmit emit) {
     const float scale = d_scale ? __ldg(d_scale) : 1.f;
     const float4* g4 = reinterpret_cast<const float4*>(g);
     const IDX w4 = (IDX)width4;
     const IDX n4 = (IDX)rows * w4;
     const IDX stride = (IDX)gridDim.x * blockDim.x;
+    int bad = 0, max_abs = 0;
     for (IDX i = (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += stride) {
-        if (!__ldg(row_active + i / w4)) continue;
-        ranger_vec4(c, scale, (int64_t)i, g4, reinterpret_cast<float4*>(p), reinterpret_cast<float4*>(gm),
-                    reinterpret_cast<float4*>(ngm), reinterpret_cast<float4*>(vm),
-                    reinterpret_cast<float4*>(slow), __ldg(g4 + i));
+        const IDX row = i / w4;
+        float4 pv;
+        if (__ldg(row_active + row)) {
+            pv = ranger_vec4(c, scale, (int64_t)i, g4, reinterpret_cast<float4*>(p), reinterpret_cast<float4*>(gm),
+                             reinterpret_cast<float4*>(ngm), reinterpret_cast<float4*>(vm),
+                             reinterpret_cast<float4*>(slow), __ldg(g4 + i));
+        } else {
+            if (!EMIT) continue;
+            pv = reinterpret_cast<const float4*>(p)[i];
+        }
+        if (EMIT) emit_group(emit, (long long)row, (int)(i - row * w4), pv, bad, max_abs);
+    }
+    if (EMIT) {
+        if (bad) atomicAdd(emit.stats, bad);
+        max_abs = __reduce_max_sync(kFullMask, max_abs);
+        if ((threadIdx.x & 31) == 0 && max_abs > 0) atomicMax(emit.stats + 1, max_abs);
     }
 }
 
@@ -120,7 +136,30 @@ extern "C" int nnue_rangerlite_update(float* p, const float* grad, float* grad_m
                                       float* neg_grad_ma, float* variance_ma, float* slow,
                                       uint8_t* row_active, const float* d_grad_scale, int64_t rows,
                                       int64_t width, const nnue_ranger_hparams* hp, void* stream) {
+    return nnue_rangerlite_update_emit(p, grad, grad_ma, neg_grad_ma, variance_ma, slow, row_active, d_grad_scale,
+                                       rows, width, hp, nullptr, stream);
+}
+
+extern "C" int nnue_rangerlite_update_emit(float* p, const float* grad, float* grad_ma,
+                                           float* neg_grad_ma, float* variance_ma, float* slow,
+                                           uint8_t* row_active, const float* d_grad_scale, int64_t rows,
+                                           int64_t width, const nnue_ranger_hparams* hp,
+                                           const nnue_table_emit* h_emit, void* stream) {
     NNUE_REQUIRE(hp != nullptr, NNUE_ERR_ARG, "nnue_rangerlite_update: null hyper-parameters");
+    if (h_emit) {
+        int e2 = 0;
+        NNUE_REQUIRE(h_emit->q16 && h_emit->d_stats && (h_emit->psqt || h_emit->P == 0), NNUE_ERR_ARG,
+                     "nnue_rangerlite_update_emit: null table pointer");
+        NNUE_REQUIRE(h_emit->L1 > 0 && h_emit->L1 % 8 == 0 && h_emit->P >= 0 && h_emit->P % 4 == 0 &&
+                         (int64_t)h_emit->L1 + h_emit->P == width,
+                     NNUE_ERR_ARG, "nnue_rangerlite_update_emit: L1 + P must be the tensor's width (L1 %% 8, P %% 4)");
+        NNUE_REQUIRE(h_emit->q16_pitch >= h_emit->L1 && h_emit->q16_pitch % 8 == 0, NNUE_ERR_ARG,
+                     "nnue_rangerlite_update_emit: bad row pitch");
+        NNUE_REQUIRE(h_emit->scale_main > 0.f && frexpf(h_emit->scale_main, &e2) == 0.5f && h_emit->scale_psqt > 0.f,
+                     NNUE_ERR_UNSUPPORTED, "nnue_rangerlite_update_emit: the main scale must be a power of two");
+        NNUE_REQUIRE(aligned16(h_emit->q16) && aligned16(h_emit->psqt), NNUE_ERR_ALIGN,
+                     "nnue_rangerlite_update_emit: 16-byte aligned table buffers");
+    }
     NNUE_REQUIRE(rows >= 0 && width >= 0, NNUE_ERR_ARG, "nnue_rangerlite_update: negative size");
     const int64_t n = rows * width;
     if (n == 0) return NNUE_OK;
@@ -134,17 +173,28 @@ extern "C" int nnue_rangerlite_update(float* p, const float* grad, float* grad_m
     const bool al = aligned16(p) && aligned16(grad) && aligned16(grad_ma) && aligned16(variance_ma) &&
                     (!neg_grad_ma || aligned16(neg_grad_ma)) && (!slow || aligned16(slow));
     const int sms = sm_count();
+    bool emitted = false;
     if (row_active && al && width % 4 == 0 && hp->phase != 1) {
         k_rows_activate<<<(unsigned)((rows + kWarpsPerCta - 1) / kWarpsPerCta), kThreads, 0, s>>>(
             grad, row_active, rows, width / 4);
         const unsigned grid = (unsigned)std::min<int64_t>((n / 4 + kThreads - 1) / kThreads, (int64_t)sms * 8);
+        TableEmit te{};
+        if (h_emit) {
+            te = TableEmit{h_emit->q16, h_emit->psqt, h_emit->d_stats, h_emit->q16_pitch / 4, h_emit->L1 / 4,
+                           h_emit->P / 4, h_emit->scale_main, h_emit->scale_psqt};
+            NNUE_CUDA_TRY(cudaMemsetAsync(h_emit->d_stats, 0, 2 * sizeof(int32_t), s));
+            emitted = true;
+        }
+        const bool narrow = n / 4 + (int64_t)grid * kThreads < 0x7fffffffLL;
         ProfScope prof("k_ranger_rows", s);
-        if (n / 4 + (int64_t)grid * kThreads < 0x7fffffffLL)
-            k_ranger_rows<unsigned><<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma, slow,
-                                                             row_active, d_grad_scale, rows, width / 4, c);
-        else
-            k_ranger_rows<int64_t><<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma, slow,
-                                                            row_active, d_grad_scale, rows, width / 4, c);
+#define LAUNCH_ROWS(II, EE)                                                                                       \
+    k_ranger_rows<II, EE><<<grid, kThreads, 0, s>>>(p, grad, grad_ma, neg_grad_ma, variance_ma, slow, row_active, \
+                                                    d_grad_scale, rows, width / 4, c, te)
+        if (narrow && h_emit) LAUNCH_ROWS(unsigned, true);
+        else if (narrow) LAUNCH_ROWS(unsigned, false);
+        else if (h_emit) LAUNCH_ROWS(int64_t, true);
+        else LAUNCH_ROWS(int64_t, false);
+#undef LAUNCH_ROWS
         note_launches(1);
     } else {
         const int64_t work = al ? (n / 4 + 1) : n;
@@ -158,6 +208,11 @@ extern "C" int nnue_rangerlite_update(float* p, const float* grad, float* grad_m
     }
     NNUE_CUDA_TRY(cudaGetLastError());
     note_launches(1);
+    if (h_emit && !emitted) {  // shapes the row kernel does not take: the table in a pass of its own
+        NNUE_CUDA_TRY(cudaMemsetAsync(h_emit->d_stats, 0, 2 * sizeof(int32_t), s));
+        return nnue_ft_quantize_table(p, nullptr, h_emit->q16, h_emit->q16_pitch, h_emit->psqt, rows, 0, h_emit->L1,
+                                      h_emit->P, h_emit->scale_main, h_emit->scale_psqt, h_emit->d_stats, stream);
+    }
     return NNUE_OK;
 }
 

@@ -269,6 +269,9 @@ class ShardedTableExchange:
                 self.table_ptrs, self.rank, e0, e1, self.grad, self.grad_ma[o0:o1],
                 None if self.neg_grad_ma is None else self.neg_grad_ma[o0:o1], self.variance_ma[o0:o1],
                 None if self.slow is None else self.slow[o0:o1], grad_scale, hp)
+        cache = getattr(self.param, "_nnue_q16_cache", None)
+        if cache is not None:
+            cache.invalidate()  # the table changed through raw (peer) stores: the forward quantizes it again
         # nobody may read its table before every rank has stored its share into it
         dist.all_reduce(self._token, group=self.group)
         if self.sliced:

@@ -117,18 +117,27 @@ class QuantizedFusedDoubleFtFunction(autograd.Function):
     its `virtual_weight`, and to the L1 part of the bias.
 
     apply(us, them, white_indices, black_indices, psqt_indices, bias, max_ft_activation, l1_size,
-          act_quant_scale, act_quant_eps, out_scale, scale_main, scale_psqt, w0, v0, w1, v1, ...)
-    with (w_i, v_i) the parameter blocks in table order, v_i None for a block without factor rows."""
+          act_quant_scale, act_quant_eps, out_scale, scale_main, scale_psqt, cache, w0, v0, w1, v1, ...)
+    with (w_i, v_i) the parameter blocks in table order, v_i None for a block without factor rows.
+    `cache`: a `_launch.QuantTableCache` (or None) for a single block without factor rows: the integer
+    table is then kept between steps and only rebuilt when the parameter changed behind its back."""
 
     @staticmethod
     def forward(ctx, us, them, white_indices, black_indices, psqt_indices, bias, max_ft_activation, l1_size,
-                act_quant_scale, act_quant_eps, out_scale, scale_main, scale_psqt, *params):
+                act_quant_scale, act_quant_eps, out_scale, scale_main, scale_psqt, cache, *params):
         l1 = int(l1_size)
         blocks = [(params[i].detach(), None if params[i + 1] is None else params[i + 1].detach())
                   for i in range(0, len(params), 2)]
-        q16, psqt, overflow = _launch.quantize_blocks(blocks, l1, scale_main, scale_psqt)
-        # a bias outside the int16 range also sends the forward down its fp32 route
-        _launch.quantize_blocks([(bias.detach().reshape(1, -1), None)], l1, scale_main, scale_psqt, overflow=overflow)
+        if cache is not None and (len(blocks) != 1 or blocks[0][1] is not None):
+            cache = None
+        if cache is not None and cache.fresh(params[0], l1, scale_main, scale_psqt):
+            q16, psqt, overflow = cache.q16, cache.psqt, cache.stats
+        else:
+            q16, psqt, overflow = _launch.quantize_blocks(blocks, l1, scale_main, scale_psqt)
+            if cache is not None:
+                cache.store(params[0], l1, scale_main, scale_psqt, q16, psqt, overflow)
+                params[0]._nnue_q16_cache = cache  # where this package's optimizer looks for it
+        _launch.quantize_bias_stats(bias, l1, scale_main, scale_psqt, overflow)
         bias_fq = torch.zeros_like(bias)
         _launch.prepare_table(bias.detach()[:l1].reshape(1, l1), None, l1, scale_main, 1.0, out=bias_fq, span="prepare_bias")
         l0, wpsqt, bpsqt, saved = _launch.fused_forward_q16(
@@ -158,11 +167,11 @@ class QuantizedFusedDoubleFtFunction(autograd.Function):
             gw = grad_table if len(ctx.rows) == 1 else grad_table[at : at + rows]
             at += rows
             gv = None
-            if nv and ctx.needs_input_grad[13 + 2 * i + 1]:
+            if nv and ctx.needs_input_grad[14 + 2 * i + 1]:
                 gv = _launch.virtual_grad(gw, nv)
                 if ex is not None:
                     ex.note_local_reader()  # the reduce overwrites the buffer: it must wait for the kernel above
             grads += [None if ex is not None else gw, gv]
         pad = ctx.num_outputs - ctx.l1_size
         grad_bias = torch.nn.functional.pad(grad_bias[: ctx.l1_size], (0, pad))  # the PSQT part of the bias never trains
-        return (None, None, None, None, None, grad_bias, None, None, None, None, None, None, None, *grads)
+        return (None, None, None, None, None, grad_bias, None, None, None, None, None, None, None, None, *grads)

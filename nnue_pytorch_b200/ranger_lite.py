@@ -161,6 +161,7 @@ class RangerLite(torch.optim.Optimizer):
             return loss
         if self.normloss_active or self.use_legacy_scoping_bug:
             self._step_tensor_ops()
+            self._drop_table_caches(active, ())
             return loss
 
         for p, _ in active:
@@ -192,6 +193,7 @@ class RangerLite(torch.optim.Optimizer):
             var_norm = torch.sqrt(total / self.param_size).clamp_min(self.eps).item()
 
         small = []  # tensors without row flags share launches
+        emitted = []  # parameters whose integer table (kept by the forward) the update kernel rewrote
         for p, group in active:
             st = self.state[p]
             wd = group.get("weight_decay", 0.0)
@@ -203,13 +205,31 @@ class RangerLite(torch.optim.Optimizer):
             if rows is None and p.numel() <= self.MULTI_TENSOR_LIMIT and p.data.is_contiguous():
                 small.append(args + (hp,))
             else:
-                _launch.ranger_update(*args, rows, self.grad_scale, hp)
+                # a feature-transformer table whose integer form the forward keeps: write the new one in the same pass
+                cache = getattr(p, "_nnue_q16_cache", None)
+                emit = cache.emit_struct(p) if cache is not None else None
+                _launch.ranger_update(*args, rows, self.grad_scale, hp, emit=emit)
+                if emit is not None:
+                    cache.mark(p)
+                    emitted.append(p)
         by_device: dict = {}
         for item in small:
             by_device.setdefault(item[0].device, []).append(item)
         for items in by_device.values():
             _launch.ranger_update_multi(items, self.grad_scale)
+        self._drop_table_caches(active, emitted)
         return loss
+
+    @staticmethod
+    def _drop_table_caches(active, emitted) -> None:
+        """The kernels write parameters through raw pointers, which torch's version counter does not see:
+        every integer table a forward keeps for a parameter updated here is stale unless the update kernel
+        rewrote it."""
+        keep = {id(p) for p in emitted}
+        for p, _ in active:
+            cache = getattr(p, "_nnue_q16_cache", None)
+            if cache is not None and id(p) not in keep:
+                cache.invalidate()
 
     MULTI_TENSOR_LIMIT = 1 << 22  # elements; larger tensors get a launch of their own
 

@@ -646,7 +646,7 @@ def test_integer_table_falls_back_when_a_weight_leaves_the_int16_range(dev):
     B, K, l1, P = 50, 40, 256, 8
     c = _random_case(B, 600, K, l1, P, seed=3, wscale=0.05)
     gen = torch.Generator().manual_seed(6)
-    for poke in ("weight", "factor", "bias"):
+    for poke in ("weight", "factor", "bias", "split often", "beyond packed sums"):
         w = torch.randn(600, l1 + P, generator=gen) * 0.2
         v = torch.randn(100, l1 + P, generator=gen) * 0.1
         bias = torch.randn(l1 + P, generator=gen) * 0.3
@@ -655,8 +655,17 @@ def test_integer_table_falls_back_when_a_weight_leaves_the_int16_range(dev):
             w[300, 250] = -129.5
         elif poke == "factor":
             v[3, 100] = 150.0
-        else:
+        elif poke == "bias":
             bias[7] = -400.0
+        elif poke == "split often":
+            # |k| up to 3200: still the integer route, the pair sums are split every ten rows; rows that many
+            # lists name carry the large values, with both signs in neighbouring columns
+            w[:40, ::3] = 12.5
+            w[:40, 1::3] = -12.25
+            c["white"][:, 0] = torch.arange(B, dtype=torch.int32) % 40
+            c["black"][:, :3] = torch.tensor([1, 2, 3], dtype=torch.int32)
+        else:
+            w[5, 9] = 20.0            # k = 5120: inside int16, beyond what the packed sums take
         a, b = _transformer_both_ways(dev, [(w, v)], bias, c, l1)
         for k in a:
             assert torch.equal(a[k], b[k]), (poke, k)

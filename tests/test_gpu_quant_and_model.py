@@ -80,6 +80,57 @@ def test_integer_eval_matches_integer_oracle(dev, L1, layout, B):
     assert len(np.unique(want)) > B // 4  # the outputs are not degenerate
 
 
+def test_integer_eval_with_a_non_default_scheme(dev):
+    """Every constant of the integer evaluation derives from `QuantizationConfig`
+    (model/quantize.py:58-73 of the reference).  A power-of-two scheme other than the default one --
+    feature transformer at 128, layers at 64 / 32 / 64, hidden activations at 64 -- against the float64
+    fake-quantized forward of the same scheme (the definition) and the integer oracle.  A scheme whose
+    scales are not powers of two (the 127 of a literal "int16 at scale 127") has no exact integer form
+    and is refused."""
+    from oracle import model_oracle, quant_oracle
+    from nnue_pytorch_b200 import positions
+    from nnue_pytorch_b200.quantize import QuantizationConfig, QuantizationManager
+    from nnue_pytorch_b200.quantized_eval import QuantizedNet
+
+    cfg = QuantizationConfig(weight_scale_l1=64.0, weight_scale_l2=32.0, weight_scale_l_out=64.0, ft_quantized_one=128.0,
+                             ft_quantized_max=127.0, hidden_quantized_one=64.0, hidden_quantized_max=63.0,
+                             inference_l0_division_factor=256.0, inference_sqr_crelu_division_factor=64.0)
+    qm = QuantizationManager(cfg)
+    consts = qm.integer_constants()
+    assert (consts["ft_shift"], consts["sqr_shift_l1"], consts["lin_shift_l1"], consts["sqr_shift_l2"],
+            consts["lin_shift_l2"], consts["out_div"], consts["ft_max"], consts["hidden_max"]) == (8, 18, 6, 16, 5, 8192, 127, 63)
+    L1, B, N = 256, 3000, positions.NUM_INPUTS_BASELINE
+    gen = np.random.default_rng(9)
+    p = {"ft_weight": gen.integers(-20, 21, (N, L1 + 8)) / 128.0, "l1_w": gen.integers(-60, 61, (256, L1)) / 64.0,
+         "l1f_w": gen.integers(-3, 4, (32, L1)) / 64.0, "l1_b": gen.integers(-4000, 4001, 256) / 4096.0,
+         "l1f_b": gen.integers(-500, 501, 32) / 4096.0, "l2_w": gen.integers(-63, 64, (256, 64)) / 32.0,
+         "l2_b": gen.integers(-2000, 2001, 256) / 2048.0, "out_w": gen.integers(-63, 64, (8, 128)) / 64.0,
+         "out_b": gen.integers(-4000, 4001, 8) / 4096.0}
+    p["ft_weight"][:, L1:] = gen.integers(-2000, 2001, (N, 8)) / 9600.0
+    p["ft_bias"] = np.concatenate([gen.integers(-40, 41, L1) / 128.0, np.zeros(8)])
+    b = positions.generate_batch(B, 23, layout="baseline")
+    f = lambda a: t(np.asarray(a), torch.float64).to(dev)  # noqa: E731
+    net = QuantizedNet(f(p["ft_weight"]), f(p["ft_bias"]), f(p["l1_w"] + np.tile(p["l1f_w"], (8, 1))),
+                       f(p["l1_b"] + np.tile(p["l1f_b"], 8)), f(p["l2_w"]), f(p["l2_b"]), f(p["out_w"]), f(p["out_b"]),
+                       L1, 8, qm)
+    got = net.evaluate(t(b.white).to(dev), t(b.black).to(dev), t(b.us[:, 0] > 0.5), t(b.piece_count))
+    scales = {"ft": 128.0, "psqt": 9600.0, "l1": 64.0, "l2": 32.0, "out": 64.0, "hidden": 64.0}
+    want = quant_oracle.integer_eval(quant_oracle.quantize_params(p, L1, scales), b.white, b.black, b.us[:, 0] > 0.5,
+                                     (b.piece_count - 1) // 4, consts)
+    assert np.array_equal(got.cpu().numpy().astype(np.int64), want)
+    # the definition: float64 forward with this scheme's fake quantization, in units of 1 / (2 * 600 * 16)
+    quant = model_oracle.Quant(ws_l1=64.0, ws_l2=32.0, ws_lout=64.0, ft_one=128.0, ft_max=127.0, hidden_one=64.0,
+                               hidden_max=63.0, l0_div=256.0, sqr_div=64.0)
+    p64 = {k: t(np.asarray(v), torch.float64) for k, v in p.items()}
+    y = model_oracle.forward(p64, t(b.us).double(), t(b.them).double(), t(b.white), t(b.black), t(b.piece_count), quant)
+    assert np.array_equal(torch.round(y[:, 0] * 19200.0).to(torch.int64).numpy(), want)
+    assert len(np.unique(want)) > B // 4
+    with pytest.raises(ValueError):  # correction factors other than 1, scales that are no powers of two
+        QuantizationManager(QuantizationConfig(ft_quantized_one=127.0, ft_quantized_max=127.0)).integer_constants()
+    with pytest.raises(ValueError, match="power of two"):
+        QuantizationManager(QuantizationConfig(weight_scale_l2=48.0)).integer_constants()
+
+
 def test_tiled_integer_eval_in_several_passes(dev):
     """A workspace smaller than the batch needs: the batch is walked in passes; same bits."""
     import ctypes as C

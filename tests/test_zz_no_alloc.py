@@ -50,6 +50,13 @@ def test_static_scratch_backward_matches_workspace_backward():
     dev = torch.device("cuda:0")
     torch.cuda.set_device(dev)
     stream = torch.cuda.current_stream().cuda_stream
+    # the set-up call: the first use on a device looks up the array's address, and with the CUDA runtime's lazy
+    # module loading that is also the moment the 32 MiB array itself takes its place in device memory
+    idx, go = _case(0, 8, 4, 16, 8, dev)
+    gw0, gb0 = torch.empty(16, 8, device=dev), torch.empty(8, device=dev)
+    assert lib.nnue_ft_sparse_bwd_static(idx.data_ptr(), go.data_ptr(), gw0.data_ptr(), gb0.data_ptr(), 8, 4, 16, 8,
+                                         stream) == 0, lib.nnue_b200_last_error()
+    torch.cuda.synchronize()
     # two calls in a row, the second on other data and another shape: whatever the first
     # left in the shared array must not leak into the second
     for seed, (B, K, N, W) in ((1, (700, 32, 3000, 264)), (2, (333, 17, 1200, 132))):
@@ -59,8 +66,7 @@ def test_static_scratch_backward_matches_workspace_backward():
         gb = torch.full((W,), float("nan"), device=dev)
         torch.cuda.synchronize()
         # the driver's own count of free device memory (torch's allocator statistics would not see an
-        # allocation made inside the library); the workspace call above has already created the
-        # library's helper stream, so nothing is left to set up except the array's address
+        # allocation made inside the library); the helper stream and the array are in place by now
         free_before, _ = torch.cuda.mem_get_info(dev)
         st = lib.nnue_ft_sparse_bwd_static(idx.data_ptr(), go.data_ptr(), gw.data_ptr(), gb.data_ptr(),
                                            B, K, N, W, stream)
