@@ -455,6 +455,13 @@ int nnue_ls_plan(const int64_t* bucket, int64_t B, int32_t C, void* plan,
 int nnue_ls_l1_fwd(const float* x, const float* W1, const float* b1,
                    const void* plan, float* o1, int64_t B, int32_t L1, int32_t C,
                    void* stream);
+/* nnue_ls_l1_fwd on the tensor cores (tcgen05.mma kind::tf32, accumulator in tensor memory), for inputs TF32
+ * holds exactly: x on the activation grid (q / 128, q <= 127) and W1 fake-quantized (k / 128, |k| < 2048), which
+ * is what the quantized model feeds this layer.  Products and partial sums are then exact and the result has the
+ * bits of nnue_ls_l1_fwd; other inputs are truncated to TF32 on the way in.  Same arguments. */
+int nnue_ls_l1_fwd_tc(const float* x, const float* W1, const float* b1,
+                      const void* plan, float* o1, int64_t B, int32_t L1, int32_t C,
+                      void* stream);
 int nnue_ls_l1_bwd(const float* x, const float* W1, const float* d_o1,
                    const void* plan, float* dx, float* dW1, float* db1,
                    int64_t B, int32_t L1, int32_t C, void* stream);

@@ -32,6 +32,7 @@ SOURCES = [
     "quant_eval.cu",
     "layer_stack.cu",
     "layer_stack_l1.cu",
+    "layer_stack_l1_tc.cu",
     "layer_stack_tail.cu",
     "layer_stack_weights.cu",
     "batch_build.cu",

@@ -435,6 +435,9 @@ def ranger_update(p, grad, grad_ma, neg_grad_ma, variance_ma, slow, row_active, 
     if row_active is not None:
         assert row_active.dtype == torch.uint8 and p.dim() == 2 and row_active.numel() == p.shape[0]
         rows, width = p.shape
+    elif emit is not None:
+        assert p.dim() == 2  # the integer table is written row by row
+        rows, width = p.shape
     else:
         rows, width = 1, p.numel()
     with torch.cuda.device(dev), _span("ranger_table" if row_active is not None or p.numel() > (1 << 22) else "ranger_small", dev):

@@ -102,9 +102,21 @@ class ComposedFeatureTransformer(nn.Module):
 
     integer_table = True  # gather an int16 table when weights are fake-quantized (same bits, half the bytes)
 
+    # True: keep the integer table between forwards and let this package's optimizer rewrite it inside its
+    # update kernel (saves a pass over the table per step).  The table is rebuilt when the parameter's storage or
+    # torch version counter changes; a write through `.data` moves neither, so whoever makes one must call
+    # `invalidate_integer_table()` (this module's own methods do).  Off by default; `TrainStep` switches it on.
+    keep_integer_table = False
+
+    def invalidate_integer_table(self) -> None:
+        cache = getattr(self, "_q16_cache", None)
+        if cache is not None:
+            cache.invalidate()
+
     def _table_cache(self):
-        """One feature block without factor rows: its integer table is kept between steps (the optimizer
-        of this package refreshes it inside its update kernel)."""
+        """One feature block without factor rows: its integer table can be kept between steps."""
+        if not self.keep_integer_table:
+            return None
         if len(self.features) != 1 or getattr(self.features[0], "virtual_weight", None) is not None:
             return None
         cache = getattr(self, "_q16_cache", None)
@@ -131,17 +143,20 @@ class ComposedFeatureTransformer(nn.Module):
     def coalesce(self) -> None:
         for f in self.features:
             f.coalesce()
+        self.invalidate_integer_table()
 
     @torch.no_grad()
     def zero_virtual_weights(self) -> None:
         for f in self.features:
             f.zero_virtual_weights()
+        self.invalidate_integer_table()
 
     @torch.no_grad()
     def init_weights(self) -> None:
         for f in self.features:
             f.init_weights(self.num_psqt_buckets, self.quantization.nnue2score)
         self.bias[self.l1_size :] = 0.0
+        self.invalidate_integer_table()
 
     @torch.no_grad()
     def get_export_weights(self) -> torch.Tensor:
@@ -153,10 +168,12 @@ class ComposedFeatureTransformer(nn.Module):
         for f in self.features:
             f.load_export_weights(export_weight[at : at + f.NUM_REAL_FEATURES])
             at += f.NUM_REAL_FEATURES
+        self.invalidate_integer_table()
 
     def clip_weights(self, quantization) -> None:
         for f in self.features:
             f.clip_weights(quantization)
+        self.invalidate_integer_table()
 
     @torch.compiler.disable  # ctypes launches: runs eagerly inside a compiled model
     def forward(

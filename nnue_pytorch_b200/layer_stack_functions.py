@@ -79,7 +79,10 @@ class PlanAhead:
 
 class FusedLayerStackFunction(autograd.Function):
     @staticmethod
-    def forward(ctx, x, bucket, W1, b1, W2, b2, W3, b3, quantization, fake_quantize_acts, plan_ahead=None):
+    def forward(ctx, x, bucket, W1, b1, W2, b2, W3, b3, quantization, fake_quantize_acts, plan_ahead=None,
+                exact_tf32=False):
+        """`exact_tf32`: x and W1 are exactly representable in TF32 (the quantized model: activations on the
+        1/128 grid, fake-quantized weights); the first layer then runs on the tensor cores, same bits."""
         dev = _require_cuda(x, bucket, W1, b1, W2, b2, W3, b3)
         x, W1, b1, W2, b2, W3, b3 = (t.contiguous() for t in (x, W1, b1, W2, b2, W3, b3))
         bucket = bucket.reshape(-1).to(torch.int64).contiguous()
@@ -100,8 +103,8 @@ class FusedLayerStackFunction(autograd.Function):
             if plan_ahead is None:
                 _lib.check(lib.nnue_ls_plan(_ptr(bucket), B, count, _ptr(plan), plan.numel() * 4, s), "nnue_ls_plan")
             with _span("ls_l1_fwd", dev):
-                _lib.check(lib.nnue_ls_l1_fwd(_ptr(x), _ptr(W1), _ptr(b1), _ptr(plan), _ptr(o1), B, L1, count, s),
-                           "nnue_ls_l1_fwd")
+                l1_fwd = lib.nnue_ls_l1_fwd_tc if exact_tf32 else lib.nnue_ls_l1_fwd
+                _lib.check(l1_fwd(_ptr(x), _ptr(W1), _ptr(b1), _ptr(plan), _ptr(o1), B, L1, count, s), "nnue_ls_l1_fwd")
             _lib.check(lib.nnue_ls_tail_fwd(_ptr(o1), _ptr(plan), _ptr(W2), _ptr(b2), _ptr(W3), _ptr(b3.reshape(-1)),
                                             C.byref(params), _ptr(o2), _ptr(y), B, count, s), "nnue_ls_tail_fwd")
         ctx.save_for_backward(x, W1, W2, W3, o1, o2, plan)
@@ -133,7 +136,7 @@ class FusedLayerStackFunction(autograd.Function):
             with _span("ls_l1_bwd", dev):
                 _lib.check(lib.nnue_ls_l1_bwd(_ptr(x), _ptr(W1), _ptr(d_o1), _ptr(plan), _ptr(dx), _ptr(dW1),
                                               _ptr(db1), B, L1, count, s), "nnue_ls_l1_bwd")
-        return dx, None, dW1, db1, dW2, db2, dW3, db3.view(ctx.b3_shape), None, None, None
+        return dx, None, dW1, db1, dW2, db2, dW3, db3.view(ctx.b3_shape), None, None, None, None
 
 
 class LayerStackWeightsFunction(autograd.Function):

@@ -93,6 +93,7 @@ class LayerStacks(nn.Module):
         return q.clip_ls_act(torch.cat([sq, x], dim=1))
 
     fused = True  # use the bucket-aware kernels when the shapes allow it
+    tensor_core_l1 = True  # first layer on the tensor cores when its inputs are exact in TF32 (quantized model)
 
     @torch.compiler.disable  # ctypes launches: runs eagerly inside a compiled model
     def plan_ahead(self, ls_indices):
@@ -113,8 +114,10 @@ class LayerStacks(nn.Module):
             l1.linear.weight, l1.linear.bias, l1.factorized_linear.weight, l1.factorized_linear.bias,
             l2.linear.weight, l2.linear.bias, out.linear.weight, out.linear.bias, self.quantization,
             fake_quantize_weights)
+        # quantized model: activations on the 1/128 grid and fake-quantized weights are exact in TF32
+        exact = bool(self.tensor_core_l1 and fake_quantize_acts and fake_quantize_weights)
         return lsf.FusedLayerStackFunction.apply(x, ls_indices, w1, b1, w2, b2, w3, b3, self.quantization,
-                                                 fake_quantize_acts, plan_ahead)
+                                                 fake_quantize_acts, plan_ahead, exact)
 
     def forward(self, x, ls_indices, fake_quantize_acts=True, fake_quantize_weights=True, plan_ahead=None):
         from . import layer_stack_functions as lsf
@@ -236,6 +239,8 @@ class TrainStep:
         (gradient reduce-scatter, sharded update, all-gather); the table then leaves the
         optimizer's parameter groups."""
         self.model = model
+        # this loop's only writers of the table are the optimizer kernels, which rewrite the integer table too
+        model.input.keep_integer_table = True
         self.clip, self.lam = clip, lam
         # False, or a tensor-valued `lam` (per-sample lambda jitter): the loss as elementwise torch ops (`sf_loss`)
         self.fused_loss = fused_loss

@@ -579,7 +579,7 @@ def _transformer_both_ways(dev, blocks, bias, c, l1, act=(128.0, 1e-5, 1.0)):
         bd = bias.clone().to(dev).requires_grad_(True)
         if integer:
             flat = [t_ for pair in ps for t_ in pair]
-            l0, wp, bp = QuantizedFusedDoubleFtFunction.apply(*args, bd, c["max_act"], l1, *act, 256.0, 9600.0, *flat)
+            l0, wp, bp = QuantizedFusedDoubleFtFunction.apply(*args, bd, c["max_act"], l1, *act, 256.0, 9600.0, None, *flat)
         else:
             tables = [PrepareTableFunction.apply(w, v, l1, 256.0, 9600.0) for w, v in ps]
             table = tables[0] if len(tables) == 1 else torch.cat(tables, dim=0)

@@ -386,3 +386,91 @@ def test_training_is_reproducible(dev):
     assert torch.equal(la, lb)
     for a, b in zip(pa, pb):
         assert torch.equal(a, b)
+
+
+def test_kept_integer_table_follows_every_change_of_the_weights(dev):
+    """The forward keeps the int16 table between steps and the optimizer kernel rewrites it; a model that
+    quantizes the table afresh in every forward must stay bit-identical through optimizer steps (a lookahead
+    merge among them), through an in-place change made with torch between two steps (weight clipping), through
+    the optimizer's train / eval pointer swap and through a step of a different optimizer path."""
+    from nnue_pytorch_b200 import positions
+    from nnue_pytorch_b200.model import ModelConfig, NNUEModel, TrainStep
+
+    def build(keep):
+        torch.manual_seed(0)
+        m = NNUEModel("HalfKAv2_hm^flat", ModelConfig(L1=256, L2=32, L3=32))
+        with torch.no_grad():
+            m.input.features[0].weight[:, :256].normal_(0, 0.05)
+        m.input.keep_integer_table = keep
+        return m.to(dev)
+
+    a, b = build(True), build(False)
+    sa, sb = TrainStep(a, clip=2.0), TrainStep(b, clip=2.0)
+    assert a.input.keep_integer_table and b.input.keep_integer_table  # TrainStep switches it on
+    b.input.keep_integer_table = False
+    batches = [tuple(t(x).to(dev) for x in positions.generate_batch(1024, 60 + i, layout="baseline").as_tuple())
+               for i in range(9)]
+
+    def same():
+        for (n, p), (_, q) in zip(a.named_parameters(), b.named_parameters()):
+            assert torch.equal(p, q), n
+
+    for i, batch in enumerate(batches):
+        la, lb = sa(batch), sb(batch)
+        assert torch.equal(la, lb), i
+        same()
+        if i == 2:  # what a trainer's weight clipping does between steps: a write through .data, then the notice
+            for m in (a, b):
+                m.input.features[0].weight.data.clamp_(-0.08, 0.08)
+                m.input.invalidate_integer_table()
+        if i == 3:  # an in-place change torch itself tracks needs no notice
+            for m in (a, b):
+                with torch.no_grad():
+                    m.input.features[0].weight.mul_(1.01)
+        if i == 5:  # evaluation in between: the slow weights take the parameters' place and go back
+            for s_, m in ((sa, a), (sb, b)):
+                s_.optimizer.eval()
+                with torch.no_grad():
+                    ya = m(*batch[:4], batch[6], True, True)
+                s_.optimizer.train()
+                m._eval_out = ya
+            assert torch.equal(a._eval_out, b._eval_out)
+        if i == 7:  # a raw-pointer update that does not rewrite the table: the cache must notice
+            for s_ in (sa, sb):
+                s_.optimizer.touched_rows_only = False
+    cache = a.input._q16_cache
+    assert cache.q16 is not None and b.input._table_cache() is None
+
+
+@pytest.mark.parametrize("B,L1", [(300, 64), (4097, 3072), (16384, 1024), (1, 32)])
+def test_tensor_core_first_layer_has_the_bits_of_the_fma_kernel(dev, B, L1):
+    """The quantized model's first layer-stack layer runs as tcgen05.mma (TF32 inputs, fp32 accumulation in
+    tensor memory).  Activations on the 1/128 grid and fake-quantized weights are exact in TF32 and their
+    partial sums exact in fp32, so the output equals the fp32 FMA kernel's bit for bit."""
+    import ctypes as C  # noqa: F401
+
+    from nnue_pytorch_b200 import _launch, _lib
+
+    lib = _lib.load()
+    gen = torch.Generator().manual_seed(B + L1)
+    count = 8
+    x = (torch.randint(0, 128, (B, L1), generator=gen).float() / 128.0).to(dev)
+    x[x > 0.6] = 0.0  # sparse like the clipped products are
+    W1 = (torch.randint(-127, 128, (count * 32, L1), generator=gen).float() / 128.0).to(dev)
+    b1 = (torch.randint(-9000, 9001, (count * 32,), generator=gen).float() / 16384.0).to(dev)
+    bucket = torch.randint(0, count, (B,), generator=gen).to(dev)
+    if B > 100:
+        bucket[bucket == 3] = 2  # an empty bucket
+    plan = torch.empty(lib.nnue_ls_plan_bytes(B, count) // 4 + 4, dtype=torch.int32, device=dev)
+    s = torch.cuda.current_stream(dev).cuda_stream
+    _lib.check(lib.nnue_ls_plan(bucket.data_ptr(), B, count, plan.data_ptr(), plan.numel() * 4, s), "nnue_ls_plan")
+    outs = []
+    for fn in (lib.nnue_ls_l1_fwd, lib.nnue_ls_l1_fwd_tc):
+        o1 = torch.full((B, 32), float("nan"), device=dev)
+        _lib.check(fn(x.data_ptr(), W1.data_ptr(), b1.data_ptr(), plan.data_ptr(), o1.data_ptr(), B, L1, count, s), "l1 fwd")
+        outs.append(o1)
+    _launch.device_status(dev)  # a bounded wait that ran out would show here
+    want = torch.einsum("bk,bok->bo", x.double().cpu(), W1.double().cpu().view(count, 32, L1)[bucket.cpu()]) \
+        + b1.double().cpu().view(count, 32)[bucket.cpu()]
+    assert torch.equal(outs[0].cpu().double(), want)  # the FMA kernel is exact on these inputs
+    assert torch.equal(outs[1], outs[0])
