@@ -103,6 +103,9 @@ def parse_args():
                          "positions expanded on the GPU, or the expanded index lists")
     ap.add_argument("--ddp", default="fused", choices=["fused", "allreduce"],
                     help="table exchange at N > 1: peer-memory reduce-scatter/update/all-gather kernels, or NCCL all-reduce")
+    ap.add_argument("--rows-on-the-wire", default="int16", choices=["int16", "both", "fp32"],
+                    help="what the fused exchange's update stores into the other ranks: the int16 / PSQT rows their "
+                         "forward gathers (fp32 rows stay with their owner until sync_table), both, or the fp32 rows only")
     a = ap.parse_args()
     if a.workload != "sweep":
         a.l1 = (a.l1 or [3072])[0]
@@ -182,10 +185,11 @@ class ClockSampler:
 
 
 # ---------------------------------------------------------------------------
-def algorithmic_bytes_fwd(batch: int, l1: int, rows_per_persp: float, k_max: int = K_ACTIVE) -> float:
-    """Embedding-bag accounting: every (position, active row) counts a full row."""
-    W = l1 + 8
-    return batch * (2 * rows_per_persp * W * 4 + 2 * k_max * 4 + 24 + 3 * l1 * 4 + 8)
+def algorithmic_bytes_fwd(batch: int, l1: int, rows_per_persp: float, k_max: int = K_ACTIVE, table_bytes: int = 4) -> float:
+    """Embedding-bag accounting: every (position, active row) counts a full row (`table_bytes` per L1 column:
+    4 for the fp32 table, 2 for the int16 one; the one PSQT column a position reads stays fp32)."""
+    row = l1 * table_bytes + (8 * 4 if table_bytes == 4 else 4)
+    return batch * (2 * rows_per_persp * row + 2 * k_max * 4 + 24 + 3 * l1 * 4 + 8)
 
 
 def algorithmic_bytes_bwd(batch: int, l1: int, rows_per_persp: float, n_rows: int = N_ROWS, k_max: int = K_ACTIVE) -> float:
@@ -236,7 +240,7 @@ def build_model(l1: int, dev, feature: str = "HalfKAv2_hm^flat"):
     return model.to(dev)
 
 
-def build_step(model, world: int, ddp: str, slices, reduce_ctas: int):
+def build_step(model, world: int, ddp: str, slices, reduce_ctas: int, wire: str = "int16"):
     """(TrainStep, exchange or None) for `world` ranks."""
     from nnue_pytorch_b200.ddp import ShardedTableExchange, make_grad_hook
     from nnue_pytorch_b200.model import TrainStep
@@ -248,7 +252,7 @@ def build_step(model, world: int, ddp: str, slices, reduce_ctas: int):
             exchange = ShardedTableExchange(table, slices=slices, reduce_ctas=reduce_ctas)
         hook = make_grad_hook(model, world, average=False, skip=[table] if exchange is not None else [])
     step = TrainStep(model, lr=8.75e-4, clip=2.0, lam=1.0, grad_hook=hook, grad_prescale=1.0 / world,
-                     table_exchange=exchange)
+                     table_exchange=exchange, integer_rows={"int16": True, "both": "with_fp32", "fp32": False}[wire])
     return step, exchange
 
 
@@ -277,7 +281,7 @@ def exchange_check(args, dev, rank: int, world: int, bench_table: torch.Tensor, 
     step_ref, _ = build_step(ref, world, "allreduce", None, reduce_ctas)
     losses_ref = [float(step_ref(b)) for b in batches]
     fused = build_model(args.l1, dev)
-    step_fused, ex = build_step(fused, world, "fused", slices, reduce_ctas)
+    step_fused, ex = build_step(fused, world, "fused", slices, reduce_ctas, args.rows_on_the_wire)
     losses = [float(step_fused(b)) for b in batches]
     ex.uninstall()
     t_ref, t_fused = ref.input.features[0].weight.detach(), fused.input.features[0].weight.detach()
@@ -363,7 +367,7 @@ def run_step(args):
         args.slices == "on" or (args.slices == "auto" and world >= 8))
     slices = [0, n_rows - 704, n_rows] if sliced else None
     reduce_ctas = tuned.get("ddp_reduce_ctas", 32)
-    step, exchange = build_step(model, world, args.ddp, slices, reduce_ctas)
+    step, exchange = build_step(model, world, args.ddp, slices, reduce_ctas, args.rows_on_the_wire)
 
     from nnue_pytorch_b200 import positions
 
@@ -458,6 +462,8 @@ def run_step(args):
                      "seconds": n_sus * ms_sus * 1e-3, "clocks": sus_clocks.summary()}
 
     check = None
+    if exchange is not None:
+        exchange.sync_table()  # the fp32 rows the other ranks own (they stay there when only integer rows travel)
     if extras and world > 1 and exchange is not None:
         check = exchange_check(args, dev, rank, world, model.input.features[0].weight, slices, reduce_ctas)
 
@@ -480,11 +486,12 @@ def run_step(args):
     k_max = 32 if native else K_ACTIVE
     alg = {
         "k_fused_fwd": algorithmic_bytes_fwd(args.batch, args.l1, rows_pp, k_max),
+        "k_fused_fwd_q16": algorithmic_bytes_fwd(args.batch, args.l1, rows_pp, k_max, table_bytes=2),
         "k_segment_chunks": algorithmic_bytes_segment(args.batch, args.l1, rows_pp, n_rows),
         "k_bwd_prologue": args.batch * (5 * args.l1 * 4 + 2 * (args.l1 + 8) * 4 + 24),
         "k_ranger_rows": 32.0 * n_rows * (args.l1 + 8),
     }
-    bound_of = {"k_fused_fwd": "l2", "k_segment_chunks": "l2", "k_bwd_prologue": "hbm", "k_ranger_rows": "hbm"}
+    bound_of = {"k_fused_fwd": "l2", "k_fused_fwd_q16": "l2", "k_segment_chunks": "l2", "k_bwd_prologue": "hbm", "k_ranger_rows": "hbm"}
     kernels = {}
     for name, rec in kprof.items():
         ms = rec["total_ms"] / max(min(args.steps, 20), 1)  # per step (a step may launch a kernel more than once)
@@ -559,6 +566,8 @@ def run_step(args):
             "parallelism": f"dp{world}",
             "table_exchange": (args.ddp if world > 1 else "none"),
             "exchange_slices": (len(exchange.bounds) - 1) if exchange is not None else None,
+            "rows_on_the_wire": (args.rows_on_the_wire if exchange is not None and getattr(exchange, "_emit", None) is not None
+                                 else ("fp32" if exchange is not None else None)),
             "backward": args.bwd_mode,
             "l2_policy": "working set per step (table 286 MB + gradient + moments + activations > 2 GB) exceeds the 126 MB L2; "
                          f"{args.pool} distinct batches cycled",

@@ -241,7 +241,11 @@ int nnue_ft_virtual_grad(const float* grad, float* out, int64_t N,
  * counts).  While d_stats[0] != 0 the kernel ignores q16 and gathers
  * round((weight + virtual) * scale_main) / scale_main from the parameter blocks themselves (h_blocks: the
  * table's row ranges in order, their `rows` adding up to N), so the results never depend on the range; the
- * host does not have to read the words.  Needs L1 % 16 == 0, P % 4 == 0, K <= 511, a power-of-two scale_main.
+ * host does not have to read the words.  d_stats may hold n_stat_parts such pairs (parts of the table quantized
+ * by different kernels or ranks): any overflow counts, the largest max |k| rules.  A block whose `weight` is NULL
+ * has no fp32 parameters to fall back to (a data-parallel rank that only receives integer rows): the route is
+ * then refused and tallied in the device status word.  Needs L1 % 16 == 0, P % 4 == 0, K <= 511, a power-of-two
+ * scale_main.
  * Replaces the same reference code as nnue_ft_prepare_table + nnue_ft_fused_fwd. */
 typedef struct nnue_ft_block {
     const float* weight;          /* [rows, L1 + P] */
@@ -257,7 +261,7 @@ int nnue_ft_quantize_table(const float* weight, const float* virtual_weight,
 int nnue_ft_fused_fwd_q16(const float* us, const float* them,
                           const int32_t* white_idx, const int32_t* black_idx,
                           const int64_t* psqt_idx, const int16_t* q16, int64_t q16_pitch, const float* psqt,
-                          const float* bias_fq, float scale_main, const int32_t* d_stats,
+                          const float* bias_fq, float scale_main, const int32_t* d_stats, int32_t n_stat_parts,
                           const nnue_ft_block* h_blocks, int32_t n_blocks,
                           float max_act, float act_quant_scale, float act_quant_eps, float out_scale,
                           float* l0, float* wpsqt, float* bpsqt, float* saved,
@@ -423,6 +427,33 @@ int nnue_ddp_update_shard(float* const* h_table_ptrs, int32_t world, int32_t ran
                           float* grad_ma, float* neg_grad_ma, float* variance_ma,
                           float* slow, const float* d_grad_scale,
                           const nnue_ranger_hparams* h_hp, void* stream);
+
+/* nnue_ddp_update_shard that also (or instead) sends the other ranks what their next forward gathers: the
+ * rows of the integer table (nnue_ft_quantize_table's format) written into EVERY rank's int16 and PSQT
+ * tables with plain peer stores.  With fp32_to_peers = 0 the fp32 rows stay with their owner: half the bytes
+ * cross NVLink, and the other ranks' fp32 tables go stale outside their own share until the caller gathers them
+ * (checkpoints, evaluation through the fp32 table).  d_stats_local (device int32[2], zeroed by the caller before the
+ * first call of a step) collects the overflow count and max |k| of this rank's share; nnue_ddp_publish_stats then
+ * stores the pair into slot `rank` of every rank's statistics array (int32 [2 * world]), which the forward reads
+ * as `n_stat_parts = world` parts. */
+typedef struct nnue_ddp_emit {
+    int16_t* const* h_q16_ptrs;    /* host array of `world` device pointers */
+    float* const* h_psqt_ptrs;
+    int32_t* const* h_stats_ptrs;
+    int32_t* d_stats_local;
+    int64_t q16_pitch;
+    int32_t L1, P;
+    float scale_main, scale_psqt;
+    int32_t fp32_to_peers;
+} nnue_ddp_emit;
+
+int nnue_ddp_update_shard_emit(float* const* h_table_ptrs, int32_t world, int32_t rank,
+                               int64_t elem_begin, int64_t elem_end, const float* grad,
+                               float* grad_ma, float* neg_grad_ma, float* variance_ma,
+                               float* slow, const float* d_grad_scale,
+                               const nnue_ranger_hparams* h_hp, const nnue_ddp_emit* h_emit,
+                               void* stream);
+int nnue_ddp_publish_stats(const nnue_ddp_emit* h_emit, int32_t world, int32_t rank, void* stream);
 
 /* ---- layer stack behind the feature transformer --------------------------
  * Bucket-aware replacement of the three wide F.linear calls + row selection of

@@ -266,20 +266,27 @@ def quantize_bias_stats(bias: torch.Tensor, l1_size: int, scale_main: float, sca
     quantize_blocks([(bias.detach().reshape(1, -1), None)], l1_size, scale_main, scale_psqt, overflow=stats)
 
 
-def quantize_blocks(blocks, l1_size: int, scale_main: float, scale_psqt: float, overflow: torch.Tensor | None = None):
+def quantize_blocks(blocks, l1_size: int, scale_main: float, scale_psqt: float, overflow: torch.Tensor | None = None,
+                    out=None):
     """The integer form of the table the forward reads when weights are fake-quantized
     (`nnue_ft_quantize_table`, one launch per parameter block).  `blocks` is a list of
     (weight [rows, W], virtual_weight [n_virtual, W] or None) in table order.  Returns
     (q16 int16 [N, L1], psqt float32 [N, P], stats int32 [2] = entries outside int16, max |k|); a given
-    `overflow` (the stats of an earlier call) is updated instead of a fresh one."""
+    `overflow` (the stats of an earlier call) is updated instead of a fresh one; `out` = (q16 [N + 1, L1], psqt [N, P])
+    to write into existing buffers."""
     dev = _require_cuda(*[t for b in blocks for t in b if t is not None])
     W = blocks[0][0].shape[1]
     P = W - l1_size
     n_total = sum(w.shape[0] for w, _ in blocks)
     pitch = l1_size  # rows back to back (a padded pitch was measured: no faster on B200)
-    q16 = torch.empty(n_total + 1, pitch, dtype=torch.int16, device=dev)
+    if out is not None:
+        q16, psqt = out
+        assert q16.dtype == torch.int16 and tuple(q16.shape) == (n_total + 1, pitch) and q16.is_contiguous()
+        assert psqt.dtype == torch.float32 and tuple(psqt.shape) == (n_total, P) and psqt.is_contiguous()
+    else:
+        q16 = torch.empty(n_total + 1, pitch, dtype=torch.int16, device=dev)
+        psqt = torch.empty(n_total, max(P, 1), dtype=torch.float32, device=dev)[:, :P]
     q16[n_total].zero_()  # the all-zero row that padding and out-of-range list entries read
-    psqt = torch.empty(n_total, max(P, 1), dtype=torch.float32, device=dev)[:, :P]
     if overflow is None:
         overflow = torch.zeros(2, dtype=torch.int32, device=dev)
     lib = _lib.load()
@@ -302,9 +309,11 @@ def quantize_blocks(blocks, l1_size: int, scale_main: float, scale_psqt: float, 
 
 def fused_forward_q16(us, them, white_indices, black_indices, psqt_indices, q16, psqt, bias_fq, overflow, blocks,
                       scale_main: float, max_ft_activation, l1_size, act_quant_scale: float = 0.0,
-                      act_quant_eps: float = 0.0, out_scale: float = 1.0):
+                      act_quant_eps: float = 0.0, out_scale: float = 1.0, master: bool = True):
     """`nnue_ft_fused_fwd_q16`: the fused forward on the tensors `quantize_blocks` made (same outputs
-    and saved tensor as `fused_forward`)."""
+    and saved tensor as `fused_forward`).  `overflow` holds one or more [overflow count, max |k|] pairs.
+    `master=False`: the fp32 rows of the (single) block are not valid on this device; a forward that would need
+    them is reported by `device_status` instead."""
     dev = _require_cuda(us, them, white_indices, black_indices, psqt_indices, q16, bias_fq, overflow)
     assert us.dtype == torch.float32 and them.dtype == torch.float32
     assert white_indices.dtype == torch.int32 and black_indices.dtype == torch.int32 and psqt_indices.dtype == torch.int64
@@ -318,6 +327,10 @@ def fused_forward_q16(us, them, white_indices, black_indices, psqt_indices, q16,
     arr = (_lib.FtBlock * len(blocks))()
     for d, (w, v) in zip(arr, blocks):
         d.weight, d.virtual_weight, d.rows, d.n_virtual = _ptr(w), _ptr(v), w.shape[0], 0 if v is None else v.shape[0]
+    if not master:
+        assert len(blocks) == 1 and blocks[0][1] is None
+        arr[0].weight = None
+    assert overflow.dtype == torch.int32 and overflow.numel() % 2 == 0 and overflow.is_contiguous()
     l0 = torch.empty(B, l1_size, dtype=torch.float32, device=dev)
     wpsqt = torch.empty(B, 1, dtype=torch.float32, device=dev)
     bpsqt = torch.empty(B, 1, dtype=torch.float32, device=dev)
@@ -325,7 +338,7 @@ def fused_forward_q16(us, them, white_indices, black_indices, psqt_indices, q16,
     with torch.cuda.device(dev), _span("fused_fwd", dev):
         st = _lib.load().nnue_ft_fused_fwd_q16(
             _ptr(us), _ptr(them), _ptr(white_indices), _ptr(black_indices), _ptr(psqt_indices), _ptr(q16), q16.shape[1],
-            psqt.data_ptr() if P > 0 else None, _ptr(bias_fq), float(scale_main), _ptr(overflow), arr, len(blocks),
+            psqt.data_ptr() if P > 0 else None, _ptr(bias_fq), float(scale_main), _ptr(overflow), overflow.numel() // 2, arr, len(blocks),
             float(max_ft_activation), float(act_quant_scale), float(act_quant_eps), float(out_scale),
             _ptr(l0), _ptr(wpsqt), _ptr(bpsqt), _ptr(saved), B, K, N, l1_size, P, _stream(dev))
     _lib.check(st, "nnue_ft_fused_fwd_q16")
@@ -393,9 +406,13 @@ class QuantTableCache:
     Code that writes the parameter through raw pointers must call `mark` (after re-emitting) or
     `invalidate`."""
 
-    def __init__(self):
+    def __init__(self, owner=None):
+        """`owner`: who keeps the buffers up to date when they are shared between devices (a
+        `ddp.ShardedTableExchange`): a stale cache is then rebuilt by `owner.rebuild_integer_rows()`, into the
+        same buffers, and `owner.fp32_rows_valid` tells whether the fp32 rows may be read on this device."""
         self.q16 = self.psqt = self.stats = None
         self.key = None
+        self.owner = owner
 
     @staticmethod
     def _key(w, l1, scale_main, scale_psqt):
@@ -513,13 +530,30 @@ def ddp_reduce_shard(grad_ptrs: list[int], rank: int, elem_begin: int, elem_end:
     _lib.check(st, "nnue_ddp_reduce_shard")
 
 
+def ddp_emit_struct(q16_ptrs, psqt_ptrs, stats_ptrs, stats_local, pitch, l1, p, scale_main, scale_psqt, fp32_to_peers):
+    """`nnue_ddp_emit` over every rank's integer-table buffers; the pointer arrays stay alive with the struct."""
+    e = _lib.DdpEmit()
+    e._keep = tuple((C.c_void_p * len(a))(*a) for a in (q16_ptrs, psqt_ptrs, stats_ptrs))
+    e.h_q16_ptrs, e.h_psqt_ptrs, e.h_stats_ptrs = e._keep
+    e.d_stats_local, e.q16_pitch, e.L1, e.P = stats_local.data_ptr(), pitch, l1, p
+    e.scale_main, e.scale_psqt, e.fp32_to_peers = float(scale_main), float(scale_psqt), int(bool(fp32_to_peers))
+    return e
+
+
 def ddp_update_shard(table_ptrs: list[int], rank: int, elem_begin: int, elem_end: int, grad, grad_ma, neg_grad_ma,
-                     variance_ma, slow, grad_scale, hp) -> None:
+                     variance_ma, slow, grad_scale, hp, emit=None) -> None:
     dev = _require_cuda(grad, grad_ma, variance_ma)
     arr = (C.c_void_p * len(table_ptrs))(*table_ptrs)
     with torch.cuda.device(dev), _span("ddp_update", dev):
-        st = _lib.load().nnue_ddp_update_shard(
+        st = _lib.load().nnue_ddp_update_shard_emit(
             arr, len(table_ptrs), rank, elem_begin, elem_end, _ptr(grad), _ptr(grad_ma), _ptr(neg_grad_ma),
-            _ptr(variance_ma), _ptr(slow), _ptr(grad_scale), C.byref(hp), _stream(dev),
+            _ptr(variance_ma), _ptr(slow), _ptr(grad_scale), C.byref(hp),
+            C.byref(emit) if emit is not None else None, _stream(dev),
         )
-    _lib.check(st, "nnue_ddp_update_shard")
+    _lib.check(st, "nnue_ddp_update_shard_emit")
+
+
+def ddp_publish_stats(emit, world: int, rank: int, device) -> None:
+    with torch.cuda.device(device):
+        st = _lib.load().nnue_ddp_publish_stats(C.byref(emit), world, rank, _stream(device))
+    _lib.check(st, "nnue_ddp_publish_stats")

@@ -92,6 +92,15 @@ class TableEmit(C.Structure):
                 ("L1", C.c_int32), ("P", C.c_int32), ("scale_main", C.c_float), ("scale_psqt", C.c_float)]
 
 
+class DdpEmit(C.Structure):
+    """Mirror of `nnue_ddp_emit`."""
+
+    _fields_ = [("h_q16_ptrs", C.POINTER(C.c_void_p)), ("h_psqt_ptrs", C.POINTER(C.c_void_p)),
+                ("h_stats_ptrs", C.POINTER(C.c_void_p)), ("d_stats_local", C.c_void_p), ("q16_pitch", C.c_int64),
+                ("L1", C.c_int32), ("P", C.c_int32), ("scale_main", C.c_float), ("scale_psqt", C.c_float),
+                ("fp32_to_peers", C.c_int32)]
+
+
 class LsWeightScales(C.Structure):
     """Mirror of `nnue_ls_weight_scales`."""
 
@@ -159,7 +168,7 @@ PROTOTYPES = {
     "nnue_ft_quantize_table": (C.c_int, [_P, _P, _P, _I64, _P, _I64, _I64, _I32, _I32, C.c_float, C.c_float, _P, _P]),
     "nnue_ft_fused_fwd_q16": (
         C.c_int,
-        [_P] * 6 + [_I64, _P, _P, C.c_float, _P, C.POINTER(FtBlock), _I32, C.c_float, C.c_float, C.c_float, C.c_float,
+        [_P] * 6 + [_I64, _P, _P, C.c_float, _P, _I32, C.POINTER(FtBlock), _I32, C.c_float, C.c_float, C.c_float, C.c_float,
                     _P, _P, _P, _P, _I64, _I32, _I64, _I32, _I32, _P],
     ),
     "nnue_ft_virtual_grad": (C.c_int, [_P, _P, _I64, _I64, _I32, _P]),
@@ -176,6 +185,11 @@ PROTOTYPES = {
         C.c_int,
         [C.POINTER(_P), _I32, _I32, _I64, _I64, _P, _P, _P, _P, _P, _P, C.POINTER(RangerHParams), _P],
     ),
+    "nnue_ddp_update_shard_emit": (
+        C.c_int,
+        [C.POINTER(_P), _I32, _I32, _I64, _I64, _P, _P, _P, _P, _P, _P, C.POINTER(RangerHParams), C.POINTER(DdpEmit), _P],
+    ),
+    "nnue_ddp_publish_stats": (C.c_int, [C.POINTER(DdpEmit), _I32, _I32, _P]),
     "nnue_grad_sumsq_multi": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_int64), _I32, _P, _P]),
     "nnue_rangerlite_update_multi": (C.c_int, [C.POINTER(RangerTensor), _I32, _P, _P]),
     "nnue_lookahead_merge": (C.c_int, [_P, _P, _I64, C.c_float, _P]),

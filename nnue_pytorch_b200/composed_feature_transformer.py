@@ -109,15 +109,18 @@ class ComposedFeatureTransformer(nn.Module):
     keep_integer_table = False
 
     def invalidate_integer_table(self) -> None:
-        cache = getattr(self, "_q16_cache", None)
-        if cache is not None:
-            cache.invalidate()
+        for cache in (getattr(self, "_q16_cache", None), getattr(self.features[0].weight, "_nnue_q16_cache", None)):
+            if cache is not None:
+                cache.invalidate()
 
     def _table_cache(self):
         """One feature block without factor rows: its integer table can be kept between steps."""
-        if not self.keep_integer_table:
-            return None
         if len(self.features) != 1 or getattr(self.features[0], "virtual_weight", None) is not None:
+            return None
+        shared = getattr(self.features[0].weight, "_nnue_q16_cache", None)
+        if shared is not None and shared.owner is not None:
+            return shared  # a data-parallel exchange ships the integer rows between the ranks
+        if not self.keep_integer_table:
             return None
         cache = getattr(self, "_q16_cache", None)
         if cache is None:
@@ -129,15 +132,20 @@ class ComposedFeatureTransformer(nn.Module):
     def _integer_table_applies(self, indices: torch.Tensor, fake_quantize_weights: bool) -> bool:
         """The int16 form of the table is exact when every fake-quantized entry is an integer over a
         power-of-two scale shared by weights and bias, and a list holds at most 511 rows."""
-        if not (self.integer_table and fake_quantize_weights and self.bias.is_cuda and indices.is_cuda):
+        if not (fake_quantize_weights and indices.is_cuda and indices.shape[1] <= 511):
+            return False
+        return self.integer_table_possible()
+
+    def integer_table_possible(self) -> bool:
+        """What `_integer_table_applies` asks of the module itself, whatever the batch."""
+        if not (self.integer_table and self.bias.is_cuda):
             return False
         if not all(_fusable_feature(f) for f in self.features) or len(self.features) > 8:
             return False
         s = self.quantization.weight_scales_dict
         scale = float(s["ft_weight"])
         pow2 = scale > 0 and math.frexp(scale)[0] == 0.5
-        return (pow2 and float(s["ft_bias"]) == scale and indices.shape[1] <= 511 and self.l1_size % 16 == 0
-                and self.num_psqt_buckets % 4 == 0)
+        return pow2 and float(s["ft_bias"]) == scale and self.l1_size % 16 == 0 and self.num_psqt_buckets % 4 == 0
 
     @torch.no_grad()
     def coalesce(self) -> None:

@@ -39,7 +39,9 @@ int cuda_fail(cudaError_t e, const char* what);
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 // Device status word: [0] = count of out-of-range indices skipped,
-// [1] = count of bounded waits that ran out.  One per device, lazily resolved.
+// [1] = count of bounded waits that ran out, [2] = segments with repeated entries too long to sort
+// in shared memory (informational), [3] = forward warps that needed fp32 table rows and had none.
+// One per device, lazily resolved.
 unsigned long long* device_status_ptr();
 
 struct Tuning {
@@ -56,6 +58,7 @@ struct Tuning {
     int fwd_q16_variant = 0;  // compiled variant of the int16-table forward (see LAUNCH_Q16)
     int overlap_csr = 1;  // 1 = build the CSR on the helper stream, beside the backward prologue
     int ddp_reduce_ctas = 0;  // > 0: grid cap of the peer-load reduce (it runs beside the sliced backward)
+    int ddp_reduce_u = 0;     // > 0: float4 per thread and rank in flight in the peer-load reduce (1, 2, 4 or 8)
 };
 Tuning& tuning();
 

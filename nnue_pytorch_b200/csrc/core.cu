@@ -133,6 +133,7 @@ extern "C" int nnue_b200_tune(const char* key, int value) {
     else if (!strcmp(key, "fwd_variant")) t.fwd_variant = value;
     else if (!strcmp(key, "fwd_q16_variant")) t.fwd_q16_variant = value;
     else if (!strcmp(key, "ddp_reduce_ctas")) t.ddp_reduce_ctas = value;
+    else if (!strcmp(key, "ddp_reduce_u")) t.ddp_reduce_u = value;
     else if (!strcmp(key, "overlap_csr")) t.overlap_csr = value;
     else {
         set_error("nnue_b200_tune: unknown key '%s'", key);
@@ -253,6 +254,11 @@ extern "C" int nnue_b200_device_status(void* stream, int64_t* h_bad_index_count,
     if (h[1]) {
         set_error("%llu bounded device-side waits ran out", h[1]);
         return NNUE_ERR_TIMEOUT;
+    }
+    if (h[3]) {
+        set_error("%llu forward warps needed the fp32 table rows (a weight left the packed int16 range) "
+                  "and were given none", h[3]);
+        return NNUE_ERR_UNSUPPORTED;
     }
     return NNUE_OK;
 }

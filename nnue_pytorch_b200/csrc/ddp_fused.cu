@@ -100,12 +100,27 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// What the update kernel sends to the other ranks besides (or instead of) the fp32 rows: the rows of the
+// integer table their forward gathers (nnue_ft_quantize_table's format).  Half the bytes over NVLink when the
+// fp32 rows stay with their owner.
+struct PeerEmit {
+    int16_t* q16[kMaxRanks];
+    float* psqt[kMaxRanks];
+    int* stats_local;      // this rank's [overflow count, max |k|] of its share, accumulated over the step
+    long long pitch4;      // q16 row pitch in groups of four int16
+    int w4, l4, p4;        // float4 per table row, of them L1 part and PSQT part
+    float scale_main, scale_psqt;
+};
+
 // Moment tensors are shard-sized: element i of the table is element i - beg4 of them.
+// FP32_TO_PEERS: the new rows go into every rank's table (else only into the owner's).  EMIT: see PeerEmit.
+template <bool FP32_TO_PEERS, bool EMIT>
 __global__ void __launch_bounds__(kThreads)
     k_ddp_update_shard(PeerPtrs tables, int world, int rank, int64_t beg4, int64_t end4,
                        const float* __restrict__ grad, float* __restrict__ gm, float* __restrict__ ngm,
                        float* __restrict__ vm, float* __restrict__ slow,
-                       const float* __restrict__ d_scale, RangerConst c) {
+                       const float* __restrict__ d_scale, RangerConst c, PeerEmit pe) {
+    int bad = 0, max_abs = 0;
     const float scale = d_scale ? __ldg(d_scale) : 1.f;
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     const float4* g4 = reinterpret_cast<const float4*>(grad);
@@ -128,9 +143,155 @@ __global__ void __launch_bounds__(kThreads)
         if (!c.use_pnm || c.step_is_odd) gm4[j] = gmv;
         if (c.use_pnm && !c.step_is_odd) ngm4[j] = ngv;
         if (c.do_merge) slow4[j] = sv;
+        if (FP32_TO_PEERS) {
 #pragma unroll
-        for (int r = 0; r < kMaxRanks; ++r)
-            if (r < world) reinterpret_cast<float4*>(tables.p[r])[i] = pv;
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < world) reinterpret_cast<float4*>(tables.p[r])[i] = pv;
+        } else {
+            own[i] = pv;
+        }
+        if (EMIT) {
+            const unsigned row = (unsigned)i / (unsigned)pe.w4;  // the host checked that the index fits 31 bits
+            const int c4 = (int)((unsigned)i - row * (unsigned)pe.w4);
+            if (c4 < pe.l4) {
+                const float x[4] = {pv.x, pv.y, pv.z, pv.w};
+                int k[4];
+#pragma unroll
+                for (int q = 0; q < 4; ++q) {
+                    float rr = rintf(__fmul_rn(x[q], pe.scale_main));
+                    if (!(fabsf(rr) <= 32767.f)) {
+                        ++bad;
+                        rr = fminf(fmaxf(rr, -32767.f), 32767.f);
+                        if (rr != rr) rr = 0.f;
+                    }
+                    k[q] = (int)rr;
+                    max_abs = max(max_abs, abs(k[q]));
+                }
+                const int2 words = make_int2(k[1] * 65536 + k[0], k[3] * 65536 + k[2]);
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r)
+                    if (r < world) reinterpret_cast<int2*>(pe.q16[r])[(long long)row * pe.pitch4 + c4] = words;
+            } else {
+                auto fq = [&](float a) { return __fdiv_rn(rintf(__fmul_rn(a, pe.scale_psqt)), pe.scale_psqt); };
+                const float4 v = make_float4(fq(pv.x), fq(pv.y), fq(pv.z), fq(pv.w));
+#pragma unroll
+                for (int r = 0; r < kMaxRanks; ++r)
+                    if (r < world) reinterpret_cast<float4*>(pe.psqt[r])[(long long)row * pe.p4 + (c4 - pe.l4)] = v;
+            }
+        }
+    }
+    if (EMIT) {
+        if (bad) atomicAdd(pe.stats_local, bad);
+        max_abs = __reduce_max_sync(kFullMask, max_abs);
+        if ((threadIdx.x & 31) == 0 && max_abs > 0) atomicMax(pe.stats_local + 1, max_abs);
+    }
+}
+
+// The emitting update when the shard is whole table rows: a warp per row, a lane takes eight neighbouring L1
+// columns at a time (ten 16-byte loads in flight, one 16-byte store of int16 per rank), no division per element.
+template <bool FP32_TO_PEERS>
+__global__ void __launch_bounds__(kThreads)
+    k_ddp_update_rows(PeerPtrs tables, int world, int rank, int64_t row_beg, int64_t row_end, int64_t beg4,
+                      const float* __restrict__ grad, float* __restrict__ gm, float* __restrict__ ngm,
+                      float* __restrict__ vm, float* __restrict__ slow,
+                      const float* __restrict__ d_scale, RangerConst c, PeerEmit pe) {
+    int bad = 0, max_abs = 0;
+    const float scale = d_scale ? __ldg(d_scale) : 1.f;
+    const int lane = threadIdx.x & 31;
+    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
+    const int64_t n_warps = (int64_t)gridDim.x * kWarpsPerCta;
+    const float4* g4 = reinterpret_cast<const float4*>(grad);
+    float4* own = reinterpret_cast<float4*>(tables.p[rank]);
+    float4* gm4 = reinterpret_cast<float4*>(gm);
+    float4* ngm4 = reinterpret_cast<float4*>(ngm);
+    float4* vm4 = reinterpret_cast<float4*>(vm);
+    float4* slow4 = reinterpret_cast<float4*>(slow);
+
+    // the update of float4 number i of the table; returns the new parameter values
+    auto load = [&](int64_t i, float4& gv, float4& pv, float4& gmv, float4& vmv, float4& ngv, float4& sv) {
+        const int64_t j = i - beg4;
+        gv = __ldcs(g4 + i);
+        pv = own[i];
+        gmv = gm4[j];
+        vmv = vm4[j];
+        ngv = c.use_pnm ? ngm4[j] : f4_zero();
+        sv = c.do_merge ? slow4[j] : f4_zero();
+    };
+    auto finish = [&](int64_t i, float4 gv, float4& pv, float4 gmv, float4 vmv, float4 ngv, float4 sv) {
+        const int64_t j = i - beg4;
+        ranger_elem(c, scale, gv.x, pv.x, gmv.x, ngv.x, vmv.x, sv.x);
+        ranger_elem(c, scale, gv.y, pv.y, gmv.y, ngv.y, vmv.y, sv.y);
+        ranger_elem(c, scale, gv.z, pv.z, gmv.z, ngv.z, vmv.z, sv.z);
+        ranger_elem(c, scale, gv.w, pv.w, gmv.w, ngv.w, vmv.w, sv.w);
+        vm4[j] = vmv;
+        if (!c.use_pnm || c.step_is_odd) gm4[j] = gmv;
+        if (c.use_pnm && !c.step_is_odd) ngm4[j] = ngv;
+        if (c.do_merge) slow4[j] = sv;
+        if (FP32_TO_PEERS) {
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < world) reinterpret_cast<float4*>(tables.p[r])[i] = pv;
+        } else {
+            own[i] = pv;
+        }
+    };
+    auto to_int = [&](float x) {
+        float rr = rintf(__fmul_rn(x, pe.scale_main));
+        if (!(fabsf(rr) <= 32767.f)) {
+            ++bad;
+            rr = fminf(fmaxf(rr, -32767.f), 32767.f);
+            if (rr != rr) rr = 0.f;
+        }
+        const int k = (int)rr;
+        max_abs = max(max_abs, abs(k));
+        return k;
+    };
+
+    const int l8 = pe.l4 >> 1;
+    const long long pitch8 = pe.pitch4 >> 1;
+    for (int64_t row = row_beg + warp; row < row_end; row += n_warps) {
+        const int64_t r4 = row * pe.w4;
+        for (int pc = lane; pc < l8; pc += 32) {
+            const int64_t i = r4 + 2 * pc;
+            float4 g0, p0, m0, v0, n0, s0, g1, p1, m1, v1, n1, s1;
+            load(i, g0, p0, m0, v0, n0, s0);
+            load(i + 1, g1, p1, m1, v1, n1, s1);
+            finish(i, g0, p0, m0, v0, n0, s0);
+            finish(i + 1, g1, p1, m1, v1, n1, s1);
+            const int k0 = to_int(p0.x), k1 = to_int(p0.y), k2 = to_int(p0.z), k3 = to_int(p0.w);
+            const int k4 = to_int(p1.x), k5 = to_int(p1.y), k6 = to_int(p1.z), k7 = to_int(p1.w);
+            const uint4 words = make_uint4((unsigned)(k1 * 65536 + k0), (unsigned)(k3 * 65536 + k2),
+                                           (unsigned)(k5 * 65536 + k4), (unsigned)(k7 * 65536 + k6));
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < world) reinterpret_cast<uint4*>(pe.q16[r])[row * pitch8 + pc] = words;
+        }
+        for (int q = lane; q < pe.p4; q += 32) {
+            const int64_t i = r4 + pe.l4 + q;
+            float4 g0, p0, m0, v0, n0, s0;
+            load(i, g0, p0, m0, v0, n0, s0);
+            finish(i, g0, p0, m0, v0, n0, s0);
+            auto fq = [&](float a) { return __fdiv_rn(rintf(__fmul_rn(a, pe.scale_psqt)), pe.scale_psqt); };
+            const float4 v = make_float4(fq(p0.x), fq(p0.y), fq(p0.z), fq(p0.w));
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; ++r)
+                if (r < world) reinterpret_cast<float4*>(pe.psqt[r])[row * pe.p4 + q] = v;
+        }
+    }
+    if (bad) atomicAdd(pe.stats_local, bad);
+    max_abs = __reduce_max_sync(kFullMask, max_abs);
+    if (lane == 0 && max_abs > 0) atomicMax(pe.stats_local + 1, max_abs);
+}
+
+// This rank's range statistics into slot `rank` of every rank's statistics array.
+struct StatPtrs {
+    int* p[kMaxRanks];
+};
+__global__ void k_ddp_publish_stats(StatPtrs all, int world, int rank, const int* __restrict__ local) {
+    const int r = threadIdx.x;
+    if (r < world) {
+        all.p[r][2 * rank] = local[0];
+        all.p[r][2 * rank + 1] = local[1];
     }
 }
 
@@ -167,15 +328,26 @@ extern "C" int nnue_ddp_reduce_shard(float* const* h_grad_ptrs, int32_t world, i
     const int cap = std::min(kReduceMaxGrid, tuning().ddp_reduce_ctas > 0 ? tuning().ddp_reduce_ctas : sm_count() * 8);
     const unsigned grid = (unsigned)std::min<int64_t>((n4 + kThreads - 1) / kThreads, (int64_t)cap);
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (world <= 2)
-        k_ddp_reduce_shard<4, 2><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq);
-    else if (world <= 4)
-        k_ddp_reduce_shard<2, 4><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq);
-    else if (world <= 8)
-        k_ddp_reduce_shard<2, 8><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq);
-    else
-        k_ddp_reduce_shard<1, kMaxRanks><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4,
-                                                                  d_sumsq);
+    const int u = tuning().ddp_reduce_u;
+#define LAUNCH_RED(UU, WW) \
+    k_ddp_reduce_shard<UU, WW><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, d_sumsq)
+    ProfScope prof("k_ddp_reduce_shard", s);
+    if (world <= 2) {
+        if (u == 8) LAUNCH_RED(8, 2);
+        else if (u == 2) LAUNCH_RED(2, 2);
+        else LAUNCH_RED(4, 2);
+    } else if (world <= 4) {
+        if (u == 4) LAUNCH_RED(4, 4);
+        else if (u == 1) LAUNCH_RED(1, 4);
+        else LAUNCH_RED(2, 4);
+    } else if (world <= 8) {
+        if (u == 4) LAUNCH_RED(4, 8);
+        else if (u == 1) LAUNCH_RED(1, 8);
+        else LAUNCH_RED(2, 8);
+    } else {
+        LAUNCH_RED(1, kMaxRanks);
+    }
+#undef LAUNCH_RED
     NNUE_CUDA_TRY(cudaGetLastError());
     note_launches(1);
     return NNUE_OK;
@@ -186,6 +358,30 @@ extern "C" int nnue_ddp_update_shard(float* const* h_table_ptrs, int32_t world, 
                                      float* grad_ma, float* neg_grad_ma, float* variance_ma, float* slow,
                                      const float* d_grad_scale, const nnue_ranger_hparams* hp,
                                      void* stream) {
+    return nnue_ddp_update_shard_emit(h_table_ptrs, world, rank, elem_begin, elem_end, grad, grad_ma, neg_grad_ma,
+                                      variance_ma, slow, d_grad_scale, hp, nullptr, stream);
+}
+
+extern "C" int nnue_ddp_publish_stats(const nnue_ddp_emit* h_emit, int32_t world, int32_t rank, void* stream) {
+    NNUE_REQUIRE(h_emit && h_emit->h_stats_ptrs && h_emit->d_stats_local, NNUE_ERR_ARG, "nnue_ddp_publish_stats: null pointer");
+    NNUE_REQUIRE(world >= 1 && world <= kMaxRanks && rank >= 0 && rank < world, NNUE_ERR_ARG,
+                 "nnue_ddp_publish_stats: bad world / rank");
+    StatPtrs sp{};
+    for (int r = 0; r < world; ++r) {
+        NNUE_REQUIRE(h_emit->h_stats_ptrs[r] != nullptr, NNUE_ERR_ARG, "nnue_ddp_publish_stats: null statistics array");
+        sp.p[r] = h_emit->h_stats_ptrs[r];
+    }
+    k_ddp_publish_stats<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(sp, world, rank, h_emit->d_stats_local);
+    NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
+    return NNUE_OK;
+}
+
+extern "C" int nnue_ddp_update_shard_emit(float* const* h_table_ptrs, int32_t world, int32_t rank,
+                                          int64_t elem_begin, int64_t elem_end, const float* grad,
+                                          float* grad_ma, float* neg_grad_ma, float* variance_ma, float* slow,
+                                          const float* d_grad_scale, const nnue_ranger_hparams* hp,
+                                          const nnue_ddp_emit* h_emit, void* stream) {
     int rc = check_shard("nnue_ddp_update_shard", reinterpret_cast<const void* const*>(h_table_ptrs), world,
                          rank, elem_begin, elem_end);
     if (rc != NNUE_OK) return rc;
@@ -203,9 +399,54 @@ extern "C" int nnue_ddp_update_shard(float* const* h_table_ptrs, int32_t world, 
     for (int r = 0; r < world; ++r) pp.p[r] = h_table_ptrs[r];
     const int64_t n4 = (elem_end - elem_begin) / 4;
     const unsigned grid = (unsigned)std::min<int64_t>((n4 + kThreads - 1) / kThreads, (int64_t)sm_count() * 8);
-    k_ddp_update_shard<<<grid, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-        pp, world, rank, elem_begin / 4, elem_end / 4, grad, grad_ma, neg_grad_ma, variance_ma, slow,
-        d_grad_scale, *hp);
+    PeerEmit pe{};
+    bool fp32_to_peers = true;
+    if (h_emit) {
+        int e2 = 0;
+        NNUE_REQUIRE(h_emit->h_q16_ptrs && h_emit->d_stats_local && (h_emit->h_psqt_ptrs || h_emit->P == 0), NNUE_ERR_ARG,
+                     "nnue_ddp_update_shard_emit: null pointer");
+        NNUE_REQUIRE(h_emit->L1 > 0 && h_emit->L1 % 8 == 0 && h_emit->P >= 0 && h_emit->P % 4 == 0 &&
+                         h_emit->q16_pitch >= h_emit->L1 && h_emit->q16_pitch % 8 == 0,
+                     NNUE_ERR_ARG, "nnue_ddp_update_shard_emit: bad table shape (L1 %% 8, P %% 4, pitch %% 8)");
+        NNUE_REQUIRE(h_emit->scale_main > 0.f && frexpf(h_emit->scale_main, &e2) == 0.5f && h_emit->scale_psqt > 0.f,
+                     NNUE_ERR_UNSUPPORTED, "nnue_ddp_update_shard_emit: the main scale must be a power of two");
+        for (int r = 0; r < world; ++r) {
+            NNUE_REQUIRE(h_emit->h_q16_ptrs[r] && aligned16(h_emit->h_q16_ptrs[r]) &&
+                             (h_emit->P == 0 || (h_emit->h_psqt_ptrs[r] && aligned16(h_emit->h_psqt_ptrs[r]))),
+                         NNUE_ERR_ALIGN, "nnue_ddp_update_shard_emit: table of rank %d is null or not 16-byte aligned", r);
+            pe.q16[r] = h_emit->h_q16_ptrs[r];
+            pe.psqt[r] = h_emit->P ? h_emit->h_psqt_ptrs[r] : nullptr;
+        }
+        NNUE_REQUIRE(elem_end / 4 < 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "nnue_ddp_update_shard_emit: table too large");
+        pe.stats_local = h_emit->d_stats_local;
+        pe.pitch4 = h_emit->q16_pitch / 4;
+        pe.l4 = h_emit->L1 / 4;
+        pe.p4 = h_emit->P / 4;
+        pe.w4 = pe.l4 + pe.p4;
+        pe.scale_main = h_emit->scale_main;
+        pe.scale_psqt = h_emit->scale_psqt;
+        fp32_to_peers = h_emit->fp32_to_peers != 0;
+    }
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    ProfScope prof("k_ddp_update_shard", s);
+#define LAUNCH_UPD(FF, EE)                                                                                        \
+    k_ddp_update_shard<FF, EE><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, grad, grad_ma, \
+                                                         neg_grad_ma, variance_ma, slow, d_grad_scale, *hp, pe)
+    const int64_t w = (int64_t)pe.w4 * 4;
+    if (h_emit && elem_begin % w == 0 && elem_end % w == 0) {
+        // whole rows (what row-sliced shares are): a warp per row
+        const int64_t r0 = elem_begin / w, r1 = elem_end / w;
+        const unsigned rgrid = (unsigned)std::min<int64_t>((r1 - r0 + kWarpsPerCta - 1) / kWarpsPerCta, (int64_t)sm_count() * 8);
+        if (fp32_to_peers)
+            k_ddp_update_rows<true><<<rgrid, kThreads, 0, s>>>(pp, world, rank, r0, r1, elem_begin / 4, grad, grad_ma,
+                                                               neg_grad_ma, variance_ma, slow, d_grad_scale, *hp, pe);
+        else
+            k_ddp_update_rows<false><<<rgrid, kThreads, 0, s>>>(pp, world, rank, r0, r1, elem_begin / 4, grad, grad_ma,
+                                                                neg_grad_ma, variance_ma, slow, d_grad_scale, *hp, pe);
+    } else if (!h_emit) LAUNCH_UPD(true, false);
+    else if (fp32_to_peers) LAUNCH_UPD(true, true);
+    else LAUNCH_UPD(false, true);
+#undef LAUNCH_UPD
     NNUE_CUDA_TRY(cudaGetLastError());
     note_launches(1);
     return NNUE_OK;

@@ -180,7 +180,8 @@ __global__ void __launch_bounds__(kThreads, MINB)
                     const int32_t* __restrict__ wi, const int32_t* __restrict__ bi,
                     const int64_t* __restrict__ psqt_idx, const int16_t* __restrict__ q16, int64_t pitch8,
                     const float* __restrict__ psqt_tab, const float* __restrict__ bias, float scale,
-                    float inv_scale, const int* __restrict__ stats, const __grid_constant__ MasterBlocks mb,
+                    float inv_scale, const int* __restrict__ stats, int n_stat_parts,
+                    const __grid_constant__ MasterBlocks mb,
                     FtAct act, float* __restrict__ l0, float* __restrict__ wpsqt, float* __restrict__ bpsqt,
                     float* __restrict__ saved, int64_t B, int K, int64_t N, int L1, int P, int n_pos_groups,
                     int want_stage, unsigned long long* status) {
@@ -222,8 +223,12 @@ __global__ void __launch_bounds__(kThreads, MINB)
     const float4* bias4 = reinterpret_cast<const float4*>(bias);
 
     float4 f[4];  // this perspective: columns 2*c8, 2*c8+1 of the first half, then of the second half
-    const int max_abs = __ldg(stats + 1);
-    if (__ldg(stats) == 0 && max_abs <= kMaxAbsPacked) {
+    int overflow = 0, max_abs = 0;
+    for (int i = 0; i < n_stat_parts; ++i) {
+        overflow |= __ldg(stats + 2 * i);
+        max_abs = max(max_abs, __ldg(stats + 2 * i + 1));
+    }
+    if (overflow == 0 && max_abs <= kMaxAbsPacked) {
         const int rows_per_split = max_abs > 0 ? min(32767 / max_abs, 512) : 512;  // >= 8 > R
         PairAcc acc;
 #pragma unroll
@@ -252,7 +257,8 @@ __global__ void __launch_bounds__(kThreads, MINB)
         float4 sl[4];
 #pragma unroll
         for (int q = 0; q < 4; ++q) sl[q] = ok ? ldg4(bias4 + (q >> 1) * h4 + 2 * c8 + (q & 1)) : f4_zero();
-        gather_master(mb, L1 + P, N, list, n, c8, h4, ok, scale, inv_scale, sl, lane, status);
+        if (mb.weight[0] != nullptr) gather_master(mb, L1 + P, N, list, n, c8, h4, ok, scale, inv_scale, sl, lane, status);
+        else if (lane == 0 && tile == 0) atomicAdd(status + 3, 1ULL);  // nothing to fall back to: reported, sums = bias
 #pragma unroll
         for (int q = 0; q < 4; ++q) f[q] = sl[q];
     }
@@ -293,7 +299,8 @@ using namespace nnue;
 extern "C" int nnue_ft_fused_fwd_q16(const float* us, const float* them, const int32_t* white_idx,
                                      const int32_t* black_idx, const int64_t* psqt_idx, const int16_t* q16,
                                      int64_t q16_pitch, const float* psqt, const float* bias_fq, float scale_main,
-                                     const int32_t* d_overflow, const nnue_ft_block* h_blocks, int32_t n_blocks,
+                                     const int32_t* d_overflow, int32_t n_stat_parts, const nnue_ft_block* h_blocks,
+                                     int32_t n_blocks,
                                      float max_act, float act_quant_scale, float act_quant_eps, float out_scale,
                                      float* l0, float* wpsqt, float* bpsqt, float* saved, int64_t B, int32_t K,
                                      int64_t N, int32_t L1, int32_t P, void* stream) {
@@ -311,6 +318,7 @@ extern "C" int nnue_ft_fused_fwd_q16(const float* us, const float* them, const i
                  "nnue_ft_fused_fwd_q16: at most 511 rows per list keep the integer sum exact (K=%d)", K);
     NNUE_REQUIRE(scale_main > 0.f && frexpf(scale_main, &sc_exp) == 0.5f, NNUE_ERR_UNSUPPORTED,
                  "nnue_ft_fused_fwd_q16: the scale must be a power of two (got %g)", (double)scale_main);
+    NNUE_REQUIRE(n_stat_parts >= 1 && n_stat_parts <= 64, NNUE_ERR_ARG, "nnue_ft_fused_fwd_q16: 1..64 statistics parts");
     NNUE_REQUIRE(n_blocks >= 1 && n_blocks <= kMaxBlocks && h_blocks, NNUE_ERR_ARG,
                  "nnue_ft_fused_fwd_q16: 1..%d parameter blocks", kMaxBlocks);
     MasterBlocks mb;
@@ -318,7 +326,8 @@ extern "C" int nnue_ft_fused_fwd_q16(const float* us, const float* them, const i
     long long at = 0;
     for (int i = 0; i < n_blocks; ++i) {
         const nnue_ft_block& b = h_blocks[i];
-        NNUE_REQUIRE(b.rows >= 0 && (b.rows == 0 || b.weight), NNUE_ERR_ARG, "nnue_ft_fused_fwd_q16: block %d has no weights", i);
+        NNUE_REQUIRE(b.rows >= 0 && (b.rows == 0 || b.weight || n_blocks == 1), NNUE_ERR_ARG,
+                     "nnue_ft_fused_fwd_q16: block %d has no weights (allowed for a single block only)", i);
         NNUE_REQUIRE(!b.virtual_weight || (b.n_virtual > 0 && b.rows % b.n_virtual == 0), NNUE_ERR_ARG,
                      "nnue_ft_fused_fwd_q16: block %d: rows are not a multiple of the factor rows", i);
         NNUE_REQUIRE(aligned16(b.weight) && aligned16(b.virtual_weight), NNUE_ERR_ALIGN,
@@ -356,7 +365,7 @@ extern "C" int nnue_ft_fused_fwd_q16(const float* us, const float* them, const i
 #define LAUNCH_Q16(RR, MB)                                                                                  \
     k_fused_fwd_q16<RR, MB><<<grid, kThreads, stage ? smem : 0, s>>>(                                       \
         us, them, white_idx, black_idx, psqt_idx, q16, q16_pitch / 8, psqt, bias_fq, scale_main, inv_scale,    \
-        d_overflow, mb,                                                                                     \
+        d_overflow, n_stat_parts, mb,                                                                       \
         act, l0, wpsqt, bpsqt, saved, B, K, N, L1, P, (int)groups, stage, status)
     // variant = rows in flight per warp (R) and CTAs per SM the register budget must allow
     const int v = tuning().fwd_q16_variant;

@@ -198,6 +198,71 @@ class ShardedTableExchange:
             self._zeroed.record()
             self._local_reader = torch.cuda.Event()
         self._local_reader_pending = False
+        self._emit = None            # set by ship_integer_rows
+        self.fp32_rows_valid = True  # False: rows outside this rank's shares are older than their owner's
+
+    def ship_integer_rows(self, l1_size: int, scale_main: float, scale_psqt: float, fp32_to_peers: bool = False) -> None:
+        """From now on `update()` sends the other ranks the rows their forward actually gathers when weights are
+        fake-quantized: the int16 table and the fake-quantized PSQT columns (`nnue_ft_quantize_table`'s format,
+        (2 L1 + 4 P) bytes per row instead of 4 (L1 + P)), written by the update kernel from the new weights it
+        holds in registers.  The forward's values do not change by a bit.
+
+        With `fp32_to_peers=False` the fp32 rows no longer cross NVLink: every rank's parameter tensor stays
+        current only inside its own shares until `sync_table()` (called by `uninstall()` and `state_dict()`; call
+        it before anything else reads the parameter: evaluation through the fp32 table, serialization).  A weight
+        that leaves the packed int16 range (|w * scale| > 4095) has no fp32 route then: `device_status` reports it.
+        Collective; the ranks' tables must agree when it is called."""
+        from . import _launch
+
+        n, w = self.param.shape
+        l1, p = int(l1_size), w - int(l1_size)
+        assert l1 % 16 == 0 and p >= 0 and p % 4 == 0, "needs L1 % 16 == 0 and a PSQT width that is a multiple of 4"
+        dev = self.table.device
+        self._q16_buf = _alloc_shared((n + 1) * l1 // 2, dev, self.group)
+        self._psqt_buf = _alloc_shared(max(n * p, 4), dev, self.group)
+        self._stats_buf = _alloc_shared(max(2 * (self.world + 1), 4), dev, self.group)
+        q16 = self._q16_buf.view(torch.int16).view(n + 1, l1)
+        psqt = self._psqt_buf[: n * p].view(n, p)
+        stats = self._stats_buf.view(torch.int32)[: 2 * (self.world + 1)]
+        q16_ptrs, self._keep_q = _map_peers(self._q16_buf, self.group)
+        psqt_ptrs, self._keep_p = _map_peers(self._psqt_buf, self.group)
+        stats_ptrs, self._keep_s = _map_peers(self._stats_buf, self.group)
+        self._stats_local = torch.zeros(2, dtype=torch.int32, device=dev)
+        self._emit = _launch.ddp_emit_struct(q16_ptrs, psqt_ptrs, stats_ptrs, self._stats_local, l1, l1, p,
+                                             scale_main, scale_psqt, fp32_to_peers)
+        self._emit_key = (l1, float(scale_main), float(scale_psqt))
+        self._fp32_to_peers = bool(fp32_to_peers)
+        self.cache = _launch.QuantTableCache(owner=self)
+        self.cache.q16, self.cache.psqt, self.cache.stats = q16, psqt, stats
+        self.param._nnue_q16_cache = self.cache
+        self.fp32_rows_valid = True
+        self.rebuild_integer_rows()
+
+    def rebuild_integer_rows(self) -> None:
+        """The integer table again from the fp32 parameter, on every rank (after something other than `update()`
+        changed it: clipping, loading a checkpoint).  Collective."""
+        from . import _launch
+
+        assert self._emit is not None
+        self.sync_table()
+        l1, sm, sp = self._emit_key
+        c = self.cache
+        whole = torch.zeros(2, dtype=torch.int32, device=self.table.device)
+        _launch.quantize_blocks([(self.param.detach(), None)], l1, sm, sp, overflow=whole, out=(c.q16, c.psqt))
+        c.stats.view(self.world + 1, 2)[: self.world] = whole  # every rank's part: the whole table's figures
+        c.stats[-2:].zero_()
+        c.store(self.param, l1, sm, sp, c.q16, c.psqt, c.stats)
+        dist.all_reduce(self._token, group=self.group)  # nobody updates (stores into peers) before all have rebuilt
+
+    def sync_table(self) -> None:
+        """Every rank's fp32 parameter current again (the owners' rows gathered).  Collective; a no-op while the
+        fp32 rows travel with every update."""
+        if self.fp32_rows_valid:
+            return
+        n, w = self.param.shape
+        mine = torch.cat([self.table[e0:e1] for e0, e1 in self.ranges])
+        self.table.copy_(gather_sharded(mine, self.bounds, w, self.group).reshape(-1))
+        self.fp32_rows_valid = True
 
     def install(self) -> None:
         """Marks the table parameter: the fused backward of every op that reads it (or a table
@@ -213,6 +278,9 @@ class ShardedTableExchange:
         """Back to plain gradients: no shared buffer, no slices."""
         from . import _lib
 
+        self.sync_table()
+        if self._emit is not None and getattr(self.param, "_nnue_q16_cache", None) is self.cache:
+            del self.param._nnue_q16_cache  # the buffers are no longer kept up to date
         if getattr(self.param, "_nnue_exchange", None) is self:
             del self.param._nnue_exchange
         _lib.tune("ddp_reduce_ctas", 0)
@@ -262,15 +330,24 @@ class ShardedTableExchange:
     def update(self, hp, grad_scale: torch.Tensor | None) -> None:
         from . import _launch
 
+        emit = self._emit
+        if emit is not None:
+            self._stats_local.zero_()
         for (e0, e1), o0, o1 in zip(self.ranges, self.state_at[:-1], self.state_at[1:]):
             if e1 == e0:
                 continue
             _launch.ddp_update_shard(
                 self.table_ptrs, self.rank, e0, e1, self.grad, self.grad_ma[o0:o1],
                 None if self.neg_grad_ma is None else self.neg_grad_ma[o0:o1], self.variance_ma[o0:o1],
-                None if self.slow is None else self.slow[o0:o1], grad_scale, hp)
+                None if self.slow is None else self.slow[o0:o1], grad_scale, hp, emit=emit)
         cache = getattr(self.param, "_nnue_q16_cache", None)
-        if cache is not None:
+        if emit is not None:
+            _launch.ddp_publish_stats(emit, self.world, self.rank, self.table.device)
+            # every row has been rewritten from its owner's new weights once the fence below has passed
+            self.cache.store(self.param, *self._emit_key, self.cache.q16, self.cache.psqt, self.cache.stats)
+            if not self._fp32_to_peers and self.world > 1:
+                self.fp32_rows_valid = False
+        elif cache is not None:
             cache.invalidate()  # the table changed through raw (peer) stores: the forward quantizes it again
         # nobody may read its table before every rank has stored its share into it
         dist.all_reduce(self._token, group=self.group)
@@ -285,6 +362,7 @@ class ShardedTableExchange:
         """Full-size optimizer state of the table, gathered from the shares: the keys and shapes the
         reference's RangerLite keeps per parameter (model/optimizers/ranger_lite.py:268-278), so a checkpoint
         written under the exchange resumes without it and the other way round.  Collective."""
+        self.sync_table()  # the model's state dict is usually taken right beside this one
         out = {"step": self.step}
         n, w = self.param.shape
         for key, attr in self._STATE_KEYS:

@@ -130,19 +130,32 @@ class QuantizedFusedDoubleFtFunction(autograd.Function):
                   for i in range(0, len(params), 2)]
         if cache is not None and (len(blocks) != 1 or blocks[0][1] is not None):
             cache = None
-        if cache is not None and cache.fresh(params[0], l1, scale_main, scale_psqt):
+        master = True
+        if cache is not None and cache.owner is not None:
+            # buffers shared between data-parallel ranks, rewritten by the exchange's update kernel
+            if not cache.fresh(params[0], l1, scale_main, scale_psqt):
+                cache.owner.rebuild_integer_rows()  # collective: every rank sees the same staleness
+                if not cache.fresh(params[0], l1, scale_main, scale_psqt):
+                    raise RuntimeError("the exchange ships integer rows at another L1 size or scale than the forward uses")
+            q16, psqt, overflow = cache.q16, cache.psqt, cache.stats
+            master = cache.owner.fp32_rows_valid
+        elif cache is not None and cache.fresh(params[0], l1, scale_main, scale_psqt):
             q16, psqt, overflow = cache.q16, cache.psqt, cache.stats
         else:
             q16, psqt, overflow = _launch.quantize_blocks(blocks, l1, scale_main, scale_psqt)
             if cache is not None:
                 cache.store(params[0], l1, scale_main, scale_psqt, q16, psqt, overflow)
                 params[0]._nnue_q16_cache = cache  # where this package's optimizer looks for it
-        _launch.quantize_bias_stats(bias, l1, scale_main, scale_psqt, overflow)
+        bias_stats = overflow
+        if overflow.numel() > 2:  # per-rank parts of the table first, the bias in the last pair
+            bias_stats = overflow[-2:]
+            bias_stats.zero_()
+        _launch.quantize_bias_stats(bias, l1, scale_main, scale_psqt, bias_stats)
         bias_fq = torch.zeros_like(bias)
         _launch.prepare_table(bias.detach()[:l1].reshape(1, l1), None, l1, scale_main, 1.0, out=bias_fq, span="prepare_bias")
         l0, wpsqt, bpsqt, saved = _launch.fused_forward_q16(
             us, them, white_indices, black_indices, psqt_indices, q16, psqt, bias_fq, overflow, blocks, scale_main,
-            max_ft_activation, l1, act_quant_scale, act_quant_eps, out_scale)
+            max_ft_activation, l1, act_quant_scale, act_quant_eps, out_scale, master=master)
         ctx.save_for_backward(us, them, white_indices, black_indices, psqt_indices, saved)
         ctx.max_ft_activation, ctx.l1_size, ctx.out_scale = float(max_ft_activation), l1, float(out_scale)
         ctx.rows = [w.shape[0] for w, _ in blocks]

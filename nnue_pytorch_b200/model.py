@@ -232,12 +232,16 @@ class TrainStep:
 
     def __init__(self, model: NNUEModel, lr: float = 8.75e-4, clip: float = 2.0, lam: float = 1.0,
                  loss_params: LossParams | None = None, grad_hook=None, grad_prescale: float = 1.0,
-                 table_exchange=None, fused_loss: bool = True):
+                 table_exchange=None, fused_loss: bool = True, integer_rows: bool | str = True):
         """`grad_prescale`: factor that turns what `grad_hook` leaves in `.grad` into the true
         gradient (1/world when the hook sums over ranks without averaging).
         `table_exchange`: a `ddp.ShardedTableExchange` that owns the feature-transformer table
         (gradient reduce-scatter, sharded update, all-gather); the table then leaves the
-        optimizer's parameter groups."""
+        optimizer's parameter groups.
+        `integer_rows`: True lets the exchange send the ranks the int16 / PSQT rows their forward reads instead of
+        the fp32 rows (`ShardedTableExchange.ship_integer_rows`; the fp32 parameter is then current on every rank
+        only after `table_exchange.sync_table()`), "with_fp32" sends both, False only the fp32 rows.  Applies when
+        the table is the model's single feature block without factor rows and its scale is a power of two."""
         self.model = model
         # this loop's only writers of the table are the optimizer kernels, which rewrite the integer table too
         model.input.keep_integer_table = True
@@ -252,6 +256,12 @@ class TrainStep:
             groups[0]["params"] = [p for p in groups[0]["params"] if p is not table_exchange.param]
             groups = [g for g in groups if g["params"]]
             table_exchange.install()
+            inp = model.input
+            if (integer_rows and len(inp.features) == 1 and inp.features[0].weight is table_exchange.param
+                    and getattr(inp.features[0], "virtual_weight", None) is None and inp.integer_table_possible()):
+                s = inp.quantization.weight_scales_dict
+                table_exchange.ship_integer_rows(inp.l1_size, s["ft_weight"], s["ft_psqt_weight"],
+                                                 fp32_to_peers=(integer_rows == "with_fp32"))
         self._table_group = {"lr": lr, "betas": (0.9, 0.999), "eps": 1e-7, "pnm_momentum": 1.0}
         self.optimizer = RangerLite(
             groups, lr=1.0, weight_decay=0.0, use_legacy_scoping_bug=False,

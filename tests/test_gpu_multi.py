@@ -1,7 +1,8 @@
-"""Two-GPU check of the peer-memory table exchange (reduce-scatter + sharded
-RangerLite + all-gather kernels) against the plain NCCL all-reduce followed by
-the full optimizer step on every rank.  Needs two CUDA devices; on a
-single-GPU box the test reports itself as skipped."""
+"""Check of the peer-memory table exchange (reduce-scatter + sharded RangerLite +
+all-gather kernels, fp32 or integer rows on the wire) against the plain NCCL
+all-reduce followed by the full optimizer step on every rank.  The one-rank case
+runs the same kernels on a single device; the others need 2 and 4 CUDA devices
+and report themselves as skipped on a smaller box."""
 
 import os
 import socket
@@ -83,14 +84,28 @@ def _worker(rank, world, port, out_dir):
         ref_state = {k: v.clone() for k, v in step_ref.optimizer.state[ref.input.features[0].weight].items()
                      if torch.is_tensor(v)}
 
-        def run(slices):
+        def run(slices, wire=True):
+            """`wire`: what the update stores into the other ranks (True: the int16 / PSQT rows of the table the
+            forward gathers, "with_fp32": those and the fp32 rows, False: fp32 rows, quantized again by every rank)."""
             fused = build()
             table = fused.input.features[0].weight
             ex = ShardedTableExchange(table, slices=slices)
             step = TrainStep(fused, clip=2.0, grad_hook=make_grad_hook(fused, world, average=False, skip=[table]),
-                             grad_prescale=1.0 / world, table_exchange=ex)
-            losses = [float(step(b)) for b in batches]
+                             grad_prescale=1.0 / world, table_exchange=ex, integer_rows=wire)
+            assert (ex._emit is not None) == bool(wire)
+            losses = []
+            for i, b in enumerate(batches):
+                if i == 3 and wire:
+                    # a write behind the exchange's back (every rank the same one, here one that changes no value):
+                    # the integer rows are rebuilt from the owners' fp32 rows at the next forward
+                    with torch.no_grad():
+                        table.mul_(1.0)
+                    fused.input.invalidate_integer_table()
+                losses.append(float(step(b)))
+            if wire is True and world > 1:
+                assert not ex.fp32_rows_valid  # rows of other owners are stale here until the gather below
             ex.uninstall()
+            assert ex.fp32_rows_valid
             _launch.device_status(dev)
             sd = ex.state_dict()
             # the checkpoint round trip: what state_dict gathered, load_state_dict scatters back to the same shares
@@ -119,6 +134,8 @@ def _worker(rank, world, port, out_dir):
             "one_slice": run(None),
             "two_slices": run([0, n_rows - 704, n_rows]),           # factor rows last, reduce overlapped
             "four_slices": run([0, 9001, 9001, n_rows - 704, n_rows]),  # an empty slice and ragged shares
+            "fp32_rows": run(None, wire=False),
+            "both_rows": run([0, n_rows - 704, n_rows], wire="with_fp32"),
             "native_one_slice": run_native(None),
             "native_two_slices": run_native([0, 12288, 24576]),
         }
@@ -127,7 +144,7 @@ def _worker(rank, world, port, out_dir):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("world", [2, 4])
+@pytest.mark.parametrize("world", [1, 2, 4])
 def test_sharded_table_exchange_matches_allreduce(tmp_path, world):
     if not torch.cuda.is_available():
         pytest.fail("GPU tests need a CUDA device")
