@@ -62,10 +62,10 @@ MEAN_ACTIVE = 34.0  # expected rows per perspective: 2 * E[k], k ~ U{2..32}
 # ncu captures summarised under profiles/.  Recorded, not re-measured by a run of this file: the entry names
 # the summary it comes from, and a kernel that changed since then has no entry.
 RECORDED_DRAM_TRAFFIC = {
-    "k_segment_chunks": (1.084e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
-    "k_bwd_prologue": (1.008e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
-    "k_ranger_rows": (2.29e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
-    "k_fused_fwd": (0.950316288e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
+    "k_segment_chunks": (1.087e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
+    "k_bwd_prologue": (0.955e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
+    "k_ranger_rows": (2.350e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
+    "k_fused_fwd_q16": (0.740e9, "profiles/train_step_L3072_B16384_dram_traffic.md"),
 }
 
 
@@ -95,9 +95,11 @@ def parse_args():
     ap.add_argument("--no-extras", action="store_true",
                     help="only the timed loops: no spans pass, sustained block, L2 probe, quant_eval, exchange check")
     ap.add_argument("--tune", action="append", default=[], help="key=value, passed to nnue_b200_tune")
-    ap.add_argument("--slices", default="auto", choices=["auto", "on", "off"],
-                    help="fused exchange with the backward delivered in two row slices and the reduce of the first "
-                         "one overlapped with the second.  auto = on from 8 GPUs")
+    ap.add_argument("--slices", default="auto", choices=["auto", "on", "rows", "cols", "off"],
+                    help="fused exchange with the backward delivered in slices and the reduce of a slice overlapped "
+                         "with the computation of the next: cols = --col-slices column slices (free for the backward), "
+                         "rows = two row slices (factor rows last), on = cols, auto = cols from 4 GPUs")
+    ap.add_argument("--col-slices", type=int, default=4, help="number of column slices of --slices cols")
     ap.add_argument("--feed", default="packed", choices=["packed", "lists"],
                     help="what the end-to-end run copies from pinned host memory every step: 72-byte packed "
                          "positions expanded on the GPU, or the expanded index lists")
@@ -240,6 +242,17 @@ def build_model(l1: int, dev, feature: str = "HalfKAv2_hm^flat"):
     return model.to(dev)
 
 
+def column_slices(l1: int, n_psqt: int, n: int) -> list[int]:
+    """`n` column slices of the table's row (floats), on the backward's tile borders, tiles split evenly."""
+    from nnue_pytorch_b200 import _launch
+
+    w, tile = l1 + n_psqt, _launch.bwd_column_tile(l1, n_psqt)
+    tiles = (w + tile - 1) // tile
+    n = max(1, min(n, tiles))
+    cuts = sorted({(tiles * i) // n for i in range(1, n)})
+    return [0] + [c * tile for c in cuts if 0 < c * tile < w] + [w]
+
+
 def build_step(model, world: int, ddp: str, slices, reduce_ctas: int, wire: str = "int16"):
     """(TrainStep, exchange or None) for `world` ranks."""
     from nnue_pytorch_b200.ddp import ShardedTableExchange, make_grad_hook
@@ -249,7 +262,8 @@ def build_step(model, world: int, ddp: str, slices, reduce_ctas: int, wire: str 
     if world > 1:
         table = model.input.features[0].weight
         if ddp == "fused":
-            exchange = ShardedTableExchange(table, slices=slices, reduce_ctas=reduce_ctas)
+            rows, cols = (slices or {}).get("rows"), (slices or {}).get("cols")
+            exchange = ShardedTableExchange(table, slices=rows, col_slices=cols, reduce_ctas=reduce_ctas)
         hook = make_grad_hook(model, world, average=False, skip=[table] if exchange is not None else [])
     step = TrainStep(model, lr=8.75e-4, clip=2.0, lam=1.0, grad_hook=hook, grad_prescale=1.0 / world,
                      table_exchange=exchange, integer_rows={"int16": True, "both": "with_fp32", "fp32": False}[wire])
@@ -284,6 +298,29 @@ def exchange_check(args, dev, rank: int, world: int, bench_table: torch.Tensor, 
     step_fused, ex = build_step(fused, world, "fused", slices, reduce_ctas, args.rows_on_the_wire)
     losses = [float(step_fused(b)) for b in batches]
     ex.uninstall()
+
+    # the same reference with the table gradient summed in RANK ORDER, ((g0 + g1) + g2) + ..., which is the order
+    # of the peer-load reduce: fp32 sums of more than two terms depend on the order, NCCL's is its own
+    from nnue_pytorch_b200.ddp import make_grad_hook
+    from nnue_pytorch_b200.model import TrainStep
+
+    ordered = build_model(args.l1, dev)
+    o_table = ordered.input.features[0].weight
+    dense_hook = make_grad_hook(ordered, world, average=False, skip=[o_table])
+
+    def ordered_hook(model):
+        dense_hook(model)
+        parts = [torch.empty_like(o_table.grad) for _ in range(world)]
+        dist.all_gather(parts, o_table.grad.contiguous())
+        total = parts[0]
+        for part in parts[1:]:
+            total += part
+        o_table.grad = total
+
+    step_ordered = TrainStep(ordered, lr=8.75e-4, clip=2.0, lam=1.0, grad_hook=ordered_hook, grad_prescale=1.0 / world)
+    for b in batches:
+        step_ordered(b)
+    t_ordered = o_table.detach()
     t_ref, t_fused = ref.input.features[0].weight.detach(), fused.input.features[0].weight.detach()
     small = max(rel(p.detach(), q.detach()) for (n, p), (_, q) in zip(fused.named_parameters(), ref.named_parameters())
                 if "features" not in n)
@@ -295,6 +332,8 @@ def exchange_check(args, dev, rank: int, world: int, bench_table: torch.Tensor, 
         "loss_rel_err": max(abs(a - b) / abs(b) for a, b in zip(losses, losses_ref)),
         "steps": len(batches),
         "reference": "NCCL all-reduce of the table gradient + full RangerLite update on every rank",
+        "table_rel_err_vs_rank_ordered_sum": rel(fused.input.features[0].weight.detach(), t_ordered),
+        "table_bitwise_equal_to_rank_ordered_sum": bool(torch.equal(fused.input.features[0].weight.detach(), t_ordered)),
     })
     init = build_model(args.l1, dev).input.features[0].weight.detach()
     d_ref, d_fused = t_ref - init, t_fused - init
@@ -363,9 +402,17 @@ def run_step(args):
     n_rows = model.input.features[0].weight.shape[0]
     # --slices: the 704 factor rows (half of all entries) form the last slice, so the reduce of the
     # 22528 real rows can run while the factor rows' gradient is still being computed
-    sliced = world > 1 and args.ddp == "fused" and not native and (
-        args.slices == "on" or (args.slices == "auto" and world >= 8))
-    slices = [0, n_rows - 704, n_rows] if sliced else None
+    slices = None
+    if world > 1 and args.ddp == "fused":
+        kind = args.slices
+        if kind == "auto":
+            kind = "cols" if world >= 4 else "off"
+        if kind == "on":
+            kind = "cols"
+        if kind == "rows" and not native:
+            slices = {"rows": [0, n_rows - 704, n_rows]}
+        elif kind == "cols":
+            slices = {"cols": column_slices(args.l1, 8, args.col_slices)}
     reduce_ctas = tuned.get("ddp_reduce_ctas", 32)
     step, exchange = build_step(model, world, args.ddp, slices, reduce_ctas, args.rows_on_the_wire)
 
@@ -537,8 +584,10 @@ def run_step(args):
     bwd_ms = spans.get("fused_bwd", {}).get("mean_ms")
     calls = {}
     if fwd_ms:
-        g = algorithmic_bytes_fwd(args.batch, args.l1, rows_pp, k_max) / (fwd_ms * 1e-3) / 1e9
-        calls["fused_fwd"] = {"ms": fwd_ms, "algorithmic_GBps": g, "hbm_algorithmic_frac": g / peak}
+        int16 = "k_fused_fwd_q16" in kprof  # the forward gathered the int16 table: half the bytes per row
+        g = algorithmic_bytes_fwd(args.batch, args.l1, rows_pp, k_max, 2 if int16 else 4) / (fwd_ms * 1e-3) / 1e9
+        calls["fused_fwd"] = {"ms": fwd_ms, "algorithmic_GBps": g, "hbm_algorithmic_frac": g / peak,
+                              "table": "int16" if int16 else "fp32"}
     if bwd_ms:
         g = algorithmic_bytes_bwd(args.batch, args.l1, rows_pp, n_rows, k_max) / (bwd_ms * 1e-3) / 1e9
         calls["fused_bwd"] = {"ms": bwd_ms, "algorithmic_GBps": g, "hbm_algorithmic_frac": g / peak,
@@ -565,7 +614,9 @@ def run_step(args):
             "l1": args.l1,
             "parallelism": f"dp{world}",
             "table_exchange": (args.ddp if world > 1 else "none"),
-            "exchange_slices": (len(exchange.bounds) - 1) if exchange is not None else None,
+            "exchange_slices": (None if exchange is None else
+                                {"columns": exchange.col_bounds} if exchange.col_bounds is not None else
+                                {"rows": exchange.bounds}),
             "rows_on_the_wire": (args.rows_on_the_wire if exchange is not None and getattr(exchange, "_emit", None) is not None
                                  else ("fp32" if exchange is not None else None)),
             "backward": args.bwd_mode,

@@ -277,13 +277,25 @@ int nnue_ft_fused_fwd_q16(const float* us, const float* them,
  * between calls.  Every successful return has recorded every event exactly
  * once, also on the routes that finish the whole gradient at once (B == 0,
  * mode = NNUE_BWD_ATOMIC; NNUE_BWD_AUTO with slices is the segment route).
- * h_slices == NULL or n_slices == 0 is nnue_ft_fused_bwd. */
+ * h_slices == NULL or n_slices == 0 is nnue_ft_fused_bwd.
+ *
+ * by_columns != 0 slices the gradient by COLUMNS instead: row_bounds then holds
+ * column bounds in floats, the first 0 and the last L1 + P, every inner bound a
+ * multiple of nnue_ft_fused_bwd_column_tile(L1, P); columns [bounds[i], bounds[i+1])
+ * of ALL rows are final when events[i] is recorded.  The gather-sum walks the
+ * table's columns tile by tile anyway, so column slices cost it nothing (row
+ * slices make it read its scratch once per slice). */
 #define NNUE_BWD_MAX_SLICES 16
 typedef struct nnue_bwd_slices {
     int32_t n_slices;
     int64_t row_bounds[NNUE_BWD_MAX_SLICES + 1];
     void* events[NNUE_BWD_MAX_SLICES];
+    int32_t by_columns;
 } nnue_bwd_slices;
+
+/* Width in floats of the column tiles of the segment route at this shape under the current tuning (0 when the
+ * shape takes the scalar route, which cannot be sliced). */
+int32_t nnue_ft_fused_bwd_column_tile(int32_t L1, int32_t P);
 
 int nnue_ft_fused_bwd_sliced(const float* us, const float* them,
                              const int32_t* white_idx, const int32_t* black_idx,
@@ -427,6 +439,13 @@ int nnue_ddp_update_shard(float* const* h_table_ptrs, int32_t world, int32_t ran
                           float* grad_ma, float* neg_grad_ma, float* variance_ma,
                           float* slow, const float* d_grad_scale,
                           const nnue_ranger_hparams* h_hp, void* stream);
+
+/* nnue_ddp_reduce_shard over a 2-D block of the gradient viewed as [rows, width]: rows [row_begin, row_end), columns
+ * [col_begin, col_end) (floats, multiples of 4).  With the backward delivering column slices
+ * (nnue_bwd_slices.by_columns), a rank reduces that slice of its own rows while later columns are computed. */
+int nnue_ddp_reduce_block(float* const* h_grad_ptrs, int32_t world, int32_t rank, int64_t row_begin,
+                          int64_t row_end, int64_t col_begin, int64_t col_end, int64_t width,
+                          float* d_sumsq, void* stream);
 
 /* nnue_ddp_update_shard that also (or instead) sends the other ranks what their next forward gathers: the
  * rows of the integer table (nnue_ft_quantize_table's format) written into EVERY rank's int16 and PSQT

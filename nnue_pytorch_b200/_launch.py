@@ -194,8 +194,8 @@ def fused_backward(
     sink: torch.Tensor | None = None, slices=None,
 ):
     """`sink`: preallocated [num_inputs, num_outputs] destination of the table gradient (a fresh
-    tensor otherwise).  `slices`: (row bounds, torch events) to deliver the gradient slice by slice
-    (`nnue_ft_fused_bwd_sliced`); both belong to this one call."""
+    tensor otherwise).  `slices`: (bounds, torch events[, by_columns]) to deliver the gradient slice by slice
+    (`nnue_ft_fused_bwd_sliced`: row bounds, or column bounds in floats with by_columns); they belong to this one call."""
     dev = _require_cuda(us, grad_l0, grad_wpsqt, grad_bpsqt, saved)
     grad_l0 = grad_l0.contiguous()
     grad_wpsqt = grad_wpsqt.contiguous()
@@ -213,10 +213,11 @@ def fused_backward(
     grad_b = torch.empty(num_outputs, dtype=torch.float32, device=dev)
     spec = None
     if slices is not None:
-        bounds, events = slices
+        bounds, events = slices[0], slices[1]
         assert len(bounds) - 1 == len(events) <= _lib.MAX_SLICES
         spec = _lib.BwdSlices()
         spec.n_slices = len(events)
+        spec.by_columns = int(bool(slices[2])) if len(slices) > 2 else 0
         for i, b in enumerate(bounds):
             spec.row_bounds[i] = int(b)
         for i, e in enumerate(events):
@@ -528,6 +529,21 @@ def ddp_reduce_shard(grad_ptrs: list[int], rank: int, elem_begin: int, elem_end:
     with torch.cuda.device(dev), _span("ddp_reduce", dev):
         st = _lib.load().nnue_ddp_reduce_shard(arr, len(grad_ptrs), rank, elem_begin, elem_end, _ptr(sumsq), _stream(dev))
     _lib.check(st, "nnue_ddp_reduce_shard")
+
+
+def ddp_reduce_block(grad_ptrs: list[int], rank: int, row_begin: int, row_end: int, col_begin: int, col_end: int,
+                     width: int, sumsq: torch.Tensor) -> None:
+    dev = _require_cuda(sumsq)
+    arr = (C.c_void_p * len(grad_ptrs))(*grad_ptrs)
+    with torch.cuda.device(dev), _span("ddp_reduce", dev):
+        st = _lib.load().nnue_ddp_reduce_block(arr, len(grad_ptrs), rank, row_begin, row_end, col_begin, col_end, width,
+                                               _ptr(sumsq), _stream(dev))
+    _lib.check(st, "nnue_ddp_reduce_block")
+
+
+def bwd_column_tile(l1_size: int, n_psqt: int) -> int:
+    """Floats per column tile of the segment backward at this shape (what column slice bounds must be multiples of)."""
+    return int(_lib.load().nnue_ft_fused_bwd_column_tile(int(l1_size), int(n_psqt)))
 
 
 def ddp_emit_struct(q16_ptrs, psqt_ptrs, stats_ptrs, stats_local, pitch, l1, p, scale_main, scale_psqt, fp32_to_peers):

@@ -76,7 +76,8 @@ MAX_SLICES = 16  # NNUE_BWD_MAX_SLICES
 class BwdSlices(C.Structure):
     """Mirror of `nnue_bwd_slices`."""
 
-    _fields_ = [("n_slices", C.c_int32), ("row_bounds", C.c_int64 * (MAX_SLICES + 1)), ("events", C.c_void_p * MAX_SLICES)]
+    _fields_ = [("n_slices", C.c_int32), ("row_bounds", C.c_int64 * (MAX_SLICES + 1)), ("events", C.c_void_p * MAX_SLICES),
+                ("by_columns", C.c_int32)]
 
 
 class FtBlock(C.Structure):
@@ -189,6 +190,8 @@ PROTOTYPES = {
         C.c_int,
         [C.POINTER(_P), _I32, _I32, _I64, _I64, _P, _P, _P, _P, _P, _P, C.POINTER(RangerHParams), C.POINTER(DdpEmit), _P],
     ),
+    "nnue_ddp_reduce_block": (C.c_int, [C.POINTER(_P), _I32, _I32, _I64, _I64, _I64, _I64, _I64, _P, _P]),
+    "nnue_ft_fused_bwd_column_tile": (_I32, [_I32, _I32]),
     "nnue_ddp_publish_stats": (C.c_int, [C.POINTER(DdpEmit), _I32, _I32, _P]),
     "nnue_grad_sumsq_multi": (C.c_int, [C.POINTER(C.c_void_p), C.POINTER(C.c_int64), _I32, _P, _P]),
     "nnue_rangerlite_update_multi": (C.c_int, [C.POINTER(RangerTensor), _I32, _P, _P]),

@@ -134,6 +134,7 @@ extern "C" int nnue_b200_tune(const char* key, int value) {
     else if (!strcmp(key, "fwd_q16_variant")) t.fwd_q16_variant = value;
     else if (!strcmp(key, "ddp_reduce_ctas")) t.ddp_reduce_ctas = value;
     else if (!strcmp(key, "ddp_reduce_u")) t.ddp_reduce_u = value;
+    else if (!strcmp(key, "col_slice_streams")) t.col_slice_streams = value;
     else if (!strcmp(key, "overlap_csr")) t.overlap_csr = value;
     else {
         set_error("nnue_b200_tune: unknown key '%s'", key);

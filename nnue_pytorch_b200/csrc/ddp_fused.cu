@@ -100,6 +100,71 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
+// The same reduce over a 2-D block of the [rows, W4] gradient: rows [row0, row0 + n_rows), float4 columns
+// [c40, c40 + cols4) (a column slice of this rank's rows).  Linear index i of the block -> row i / cols4.
+template <int UN, int WMAX>
+__global__ void __launch_bounds__(kThreads)
+    k_ddp_reduce_block(PeerPtrs grads, int world, int rank, unsigned row0, unsigned n4, unsigned cols4, unsigned c40,
+                       unsigned W4, float* __restrict__ sumsq) {
+    __shared__ float s_w[kWarpsPerCta];
+    __shared__ bool s_last;
+    const unsigned stride = gridDim.x * blockDim.x;
+    float acc = 0.f;
+    auto at = [&](unsigned i) -> int64_t {
+        const unsigned r = i / cols4;
+        return (int64_t)(row0 + r) * W4 + c40 + (i - r * cols4);
+    };
+    for (unsigned i0 = blockIdx.x * blockDim.x + threadIdx.x; i0 < n4; i0 += stride * UN) {
+        float4 v[UN][WMAX];
+        int64_t idx[UN];
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            const unsigned i = i0 + u * stride;
+            idx[u] = i < n4 ? at(i) : -1;
+#pragma unroll
+            for (int r = 0; r < WMAX; ++r)
+                if (r < world && idx[u] >= 0) v[u][r] = __ldcs(reinterpret_cast<const float4*>(grads.p[r]) + idx[u]);
+        }
+#pragma unroll
+        for (int u = 0; u < UN; ++u) {
+            if (idx[u] < 0) break;
+            float4 s = v[u][0];
+#pragma unroll
+            for (int r = 1; r < WMAX; ++r)
+                if (r < world) s = f4_add(s, v[u][r]);
+            reinterpret_cast<float4*>(grads.p[rank])[idx[u]] = s;
+            acc += s.x * s.x + s.y * s.y + s.z * s.z + s.w * s.w;
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) acc += __shfl_xor_sync(kFullMask, acc, d);
+    if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = acc;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < kWarpsPerCta; ++w) t += s_w[w];
+        g_reduce_partial[blockIdx.x] = t;
+        __threadfence();
+        s_last = atomicAdd(&g_reduce_arrived, 1u) == gridDim.x - 1;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    float tot = 0.f;
+    for (unsigned i = threadIdx.x; i < gridDim.x; i += kThreads) tot += __ldcg(&g_reduce_partial[i]);
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) tot += __shfl_xor_sync(kFullMask, tot, d);
+    __syncthreads();
+    if ((threadIdx.x & 31) == 0) s_w[threadIdx.x >> 5] = tot;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < kWarpsPerCta; ++w) t += s_w[w];
+        *sumsq += t;
+        g_reduce_arrived = 0;
+    }
+}
+
 // What the update kernel sends to the other ranks besides (or instead of) the fp32 rows: the rows of the
 // integer table their forward gathers (nnue_ft_quantize_table's format).  Half the bytes over NVLink when the
 // fp32 rows stay with their owner.
@@ -187,11 +252,13 @@ __global__ void __launch_bounds__(kThreads)
     }
 }
 
-// The emitting update when the shard is whole table rows: a warp per row, a lane takes eight neighbouring L1
-// columns at a time (ten 16-byte loads in flight, one 16-byte store of int16 per rank), no division per element.
+// The emitting update when the shard is whole table rows: a warp per unit (a row, or one of `parts` equal column
+// ranges of a row; the host sizes the grid so that every warp gets the same number of units), a lane takes eight
+// neighbouring L1 columns at a time (ten 16-byte loads in flight, one 16-byte store of int16 per rank), no
+// division per element.
 template <bool FP32_TO_PEERS>
 __global__ void __launch_bounds__(kThreads)
-    k_ddp_update_rows(PeerPtrs tables, int world, int rank, int64_t row_beg, int64_t row_end, int64_t beg4,
+    k_ddp_update_rows(PeerPtrs tables, int world, int rank, int64_t row_beg, int64_t row_end, int parts, int64_t beg4,
                       const float* __restrict__ grad, float* __restrict__ gm, float* __restrict__ ngm,
                       float* __restrict__ vm, float* __restrict__ slow,
                       const float* __restrict__ d_scale, RangerConst c, PeerEmit pe) {
@@ -247,11 +314,14 @@ __global__ void __launch_bounds__(kThreads)
         return k;
     };
 
-    const int l8 = pe.l4 >> 1;
+    const int l8 = pe.l4 >> 1, per_part = l8 / parts;
     const long long pitch8 = pe.pitch4 >> 1;
-    for (int64_t row = row_beg + warp; row < row_end; row += n_warps) {
+    const int64_t n_units = (row_end - row_beg) * parts;
+    for (int64_t unit = warp; unit < n_units; unit += n_warps) {
+        const int64_t row = row_beg + unit / parts;
+        const int part = (int)(unit % parts);
         const int64_t r4 = row * pe.w4;
-        for (int pc = lane; pc < l8; pc += 32) {
+        for (int pc = part * per_part + lane; pc < (part + 1) * per_part; pc += 32) {
             const int64_t i = r4 + 2 * pc;
             float4 g0, p0, m0, v0, n0, s0, g1, p1, m1, v1, n1, s1;
             load(i, g0, p0, m0, v0, n0, s0);
@@ -266,7 +336,7 @@ __global__ void __launch_bounds__(kThreads)
             for (int r = 0; r < kMaxRanks; ++r)
                 if (r < world) reinterpret_cast<uint4*>(pe.q16[r])[row * pitch8 + pc] = words;
         }
-        for (int q = lane; q < pe.p4; q += 32) {
+        for (int q = lane; q < (part == 0 ? pe.p4 : 0); q += 32) {
             const int64_t i = r4 + pe.l4 + q;
             float4 g0, p0, m0, v0, n0, s0;
             load(i, g0, p0, m0, v0, n0, s0);
@@ -348,6 +418,47 @@ extern "C" int nnue_ddp_reduce_shard(float* const* h_grad_ptrs, int32_t world, i
         LAUNCH_RED(1, kMaxRanks);
     }
 #undef LAUNCH_RED
+    NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
+    return NNUE_OK;
+}
+
+extern "C" int nnue_ddp_reduce_block(float* const* h_grad_ptrs, int32_t world, int32_t rank, int64_t row_begin,
+                                     int64_t row_end, int64_t col_begin, int64_t col_end, int64_t width,
+                                     float* d_sumsq, void* stream) {
+    int rc = check_shard("nnue_ddp_reduce_block", reinterpret_cast<const void* const*>(h_grad_ptrs), world, rank, 0, 0);
+    if (rc != NNUE_OK) return rc;
+    NNUE_REQUIRE(d_sumsq != nullptr, NNUE_ERR_ARG, "nnue_ddp_reduce_block: null norm accumulator");
+    NNUE_REQUIRE(width > 0 && width % 4 == 0 && col_begin >= 0 && col_begin <= col_end && col_end <= width &&
+                     col_begin % 4 == 0 && col_end % 4 == 0 && row_begin >= 0 && row_begin <= row_end,
+                 NNUE_ERR_ARG, "nnue_ddp_reduce_block: bad block (whole float4 columns inside the row width)");
+    const int64_t cols4 = (col_end - col_begin) / 4, n4 = (row_end - row_begin) * cols4;
+    if (n4 == 0) return NNUE_OK;
+    NNUE_REQUIRE(n4 < 0x7fffffffLL - (int64_t)kReduceMaxGrid * kThreads * 8 && row_end < 0x7fffffffLL && width / 4 < 0x7fffffffLL,
+                 NNUE_ERR_UNSUPPORTED, "nnue_ddp_reduce_block: block too large for 32-bit indices");
+    PeerPtrs pp{};
+    for (int r = 0; r < world; ++r) pp.p[r] = h_grad_ptrs[r];
+    const int cap = std::min(kReduceMaxGrid, tuning().ddp_reduce_ctas > 0 ? tuning().ddp_reduce_ctas : sm_count() * 8);
+    const unsigned grid = (unsigned)std::min<int64_t>((n4 + kThreads - 1) / kThreads, (int64_t)cap);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    const int u = tuning().ddp_reduce_u;
+#define LAUNCH_BLK(UU, WW)                                                                                          \
+    k_ddp_reduce_block<UU, WW><<<grid, kThreads, 0, s>>>(pp, world, rank, (unsigned)row_begin, (unsigned)n4, (unsigned)cols4, \
+                                                         (unsigned)(col_begin / 4), (unsigned)(width / 4), d_sumsq)
+    ProfScope prof("k_ddp_reduce_block", s);
+    if (world <= 2) {
+        if (u == 8) LAUNCH_BLK(8, 2);
+        else LAUNCH_BLK(4, 2);
+    } else if (world <= 4) {
+        if (u == 4) LAUNCH_BLK(4, 4);
+        else LAUNCH_BLK(2, 4);
+    } else if (world <= 8) {
+        if (u == 4) LAUNCH_BLK(4, 8);
+        else LAUNCH_BLK(2, 8);
+    } else {
+        LAUNCH_BLK(1, kMaxRanks);
+    }
+#undef LAUNCH_BLK
     NNUE_CUDA_TRY(cudaGetLastError());
     note_launches(1);
     return NNUE_OK;
@@ -436,12 +547,19 @@ extern "C" int nnue_ddp_update_shard_emit(float* const* h_table_ptrs, int32_t wo
     if (h_emit && elem_begin % w == 0 && elem_end % w == 0) {
         // whole rows (what row-sliced shares are): a warp per row
         const int64_t r0 = elem_begin / w, r1 = elem_end / w;
-        const unsigned rgrid = (unsigned)std::min<int64_t>((r1 - r0 + kWarpsPerCta - 1) / kWarpsPerCta, (int64_t)sm_count() * 8);
+        const int l8 = h_emit->L1 / 8;
+        int parts = 1;  // units of whole warps' worth of column groups, so that no lane idles
+        for (int q = 8; q > 1; q >>= 1)
+            if (l8 % (32 * q) == 0) { parts = q; break; }
+        // every warp the same number of units: k = units per warp that fits the resident grid, then just enough CTAs
+        const int64_t units = (r1 - r0) * parts, max_warps = (int64_t)sm_count() * 8 * kWarpsPerCta;
+        const int64_t per_warp = (units + max_warps - 1) / max_warps;
+        const unsigned rgrid = (unsigned)((units + per_warp * kWarpsPerCta - 1) / (per_warp * kWarpsPerCta));
         if (fp32_to_peers)
-            k_ddp_update_rows<true><<<rgrid, kThreads, 0, s>>>(pp, world, rank, r0, r1, elem_begin / 4, grad, grad_ma,
+            k_ddp_update_rows<true><<<rgrid, kThreads, 0, s>>>(pp, world, rank, r0, r1, parts, elem_begin / 4, grad, grad_ma,
                                                                neg_grad_ma, variance_ma, slow, d_grad_scale, *hp, pe);
         else
-            k_ddp_update_rows<false><<<rgrid, kThreads, 0, s>>>(pp, world, rank, r0, r1, elem_begin / 4, grad, grad_ma,
+            k_ddp_update_rows<false><<<rgrid, kThreads, 0, s>>>(pp, world, rank, r0, r1, parts, elem_begin / 4, grad, grad_ma,
                                                                 neg_grad_ma, variance_ma, slow, d_grad_scale, *hp, pe);
     } else if (!h_emit) LAUNCH_UPD(true, false);
     else if (fp32_to_peers) LAUNCH_UPD(true, true);

@@ -508,6 +508,11 @@ static int resolve_mode(int mode) {
     return mode;
 }
 
+extern "C" int32_t nnue_ft_fused_bwd_column_tile(int32_t L1, int32_t P) {
+    if (L1 <= 0 || P < 0) return 0;
+    return (L1 % 8 == 0 && P % 4 == 0) ? csr_column_tile(L1 + P) : 0;
+}
+
 extern "C" size_t nnue_ft_fused_bwd_workspace_bytes(int64_t B, int32_t K, int64_t N, int32_t L1,
                                                     int32_t P, int32_t mode) {
     if (B < 0 || K < 0 || N < 0 || L1 <= 0 || P < 0) return 0;
@@ -544,7 +549,19 @@ static int fused_bwd_impl(const float* us, const float* them, const int32_t* whi
                  "nnue_ft_fused_bwd: unknown mode %d", mode);
     NNUE_REQUIRE(n_slices >= 0 && n_slices <= NNUE_BWD_MAX_SLICES, NNUE_ERR_ARG,
                  "nnue_ft_fused_bwd_sliced: 0..%d slices, got %d", NNUE_BWD_MAX_SLICES, n_slices);
-    if (n_slices > 0) {
+    const bool by_columns = n_slices > 0 && slices->by_columns != 0;
+    if (by_columns) {
+        const int tile_w = csr_column_tile(L1 + P);
+        NNUE_REQUIRE(slices->row_bounds[0] == 0 && slices->row_bounds[n_slices] == (int64_t)L1 + P, NNUE_ERR_ARG,
+                     "nnue_ft_fused_bwd_sliced: column bounds must run from 0 to L1 + P = %d", L1 + P);
+        for (int i = 0; i < n_slices; ++i) {
+            NNUE_REQUIRE(slices->row_bounds[i] <= slices->row_bounds[i + 1], NNUE_ERR_ARG,
+                         "nnue_ft_fused_bwd_sliced: column bounds must not decrease");
+            NNUE_REQUIRE(tile_w > 0 && (i == 0 || slices->row_bounds[i] % tile_w == 0 || slices->row_bounds[i] == (int64_t)L1 + P),
+                         NNUE_ERR_ARG, "nnue_ft_fused_bwd_sliced: inner column bounds must be multiples of %d floats "
+                         "(nnue_ft_fused_bwd_column_tile)", tile_w);
+        }
+    } else if (n_slices > 0) {
         NNUE_REQUIRE(slices->row_bounds[0] == 0 && slices->row_bounds[n_slices] == N, NNUE_ERR_ARG,
                      "nnue_ft_fused_bwd_sliced: row bounds must run from 0 to N = %lld", (long long)N);
         for (int i = 0; i < n_slices; ++i)
@@ -653,6 +670,32 @@ static int fused_bwd_impl(const float* us, const float* them, const int32_t* whi
     if (n_slices > 0 && vec && plan.S > 0) {
         // the gradient in row slices, an event after each: a consumer on another stream (the
         // data-parallel reduce) starts on slice i while slice i + 1 is computed
+        if (by_columns) {
+            // Column slices write disjoint columns, so their launches need no order among themselves: they
+            // alternate between the caller's stream and the helper stream, and the CTAs of slice i + 1 fill the
+            // SMs that the last wave of slice i leaves idle (each slice is only a few waves long).
+            SideStreamView side;
+            const bool two = tuning().col_slice_streams != 0 && n_slices > 1 && side_stream_get(side);
+            if (two) {
+                NNUE_CUDA_TRY(cudaEventRecord(side.fork, s));  // the helper sees G, the CSR and the caller's earlier work
+                NNUE_CUDA_TRY(cudaStreamWaitEvent(side.stream, side.fork, 0));
+            }
+            int rc_all = NNUE_OK;
+            for (int i = 0; i < n_slices; ++i) {
+                cudaStream_t st = (two && (i & 1)) ? side.stream : s;
+                rc = csr_reduce(plan, G, (int)W, grad_weight, st, 0, -1, slices->row_bounds[i], slices->row_bounds[i + 1]);
+                if (rc != NNUE_OK) { rc_all = rc; break; }
+                if (slices->events[i] && cudaEventRecord(static_cast<cudaEvent_t>(slices->events[i]), st) != cudaSuccess) {
+                    rc_all = cuda_fail(cudaGetLastError(), "slice event");
+                    break;
+                }
+            }
+            if (two) {  // always: the caller's stream must see the helper's work
+                NNUE_CUDA_TRY(cudaEventRecord(side.join, side.stream));
+                NNUE_CUDA_TRY(cudaStreamWaitEvent(s, side.join, 0));
+            }
+            return rc_all;
+        }
         for (int i = 0; i < n_slices; ++i) {
             rc = csr_reduce(plan, G, (int)W, grad_weight, s, slices->row_bounds[i], slices->row_bounds[i + 1]);
             if (rc != NNUE_OK) return rc;

@@ -330,6 +330,7 @@ __global__ void __launch_bounds__(kThreads)
 // chunk on a slice border runs in both slices and writes the same values twice.
 struct RowRange {
     int begin, end, max_chunks;
+    int tile0;  // first column tile of the launch (column slices); blockIdx.x counts tiles from it
 };
 __device__ __forceinline__ bool chunk_in_range(const int32_t* __restrict__ chunk_row, int c, const RowRange& rr) {
     if (__ldg(chunk_row + c) >= rr.end) return false;
@@ -365,7 +366,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
                      float4* __restrict__ partial, int64_t N, int n_chunk_groups, int S,
                      unsigned long long* status, RowRange rr) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x / n_chunk_groups;
+    const int tile = rr.tile0 + blockIdx.x / n_chunk_groups;
     const int c = (blockIdx.x % n_chunk_groups) * kWarpsPerCta + warp;
     const int E = __ldg(offsets + N);
     const int e_beg = c * S;
@@ -427,7 +428,7 @@ __global__ void __launch_bounds__(kThreads)
                     const float4* __restrict__ partial, float4* __restrict__ out, int64_t W4,
                     int64_t N, int n_chunk_groups, int S, RowRange rr) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = blockIdx.x / n_chunk_groups;
+    const int tile = rr.tile0 + blockIdx.x / n_chunk_groups;
     const int c = (blockIdx.x % n_chunk_groups) * kWarpsPerCta + warp;
     const int E = __ldg(offsets + N);
     const int e_beg = c * S;
@@ -645,15 +646,26 @@ int csr_build(const CsrPlan& plan, const int32_t* const* lists, cudaStream_t s) 
     return NNUE_OK;
 }
 
+static int segment_unroll(int64_t W4) {
+    int U = tuning().bwd_u;
+    if (U != 1 && U != 2 && U != 4) U = 2;
+    while (U > 1 && W4 <= 32 * (U / 2)) U /= 2;
+    return U;
+}
+
+int csr_column_tile(int W) { return W % 4 == 0 ? 32 * segment_unroll(W / 4) * 4 : 0; }
+
 int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStream_t s, int64_t row_begin,
-               int64_t row_end) {
+               int64_t row_end, int64_t col_begin, int64_t col_end) {
     const int64_t N = plan.N, src_rows = plan.B * plan.n_lists;
     if (N == 0) return NNUE_OK;
     if (row_end < 0 || row_end > N) row_end = N;
+    if (col_end < 0 || col_end > W) col_end = W;
     NNUE_REQUIRE(row_begin >= 0 && row_begin <= row_end, NNUE_ERR_ARG, "csr: bad row range");
-    if (row_begin == row_end) return NNUE_OK;
-    const bool whole = row_begin == 0 && row_end == N;
-    const RowRange rr{(int)row_begin, (int)row_end, (int)plan.max_chunks};
+    NNUE_REQUIRE(col_begin >= 0 && col_begin <= col_end, NNUE_ERR_ARG, "csr: bad column range");
+    if (row_begin == row_end || col_begin == col_end) return NNUE_OK;
+    const bool whole = row_begin == 0 && row_end == N && col_begin == 0 && col_end == W;
+    RowRange rr{(int)row_begin, (int)row_end, (int)plan.max_chunks, 0};
     unsigned long long* status = device_status_ptr();
     NNUE_REQUIRE(status, NNUE_ERR_CUDA, "csr: no device status word");
     const int64_t row_groups = (N + kWarpsPerCta - 1) / kWarpsPerCta;
@@ -661,10 +673,14 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
     const bool vec = (W % 4 == 0) && aligned16(src) && aligned16(out);
     if (vec) {
         const int64_t W4 = W / 4;
-        int U = tuning().bwd_u;
-        if (U != 1 && U != 2 && U != 4) U = 2;
-        while (U > 1 && W4 <= 32 * (U / 2)) U /= 2;
-        const int64_t tiles = (W4 + 32 * U - 1) / (32 * U);
+        const int U = segment_unroll(W4);
+        const int64_t all_tiles = (W4 + 32 * U - 1) / (32 * U);
+        const int tile_w = 32 * U * 4;
+        NNUE_REQUIRE(col_begin % tile_w == 0 && (col_end % tile_w == 0 || col_end == W), NNUE_ERR_ARG,
+                     "csr: column bounds must be multiples of %d floats", tile_w);
+        const int64_t tile_b = col_begin / tile_w, tile_e = col_end == W ? all_tiles : col_end / tile_w;
+        const int64_t tiles = S > 0 ? tile_e - tile_b : all_tiles;
+        rr.tile0 = (int)tile_b;
         const float4* s4 = reinterpret_cast<const float4*>(src);
         float4* o4 = reinterpret_cast<float4*>(out);
         if (S > 0) {
@@ -672,7 +688,7 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
             NNUE_REQUIRE(tiles * groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
             const unsigned grid = (unsigned)(tiles * groups);
             float4* p4 = reinterpret_cast<float4*>(plan.partial);
-            {
+            if (tile_b == 0) {  // whole rows, with the first column slice
                 ProfScope prof("k_zero_empty_rows", s);
                 k_zero_empty_rows<<<(unsigned)((row_end - row_begin + kWarpsPerCta - 1) / kWarpsPerCta), kThreads, 0, s>>>(
                     plan.offsets, o4, W4, row_begin, row_end);
@@ -703,7 +719,7 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
             else k_segment_fixup<4><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);
             note_launches(3);
         } else {
-            NNUE_REQUIRE(whole, NNUE_ERR_UNSUPPORTED, "csr: row slices need the chunked reduction (seg_chunk > 0)");
+            NNUE_REQUIRE(whole, NNUE_ERR_UNSUPPORTED, "csr: slices need the chunked reduction (seg_chunk > 0)");
             NNUE_REQUIRE(tiles * row_groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
             const unsigned grid = (unsigned)(tiles * row_groups);
             const int long_row = tuning().long_row;
@@ -719,7 +735,7 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
             note_launches(1);
         }
     } else {
-        NNUE_REQUIRE(whole, NNUE_ERR_UNSUPPORTED, "csr: row slices need 16-byte aligned rows");
+        NNUE_REQUIRE(whole, NNUE_ERR_UNSUPPORTED, "csr: slices need 16-byte aligned rows");
         const int64_t tiles = (W + 31) / 32;
         NNUE_REQUIRE(tiles * row_groups <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "csr: grid too large");
         k_segment_reduce_scalar<<<(unsigned)(tiles * row_groups), kThreads, 0, s>>>(

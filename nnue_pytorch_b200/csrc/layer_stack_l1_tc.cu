@@ -13,7 +13,9 @@
 // stages: all threads copy their 16-byte pieces with cp.async straight into the
 // 128-byte-swizzled K-major layout the matrix descriptors name, one thread issues
 // four tcgen05.mma (M = 128, N = 32, K = 8) per stage and commits them to the
-// stage's mbarrier, which frees the stage for the next copy.  The instruction is
+// stage's mbarrier, which frees the stage for a later copy: the copy of chunk
+// c + kTcAhead waits for the instructions of chunk c - kTcLag, issued kTcLag
+// iterations earlier, so their latency stays off the loop's critical path.  The instruction is
 // M = 128 (rows = TMEM lanes, one per position); rows 64..127 multiply whatever
 // follows the tile in shared memory and are never read back.  The accumulator
 // (128 lanes x 32 columns of tensor memory) comes back with tcgen05.ld, one
@@ -23,13 +25,16 @@
 
 namespace nnue {
 
-constexpr int kTcStages = 6;
+constexpr int kTcStages = 8;                      // ring of shared-memory stages
+constexpr int kTcLag = 3;                         // chunks whose tcgen05.mma may still be running when the next is issued
+constexpr int kTcAhead = kTcStages - kTcLag;      // chunks whose copies are in flight
 constexpr int kTcK = 32;                          // floats per stage along K: one 128-byte swizzle row
 constexpr int kTcABytes = kTP * 128;              // 8 KiB: 64 positions x 128 B
 constexpr int kTcBBytes = kLsOut * 128;           // 4 KiB: 32 outputs x 128 B
 constexpr int kTcStageBytes = kTcABytes + kTcBBytes;
 constexpr int kTcTailBytes = 128 * 128 - kTcStageBytes;  // what an M = 128 read of the last stage reaches beyond it
-constexpr int kTcSmemBytes = 1024 + kTcStages * kTcStageBytes + kTcTailBytes + 64;
+constexpr int kTcBarBytes = 16 * ((8 * (kTcStages + 1) + 15) / 16);  // one mbarrier per stage and one for the tile
+constexpr int kTcSmemBytes = 1024 + kTcStages * kTcStageBytes + kTcTailBytes + kTcBarBytes;
 constexpr int kTcThreads = 128;
 constexpr int kTcCols = 32;                       // TMEM columns: the 32 outputs
 
@@ -127,9 +132,9 @@ __global__ void __launch_bounds__(kTcThreads)
 
     bool failed = false;
 #pragma unroll
-    for (int c = 0; c < kTcStages - 1; ++c) issue(c);
+    for (int c = 0; c < kTcAhead; ++c) issue(c);
     for (int c = 0; c < chunks; ++c) {
-        cp_async_wait<kTcStages - 2>();                                   // this thread's pieces of chunk c are in
+        cp_async_wait<kTcAhead - 1>();                                    // this thread's pieces of chunk c are in
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");      // ... and visible to the tensor core's reads
         __syncthreads();                                                  // ... and so are everybody's
         if (tid == 0 && !failed) {
@@ -142,11 +147,11 @@ __global__ void __launch_bounds__(kTcThreads)
             umma_commit(bar_free + c % kTcStages);
             if (c == chunks - 1) umma_commit(bar_done);
         }
-        // the stage chunk c + kTcStages - 1 goes into was read by the MMAs of chunk c - 1
-        const int next = c + kTcStages - 1;
-        if (next < chunks && c >= 1) {
-            const int s = (c - 1) % kTcStages;
-            if (!mbar_wait_bounded(bar_free + s, (unsigned)(((c - 1) / kTcStages) & 1))) failed = true;
+        // the stage chunk c + kTcAhead goes into was read by the MMAs of chunk c - kTcLag
+        const int next = c + kTcAhead;
+        if (next < chunks && c >= kTcLag) {
+            const int s = (c - kTcLag) % kTcStages;
+            if (!mbar_wait_bounded(bar_free + s, (unsigned)(((c - kTcLag) / kTcStages) & 1))) failed = true;
         }
         if (__syncthreads_or(failed)) {  // one decision for the CTA
             failed = true;

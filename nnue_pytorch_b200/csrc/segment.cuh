@@ -58,7 +58,11 @@ bool side_stream_get(SideStreamView& out);
 // out[r, :] = sum of the source rows named by the entries of r, for every r < N.
 // Rows [row_begin, row_end) only (row_end < 0: to the last row); the chunked
 // vector path supports any range, the fallbacks only the whole table.
+// Columns [col_begin, col_end) only (floats; col_end < 0: to the last column): the chunked vector path, bounds on
+// whole column tiles (csr_column_tile).
 int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStream_t s, int64_t row_begin = 0,
-               int64_t row_end = -1);
+               int64_t row_end = -1, int64_t col_begin = 0, int64_t col_end = -1);
+// Floats per column tile of the chunked vector path for rows of W floats (0: W is not a multiple of 4).
+int csr_column_tile(int W);
 
 }  // namespace nnue

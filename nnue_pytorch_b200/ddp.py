@@ -150,10 +150,14 @@ class ShardedTableExchange:
     reduce traffic then hides behind their computation."""
 
     def __init__(self, param: torch.nn.Parameter, group=None, pnm: bool = True, lookahead: bool = True,
-                 slices: list[int] | None = None, reduce_ctas: int = 32):
+                 slices: list[int] | None = None, reduce_ctas: int = 32, col_slices: list[int] | None = None):
         """`reduce_ctas`: grid cap of the peer-load reduce while it runs beside the sliced backward
         (it needs few SMs to fill the links and takes them from the gather kernel); measured on
-        8 GPUs: 32 -> 3.42 ms per step, 64 -> 3.43, 96 -> 3.53, uncapped and unsliced 3.55."""
+        8 GPUs: 32 -> 3.42 ms per step, 64 -> 3.43, 96 -> 3.53, uncapped and unsliced 3.55.
+        `col_slices` (column bounds in floats, first 0, last the row width, inner ones multiples of
+        `_launch.bwd_column_tile`) slices the gradient by columns instead: the backward's gather-sum walks the
+        columns tile by tile anyway, so the slices cost it nothing, every rank keeps ONE share of whole rows, and
+        the reduce of column slice i (this rank's rows, those columns) runs beside the computation of slice i + 1."""
         assert param.is_cuda and param.dim() == 2 and param.dtype == torch.float32
         self.group = group if group is not None else dist.group.WORLD
         self.world, self.rank = dist.get_world_size(self.group), dist.get_rank(self.group)
@@ -164,6 +168,12 @@ class ShardedTableExchange:
         assert self.bounds[0] == 0 and self.bounds[-1] == n and all(
             a <= b for a, b in zip(self.bounds[:-1], self.bounds[1:])), "slices must run from 0 to the row count"
         assert len(self.bounds) - 1 <= 16
+        self.col_bounds = None
+        if col_slices:
+            assert not slices, "row slices and column slices exclude each other"
+            self.col_bounds = [int(b) for b in col_slices]
+            assert self.col_bounds[0] == 0 and self.col_bounds[-1] == w and len(self.col_bounds) - 1 <= 16 and all(
+                a <= b and a % 4 == 0 for a, b in zip(self.col_bounds[:-1], self.col_bounds[1:])), "bad column slices"
         dev = param.device
         self.table = _alloc_shared(n * w, dev, self.group)
         self.grad = _alloc_shared(n * w, dev, self.group)
@@ -186,11 +196,12 @@ class ShardedTableExchange:
         self.ft_sumsq = torch.zeros(1, device=dev)
         self._token = torch.zeros(1, device=dev)
         self.grad_view = self.grad.view(n, w)
-        self.sliced = len(self.ranges) > 1
+        self.sliced = len(self.ranges) > 1 or self.col_bounds is not None
         self.reduce_ctas = int(reduce_ctas)
         if self.sliced:
             self.comm_stream = torch.cuda.Stream(dev, priority=-1)  # its CTAs go first when an SM frees up
-            self.slice_events = [torch.cuda.Event() for _ in self.ranges]
+            n_events = len(self.col_bounds) - 1 if self.col_bounds is not None else len(self.ranges)
+            self.slice_events = [torch.cuda.Event() for _ in range(n_events)]
             for e in self.slice_events:
                 e.record()  # creates the CUDA event the library will record
             self._reduced = torch.cuda.Event()
@@ -286,8 +297,12 @@ class ShardedTableExchange:
         _lib.tune("ddp_reduce_ctas", 0)
 
     def slice_spec(self):
-        """(row bounds, events) for `nnue_ft_fused_bwd_sliced`, or None when the gradient is taken whole."""
-        return (self.bounds, self.slice_events) if self.sliced else None
+        """(bounds, events, by_columns) for `nnue_ft_fused_bwd_sliced`, or None when the gradient is taken whole."""
+        if not self.sliced:
+            return None
+        if self.col_bounds is not None:
+            return (self.col_bounds, self.slice_events, True)
+        return (self.bounds, self.slice_events, False)
 
     def note_local_reader(self) -> None:
         """Called after a kernel of THIS rank that reads the unsummed gradient buffer has been
@@ -318,10 +333,18 @@ class ShardedTableExchange:
                 comm.wait_event(self._local_reader)
                 self._local_reader_pending = False
             with torch.cuda.stream(comm):
-                for ev, (e0, e1) in zip(self.slice_events, self.ranges):
-                    comm.wait_event(ev)                           # this rank has finished the slice ...
-                    dist.all_reduce(self._token, group=self.group)  # ... and so has every other rank
-                    _launch.ddp_reduce_shard(self.grad_ptrs, self.rank, e0, e1, self.ft_sumsq)
+                if self.col_bounds is not None:
+                    w = self.param.shape[1]
+                    r0, r1 = self.ranges[0][0] // w, self.ranges[0][1] // w
+                    for ev, c0, c1 in zip(self.slice_events, self.col_bounds[:-1], self.col_bounds[1:]):
+                        comm.wait_event(ev)
+                        dist.all_reduce(self._token, group=self.group)
+                        _launch.ddp_reduce_block(self.grad_ptrs, self.rank, r0, r1, c0, c1, w, self.ft_sumsq)
+                else:
+                    for ev, (e0, e1) in zip(self.slice_events, self.ranges):
+                        comm.wait_event(ev)                           # this rank has finished the slice ...
+                        dist.all_reduce(self._token, group=self.group)  # ... and so has every other rank
+                        _launch.ddp_reduce_shard(self.grad_ptrs, self.rank, e0, e1, self.ft_sumsq)
                 self._reduced.record(comm)
             cur.wait_event(self._reduced)
         dist.all_reduce(self.ft_sumsq, group=self.group)

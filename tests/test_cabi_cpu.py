@@ -53,9 +53,10 @@ def test_host_side_argument_validation(lib):
     assert lib.nnue_b200_tune(b"no_such_knob", 1) == -1
     assert lib.nnue_rangerlite_update(None, None, None, None, None, None, None, None, 1, 1, None, None) == -1
     # newer entry points: the same convention
-    def sliced(n, *bounds):
+    def sliced(n, *bounds, by_columns=0):
         sp = _lib.BwdSlices()
         sp.n_slices = n
+        sp.by_columns = by_columns
         for i, b in enumerate(bounds):
             sp.row_bounds[i] = b
         return lib.nnue_ft_fused_bwd_sliced(None, None, None, None, None, 1.0, 1.0, None, None, None, None, None, None,
@@ -66,6 +67,10 @@ def test_host_side_argument_validation(lib):
     assert sliced(1, 0, 9) == -1 and b"row bounds" in lib.nnue_b200_last_error()       # does not end at N
     assert sliced(17, 0) == -1 and b"slices" in lib.nnue_b200_last_error()             # too many
     assert sliced(2, 0, 4, 10) == -1 and b"null output" in lib.nnue_b200_last_error()  # valid slices: next check
+    assert sliced(1, 0, 10, by_columns=1) == -1 and b"column bounds" in lib.nnue_b200_last_error()   # must end at L1 + P
+    assert sliced(2, 0, 8, 16, by_columns=1) == -1 and b"multiples of 128" in lib.nnue_b200_last_error()
+    assert sliced(1, 0, 16, by_columns=1) == -1 and b"null output" in lib.nnue_b200_last_error()
+    assert lib.nnue_ft_fused_bwd_column_tile(3072, 8) == 256 and lib.nnue_ft_fused_bwd_column_tile(7, 8) == 0
     assert lib.nnue_l2_read_probe(None, 0, 1, 1, 0, None, None) == -1
     assert lib.nnue_b200_profile(1) == 0 and lib.nnue_b200_profile(0) == 0
     assert lib.nnue_batch_build_halfka(None, 4, 7, 64, None, None, None, None, None, None, None, None, None) == -1  # layout

@@ -401,12 +401,17 @@ def test_fused_epilogue_matches_separate_ops(dev):
 
 
 @pytest.mark.parametrize("mode", ["segment", "atomic"])
-@pytest.mark.parametrize("bounds", [[0, 23232], [0, 5000, 23232], [0, 7509, 15018, 22528, 23232], [0, 0, 1, 23231, 23232, 23232]])
+@pytest.mark.parametrize("bounds", [[0, 23232], [0, 5000, 23232], [0, 7509, 15018, 22528, 23232], [0, 0, 1, 23231, 23232, 23232],
+                                    ("cols", [0, 264]), ("cols", [0, 256, 264]), ("cols", [0, 0, 256, 256, 264, 264])])
 def test_sliced_backward_is_bitwise_the_unsliced_one(dev, bounds, mode):
     """The gradient produced slice by slice (what the data-parallel exchange
     consumes while later slices are still computed) has the bits of the
     one-launch gradient, and every slice event is recorded by the call -- also
-    on the atomic route, which finishes the whole gradient at once."""
+    on the atomic route, which finishes the whole gradient at once.  Slices are
+    row ranges, or (marked "cols") column ranges on the gather-sum's tile borders."""
+    by_columns = isinstance(bounds, tuple)
+    if by_columns:
+        bounds = bounds[1]
     from nnue_pytorch_b200 import _launch, positions
 
     b = positions.generate_batch(2048, 11, layout="baseline")
@@ -437,7 +442,7 @@ def test_sliced_backward_is_bitwise_the_unsliced_one(dev, bounds, mode):
     # record above, while an event it does record stays pending until the work in front of it drains
     torch.cuda._sleep(200_000_000)
     sink = torch.full((positions.NUM_INPUTS_BASELINE, 264), float("nan"), device=dev)
-    got_w, got_b = backward((bounds, events), sink)
+    got_w, got_b = backward((bounds, events, by_columns), sink)
     assert not any(e.query() for e in events), "every slice event must be re-recorded behind the pending work"
     blocker.record()
     torch.cuda.synchronize()
@@ -447,6 +452,21 @@ def test_sliced_backward_is_bitwise_the_unsliced_one(dev, bounds, mode):
         assert torch.equal(got_w, ref_w) and torch.equal(got_b, ref_b)
     else:
         assert max_rel_err(got_w.cpu(), ref_w.cpu()) <= TOL and max_rel_err(got_b.cpu(), ref_b.cpu()) <= TOL
+
+
+def test_column_slices_must_sit_on_tile_borders(dev):
+    from nnue_pytorch_b200 import _launch, _lib
+
+    assert _launch.bwd_column_tile(256, 8) == 256 and _launch.bwd_column_tile(3072, 8) == 256
+    assert _launch.bwd_column_tile(255, 8) == 0  # the scalar route has no tiles
+    z = lambda *s, dt=torch.float32: torch.zeros(*s, dtype=dt, device=dev)  # noqa: E731
+    ev = [torch.cuda.Event() for _ in range(2)]
+    for e in ev:
+        e.record()
+    with pytest.raises(_lib.NnueB200Error, match="multiples of 256"):
+        _launch.fused_backward(z(4, 1), z(4, 1), z(4, 8, dt=torch.int32), z(4, 8, dt=torch.int32), z(4, dt=torch.int64),
+                               1.0, 256, 100, 264, z(4, 256), z(4, 1), z(4, 1), z(4, 4, 128), mode="segment",
+                               slices=([0, 128, 264], ev, True))
 
 
 def test_sliced_backward_records_events_for_an_empty_batch(dev):

@@ -84,12 +84,12 @@ def _worker(rank, world, port, out_dir):
         ref_state = {k: v.clone() for k, v in step_ref.optimizer.state[ref.input.features[0].weight].items()
                      if torch.is_tensor(v)}
 
-        def run(slices, wire=True):
+        def run(slices, wire=True, cols=None):
             """`wire`: what the update stores into the other ranks (True: the int16 / PSQT rows of the table the
             forward gathers, "with_fp32": those and the fp32 rows, False: fp32 rows, quantized again by every rank)."""
             fused = build()
             table = fused.input.features[0].weight
-            ex = ShardedTableExchange(table, slices=slices)
+            ex = ShardedTableExchange(table, slices=slices, col_slices=cols)
             step = TrainStep(fused, clip=2.0, grad_hook=make_grad_hook(fused, world, average=False, skip=[table]),
                              grad_prescale=1.0 / world, table_exchange=ex, integer_rows=wire)
             assert (ex._emit is not None) == bool(wire)
@@ -136,9 +136,21 @@ def _worker(rank, world, port, out_dir):
             "four_slices": run([0, 9001, 9001, n_rows - 704, n_rows]),  # an empty slice and ragged shares
             "fp32_rows": run(None, wire=False),
             "both_rows": run([0, n_rows - 704, n_rows], wire="with_fp32"),
+            "one_column_slice": run(None, cols=[0, 136]),
             "native_one_slice": run_native(None),
             "native_two_slices": run_native([0, 12288, 24576]),
         }
+        # column slices sit on the gather-sum's tile borders: 128 floats with one float4 per lane, so the
+        # 136-float rows of this small model split into two
+        from nnue_pytorch_b200 import _lib
+
+        _lib.tune("bwd_u", 1)
+        try:
+            assert _launch.bwd_column_tile(128, 8) == 128
+            report["two_column_slices"] = run(None, cols=[0, 128, 136])
+            report["column_slices_with_an_empty_one"] = run(None, cols=[0, 128, 128, 136], wire=False)
+        finally:
+            _lib.tune("bwd_u", 2)
         torch.save(report, os.path.join(out_dir, f"rank{rank}.pt"))
     finally:
         dist.destroy_process_group()
