@@ -97,8 +97,10 @@ def parse_args():
     ap.add_argument("--tune", action="append", default=[], help="key=value, passed to nnue_b200_tune")
     ap.add_argument("--slices", default="auto", choices=["auto", "on", "rows", "cols", "off"],
                     help="fused exchange with the backward delivered in slices and the reduce of a slice overlapped "
-                         "with the computation of the next: cols = --col-slices column slices (free for the backward), "
-                         "rows = two row slices (factor rows last), on = cols, auto = cols from 4 GPUs")
+                         "with the computation of the next: rows = two row slices (factor rows last), cols = "
+                         "--col-slices column slices, on = rows, auto = rows from 4 GPUs (measured: 2 GPUs 2.69 ms "
+                         "unsliced against 2.77 in column slices; 4 GPUs 2.76 unsliced, 2.72 rows, 2.78 columns; "
+                         "8 GPUs 2.90 unsliced, 2.72 rows, 2.93 columns)")
     ap.add_argument("--col-slices", type=int, default=4, help="number of column slices of --slices cols")
     ap.add_argument("--feed", default="packed", choices=["packed", "lists"],
                     help="what the end-to-end run copies from pinned host memory every step: 72-byte packed "
@@ -406,14 +408,15 @@ def run_step(args):
     if world > 1 and args.ddp == "fused":
         kind = args.slices
         if kind == "auto":
-            kind = "cols" if world >= 4 else "off"
+            kind = "rows" if world >= 4 else "off"
         if kind == "on":
-            kind = "cols"
+            kind = "rows"
         if kind == "rows" and not native:
             slices = {"rows": [0, n_rows - 704, n_rows]}
         elif kind == "cols":
             slices = {"cols": column_slices(args.l1, 8, args.col_slices)}
-    reduce_ctas = tuned.get("ddp_reduce_ctas", 32)
+    # grid cap of the reduce that runs beside the sliced backward: few CTAs fill the links of 7 peers, 3 peers need more
+    reduce_ctas = tuned.get("ddp_reduce_ctas", 32 if world >= 8 else 96)
     step, exchange = build_step(model, world, args.ddp, slices, reduce_ctas, args.rows_on_the_wire)
 
     from nnue_pytorch_b200 import positions
@@ -720,7 +723,16 @@ def sweep_point(l1, batch, active, mode, iters, warmup, flush, dev, features, sk
     def bwd():
         _launch.fused_backward(us, them, wi, bi, ps, max_act, l1, n_rows, W, gl0, gp, gp, saved[0], mode)
 
+    # the forward of the quantized model: the same operator on the int16 image of the fake-quantized table
+    q16, psqt_tab, q_stats = _launch.quantize_blocks([(w, None)], l1, 256.0, 9600.0)
+    bias_fq = torch.zeros_like(bias)
+    _launch.prepare_table(bias[:l1].reshape(1, l1), None, l1, 256.0, 1.0, out=bias_fq, span="prepare_bias")
+
+    def fwd16():
+        _launch.fused_forward_q16(us, them, wi, bi, ps, q16, psqt_tab, bias_fq, q_stats, [(w, None)], 256.0, max_act, l1)
+
     t_f = _time_launches(fwd, iters, warmup, fl)
+    t_f16 = _time_launches(fwd16, iters, warmup, fl)
     t_b = _time_launches(bwd, iters, warmup, fl)
     warm = None
     if flush:  # the steady-state figures as well: same launches back to back, nothing evicted in between
@@ -732,6 +744,9 @@ def sweep_point(l1, batch, active, mode, iters, warmup, flush, dev, features, sk
         "l1": l1, "batch": batch, "active_real_per_perspective": active or "U[2,32]", "rows_per_perspective": rows_per_persp,
         "skew": skew, "list_stats": stats,
         "fwd_ms": t_f, "fwd_algorithmic_GBps": common / t_f / 1e6, "fwd_frac_of_hbm": common / t_f / 1e6 / peak,
+        "fwd_int16_ms": t_f16,
+        "fwd_int16_algorithmic_GBps": algorithmic_bytes_fwd(batch, l1, rows_per_persp, k_max, 2) / t_f16 / 1e6,
+        "fwd_int16_frac_of_hbm": algorithmic_bytes_fwd(batch, l1, rows_per_persp, k_max, 2) / t_f16 / 1e6 / peak,
         "bwd_ms": t_b, "bwd_algorithmic_GBps": (common + n_rows * W * 4) / t_b / 1e6,
         "bwd_frac_of_hbm": (common + n_rows * W * 4) / t_b / 1e6 / peak,
         "rows": n_rows, "max_active": k_max,

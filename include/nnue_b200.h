@@ -607,6 +607,27 @@ int nnue_quant_eval_tiled(const int32_t* white_idx, const int32_t* black_idx,
                           const nnue_quant_params* h_qp, void* workspace,
                           size_t workspace_bytes, void* stream);
 
+/* The tiled evaluation on a PACKED copy of the feature-transformer table, for nets whose |ft_w| <= 4095 (trained
+ * nets are far below): nnue_quant_pack_table writes int16 [N + 1, L1] in which every pair of neighbouring columns is
+ * the int32 number ft_w[c + 1] * 65536 + ft_w[c] (a negative low value borrows from the high half) and the last row
+ * is zero, and leaves max |ft_w| in *d_max_abs (device int32; the caller reads it once and passes it on).  The gather
+ * then adds two columns per 32-bit add with a branch-free row loop (padding reads the zero row), a warp per
+ * (position, perspective).  Bit-identical to nnue_quant_eval_tiled; refused when max_abs > 4095 or K > 511. */
+int nnue_quant_pack_table(const int16_t* ft_w, int16_t* packed, int32_t* d_max_abs, int64_t N, int32_t L1,
+                          void* stream);
+int nnue_quant_eval_packed(const int32_t* white_idx, const int32_t* black_idx,
+                           const uint8_t* stm_white, const int32_t* bucket,
+                           const int16_t* ft_w_packed, int32_t max_abs,
+                           const int32_t* ft_psqt, const int32_t* ft_b,
+                           const int8_t* l1_w, const int32_t* l1_b,
+                           const int8_t* l2_w, const int32_t* l2_b,
+                           const int8_t* out_w, const int32_t* out_b,
+                           int32_t* out,
+                           int64_t B, int32_t K, int64_t N, int32_t L1, int32_t L2,
+                           int32_t L3, int32_t P, int32_t buckets,
+                           const nnue_quant_params* h_qp, void* workspace,
+                           size_t workspace_bytes, void* stream);
+
 /* ---- L: training loss and its gradient, one launch ------------------------
  * `calculate_sf_loss` with `remap_tablebase_score` (model/nnue.py:18-69), fused
  * with the PSQT term of the model output (model/model.py:107-133) and the

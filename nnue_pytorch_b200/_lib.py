@@ -222,6 +222,11 @@ PROTOTYPES = {
         C.c_int,
         [_P] * 14 + [_I64, _I32, _I64, _I32, _I32, _I32, _I32, _I32, C.POINTER(QuantParams), _P, _SZ, _P],
     ),
+    "nnue_quant_pack_table": (C.c_int, [_P, _P, _P, _I64, _I32, _P]),
+    "nnue_quant_eval_packed": (
+        C.c_int,
+        [_P] * 5 + [_I32] + [_P] * 9 + [_I64, _I32, _I64, _I32, _I32, _I32, _I32, _I32, C.POINTER(QuantParams), _P, _SZ, _P],
+    ),
     "nnue_batch_build_halfka": (C.c_int, [_P, _I64, _I32, _I32, _P, _P, _P, _P, _P, _P, _P, _P, _P]),
 }
 

@@ -358,7 +358,10 @@ __global__ void __launch_bounds__(kThreads)
     chunk_row[c] = (int32_t)lo;
 }
 
-template <int U, int R, int MINB>
+// OFFS: the launch covers the column tiles from rr.tile0 on (column slices).  A template parameter, because the
+// added offset alone cost the whole-table launch 3 % (0.852 -> 0.878 ms at the benchmark shape, measured on one GPU
+// with the two builds side by side).
+template <int U, int R, int MINB, bool OFFS>
 __global__ void __launch_bounds__(kThreads, MINB)
     k_segment_chunks(const float4* __restrict__ src, int64_t W4, int64_t src_rows,
                      const int32_t* __restrict__ offsets, const int32_t* __restrict__ entries,
@@ -366,7 +369,7 @@ __global__ void __launch_bounds__(kThreads, MINB)
                      float4* __restrict__ partial, int64_t N, int n_chunk_groups, int S,
                      unsigned long long* status, RowRange rr) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = rr.tile0 + blockIdx.x / n_chunk_groups;
+    const int tile = OFFS ? rr.tile0 + blockIdx.x / n_chunk_groups : blockIdx.x / n_chunk_groups;
     const int c = (blockIdx.x % n_chunk_groups) * kWarpsPerCta + warp;
     const int E = __ldg(offsets + N);
     const int e_beg = c * S;
@@ -422,13 +425,13 @@ __global__ void __launch_bounds__(kThreads, MINB)
 
 // One warp per (chunk, tile): if the row whose piece opens this chunk also ends
 // in this chunk, add up its pieces from the chunk it started in to this one.
-template <int U>
+template <int U, bool OFFS>
 __global__ void __launch_bounds__(kThreads)
     k_segment_fixup(const int32_t* __restrict__ offsets, const int32_t* __restrict__ chunk_row,
                     const float4* __restrict__ partial, float4* __restrict__ out, int64_t W4,
                     int64_t N, int n_chunk_groups, int S, RowRange rr) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile = rr.tile0 + blockIdx.x / n_chunk_groups;
+    const int tile = OFFS ? rr.tile0 + blockIdx.x / n_chunk_groups : blockIdx.x / n_chunk_groups;
     const int c = (blockIdx.x % n_chunk_groups) * kWarpsPerCta + warp;
     const int E = __ldg(offsets + N);
     const int e_beg = c * S;
@@ -695,10 +698,16 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
             }
             // variant = rows per register buffer (R) and CTAs per SM the register budget must allow
             const int v = tuning().bwd_r;
-#define LAUNCH_CHUNKS(UU, RR, MB)                                                                  \
-    k_segment_chunks<UU, RR, MB><<<grid, kThreads, 0, s>>>(s4, W4, src_rows, plan.offsets,         \
-                                                           plan.entries, plan.chunk_row, o4, p4, N, \
-                                                           (int)groups, S, status, rr)
+            const bool offs = tile_b != 0;
+#define LAUNCH_CHUNKS(UU, RR, MB)                                                                            \
+    do {                                                                                                     \
+        if (offs)                                                                                            \
+            k_segment_chunks<UU, RR, MB, true><<<grid, kThreads, 0, s>>>(s4, W4, src_rows, plan.offsets, plan.entries, \
+                                                                         plan.chunk_row, o4, p4, N, (int)groups, S, status, rr); \
+        else                                                                                                 \
+            k_segment_chunks<UU, RR, MB, false><<<grid, kThreads, 0, s>>>(s4, W4, src_rows, plan.offsets, plan.entries, \
+                                                                          plan.chunk_row, o4, p4, N, (int)groups, S, status, rr); \
+    } while (0)
             {
             ProfScope prof("k_segment_chunks", s);
             if (U == 1) {
@@ -714,9 +723,15 @@ int csr_reduce(const CsrPlan& plan, const float* src, int W, float* out, cudaStr
             }
 #undef LAUNCH_CHUNKS
             ProfScope prof_fix("k_segment_fixup", s);
-            if (U == 1) k_segment_fixup<1><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);
-            else if (U == 2) k_segment_fixup<2><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);
-            else k_segment_fixup<4><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);
+#define LAUNCH_FIXUP(UU)                                                                                              \
+    do {                                                                                                              \
+        if (offs) k_segment_fixup<UU, true><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr); \
+        else k_segment_fixup<UU, false><<<grid, kThreads, 0, s>>>(plan.offsets, plan.chunk_row, p4, o4, W4, N, (int)groups, S, rr);    \
+    } while (0)
+            if (U == 1) LAUNCH_FIXUP(1);
+            else if (U == 2) LAUNCH_FIXUP(2);
+            else LAUNCH_FIXUP(4);
+#undef LAUNCH_FIXUP
             note_launches(3);
         } else {
             NNUE_REQUIRE(whole, NNUE_ERR_UNSUPPORTED, "csr: slices need the chunked reduction (seg_chunk > 0)");

@@ -12,6 +12,7 @@
 #include <algorithm>
 
 #include "common.cuh"
+#include "gather_q16.cuh"
 
 namespace nnue {
 
@@ -319,6 +320,86 @@ __global__ void __launch_bounds__(kThreads, 3)
     }
 }
 
+// The gather on the packed form of the table (nnue_quant_pack_table: neighbouring columns as ONE int32 number,
+// one more row of zeros), with the training forward's loop: a warp per (position, perspective), branch-free batches
+// of R rows, one 32-bit add per two columns, split into int32 sums before the low half can overflow.  Taken when
+// every |ft_w| <= kMaxAbsPacked; same bits as k_quant_gather.
+constexpr int kQPackedPos = kWarpsPerCta / 2;
+template <int R>
+__global__ void __launch_bounds__(kThreads, 4)
+    k_quant_gather_packed(const int32_t* __restrict__ white_idx, const int32_t* __restrict__ black_idx,
+                          const uint8_t* __restrict__ stm_white, const int32_t* __restrict__ bucket,
+                          const int16_t* __restrict__ ft_w_packed, const int32_t* __restrict__ ft_psqt,
+                          const int32_t* __restrict__ ft_b, int8_t* __restrict__ x0, int32_t* __restrict__ psq,
+                          int64_t p_begin, int64_t p_end, QuantDims d, nnue_quant_params q, int n_groups,
+                          int rows_per_split, unsigned long long* status) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int side = warp & 1, pair = warp >> 1;
+    const int tile = blockIdx.x / n_groups;
+    const int64_t p = p_begin + (int64_t)(blockIdx.x % n_groups) * kQPackedPos + pair;
+    if (p >= p_end) return;
+    const int h = d.L1 >> 1, h8 = h >> 3;
+    const int c = tile * 32 + lane;
+    const bool live = c < h8;
+    const int stm = stm_white[p] ? 1 : 0;
+    // side 0 is the side to move ("us"), side 1 the other
+    const int32_t* list = ((side == 0) == (stm != 0) ? white_idx : black_idx) + p * d.K;
+    const int n = count_active(list, d.K, lane);
+
+    PairAcc acc;
+#pragma unroll
+    for (int hlf = 0; hlf < 2; ++hlf) {
+        const int4* b = reinterpret_cast<const int4*>(ft_b + hlf * h + 8 * (live ? c : 0));
+        const int4 v0 = __ldg(b), v1 = __ldg(b + 1);
+        acc.lo[hlf][0] = v0.x, acc.hi[hlf][0] = v0.y, acc.lo[hlf][1] = v0.z, acc.hi[hlf][1] = v0.w;
+        acc.lo[hlf][2] = v1.x, acc.hi[hlf][2] = v1.y, acc.lo[hlf][3] = v1.z, acc.hi[hlf][3] = v1.w;
+    }
+    // lanes beyond the last column read column group 0 (valid memory); their sums are never stored
+    const uint4* base0 = reinterpret_cast<const uint4*>(ft_w_packed) + (live ? c : 0);
+    gather_q16<R>(base0, base0 + h8, d.L1 >> 3, (int)d.N, list, n, rows_per_split, acc, lane, status);
+    if (live) {
+        unsigned w[2] = {0, 0};  // 8 int8: the clipped products of this perspective
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+            const int a0 = clampi((j & 1) ? acc.hi[0][j >> 1] : acc.lo[0][j >> 1], 0, q.ft_max);
+            const int a1 = clampi((j & 1) ? acc.hi[1][j >> 1] : acc.lo[1][j >> 1], 0, q.ft_max);
+            w[j >> 2] |= ((unsigned)min((a0 * a1) >> q.ft_shift, q.hidden_max) & 0xffu) << (8 * (j & 3));
+        }
+        *reinterpret_cast<uint2*>(x0 + (p - p_begin) * d.L1 + side * h + 8 * c) = make_uint2(w[0], w[1]);
+    }
+    if (tile == 0) {  // PSQT of this perspective; the two warps of a position add their halves of the difference
+        int bk = bucket[p];
+        if (bk < 0 || bk >= d.buckets || bk >= d.P) bk = 0;  // k_quant_layers reports it
+        int s = 0;
+        for (int k = lane; k < n; k += 32) {
+            const int r = list[k];
+            if (r >= 0 && (int64_t)r < d.N) s += __ldg(ft_psqt + (int64_t)r * d.P + bk);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(kFullMask, s, o);
+        if (lane == 0) atomicAdd(psq + (p - p_begin), side == 0 ? s : -s);  // integer: the order does not matter
+    }
+}
+
+// int16 [N, L1] -> the packed form: [N + 1, L1] int16 read as int32 numbers k[c + 1] * 65536 + k[c], last row zeros.
+__global__ void __launch_bounds__(kThreads)
+    k_quant_pack_table(const int16_t* __restrict__ ft_w, int32_t* __restrict__ packed, int64_t n_words, int64_t n_src_words,
+                       int32_t* __restrict__ max_abs) {
+    int m = 0;
+    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n_words; i += stride) {
+        int word = 0;
+        if (i < n_src_words) {
+            const int k0 = ft_w[2 * i], k1 = ft_w[2 * i + 1];
+            word = k1 * 65536 + k0;
+            m = max(m, max(abs(k0), abs(k1)));
+        }
+        packed[i] = word;
+    }
+    m = __reduce_max_sync(kFullMask, m);
+    if ((threadIdx.x & 31) == 0 && m > 0) atomicMax(max_abs, m);
+}
+
 constexpr int kQLayerThreads = 128;
 __global__ void __launch_bounds__(kQLayerThreads)
     k_quant_layers(const int8_t* __restrict__ x0, const int32_t* __restrict__ psq,
@@ -393,8 +474,24 @@ extern "C" size_t nnue_quant_eval_workspace_bytes(int64_t B, int32_t L1) {
     return (size_t)chunk * ((size_t)L1 + sizeof(int32_t)) + 256;
 }
 
-extern "C" int nnue_quant_eval_tiled(const int32_t* white_idx, const int32_t* black_idx,
+extern "C" int nnue_quant_pack_table(const int16_t* ft_w, int16_t* packed, int32_t* d_max_abs, int64_t N, int32_t L1,
+                                     void* stream) {
+    NNUE_REQUIRE(N >= 0 && L1 > 0 && L1 % 2 == 0, NNUE_ERR_ARG, "nnue_quant_pack_table: bad size (L1 must be even)");
+    NNUE_REQUIRE(ft_w && packed && d_max_abs && (reinterpret_cast<uintptr_t>(packed) & 3u) == 0, NNUE_ERR_ARG,
+                 "nnue_quant_pack_table: null or unaligned pointer");
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    NNUE_CUDA_TRY(cudaMemsetAsync(d_max_abs, 0, sizeof(int32_t), s));
+    const int64_t src = N * (L1 / 2), all = (N + 1) * (L1 / 2);
+    const unsigned grid = (unsigned)std::min<int64_t>((all + kThreads - 1) / kThreads, (int64_t)sm_count() * 8);
+    k_quant_pack_table<<<grid, kThreads, 0, s>>>(ft_w, reinterpret_cast<int32_t*>(packed), all, src, d_max_abs);
+    NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
+    return NNUE_OK;
+}
+
+static int quant_eval_tiled_impl(const int32_t* white_idx, const int32_t* black_idx,
                                      const uint8_t* stm_white, const int32_t* bucket, const int16_t* ft_w,
+                                     const int16_t* ft_w_packed, int32_t max_abs,
                                      const int32_t* ft_psqt, const int32_t* ft_b, const int8_t* l1_w,
                                      const int32_t* l1_b, const int8_t* l2_w, const int32_t* l2_b,
                                      const int8_t* out_w, const int32_t* out_b, int32_t* out, int64_t B,
@@ -405,14 +502,20 @@ extern "C" int nnue_quant_eval_tiled(const int32_t* white_idx, const int32_t* bl
     NNUE_REQUIRE(B >= 0 && K >= 0 && N >= 0 && L1 > 0 && L2 > 1 && L3 > 0 && P > 0 && buckets > 0,
                  NNUE_ERR_ARG, "nnue_quant_eval_tiled: bad size");
     if (B == 0) return NNUE_OK;
-    NNUE_REQUIRE(white_idx && black_idx && stm_white && bucket && ft_w && ft_psqt && ft_b && l1_w &&
+    NNUE_REQUIRE(white_idx && black_idx && stm_white && bucket && (ft_w || ft_w_packed) && ft_psqt && ft_b && l1_w &&
                      l1_b && l2_w && l2_b && out_w && out_b && out,
                  NNUE_ERR_ARG, "nnue_quant_eval_tiled: null pointer");
+    if (ft_w_packed) {
+        NNUE_REQUIRE(max_abs >= 0 && max_abs <= kMaxAbsPacked, NNUE_ERR_UNSUPPORTED,
+                     "nnue_quant_eval_packed: the packed gather takes |ft_w| <= %d (got %d)", kMaxAbsPacked, max_abs);
+        NNUE_REQUIRE(K <= 511 && (N + 1) * (int64_t)(L1 / 8) < 0x7fffffffLL && aligned16(ft_w_packed), NNUE_ERR_UNSUPPORTED,
+                     "nnue_quant_eval_packed: at most 511 rows per list, 32-bit row offsets, 16-byte aligned table");
+    }
     NNUE_REQUIRE(L1 % 32 == 0, NNUE_ERR_UNSUPPORTED,
                  "nnue_quant_eval_tiled: L1 must be a multiple of 32 (16-byte int16 chunks per half), got %d", L1);
     NNUE_REQUIRE(L2 <= kQMaxL2 && L3 <= kQMaxL2, NNUE_ERR_UNSUPPORTED,
                  "nnue_quant_eval_tiled: hidden layers wider than %d are not covered", kQMaxL2);
-    NNUE_REQUIRE(aligned16(ft_w) && aligned16(l1_w) && aligned16(ft_b), NNUE_ERR_ALIGN,
+    NNUE_REQUIRE((ft_w_packed || aligned16(ft_w)) && aligned16(l1_w) && aligned16(ft_b), NNUE_ERR_ALIGN,
                  "nnue_quant_eval_tiled: ft_w / ft_b / l1_w must be 16-byte aligned");
     NNUE_REQUIRE(qp->out_div > 0 && qp->ft_shift >= 0 && qp->sqr_shift_l1 >= 0 && qp->sqr_shift_l2 >= 0,
                  NNUE_ERR_ARG, "nnue_quant_eval_tiled: bad quantization parameters");
@@ -440,7 +543,16 @@ extern "C" int nnue_quant_eval_tiled(const int32_t* white_idx, const int32_t* bl
         int32_t* psq = reinterpret_cast<int32_t*>(ws + (size_t)chunk * L1);
         const int64_t groups = (p1 - p0 + kWarpsPerCta - 1) / kWarpsPerCta;
         NNUE_REQUIRE(groups * tiles <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "nnue_quant_eval_tiled: grid too large");
-        {
+        if (ft_w_packed) {
+            const int64_t groups4 = (p1 - p0 + kQPackedPos - 1) / kQPackedPos;
+            NNUE_REQUIRE(groups4 * tiles <= 0x7fffffffLL, NNUE_ERR_UNSUPPORTED, "nnue_quant_eval_packed: grid too large");
+            NNUE_CUDA_TRY(cudaMemsetAsync(psq, 0, (size_t)(p1 - p0) * sizeof(int32_t), s));  // the two perspectives add into it
+            const int rows_per_split = max_abs > 0 ? std::min(32767 / max_abs, 512) : 512;
+            ProfScope prof("k_quant_gather_packed", s);
+            k_quant_gather_packed<3><<<(unsigned)(groups4 * tiles), kThreads, 0, s>>>(
+                white_idx, black_idx, stm_white, bucket, ft_w_packed, ft_psqt, ft_b, x0, psq, p0, p1, d, *qp, (int)groups4,
+                rows_per_split, status);
+        } else {
             ProfScope prof("k_quant_gather", s);
             k_quant_gather<<<(unsigned)(groups * tiles), kThreads, 0, s>>>(white_idx, black_idx, stm_white, bucket,
                                                                           ft_w, ft_psqt, ft_b, x0, psq, p0, p1, d,
@@ -454,4 +566,31 @@ extern "C" int nnue_quant_eval_tiled(const int32_t* white_idx, const int32_t* bl
         note_launches(2);
     }
     return NNUE_OK;
+}
+
+extern "C" int nnue_quant_eval_tiled(const int32_t* white_idx, const int32_t* black_idx,
+                                     const uint8_t* stm_white, const int32_t* bucket, const int16_t* ft_w,
+                                     const int32_t* ft_psqt, const int32_t* ft_b, const int8_t* l1_w,
+                                     const int32_t* l1_b, const int8_t* l2_w, const int32_t* l2_b,
+                                     const int8_t* out_w, const int32_t* out_b, int32_t* out, int64_t B,
+                                     int32_t K, int64_t N, int32_t L1, int32_t L2, int32_t L3, int32_t P,
+                                     int32_t buckets, const nnue_quant_params* qp, void* workspace,
+                                     size_t workspace_bytes, void* stream) {
+    return quant_eval_tiled_impl(white_idx, black_idx, stm_white, bucket, ft_w, nullptr, 0, ft_psqt, ft_b, l1_w, l1_b, l2_w,
+                                 l2_b, out_w, out_b, out, B, K, N, L1, L2, L3, P, buckets, qp, workspace, workspace_bytes,
+                                 stream);
+}
+
+extern "C" int nnue_quant_eval_packed(const int32_t* white_idx, const int32_t* black_idx,
+                                      const uint8_t* stm_white, const int32_t* bucket, const int16_t* ft_w_packed,
+                                      int32_t max_abs, const int32_t* ft_psqt, const int32_t* ft_b, const int8_t* l1_w,
+                                      const int32_t* l1_b, const int8_t* l2_w, const int32_t* l2_b,
+                                      const int8_t* out_w, const int32_t* out_b, int32_t* out, int64_t B,
+                                      int32_t K, int64_t N, int32_t L1, int32_t L2, int32_t L3, int32_t P,
+                                      int32_t buckets, const nnue_quant_params* qp, void* workspace,
+                                      size_t workspace_bytes, void* stream) {
+    NNUE_REQUIRE(ft_w_packed != nullptr, NNUE_ERR_ARG, "nnue_quant_eval_packed: null table");
+    return quant_eval_tiled_impl(white_idx, black_idx, stm_white, bucket, nullptr, ft_w_packed, max_abs, ft_psqt, ft_b, l1_w,
+                                 l1_b, l2_w, l2_b, out_w, out_b, out, B, K, N, L1, L2, L3, P, buckets, qp, workspace,
+                                 workspace_bytes, stream);
 }

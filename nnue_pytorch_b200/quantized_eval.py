@@ -58,6 +58,24 @@ class QuantizedNet:
         self.out_w = _to_int(out_weight, s["ls_output_weight"], torch.int8)
         self.out_b = _to_int(out_bias.reshape(-1), s["ls_output_bias"], torch.int32)
         self._qp = _lib.QuantParams(**self.consts)
+        self._pack()
+
+    PACKED_MAX_ABS = 4095  # the packed gather's limit on |ft_w| (nnue_quant_eval_packed)
+
+    def _pack(self) -> None:
+        """The packed copy of the table the fast gather reads (`nnue_quant_pack_table`) and max |ft_w|, read once."""
+        self.ft_w_packed, self.ft_max_abs = None, None
+        if self.L1 % 32 != 0 or self.N == 0:
+            return
+        packed = torch.empty(self.N + 1, self.L1, dtype=torch.int16, device=self.device)
+        max_abs = torch.zeros(1, dtype=torch.int32, device=self.device)
+        with torch.cuda.device(self.device):
+            st = _lib.load().nnue_quant_pack_table(self.ft_w.data_ptr(), packed.data_ptr(), max_abs.data_ptr(), self.N,
+                                                   self.L1, torch.cuda.current_stream(self.device).cuda_stream)
+        _lib.check(st, "nnue_quant_pack_table")
+        self.ft_max_abs = int(max_abs.item())
+        if self.ft_max_abs <= self.PACKED_MAX_ABS:
+            self.ft_w_packed = packed
 
     @classmethod
     def from_model(cls, model) -> "QuantizedNet":
@@ -101,13 +119,17 @@ class QuantizedNet:
         self.out_w = put(np.concatenate([b[2][0] for b in nf.fc]), torch.int8)
         self.out_b = put(np.concatenate([b[2][1] for b in nf.fc]), torch.int32)
         self._qp = _lib.QuantParams(**self.consts)
+        self._pack()
         return self
 
     @torch.no_grad()
-    def evaluate(self, white_indices, black_indices, stm_white, piece_count, tiled: bool = True) -> torch.Tensor:
+    def evaluate(self, white_indices, black_indices, stm_white, piece_count, tiled: bool = True,
+                 packed: bool = True) -> torch.Tensor:
         """int32 [B]: the evaluation in units of 1/(2 * nnue2score * weight_scale_out)
         (= 1/19200 by default) of the float model output.  `tiled=False` runs the
-        one-kernel form (no scratch memory, slower); the results are the same bits."""
+        one-kernel form (no scratch memory, slower), `packed=False` the tiled form on the plain
+        int16 table (what nets with |ft_w| > 4095 or lists beyond 511 rows get anyway); the
+        results are the same bits."""
         dev = self.device
         assert white_indices.dtype == torch.int32 and black_indices.dtype == torch.int32
         assert white_indices.is_cuda and white_indices.is_contiguous() and black_indices.is_contiguous()
@@ -119,6 +141,18 @@ class QuantizedNet:
         lib = _lib.load()
         if tiled and B > 0:
             ws = torch.empty(lib.nnue_quant_eval_workspace_bytes(B, self.L1), dtype=torch.uint8, device=dev)
+            if packed and self.ft_w_packed is not None and K <= 511:
+                with torch.cuda.device(dev):
+                    st = lib.nnue_quant_eval_packed(
+                        white_indices.data_ptr(), black_indices.data_ptr(), stm.data_ptr(), bucket.data_ptr(),
+                        self.ft_w_packed.data_ptr(), self.ft_max_abs, self.ft_psqt.data_ptr(), self.ft_b.data_ptr(),
+                        self.l1_w.data_ptr(), self.l1_b.data_ptr(), self.l2_w.data_ptr(), self.l2_b.data_ptr(),
+                        self.out_w.data_ptr(), self.out_b.data_ptr(), out.data_ptr(),
+                        B, K, self.N, self.L1, self.L2, self.L3, self.P, self.buckets,
+                        C.byref(self._qp), ws.data_ptr(), ws.numel(), torch.cuda.current_stream(dev).cuda_stream,
+                    )
+                _lib.check(st, "nnue_quant_eval_packed")
+                return out
             with torch.cuda.device(dev):
                 st = lib.nnue_quant_eval_tiled(
                     white_indices.data_ptr(), black_indices.data_ptr(), stm.data_ptr(), bucket.data_ptr(),

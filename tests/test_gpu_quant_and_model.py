@@ -39,9 +39,9 @@ def test_integer_eval_matches_reference_float64(dev):
     assert np.array_equal(out.cpu().numpy().astype(np.int64), g["eval_int"][:, 0])
 
 
-def _random_quant_params(L1, N, gen, buckets=8, L2=32, L3=32):
+def _random_quant_params(L1, N, gen, buckets=8, L2=32, L3=32, ft_range=24):
     p = {}
-    w = gen.integers(-24, 25, (N, L1 + 8)) / 256.0
+    w = gen.integers(-ft_range, ft_range + 1, (N, L1 + 8)) / 256.0
     w[:, L1:] = gen.integers(-2000, 2001, (N, 8)) / 9600.0
     p["ft_weight"] = w
     bias = np.zeros(L1 + 8)
@@ -58,25 +58,34 @@ def _random_quant_params(L1, N, gen, buckets=8, L2=32, L3=32):
     return p
 
 
-@pytest.mark.parametrize("L1,layout,B", [(1024, "baseline", 4096), (3072, "baseline", 2048), (256, "native", 3000)])
-def test_integer_eval_matches_integer_oracle(dev, L1, layout, B):
+@pytest.mark.parametrize("L1,layout,B,ft_range", [(1024, "baseline", 4096, 24), (3072, "baseline", 2048, 24),
+                                                  (256, "native", 3000, 24), (512, "baseline", 3001, 4095),
+                                                  (512, "baseline", 1000, 4096), (256, "native", 2000, 30000)])
+def test_integer_eval_matches_integer_oracle(dev, L1, layout, B, ft_range):
+    """The three forms of the evaluation (packed gather, plain tiled gather, one kernel) against the integer
+    oracle.  Table entries up to 4095 in magnitude take the packed gather (pair sums split every 8 rows at that
+    size); one entry beyond it and the net is served by the plain int16 gather."""
     from oracle import quant_oracle
     from nnue_pytorch_b200 import positions
     from nnue_pytorch_b200.quantize import QuantizationManager
 
-    gen = np.random.default_rng(L1)
+    gen = np.random.default_rng(L1 + ft_range)
     N = positions.NUM_INPUTS_BASELINE if layout == "baseline" else positions.NUM_INPUTS_NATIVE
-    p = _random_quant_params(L1, N, gen)
+    p = _random_quant_params(L1, N, gen, ft_range=ft_range)
+    if ft_range > 24:
+        p["ft_weight"][0, 0] = ft_range / 256.0  # the bound itself occurs
     b = positions.generate_batch(B, 17, layout=layout)
     consts = QuantizationManager().integer_constants()
     want = quant_oracle.integer_eval(quant_oracle.quantize_params(p, L1), b.white, b.black, b.us[:, 0] > 0.5,
                                      (b.piece_count - 1) // 4, consts)
     net = _net_from_params(p, L1, dev)
     args = (t(b.white).to(dev), t(b.black).to(dev), t(b.us[:, 0] > 0.5), t(b.piece_count))
-    got = net.evaluate(*args)                    # gather kernel with an L2-resident slice + layer kernel
+    assert (net.ft_w_packed is not None) == (ft_range <= 4095) and net.ft_max_abs == ft_range
+    got = net.evaluate(*args)                    # packed gather (when the table allows it) + layer kernel
+    plain = net.evaluate(*args, packed=False)    # gather on the plain int16 table + layer kernel
     single = net.evaluate(*args, tiled=False)    # one kernel per position
     assert np.array_equal(got.cpu().numpy().astype(np.int64), want)
-    assert torch.equal(got, single)
+    assert torch.equal(got, single) and torch.equal(got, plain)
     assert len(np.unique(want)) > B // 4  # the outputs are not degenerate
 
 
