@@ -37,6 +37,7 @@ One JSON line is printed by rank 0.
 from __future__ import annotations
 
 import argparse
+import gc
 import json
 import os
 import statistics
@@ -449,6 +450,10 @@ def run_step(args):
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         loss_host = 0.0
+        # a full collection of the interpreter's garbage (tens of milliseconds with this heap) inside the loop would
+        # stall the host while the GPU's queue is still shallow: collect now, keep the collector off while timing
+        gc.collect()
+        gc.disable()
         e0.record()
         if resident:
             t_host = time.perf_counter()
@@ -471,6 +476,7 @@ def run_step(args):
             done[(n_steps - 1) % 2].synchronize()
             loss_host = float(slots[(n_steps - 1) % 2])
         e1.record()
+        gc.enable()
         barrier()
         ms = e0.elapsed_time(e1) / n_steps
         if world > 1:

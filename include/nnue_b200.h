@@ -515,6 +515,17 @@ int nnue_ls_l1_fwd_tc(const float* x, const float* W1, const float* b1,
 int nnue_ls_l1_bwd(const float* x, const float* W1, const float* d_o1,
                    const void* plan, float* dx, float* dW1, float* db1,
                    int64_t B, int32_t L1, int32_t C, void* stream);
+/* nnue_ls_l1_bwd with the INPUT gradient on the tensor cores, for W1 that TF32 holds exactly (the quantized model):
+ * d_o1 is split into three TF32-exact parts (hi + mid + lo = d_o1, every subtraction exact), so every product the
+ * tensor core forms is exact and only the fp32 accumulation of its 96 terms rounds (not the bits of the FMA kernel:
+ * another summation order; 1e-6 of the tensor's max-norm).  The weight and bias gradients come from the FMA kernel
+ * (their sums run over the whole batch).  Needs L1 %% 128 == 0 and nnue_ls_l1_bwd_tc_workspace_bytes(L1, C) bytes of
+ * scratch (the transposed weights); dx == NULL is nnue_ls_l1_bwd. */
+size_t nnue_ls_l1_bwd_tc_workspace_bytes(int32_t L1, int32_t C);
+int nnue_ls_l1_bwd_tc(const float* x, const float* W1, const float* d_o1,
+                      const void* plan, float* dx, float* dW1, float* db1,
+                      int64_t B, int32_t L1, int32_t C, void* workspace,
+                      size_t workspace_bytes, void* stream);
 int nnue_ls_tail_fwd(const float* o1, const void* plan, const float* W2,
                      const float* b2, const float* W3, const float* b3,
                      const nnue_ls_params* h_params, float* o2, float* y,

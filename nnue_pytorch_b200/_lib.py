@@ -202,6 +202,8 @@ PROTOTYPES = {
     "nnue_ls_plan": (C.c_int, [_P, _I64, _I32, _P, _SZ, _P]),
     "nnue_ls_l1_fwd": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _P]),
     "nnue_ls_l1_fwd_tc": (C.c_int, [_P, _P, _P, _P, _P, _I64, _I32, _I32, _P]),
+    "nnue_ls_l1_bwd_tc_workspace_bytes": (_SZ, [_I32, _I32]),
+    "nnue_ls_l1_bwd_tc": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _P, _SZ, _P]),
     "nnue_ls_l1_bwd": (C.c_int, [_P, _P, _P, _P, _P, _P, _P, _I64, _I32, _I32, _P]),
     "nnue_ls_tail_fwd": (C.c_int, [_P, _P, _P, _P, _P, _P, C.POINTER(LsParams), _P, _P, _I64, _I32, _P]),
     "nnue_ls_tail_bwd_workspace_bytes": (_SZ, [_I64, _I32]),

@@ -58,6 +58,8 @@ struct Tuning {
     int fwd_q16_variant = 0;  // compiled variant of the int16-table forward (see LAUNCH_Q16)
     int overlap_csr = 1;  // 1 = build the CSR on the helper stream, beside the backward prologue
     int ddp_reduce_ctas = 0;  // > 0: grid cap of the peer-load reduce (it runs beside the sliced backward)
+    int ls_dw_tc = 0;           // 1: the first layer's weight gradient of the quantized model on the tensor cores too
+                                // (correct, measured slower than the FMA kernel: 0.163 against 0.111 ms)
     int col_slice_streams = 1;  // 1: column slices of the backward alternate between two streams
     int ddp_reduce_u = 0;     // > 0: float4 per thread and rank in flight in the peer-load reduce (1, 2, 4 or 8)
 };

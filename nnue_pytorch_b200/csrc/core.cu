@@ -135,6 +135,7 @@ extern "C" int nnue_b200_tune(const char* key, int value) {
     else if (!strcmp(key, "ddp_reduce_ctas")) t.ddp_reduce_ctas = value;
     else if (!strcmp(key, "ddp_reduce_u")) t.ddp_reduce_u = value;
     else if (!strcmp(key, "col_slice_streams")) t.col_slice_streams = value;
+    else if (!strcmp(key, "ls_dw_tc")) t.ls_dw_tc = value;
     else if (!strcmp(key, "overlap_csr")) t.overlap_csr = value;
     else {
         set_error("nnue_b200_tune: unknown key '%s'", key);

@@ -77,6 +77,10 @@ class PlanAhead:
         return self.plan
 
 
+# False: the first layer's input gradient stays on the fp32 FMA kernel also in the quantized model
+TENSOR_CORE_DX = True
+
+
 class FusedLayerStackFunction(autograd.Function):
     @staticmethod
     def forward(ctx, x, bucket, W1, b1, W2, b2, W3, b3, quantization, fake_quantize_acts, plan_ahead=None,
@@ -109,6 +113,7 @@ class FusedLayerStackFunction(autograd.Function):
                                             C.byref(params), _ptr(o2), _ptr(y), B, count, s), "nnue_ls_tail_fwd")
         ctx.save_for_backward(x, W1, W2, W3, o1, o2, plan)
         ctx.params, ctx.count, ctx.b3_shape = params, count, tuple(b3.shape)
+        ctx.exact_tf32 = bool(exact_tf32)
         return y
 
     @staticmethod
@@ -134,8 +139,14 @@ class FusedLayerStackFunction(autograd.Function):
                                             C.byref(ctx.params), _ptr(d_o1), _ptr(dW2), _ptr(db2), _ptr(dW3),
                                             _ptr(db3), _ptr(ws), ws.numel(), B, count, s), "nnue_ls_tail_bwd")
             with _span("ls_l1_bwd", dev):
-                _lib.check(lib.nnue_ls_l1_bwd(_ptr(x), _ptr(W1), _ptr(d_o1), _ptr(plan), _ptr(dx), _ptr(dW1),
-                                              _ptr(db1), B, L1, count, s), "nnue_ls_l1_bwd")
+                if ctx.exact_tf32 and dx is not None and L1 % 128 == 0 and TENSOR_CORE_DX:
+                    # W1 is exact in TF32 (see forward): the input gradient on the tensor cores
+                    ws1 = torch.empty(lib.nnue_ls_l1_bwd_tc_workspace_bytes(L1, count), dtype=torch.uint8, device=dev)
+                    _lib.check(lib.nnue_ls_l1_bwd_tc(_ptr(x), _ptr(W1), _ptr(d_o1), _ptr(plan), _ptr(dx), _ptr(dW1),
+                                                     _ptr(db1), B, L1, count, _ptr(ws1), ws1.numel(), s), "nnue_ls_l1_bwd_tc")
+                else:
+                    _lib.check(lib.nnue_ls_l1_bwd(_ptr(x), _ptr(W1), _ptr(d_o1), _ptr(plan), _ptr(dx), _ptr(dW1),
+                                                  _ptr(db1), B, L1, count, s), "nnue_ls_l1_bwd")
         return dx, None, dW1, db1, dW2, db2, dW3, db3.view(ctx.b3_shape), None, None, None, None
 
 

@@ -483,3 +483,67 @@ def test_tensor_core_first_layer_has_the_bits_of_the_fma_kernel(dev, B, L1):
         + b1.double().cpu().view(count, 32)[bucket.cpu()]
     assert torch.equal(outs[0].cpu().double(), want)  # the FMA kernel is exact on these inputs
     assert torch.equal(outs[1], outs[0])
+
+
+@pytest.mark.parametrize("B,L1", [(5, 128), (777, 512), (4097, 3072), (16384, 3072)])
+def test_tensor_core_input_gradient_matches_the_fma_kernel(dev, B, L1):
+    """The quantized model's first-layer INPUT gradient on tcgen05: d_o1 (an arbitrary fp32 gradient) goes in as
+    three TF32-exact parts, W1 (k / 128) is exact, so every product is exact and only the fp32 accumulation
+    rounds.  Against the float64 product, the tensor-core result must be as close as the fp32 FMA kernel's (within
+    a factor of two) and within 1e-6 of the tensor's max-norm; the weight and bias gradients are the FMA kernel's."""
+    from nnue_pytorch_b200 import _launch, _lib
+
+    lib = _lib.load()
+    gen = torch.Generator().manual_seed(3 * B + L1)
+    count = 8
+    x = (torch.randint(0, 128, (B, L1), generator=gen).float() / 128.0).to(dev)
+    W1 = (torch.randint(-127, 128, (count * 32, L1), generator=gen).float() / 128.0).to(dev)
+    d_o1 = (torch.randn(B, 32, generator=gen) * torch.rand(B, 1, generator=gen) * 1e-3).to(dev)  # a wide range of sizes
+    bucket = torch.randint(0, count, (B,), generator=gen).to(dev)
+    if B > 100:
+        bucket[bucket == 3] = 2  # an empty bucket
+    plan = torch.empty(lib.nnue_ls_plan_bytes(B, count) // 4 + 4, dtype=torch.int32, device=dev)
+    s = torch.cuda.current_stream(dev).cuda_stream
+    _lib.check(lib.nnue_ls_plan(bucket.data_ptr(), B, count, plan.data_ptr(), plan.numel() * 4, s), "nnue_ls_plan")
+
+    def run(tc):
+        dx = torch.full((B, L1), float("nan"), device=dev)
+        dW1 = torch.full_like(W1, float("nan"))
+        db1 = torch.full((count * 32,), float("nan"), device=dev)
+        if tc:
+            ws = torch.empty(lib.nnue_ls_l1_bwd_tc_workspace_bytes(L1, count), dtype=torch.uint8, device=dev)
+            st = lib.nnue_ls_l1_bwd_tc(x.data_ptr(), W1.data_ptr(), d_o1.data_ptr(), plan.data_ptr(), dx.data_ptr(),
+                                       dW1.data_ptr(), db1.data_ptr(), B, L1, count, ws.data_ptr(), ws.numel(), s)
+        else:
+            st = lib.nnue_ls_l1_bwd(x.data_ptr(), W1.data_ptr(), d_o1.data_ptr(), plan.data_ptr(), dx.data_ptr(),
+                                    dW1.data_ptr(), db1.data_ptr(), B, L1, count, s)
+        _lib.check(st, "l1 bwd")
+        return dx, dW1, db1
+
+    fma = run(False)
+    tc_dx_only = run(True)
+    _lib.tune("ls_dw_tc", 1)  # off by default: the weight gradient's tensor-core form is correct but slower
+    try:
+        tc = run(True)
+    finally:
+        _lib.tune("ls_dw_tc", 0)
+    _launch.device_status(dev)  # a bounded wait that ran out would show here
+    assert torch.equal(tc_dx_only[1], fma[1]) and torch.equal(tc_dx_only[2], fma[2]) and torch.equal(tc_dx_only[0], tc[0])
+    # the weight gradient: x is exact in TF32, d_o1 enters in three exact parts, sums of 512 positions in tensor memory
+    onehot = torch.nn.functional.one_hot(bucket, count).double()
+    want_w = torch.einsum("bc,bo,bk->cok", onehot, d_o1.double(), x.double()).reshape(count * 32, L1)
+    want_b = torch.einsum("bc,bo->co", onehot, d_o1.double()).reshape(-1)
+    for name, got_tc, got_fma, ref in (("dW1", tc[1], fma[1], want_w), ("db1", tc[2], fma[2], want_b)):
+        sc = max(float(ref.abs().max()), 1e-30)
+        e_t = float((got_tc.double() - ref).abs().max()) / sc
+        e_f = float((got_fma.double() - ref).abs().max()) / sc
+        print(f"B={B} L1={L1}: max-norm relative error of {name}: tensor cores {e_t:.3e}, FMA kernel {e_f:.3e}")
+        assert not torch.isnan(got_tc).any()
+        assert e_t <= 2e-6 and e_t <= 2 * e_f + 2e-7, name
+    want = torch.einsum("bo,bok->bk", d_o1.double(), W1.double().view(count, 32, L1)[bucket])
+    scale = float(want.abs().max())
+    e_tc = float((tc[0].double() - want).abs().max()) / scale
+    e_fma = float((fma[0].double() - want).abs().max()) / scale
+    print(f"B={B} L1={L1}: max-norm relative error of dx: tensor cores {e_tc:.3e}, FMA kernel {e_fma:.3e}")
+    assert not torch.isnan(tc[0]).any()
+    assert e_tc <= 1e-6 and e_tc <= 2 * e_fma + 1e-7
