@@ -430,20 +430,26 @@ __global__ void __launch_bounds__(kTcThreads)
 //   dW1[bucket, o, c] = sum over the bucket's positions p of d_o1[p, o] * x[p, c]
 // M = 128 columns c of one bucket's W1, N = 96 = the three TF32-exact parts of d_o1 (lo, mid, hi: see the input
 // gradient above) x 32 outputs, K = the bucket's positions, 32 per stage.  x (q / 128) is exact in TF32, so every
-// product is exact.  Both operands are wanted K-major, i.e. transposed against how x and d_o1 lie in memory: the
-// loader gives every LANE one position (a lane reads 128 contiguous bytes of its row of x, a quarter of the CTA's
-// columns per warp) and stores scalars into the 128-byte-swizzled layout, where the 32 positions of a column fall
-// into 32 different banks.  The sum over positions is kept in tensor memory for kDwChunkStages stages (512
-// positions) at a time and added to fp32 registers between chunks, which bounds the length of the tensor core's own
-// accumulation chain.  The three parts are added in the epilogue, small ones first.  CTA = (bucket, 128 columns).
+// product is exact.  Both operands are wanted K-major, i.e. transposed against how x and d_o1 lie in memory.
+// The rows of a stage (32 positions: 512 B of x, 128 B of d_o1 each) come in by cp.async, two stages ahead, into
+// a raw tile whose rows are 16 B longer than their payload; then every LANE takes one position, reads its row
+// (conflict-free thanks to the padding) and stores scalars into the 128-byte-swizzled operand layout, where the 32
+// positions of a column fall into 32 different banks.  Operand buffers alternate, so that stage s + 1 is
+// transposed while the tensor core works on stage s.  The sum over positions stays in tensor memory for
+// kDwChunkStages stages (512 positions) at a time and is added to fp32 registers between chunks, which bounds the
+// length of the tensor core's own accumulation chain.  The three parts are added in the epilogue, small ones
+// first.  CTA = (bucket, 128 columns); 99 KiB of shared memory: two CTAs per SM.
 constexpr int kDwM = 128;
 constexpr int kDwN = 96;
-constexpr int kDwRing = 3;
 constexpr int kDwABytesTc = kDwM * 128;                     // 16 KiB: 128 columns x 32 positions
 constexpr int kDwBBytesTc = kDwN * 128;                     // 12 KiB: 96 rows (part, o) x 32 positions
-constexpr int kDwStageBytesTc = kDwABytesTc + kDwBBytesTc;  // 28 KiB
+constexpr int kDwOperandBytes = kDwABytesTc + kDwBBytesTc;  // 28 KiB
+constexpr int kDwRawStages = 2;
+constexpr int kDwXPitch = kDwM * 4 + 16;                    // bytes per raw row of x
+constexpr int kDwDPitch = kLsOut * 4 + 16;                  // bytes per raw row of d_o1
+constexpr int kDwRawBytes = 32 * (kDwXPitch + kDwDPitch);   // 21 KiB
 constexpr int kDwChunkStages = 16;
-constexpr int kDwSmemBytesTc = 1024 + kDwRing * kDwStageBytesTc + 64;
+constexpr int kDwSmemBytesTc = 1024 + 2 * kDwOperandBytes + kDwRawStages * kDwRawBytes + 64;
 constexpr int kDwTmemCols = 128;
 constexpr uint32_t kIdescTf32N96 = (1u << 4) | (2u << 7) | (2u << 10) | ((uint32_t)(kDwN >> 3) << 17) | ((128u >> 4) << 24);
 
@@ -456,7 +462,7 @@ __device__ __forceinline__ void umma_tf32_n96(uint32_t tmem_d, uint64_t a_desc, 
         : "memory");
 }
 
-__global__ void __launch_bounds__(kTcThreads)
+__global__ void __launch_bounds__(kTcThreads, 2)
     k_ls_l1_dw_tc(const float* __restrict__ x, const float* __restrict__ d_o1, LsPlanView plan,
                   float* __restrict__ dW1, float* __restrict__ db1, int L1, int n_col_blocks,
                   unsigned long long* status) {
@@ -471,11 +477,13 @@ __global__ void __launch_bounds__(kTcThreads)
     const int c0 = cb * kDwM;
 
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    unsigned char* stage0 = smem_raw + (base - smem_u32(smem_raw));
-    uint64_t* bar_free = reinterpret_cast<uint64_t*>(stage0 + kDwRing * kDwStageBytesTc);  // [kDwRing]
-    uint64_t* bar_chunk = bar_free + kDwRing;
+    unsigned char* op0 = smem_raw + (base - smem_u32(smem_raw));   // two operand buffers (1024-byte aligned)
+    unsigned char* raw0 = op0 + 2 * kDwOperandBytes;               // the raw ring
+    uint64_t* bar_free = reinterpret_cast<uint64_t*>(raw0 + kDwRawStages * kDwRawBytes);  // [2]: operand buffer read
+    uint64_t* bar_chunk = bar_free + 2;
     if (tid == 0) {
-        for (int s = 0; s < kDwRing; ++s) mbar_init(bar_free + s, 1);
+        mbar_init(bar_free, 1);
+        mbar_init(bar_free + 1, 1);
         mbar_init(bar_chunk, 1);
         fence_barrier_init();
     }
@@ -495,25 +503,37 @@ __global__ void __launch_bounds__(kTcThreads)
     for (int i = 0; i < kDwN; ++i) racc[i] = 0.f;
     const int n_st = (end - beg + 31) / 32;
 
-    float4 xa[8], da[2];  // this lane's position of the stage in flight: 32 columns of x, 8 outputs of d_o1
-    auto load = [&](int s) {
-        const int k = beg + 32 * s + lane;
-        const bool ok = k < end;
-        const int64_t p = ok ? (int64_t)__ldg(plan.perm + k) : 0;
-        const float4* xr = reinterpret_cast<const float4*>(x + p * L1 + c0 + 32 * warp);
-        const float4* dr = reinterpret_cast<const float4*>(d_o1 + p * kLsOut + 8 * warp);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) xa[i] = ok ? __ldg(xr + i) : f4_zero();
-#pragma unroll
-        for (int i = 0; i < 2; ++i) da[i] = ok ? __ldg(dr + i) : f4_zero();
+    // copies: thread t brings pieces (t & 3) + 4 i of row t >> 2 of the stage (8 of x, 2 of d_o1)
+    const int crow = tid >> 2, cq = tid & 3;
+    auto row_of = [&](int s) -> int64_t {  // position of this thread's row in stage s, -1 past the end
+        const int k = beg + 32 * s + crow;
+        return (s < n_st && k < end) ? (int64_t)__ldg(plan.perm + k) : -1;
     };
+    auto issue = [&](int s, int64_t p) {   // stage s into raw slot s % kDwRawStages; rows past the end: zeros
+        if (s < n_st) {
+            unsigned char* rx = raw0 + (s % kDwRawStages) * kDwRawBytes + crow * kDwXPitch;
+            unsigned char* rd = raw0 + (s % kDwRawStages) * kDwRawBytes + 32 * kDwXPitch + crow * kDwDPitch;
+            const bool ok = p >= 0;
+            const float* xs = x + (ok ? p : 0) * L1 + c0;
+            const float* ds = d_o1 + (ok ? p : 0) * kLsOut;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) cp_async16(rx + 16 * (cq + 4 * i), xs + 4 * (cq + 4 * i), ok);
+#pragma unroll
+            for (int i = 0; i < 2; ++i) cp_async16(rd + 16 * (cq + 4 * i), ds + 4 * (cq + 4 * i), ok);
+        }
+        cp_async_commit();
+    };
+    // transposition: lane = position of the stage, warp w takes columns [32 w, 32 w + 32) and outputs [8 w, 8 w + 8)
     const uint32_t kq = (uint32_t)(lane >> 2), kr = (uint32_t)((lane & 3) * 4);
-    auto store = [&](int slot) {
-        unsigned char* A = stage0 + slot * kDwStageBytesTc;
+    auto transpose = [&](int s) {
+        const unsigned char* rx = raw0 + (s % kDwRawStages) * kDwRawBytes + lane * kDwXPitch + 128 * warp;
+        const unsigned char* rd = raw0 + (s % kDwRawStages) * kDwRawBytes + 32 * kDwXPitch + lane * kDwDPitch + 32 * warp;
+        unsigned char* A = op0 + (s & 1) * kDwOperandBytes;
         unsigned char* Bp = A + kDwABytesTc;
 #pragma unroll
         for (int i = 0; i < 8; ++i) {
-            const float v[4] = {xa[i].x, xa[i].y, xa[i].z, xa[i].w};
+            const float4 q4 = *reinterpret_cast<const float4*>(rx + 16 * i);
+            const float v[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const uint32_t m = (uint32_t)(32 * warp + 4 * i + j);
@@ -522,7 +542,8 @@ __global__ void __launch_bounds__(kTcThreads)
         }
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
-            const float v[4] = {da[i].x, da[i].y, da[i].z, da[i].w};
+            const float4 q4 = *reinterpret_cast<const float4*>(rd + 16 * i);
+            const float v[4] = {q4.x, q4.y, q4.z, q4.w};
 #pragma unroll
             for (int j = 0; j < 4; ++j) {
                 const float hi = __uint_as_float(__float_as_uint(v[j]) & 0xFFFFE000u);
@@ -539,58 +560,61 @@ __global__ void __launch_bounds__(kTcThreads)
     };
 
     bool failed = false;
-    if (n_st > 0) load(0);
+    int64_t p_next = row_of(kDwRawStages);  // row of the stage issued in the first trip
+    for (int s = 0; s < kDwRawStages; ++s) issue(s, row_of(s));
     for (int s = 0; s < n_st; ++s) {
-        const int slot = s % kDwRing;
-        // the slot was read by the instructions of stage s - kDwRing
-        if (s >= kDwRing && !mbar_wait_bounded(bar_free + slot, (unsigned)((s / kDwRing - 1) & 1))) failed = true;
-        if (!failed) store(slot);
-        if (s + 1 < n_st) load(s + 1);  // in flight while this stage is handed over
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-        if (__syncthreads_or(failed)) {
+        cp_async_wait<kDwRawStages - 1>();  // this thread's pieces of stage s are in
+        // the operand buffer was read by the instructions of stage s - 2
+        if (s >= 2 && !mbar_wait_bounded(bar_free + (s & 1), (unsigned)((s / 2 - 1) & 1))) failed = true;
+        if (__syncthreads_or(failed)) {     // ... and so are everybody's
             failed = true;
             break;
         }
+        transpose(s);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncthreads();                    // operands complete; the raw slot may be refilled
         const bool last_of_chunk = (s % kDwChunkStages) == kDwChunkStages - 1 || s == n_st - 1;
         if (tid == 0) {
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const uint32_t a_addr = base + (uint32_t)(slot * kDwStageBytesTc);
+            const uint32_t a_addr = base + (uint32_t)((s & 1) * kDwOperandBytes);
             const uint64_t a_desc = umma_desc_k_sw128(a_addr), b_desc = umma_desc_k_sw128(a_addr + kDwABytesTc);
 #pragma unroll
             for (int k = 0; k < 4; ++k)
                 umma_tf32_n96(tmem, a_desc + 2 * k, b_desc + 2 * k, ((s % kDwChunkStages) | k) != 0);
-            umma_commit(bar_free + slot);
+            umma_commit(bar_free + (s & 1));
             if (last_of_chunk) umma_commit(bar_chunk);
         }
+        issue(s + kDwRawStages, p_next);
+        p_next = row_of(s + kDwRawStages + 1);
         if (last_of_chunk) {  // the chunk's sums out of tensor memory into the fp32 registers
             if (!mbar_wait_bounded(bar_chunk, (unsigned)((s / kDwChunkStages) & 1))) failed = true;
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            if (!failed) {
-#pragma unroll
-                for (int c = 0; c < kDwN / 32; ++c) {
-                    uint32_t v[32];
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
-                          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
-                          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
-                          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                        : "r"(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(32 * c))
-                        : "memory");
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-                    for (int i = 0; i < 32; ++i) racc[32 * c + i] = __fadd_rn(racc[32 * c + i], __uint_as_float(v[i]));
-                }
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             if (__syncthreads_or(failed)) {
                 failed = true;
                 break;
             }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#pragma unroll
+            for (int c = 0; c < kDwN / 32; ++c) {
+                uint32_t v[32];
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+                      "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+                      "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+                      "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(tmem + ((uint32_t)(warp * 32) << 16) + (uint32_t)(32 * c))
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int i = 0; i < 32; ++i) racc[32 * c + i] = __fadd_rn(racc[32 * c + i], __uint_as_float(v[i]));
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncthreads();  // the next chunk starts a fresh sum in tensor memory
         }
     }
+    cp_async_wait<0>();
     if (!failed) {
         const int m = warp * 32 + lane;  // lane of tensor memory = column of the block
 #pragma unroll
