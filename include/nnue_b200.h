@@ -258,6 +258,12 @@ int nnue_ft_quantize_table(const float* weight, const float* virtual_weight,
                            int16_t* q16, int64_t q16_pitch, float* psqt, int64_t N, int64_t n_virtual,
                            int32_t L1, int32_t P, float scale_main, float scale_psqt,
                            int32_t* d_stats, void* stream);
+
+/* The bias of nnue_ft_fused_fwd_q16 in one small launch: bias_fq[0, L1) = round(bias * scale_main) / scale_main (the
+ * bits nnue_ft_prepare_table gives), bias_fq[L1, L1 + P) = 0, and the range statistics of the L1 part (entries beyond
+ * int16, max |k|) added to d_stats[0..1] or, with overwrite_stats != 0, written over them. */
+int nnue_ft_prepare_bias_q16(const float* bias, float* bias_fq, int32_t L1, int32_t P, float scale_main,
+                             int32_t* d_stats, int32_t overwrite_stats, void* stream);
 int nnue_ft_fused_fwd_q16(const float* us, const float* them,
                           const int32_t* white_idx, const int32_t* black_idx,
                           const int64_t* psqt_idx, const int16_t* q16, int64_t q16_pitch, const float* psqt,

@@ -260,6 +260,19 @@ def prepare_table(weight, virtual_weight, l1_size: int, scale_main: float, scale
     return out
 
 
+def prepare_bias_q16(bias: torch.Tensor, l1_size: int, scale_main: float, stats: torch.Tensor, overwrite: bool) -> torch.Tensor:
+    """`nnue_ft_prepare_bias_q16`: the fake-quantized bias the int16 forward adds (PSQT part zero) and its range
+    statistics into `stats` (int32 [2]; added, or written over with `overwrite`), one launch."""
+    dev = _require_cuda(bias, stats)
+    assert bias.dtype == torch.float32 and bias.is_contiguous() and stats.dtype == torch.int32 and stats.numel() == 2
+    out = torch.empty_like(bias)
+    with torch.cuda.device(dev), _span("prepare_bias", dev):
+        st = _lib.load().nnue_ft_prepare_bias_q16(_ptr(bias), _ptr(out), int(l1_size), bias.numel() - int(l1_size),
+                                                  float(scale_main), _ptr(stats), int(bool(overwrite)), _stream(dev))
+    _lib.check(st, "nnue_ft_prepare_bias_q16")
+    return out
+
+
 def quantize_bias_stats(bias: torch.Tensor, l1_size: int, scale_main: float, scale_psqt: float, stats: torch.Tensor) -> None:
     """Adds the bias to the range statistics of a table (a bias outside the int16 range also sends the
     forward down its fp32 route): the bias goes through `nnue_ft_quantize_table` as a one-row table whose

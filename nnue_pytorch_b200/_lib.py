@@ -224,6 +224,7 @@ PROTOTYPES = {
         C.c_int,
         [_P] * 14 + [_I64, _I32, _I64, _I32, _I32, _I32, _I32, _I32, C.POINTER(QuantParams), _P, _SZ, _P],
     ),
+    "nnue_ft_prepare_bias_q16": (C.c_int, [_P, _P, _I32, _I32, C.c_float, _P, _I32, _P]),
     "nnue_quant_pack_table": (C.c_int, [_P, _P, _P, _I64, _I32, _P]),
     "nnue_quant_eval_packed": (
         C.c_int,

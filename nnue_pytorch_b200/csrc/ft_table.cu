@@ -214,6 +214,64 @@ extern "C" int nnue_ft_virtual_grad(const float* grad, float* out, int64_t N, in
     return NNUE_OK;
 }
 
+// The bias of the int16 forward in one launch of one CTA: bias_fq[c] = round(bias[c] * scale) / scale for the L1
+// columns (the bits of nnue_ft_prepare_table), zeros for the PSQT columns (that part of the bias never trains and
+// the operator adds zeros), and the range statistics of the L1 part into stats (added to what is there, or
+// written over it).
+__global__ void __launch_bounds__(kThreads)
+    k_bias_q16(const float* __restrict__ bias, float* __restrict__ out, int L1, int P, float scale, float inv_scale,
+               int* __restrict__ stats, int overwrite) {
+    __shared__ int s_bad[kWarpsPerCta], s_max[kWarpsPerCta];
+    int bad = 0, mx = 0;
+    for (int c = threadIdx.x; c < L1 + P; c += kThreads) {
+        float v = 0.f;
+        if (c < L1) {
+            float r = rintf(__fmul_rn(__ldg(bias + c), scale));
+            v = __fmul_rn(r, inv_scale);
+            if (!(fabsf(r) <= 32767.f)) {
+                ++bad;
+                r = fminf(fmaxf(r, -32767.f), 32767.f);
+                if (r != r) r = 0.f;
+            }
+            mx = max(mx, abs((int)r));
+        }
+        out[c] = v;
+    }
+    bad = __reduce_add_sync(kFullMask, bad);
+    mx = __reduce_max_sync(kFullMask, mx);
+    if ((threadIdx.x & 31) == 0) {
+        s_bad[threadIdx.x >> 5] = bad;
+        s_max[threadIdx.x >> 5] = mx;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < kWarpsPerCta; ++w) {
+            bad += s_bad[w];
+            mx = max(mx, s_max[w]);
+        }
+        if (overwrite) {
+            stats[0] = bad;
+            stats[1] = mx;
+        } else {
+            if (bad) atomicAdd(stats, bad);
+            if (mx > 0) atomicMax(stats + 1, mx);
+        }
+    }
+}
+
+extern "C" int nnue_ft_prepare_bias_q16(const float* bias, float* bias_fq, int32_t L1, int32_t P, float scale_main,
+                                        int32_t* d_stats, int32_t overwrite_stats, void* stream) {
+    NNUE_REQUIRE(L1 > 0 && P >= 0 && bias && bias_fq && d_stats, NNUE_ERR_ARG, "nnue_ft_prepare_bias_q16: bad argument");
+    int exp2 = 0;
+    NNUE_REQUIRE(scale_main > 0.f && frexpf(scale_main, &exp2) == 0.5f, NNUE_ERR_UNSUPPORTED,
+                 "nnue_ft_prepare_bias_q16: the scale must be a power of two (got %g)", (double)scale_main);
+    k_bias_q16<<<1, kThreads, 0, static_cast<cudaStream_t>(stream)>>>(bias, bias_fq, L1, P, scale_main, 1.0f / scale_main,
+                                                                     d_stats, overwrite_stats);
+    NNUE_CUDA_TRY(cudaGetLastError());
+    note_launches(1);
+    return NNUE_OK;
+}
+
 extern "C" int nnue_ft_quantize_table(const float* weight, const float* virtual_weight, int16_t* q16,
                                       int64_t q16_pitch, float* psqt, int64_t N, int64_t n_virtual, int32_t L1,
                                       int32_t P, float scale_main, float scale_psqt, int32_t* d_overflow,

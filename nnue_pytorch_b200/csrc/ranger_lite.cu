@@ -54,13 +54,22 @@ __global__ void __launch_bounds__(kThreads)
     const int lane = threadIdx.x & 31;
     const int64_t row = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
     if (row >= rows || row_active[row]) return;  // warp-uniform
+    // rows that never get a gradient (features no legal position has) stay inactive for good and are scanned in
+    // full every step: eight independent loads per trip, so that a scan costs three load latencies, not 24
     const float4* g4 = reinterpret_cast<const float4*>(g) + row * width4;
     int nz = 0;
-    for (int64_t c = lane; c < width4 && !nz; c += 32) {
-        const float4 v = __ldg(g4 + c);
-        nz = (v.x != 0.f) | (v.y != 0.f) | (v.z != 0.f) | (v.w != 0.f);
+    for (int64_t c0 = 0; c0 < width4 && !nz; c0 += 8 * 32) {
+        float4 v[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int64_t c = c0 + 32 * i + lane;
+            v[i] = c < width4 ? __ldg(g4 + c) : f4_zero();
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) nz |= (v[i].x != 0.f) | (v[i].y != 0.f) | (v[i].z != 0.f) | (v[i].w != 0.f);
+        nz = __any_sync(kFullMask, nz);
     }
-    if (__any_sync(kFullMask, nz) && lane == 0) row_active[row] = 1;
+    if (nz && lane == 0) row_active[row] = 1;
 }
 
 // IDX = unsigned when the float4 count (plus one grid stride) fits 32 bits: cheap row lookup.

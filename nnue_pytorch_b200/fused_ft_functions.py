@@ -146,13 +146,10 @@ class QuantizedFusedDoubleFtFunction(autograd.Function):
             if cache is not None:
                 cache.store(params[0], l1, scale_main, scale_psqt, q16, psqt, overflow)
                 params[0]._nnue_q16_cache = cache  # where this package's optimizer looks for it
-        bias_stats = overflow
-        if overflow.numel() > 2:  # per-rank parts of the table first, the bias in the last pair
-            bias_stats = overflow[-2:]
-            bias_stats.zero_()
-        _launch.quantize_bias_stats(bias, l1, scale_main, scale_psqt, bias_stats)
-        bias_fq = torch.zeros_like(bias)
-        _launch.prepare_table(bias.detach()[:l1].reshape(1, l1), None, l1, scale_main, 1.0, out=bias_fq, span="prepare_bias")
+        # per-rank parts of the table first and the bias in a pair of its own (written over every step), or one
+        # pair that the bias's figures are added to (the optimizer kernel resets it when it rewrites the table)
+        parts = overflow.numel() > 2
+        bias_fq = _launch.prepare_bias_q16(bias.detach(), l1, scale_main, overflow[-2:] if parts else overflow, parts)
         l0, wpsqt, bpsqt, saved = _launch.fused_forward_q16(
             us, them, white_indices, black_indices, psqt_indices, q16, psqt, bias_fq, overflow, blocks, scale_main,
             max_ft_activation, l1, act_quant_scale, act_quant_eps, out_scale, master=master)
