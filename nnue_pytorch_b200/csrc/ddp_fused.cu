@@ -179,24 +179,37 @@ struct PeerEmit {
 
 // Moment tensors are shard-sized: element i of the table is element i - beg4 of them.
 // FP32_TO_PEERS: the new rows go into every rank's table (else only into the owner's).  EMIT: see PeerEmit.
-template <bool FP32_TO_PEERS, bool EMIT>
+// IDX = unsigned when the float4 indices (plus one grid stride) fit 32 bits.  The other ranks' pointers sit in shared
+// memory and the stores to them are short rolled loops: the kernel then needs as few registers as the single-GPU
+// update (it measured a quarter slower with the pointers in unrolled, predicated loops: fewer warps per SM).
+template <bool FP32_TO_PEERS, bool EMIT, typename IDX>
 __global__ void __launch_bounds__(kThreads)
-    k_ddp_update_shard(PeerPtrs tables, int world, int rank, int64_t beg4, int64_t end4,
+    k_ddp_update_shard(PeerPtrs tables, int world, int rank, int64_t beg4_, int64_t end4_,
                        const float* __restrict__ grad, float* __restrict__ gm, float* __restrict__ ngm,
                        float* __restrict__ vm, float* __restrict__ slow,
                        const float* __restrict__ d_scale, RangerConst c, PeerEmit pe) {
+    __shared__ float4* s_tab[kMaxRanks];
+    __shared__ int2* s_q16[kMaxRanks];
+    __shared__ float4* s_psqt[kMaxRanks];
+    if (threadIdx.x < kMaxRanks) {
+        s_tab[threadIdx.x] = reinterpret_cast<float4*>(tables.p[threadIdx.x]);
+        s_q16[threadIdx.x] = reinterpret_cast<int2*>(pe.q16[threadIdx.x]);
+        s_psqt[threadIdx.x] = reinterpret_cast<float4*>(pe.psqt[threadIdx.x]);
+    }
+    __syncthreads();
     int bad = 0, max_abs = 0;
     const float scale = d_scale ? __ldg(d_scale) : 1.f;
-    const int64_t stride = (int64_t)gridDim.x * blockDim.x;
+    const IDX beg4 = (IDX)beg4_, end4 = (IDX)end4_;
+    const IDX stride = (IDX)gridDim.x * blockDim.x;
     const float4* g4 = reinterpret_cast<const float4*>(grad);
-    float4* own = reinterpret_cast<float4*>(tables.p[rank]);
+    float4* own = s_tab[rank];
     float4* gm4 = reinterpret_cast<float4*>(gm);
     float4* ngm4 = reinterpret_cast<float4*>(ngm);
     float4* vm4 = reinterpret_cast<float4*>(vm);
     float4* slow4 = reinterpret_cast<float4*>(slow);
-    for (int64_t i = beg4 + (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < end4; i += stride) {
-        const int64_t j = i - beg4;
-        const float4 gv = __ldcs(g4 + i);
+    for (IDX i = beg4 + (IDX)blockIdx.x * blockDim.x + threadIdx.x; i < end4; i += stride) {
+        const IDX j = i - beg4;
+        const float4 gv = __ldg(g4 + i);
         float4 pv = own[i], gmv = gm4[j], vmv = vm4[j];
         float4 ngv = c.use_pnm ? ngm4[j] : f4_zero();
         float4 sv = c.do_merge ? slow4[j] : f4_zero();
@@ -209,9 +222,8 @@ __global__ void __launch_bounds__(kThreads)
         if (c.use_pnm && !c.step_is_odd) ngm4[j] = ngv;
         if (c.do_merge) slow4[j] = sv;
         if (FP32_TO_PEERS) {
-#pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r)
-                if (r < world) reinterpret_cast<float4*>(tables.p[r])[i] = pv;
+#pragma unroll 1
+            for (int r = 0; r < world; ++r) s_tab[r][i] = pv;
         } else {
             own[i] = pv;
         }
@@ -233,15 +245,15 @@ __global__ void __launch_bounds__(kThreads)
                     max_abs = max(max_abs, abs(k[q]));
                 }
                 const int2 words = make_int2(k[1] * 65536 + k[0], k[3] * 65536 + k[2]);
-#pragma unroll
-                for (int r = 0; r < kMaxRanks; ++r)
-                    if (r < world) reinterpret_cast<int2*>(pe.q16[r])[(long long)row * pe.pitch4 + c4] = words;
+                const long long at = (long long)row * pe.pitch4 + c4;
+#pragma unroll 1
+                for (int r = 0; r < world; ++r) s_q16[r][at] = words;
             } else {
                 auto fq = [&](float a) { return __fdiv_rn(rintf(__fmul_rn(a, pe.scale_psqt)), pe.scale_psqt); };
                 const float4 v = make_float4(fq(pv.x), fq(pv.y), fq(pv.z), fq(pv.w));
-#pragma unroll
-                for (int r = 0; r < kMaxRanks; ++r)
-                    if (r < world) reinterpret_cast<float4*>(pe.psqt[r])[(long long)row * pe.p4 + (c4 - pe.l4)] = v;
+                const long long at = (long long)row * pe.p4 + (c4 - pe.l4);
+#pragma unroll 1
+                for (int r = 0; r < world; ++r) s_psqt[r][at] = v;
             }
         }
     }
@@ -250,107 +262,6 @@ __global__ void __launch_bounds__(kThreads)
         max_abs = __reduce_max_sync(kFullMask, max_abs);
         if ((threadIdx.x & 31) == 0 && max_abs > 0) atomicMax(pe.stats_local + 1, max_abs);
     }
-}
-
-// The emitting update when the shard is whole table rows: a warp per unit (a row, or one of `parts` equal column
-// ranges of a row; the host sizes the grid so that every warp gets the same number of units), a lane takes eight
-// neighbouring L1 columns at a time (ten 16-byte loads in flight, one 16-byte store of int16 per rank), no
-// division per element.
-template <bool FP32_TO_PEERS>
-__global__ void __launch_bounds__(kThreads)
-    k_ddp_update_rows(PeerPtrs tables, int world, int rank, int64_t row_beg, int64_t row_end, int parts, int64_t beg4,
-                      const float* __restrict__ grad, float* __restrict__ gm, float* __restrict__ ngm,
-                      float* __restrict__ vm, float* __restrict__ slow,
-                      const float* __restrict__ d_scale, RangerConst c, PeerEmit pe) {
-    int bad = 0, max_abs = 0;
-    const float scale = d_scale ? __ldg(d_scale) : 1.f;
-    const int lane = threadIdx.x & 31;
-    const int64_t warp = (int64_t)blockIdx.x * kWarpsPerCta + (threadIdx.x >> 5);
-    const int64_t n_warps = (int64_t)gridDim.x * kWarpsPerCta;
-    const float4* g4 = reinterpret_cast<const float4*>(grad);
-    float4* own = reinterpret_cast<float4*>(tables.p[rank]);
-    float4* gm4 = reinterpret_cast<float4*>(gm);
-    float4* ngm4 = reinterpret_cast<float4*>(ngm);
-    float4* vm4 = reinterpret_cast<float4*>(vm);
-    float4* slow4 = reinterpret_cast<float4*>(slow);
-
-    // the update of float4 number i of the table; returns the new parameter values
-    auto load = [&](int64_t i, float4& gv, float4& pv, float4& gmv, float4& vmv, float4& ngv, float4& sv) {
-        const int64_t j = i - beg4;
-        gv = __ldcs(g4 + i);
-        pv = own[i];
-        gmv = gm4[j];
-        vmv = vm4[j];
-        ngv = c.use_pnm ? ngm4[j] : f4_zero();
-        sv = c.do_merge ? slow4[j] : f4_zero();
-    };
-    auto finish = [&](int64_t i, float4 gv, float4& pv, float4 gmv, float4 vmv, float4 ngv, float4 sv) {
-        const int64_t j = i - beg4;
-        ranger_elem(c, scale, gv.x, pv.x, gmv.x, ngv.x, vmv.x, sv.x);
-        ranger_elem(c, scale, gv.y, pv.y, gmv.y, ngv.y, vmv.y, sv.y);
-        ranger_elem(c, scale, gv.z, pv.z, gmv.z, ngv.z, vmv.z, sv.z);
-        ranger_elem(c, scale, gv.w, pv.w, gmv.w, ngv.w, vmv.w, sv.w);
-        vm4[j] = vmv;
-        if (!c.use_pnm || c.step_is_odd) gm4[j] = gmv;
-        if (c.use_pnm && !c.step_is_odd) ngm4[j] = ngv;
-        if (c.do_merge) slow4[j] = sv;
-        if (FP32_TO_PEERS) {
-#pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r)
-                if (r < world) reinterpret_cast<float4*>(tables.p[r])[i] = pv;
-        } else {
-            own[i] = pv;
-        }
-    };
-    auto to_int = [&](float x) {
-        float rr = rintf(__fmul_rn(x, pe.scale_main));
-        if (!(fabsf(rr) <= 32767.f)) {
-            ++bad;
-            rr = fminf(fmaxf(rr, -32767.f), 32767.f);
-            if (rr != rr) rr = 0.f;
-        }
-        const int k = (int)rr;
-        max_abs = max(max_abs, abs(k));
-        return k;
-    };
-
-    const int l8 = pe.l4 >> 1, per_part = l8 / parts;
-    const long long pitch8 = pe.pitch4 >> 1;
-    const int64_t n_units = (row_end - row_beg) * parts;
-    for (int64_t unit = warp; unit < n_units; unit += n_warps) {
-        const int64_t row = row_beg + unit / parts;
-        const int part = (int)(unit % parts);
-        const int64_t r4 = row * pe.w4;
-        for (int pc = part * per_part + lane; pc < (part + 1) * per_part; pc += 32) {
-            const int64_t i = r4 + 2 * pc;
-            float4 g0, p0, m0, v0, n0, s0, g1, p1, m1, v1, n1, s1;
-            load(i, g0, p0, m0, v0, n0, s0);
-            load(i + 1, g1, p1, m1, v1, n1, s1);
-            finish(i, g0, p0, m0, v0, n0, s0);
-            finish(i + 1, g1, p1, m1, v1, n1, s1);
-            const int k0 = to_int(p0.x), k1 = to_int(p0.y), k2 = to_int(p0.z), k3 = to_int(p0.w);
-            const int k4 = to_int(p1.x), k5 = to_int(p1.y), k6 = to_int(p1.z), k7 = to_int(p1.w);
-            const uint4 words = make_uint4((unsigned)(k1 * 65536 + k0), (unsigned)(k3 * 65536 + k2),
-                                           (unsigned)(k5 * 65536 + k4), (unsigned)(k7 * 65536 + k6));
-#pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r)
-                if (r < world) reinterpret_cast<uint4*>(pe.q16[r])[row * pitch8 + pc] = words;
-        }
-        for (int q = lane; q < (part == 0 ? pe.p4 : 0); q += 32) {
-            const int64_t i = r4 + pe.l4 + q;
-            float4 g0, p0, m0, v0, n0, s0;
-            load(i, g0, p0, m0, v0, n0, s0);
-            finish(i, g0, p0, m0, v0, n0, s0);
-            auto fq = [&](float a) { return __fdiv_rn(rintf(__fmul_rn(a, pe.scale_psqt)), pe.scale_psqt); };
-            const float4 v = make_float4(fq(p0.x), fq(p0.y), fq(p0.z), fq(p0.w));
-#pragma unroll
-            for (int r = 0; r < kMaxRanks; ++r)
-                if (r < world) reinterpret_cast<float4*>(pe.psqt[r])[row * pe.p4 + q] = v;
-        }
-    }
-    if (bad) atomicAdd(pe.stats_local, bad);
-    max_abs = __reduce_max_sync(kFullMask, max_abs);
-    if (lane == 0 && max_abs > 0) atomicMax(pe.stats_local + 1, max_abs);
 }
 
 // This rank's range statistics into slot `rank` of every rank's statistics array.
@@ -540,28 +451,17 @@ extern "C" int nnue_ddp_update_shard_emit(float* const* h_table_ptrs, int32_t wo
     }
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     ProfScope prof("k_ddp_update_shard", s);
+    const bool narrow = elem_end / 4 + (int64_t)grid * kThreads < 0x7fffffffLL;
 #define LAUNCH_UPD(FF, EE)                                                                                        \
-    k_ddp_update_shard<FF, EE><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, grad, grad_ma, \
-                                                         neg_grad_ma, variance_ma, slow, d_grad_scale, *hp, pe)
-    const int64_t w = (int64_t)pe.w4 * 4;
-    if (h_emit && elem_begin % w == 0 && elem_end % w == 0) {
-        // whole rows (what row-sliced shares are): a warp per row
-        const int64_t r0 = elem_begin / w, r1 = elem_end / w;
-        const int l8 = h_emit->L1 / 8;
-        int parts = 1;  // units of whole warps' worth of column groups, so that no lane idles
-        for (int q = 8; q > 1; q >>= 1)
-            if (l8 % (32 * q) == 0) { parts = q; break; }
-        // every warp the same number of units: k = units per warp that fits the resident grid, then just enough CTAs
-        const int64_t units = (r1 - r0) * parts, max_warps = (int64_t)sm_count() * 8 * kWarpsPerCta;
-        const int64_t per_warp = (units + max_warps - 1) / max_warps;
-        const unsigned rgrid = (unsigned)((units + per_warp * kWarpsPerCta - 1) / (per_warp * kWarpsPerCta));
-        if (fp32_to_peers)
-            k_ddp_update_rows<true><<<rgrid, kThreads, 0, s>>>(pp, world, rank, r0, r1, parts, elem_begin / 4, grad, grad_ma,
-                                                               neg_grad_ma, variance_ma, slow, d_grad_scale, *hp, pe);
-        else
-            k_ddp_update_rows<false><<<rgrid, kThreads, 0, s>>>(pp, world, rank, r0, r1, parts, elem_begin / 4, grad, grad_ma,
-                                                                neg_grad_ma, variance_ma, slow, d_grad_scale, *hp, pe);
-    } else if (!h_emit) LAUNCH_UPD(true, false);
+    do {                                                                                                          \
+        if (narrow)                                                                                               \
+            k_ddp_update_shard<FF, EE, unsigned><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, grad, \
+                                                                           grad_ma, neg_grad_ma, variance_ma, slow, d_grad_scale, *hp, pe); \
+        else                                                                                                      \
+            k_ddp_update_shard<FF, EE, int64_t><<<grid, kThreads, 0, s>>>(pp, world, rank, elem_begin / 4, elem_end / 4, grad,  \
+                                                                          grad_ma, neg_grad_ma, variance_ma, slow, d_grad_scale, *hp, pe); \
+    } while (0)
+    if (!h_emit) LAUNCH_UPD(true, false);
     else if (fp32_to_peers) LAUNCH_UPD(true, true);
     else LAUNCH_UPD(false, true);
 #undef LAUNCH_UPD

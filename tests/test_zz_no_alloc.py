@@ -65,7 +65,7 @@ def test_static_scratch_backward_matches_workspace_backward():
         gw = torch.full((N, W), float("nan"), device=dev)
         gb = torch.full((W,), float("nan"), device=dev)
         torch.cuda.synchronize()
-        # the driver's own count of free device memory (torch's allocator statistics would not see an
+        # the CUDA driver's own count of free device memory (torch's allocator statistics would not see an
         # allocation made inside the library); the helper stream and the array are in place by now
         free_before, _ = torch.cuda.mem_get_info(dev)
         st = lib.nnue_ft_sparse_bwd_static(idx.data_ptr(), go.data_ptr(), gw.data_ptr(), gb.data_ptr(),
