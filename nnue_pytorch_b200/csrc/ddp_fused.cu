@@ -10,10 +10,16 @@
 //                        buffer with plain peer loads, adds in rank order,
 //                        keeps the sum in its own buffer and accumulates the
 //                        squared norm   (reduce-scatter + norm, one kernel)
+//   k_ddp_reduce_block   the same over a column slice of its rows (the
+//                        backward can deliver the gradient in column slices)
 //   k_ddp_update_shard   RangerLite on the shard (moments exist for the shard
-//                        only) and stores the new rows into EVERY rank's
-//                        table with plain peer stores
+//                        only) and stores into EVERY rank's memory, with plain
+//                        peer stores, what the ranks read next: the fp32 rows,
+//                        or the int16 / PSQT rows of the table their forward
+//                        gathers (half the bytes; the fp32 rows then stay home)
 //                                          (optimizer + all-gather, one kernel)
+//   k_ddp_publish_stats  this rank's range statistics of its int16 rows into
+//                        a slot of every rank's statistics array
 //
 // No kernel waits on another GPU: ordering between ranks comes from the tiny
 // NCCL collectives the host issues between the phases (a collective cannot
