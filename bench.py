@@ -129,7 +129,11 @@ def measured_peak_gbs():
 
 # ---------------------------------------------------------------------------
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs.
+
+    nvidia-smi's start (it initialises the management library for every GPU of the machine) disturbs the process it
+    watches for a moment, so the sampler is started BEFORE the warm-up steps; `window()` then marks the timed
+    region, and only samples that arrived inside it are summarised."""
 
     FIELDS = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
@@ -137,6 +141,7 @@ class ClockSampler:
 
     def __init__(self, index: int):
         self.index, self.proc, self.lines, self.skip = index, None, [], 0
+        self.t0, self.t1 = None, None
 
     def __enter__(self):
         try:
@@ -157,7 +162,20 @@ class ClockSampler:
 
     def _pump(self):
         for line in self.proc.stdout:
-            self.lines.append(line.strip())
+            self.lines.append((time.time(), line.strip()))
+
+    def window(self):
+        """Context manager around the timed region: samples outside it are dropped from the summary."""
+        sampler = self
+
+        class _Window:
+            def __enter__(self):
+                sampler.t0 = time.time()
+
+            def __exit__(self, *exc):
+                sampler.t1 = time.time()
+
+        return _Window()
 
     def __exit__(self, *exc):
         if self.proc is not None:
@@ -170,7 +188,11 @@ class ClockSampler:
     def summary(self):
         sm, mx, power, reasons = [], [], [], set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for ln in self.lines[self.skip:]:
+        kept = [ln for stamp, ln in self.lines[self.skip:]
+                if not ((self.t0 is not None and stamp < self.t0) or (self.t1 is not None and stamp > self.t1))]
+        if not kept:  # a timed region shorter than the sampling period: the samples of the warm-up steps before it
+            kept = [ln for _, ln in self.lines[self.skip:]]
+        for ln in kept:
             parts = [p.strip() for p in ln.split(",")]
             if len(parts) < 7:
                 continue
@@ -486,12 +508,12 @@ def run_step(args):
         return ms, (loss_host if not resident else float(loss))
 
     warm = max(args.warmup, 3)
-    timed(warm, True)  # warm-up (also builds allocator pools, lazy attributes)
-
-    launches0 = lib.nnue_b200_launch_count()
-    with ClockSampler(local) as clocks:
-        ms_resident, loss_val = timed(args.steps, True)
-    launches = (lib.nnue_b200_launch_count() - launches0) // max(args.steps, 1)
+    with ClockSampler(local) as clocks:  # started before the warm-up: its start-up is not part of the timed steps
+        timed(warm, True)  # warm-up (also builds allocator pools, lazy attributes)
+        launches0 = lib.nnue_b200_launch_count()
+        with clocks.window():
+            ms_resident, loss_val = timed(args.steps, True)
+        launches = (lib.nnue_b200_launch_count() - launches0) // max(args.steps, 1)
     timed(warm, False)  # warm-up of the end-to-end path (copy-stream allocations, pinned slots)
     ms_e2e, loss_e2e = timed(args.steps, False)
     _launch.device_status(dev)
