@@ -103,6 +103,9 @@ def parse_args():
                          "unsliced against 2.77 in column slices; 4 GPUs 2.76 unsliced, 2.72 rows, 2.78 columns; "
                          "8 GPUs 2.90 unsliced, 2.72 rows, 2.93 columns)")
     ap.add_argument("--col-slices", type=int, default=4, help="number of column slices of --slices cols")
+    ap.add_argument("--clock-period-ms", type=int, default=50,
+                    help="sampling period of nvidia-smi during the timed steps (every query takes a driver lock that "
+                         "kernel launches wait for; measured per step at 20 ms 2.507 ms, at 100 ms 2.504)")
     ap.add_argument("--feed", default="packed", choices=["packed", "lists"],
                     help="what the end-to-end run copies from pinned host memory every step: 72-byte packed "
                          "positions expanded on the GPU, or the expanded index lists")
@@ -139,15 +142,16 @@ class ClockSampler:
               "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
               "clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
+    def __init__(self, index: int, period_ms: int = 50):
         self.index, self.proc, self.lines, self.skip = index, None, [], 0
+        self.period_ms = int(period_ms)
         self.t0, self.t1 = None, None
 
     def __enter__(self):
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits",
-                 "-lms", "20"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._pump, daemon=True)
             self.thread.start()
             # nvidia-smi needs a moment to start: wait for its first line, then count only what follows,
@@ -508,7 +512,7 @@ def run_step(args):
         return ms, (loss_host if not resident else float(loss))
 
     warm = max(args.warmup, 3)
-    with ClockSampler(local) as clocks:  # started before the warm-up: its start-up is not part of the timed steps
+    with ClockSampler(local, args.clock_period_ms) as clocks:  # started before the warm-up: its start-up is not part of the timed steps
         timed(warm, True)  # warm-up (also builds allocator pools, lazy attributes)
         launches0 = lib.nnue_b200_launch_count()
         with clocks.window():
