@@ -145,3 +145,18 @@ def test_packed_position_record_matches_the_header_struct():
     body = header[header.index("typedef struct nnue_packed_position {"):header.index("} nnue_packed_position;")]
     assert [ln.split()[1].split("[")[0].rstrip(";") for ln in body.splitlines()[1:] if ln.strip()] == [
         "piece", "score", "outcome2", "stm_white", "count", "pad"]
+
+
+def test_column_slices_of_the_benchmark_sit_on_tile_borders():
+    """`bench.column_slices` asks the library for the backward's column tile (a host-side query) and cuts the
+    table's row into slices on tile borders, the last one taking the PSQT columns."""
+    import importlib.util
+    import os
+
+    spec = importlib.util.spec_from_file_location("bench_module", os.path.join(os.path.dirname(__file__), os.pardir, "bench.py"))
+    bench = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(bench)
+    assert bench.column_slices(3072, 8, 4) == [0, 768, 1536, 2304, 3080]
+    assert bench.column_slices(3072, 8, 1) == [0, 3080]
+    assert bench.column_slices(3072, 8, 13) == [256 * i for i in range(13)] + [3080]
+    assert bench.column_slices(128, 8, 4) == [0, 136]  # one tile only: nothing to cut
