@@ -273,13 +273,6 @@ def prepare_bias_q16(bias: torch.Tensor, l1_size: int, scale_main: float, stats:
     return out
 
 
-def quantize_bias_stats(bias: torch.Tensor, l1_size: int, scale_main: float, scale_psqt: float, stats: torch.Tensor) -> None:
-    """Adds the bias to the range statistics of a table (a bias outside the int16 range also sends the
-    forward down its fp32 route): the bias goes through `nnue_ft_quantize_table` as a one-row table whose
-    integer output is dropped."""
-    quantize_blocks([(bias.detach().reshape(1, -1), None)], l1_size, scale_main, scale_psqt, overflow=stats)
-
-
 def quantize_blocks(blocks, l1_size: int, scale_main: float, scale_psqt: float, overflow: torch.Tensor | None = None,
                     out=None):
     """The integer form of the table the forward reads when weights are fake-quantized
