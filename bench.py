@@ -15,7 +15,7 @@ one forward + backward + optimizer update over one batch.
 
 One JSON line is printed by rank 0.
   value       positions/s over exactly K steps with the batches resident in HBM, CUDA events, max over
-              ranks, no per-call timers running.
+              ranks, no per-call timers running; the host stays at most LOOKAHEAD steps ahead of the GPU.
   e2e         the same with every batch copied from pinned host memory on a side stream (one batch
               ahead) and the loss of every step copied back to the host, which reads it one step later.
               `--feed packed` (default): the host copy is the 72-byte packed position records and the
@@ -31,7 +31,11 @@ One JSON line is printed by rank 0.
               SM clock the GPU settles at under its power limit.
   quant_eval  integer evaluation throughput of the same architecture (calls of one batch).
   exchange_check (N > 1)  untimed, after the timed loops: the fused table exchange against a plain
-              all-reduce + full update from the same initial state, and whether all ranks hold the same table.
+              all-reduce + full update from the same initial state (and against the same with the table
+              gradient summed in rank order, which it must equal bit for bit), and whether all ranks hold
+              the same table.
+N > 1: `--slices auto|rows|cols|off` (overlap of the gradient reduce with the backward), `--rows-on-the-wire
+int16|both|fp32` (what the sharded update stores into the other ranks), `--ddp fused|allreduce`.
 """
 
 from __future__ import annotations
