@@ -160,3 +160,34 @@ def test_column_slices_of_the_benchmark_sit_on_tile_borders():
     assert bench.column_slices(3072, 8, 1) == [0, 3080]
     assert bench.column_slices(3072, 8, 13) == [256 * i for i in range(13)] + [3080]
     assert bench.column_slices(128, 8, 4) == [0, 136]  # one tile only: nothing to cut
+
+
+def test_kept_integer_table_cache_keys_on_storage_and_version():
+    """The cache of the integer table is fresh only for the very storage and torch version counter it was made
+    from, with the same sizes and scales; a write through `.data` moves neither (which is why callers that make one
+    invalidate the cache themselves)."""
+    import torch
+
+    from nnue_pytorch_b200._launch import QuantTableCache
+
+    w = torch.nn.Parameter(torch.zeros(6, 24))
+    q16, psqt, stats = torch.zeros(7, 16, dtype=torch.int16), torch.zeros(6, 8), torch.zeros(2, dtype=torch.int32)
+    cache = QuantTableCache()
+    assert not cache.fresh(w, 16, 256.0, 9600.0) and cache.emit_struct(w) is None
+    cache.store(w, 16, 256.0, 9600.0, q16, psqt, stats)
+    assert cache.fresh(w, 16, 256.0, 9600.0)
+    assert not cache.fresh(w, 16, 128.0, 9600.0) and not cache.fresh(w, 8, 256.0, 9600.0)  # other scale, other split
+    e = cache.emit_struct(w)
+    assert e is not None and (e.L1, e.P, e.q16_pitch) == (16, 8, 16) and e.q16 == q16.data_ptr()
+    with torch.no_grad():
+        w.add_(1.0)                      # an in-place change through torch moves the version counter
+    assert not cache.fresh(w, 16, 256.0, 9600.0) and cache.emit_struct(w) is None
+    cache.mark(w)                        # "the buffers hold the table of w as it is now"
+    assert cache.fresh(w, 16, 256.0, 9600.0)
+    w.data.mul_(2.0)                     # a write behind the counter's back is NOT seen ...
+    assert cache.fresh(w, 16, 256.0, 9600.0)
+    cache.invalidate()                   # ... so whoever makes one says so
+    assert not cache.fresh(w, 16, 256.0, 9600.0)
+    w.data = torch.ones(6, 24)           # new storage: never fresh
+    cache.store(torch.nn.Parameter(torch.zeros(6, 24)), 16, 256.0, 9600.0, q16, psqt, stats)
+    assert not cache.fresh(w, 16, 256.0, 9600.0)
